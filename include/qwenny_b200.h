@@ -1,0 +1,77 @@
+/* qwenny_b200 — C ABI of the B200-native decode / verify hot path.
+ *
+ * The reference (hellerchr/qwenny) has no linked native library: its Rust host loads a PTX module and launches
+ * `extern "C" __global__` kernels by name (src/cuda/core.rs:42-46, src/cuda/qwen/mod.rs:350-361). The boundary a
+ * replacement has to honour is therefore "one call per kernel launch site, the kernel's own argument list, the
+ * device-memory layouts the host packs". Each entry point below stands for one such launch site: same argument
+ * order and meaning as the kernel it replaces, plus the context (scratch, SM count) and the CUDA stream the host
+ * launches on. Geometry (grid, block, shared memory), which the reference host computes, is chosen inside.
+ *
+ * Conventions: every pointer is a device pointer unless its name starts with `h_`; `stream` is a cudaStream_t /
+ * CUstream passed as void*; every call only enqueues work (stream-capturable, no allocation, no host sync) and
+ * returns 0 or a QB_ERR_* / cudaError_t code (the reference surfaces a CUresult from launch or sync the same way,
+ * src/server.rs:640-650). Sizes are the 27B build's compile-time constants (kernels/qwen.cu:8-35 with QWEN_27B).
+ */
+#ifndef QWENNY_B200_H
+#define QWENNY_B200_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QB_OK 0
+#define QB_ERR_ARG 1000      /* a shape or pointer the kernels cannot take */
+#define QB_ERR_DEVICE 1001   /* a bounded device-side wait ran out (see qb_device_error) */
+#define QB_ERR_UNSUPPORTED 1002
+
+typedef struct qb_ctx qb_ctx;
+
+/* Epilogues of a matrix product: src/cuda/core.rs:58-64 (enum Epi). */
+enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2 };
+
+/* ---- context: what Gemm::load allocates once (src/cuda/core.rs:437-464: SM count, Marlin's `red` and `locks`).
+ * Allocates the split-K scratch and tickets on `device`; everything after creation is allocation-free. */
+int qb_create(int device, qb_ctx** out);
+void qb_destroy(qb_ctx* ctx);
+/* Non-zero once a kernel gave up a bounded wait (1 producer, 2 consumer, ...); reads and clears the word (syncs). */
+int qb_device_error(qb_ctx* ctx);
+int qb_sm_count(const qb_ctx* ctx);
+const char* qb_version(void);
+
+/* ---- W4A16 product over a Marlin-packed matrix. Replaces the launches of Gemm::marlin
+ * (src/cuda/core.rs:569-612) of marlin_m1_n8_{plain,silu,argmax} (kernels/marlin.cuh:588-602) for m <= 16 rows.
+ *   X      f16 [.][k]; rows row0 .. row0+m-1 are read, or rows xrows[0..m) when xrows != NULL (this folds
+ *          marlin_gather, kernels/marlin.cuh:605-608, into the product)
+ *   B      Marlin words, k/16 x 2n u32 (src/cuda/core.rs:262-311 pack_marlin); S f16 [k/128][n] permuted scales
+ *   Y      plain/argmax: f32 [.][n]; silu: f16 [.][n/2]; rows row0 .. (xrows: rows 0..m-1)
+ *   keys   argmax: u64 [.], maximised with (ordered(logit) << 32 | ~index) over outputs < n_valid
+ * n a multiple of 256 and k of 128 as the reference requires (src/cuda/core.rs:160-164). Plain products are
+ * complete (one part), as Marlin's. */
+int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
+                   int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
+
+/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), split-K factor, ring depth and
+ * blocks per SM of the next qb_marlin_gemm calls; zeros restore the built-in choice. */
+int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nsplit, int nstages, int ctas_per_sm);
+
+/* ---- host-side weight packers (load time; host pointers). They produce the layouts the reference's loader
+ * produces, which every kernel here reads unchanged.
+ * qb_row_order    row_order, src/cuda/core.rs:106-114
+ * qb_pack_marlin  pack_marlin + marlin_word + marlin_scale (symmetric), src/cuda/core.rs:244-311; h_q is the
+ *                 stored matrix as Quant holds it (src/checkpoint.rs:20-31): u32 [rows][cols/8], q + 8 in nibbles
+ * qb_pack_f16     pack (f16 branch) + frag, src/cuda/core.rs:222-227,337-391
+ * qb_split_for    split_for, src/cuda/core.rs:393-398 */
+int qb_row_order(int rows, int silu, int* h_order);
+int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int cols, int group, const int* h_order,
+                   int n, uint32_t* h_words, uint16_t* h_scales_f16);
+int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n, uint16_t* h_out);
+int qb_split_for(int tiles, int cols, int bits, int kd);
+
+/* Programmatic dependent launch for the kernels that support it (their weight prefetch then overlaps the tail of
+ * the previous kernel of the stream). Off by default. */
+int qb_set_pdl(qb_ctx* ctx, int on);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,56 @@
+"""ctypes binding of libqwenny_b200.so (the C ABI declared in include/qwenny_b200.h).
+
+There is no fallback: if the library has not been built (python -m qwenny_b200.build) loading raises, and every
+entry point that computes needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqwenny_b200.so")
+
+P, I, LL, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+# name -> argument types (all return int unless listed in _RESTYPE)
+SIGNATURES = {
+    "qb_create": [I, C.POINTER(P)],
+    "qb_destroy": [P],
+    "qb_device_error": [P],
+    "qb_sm_count": [P],
+    "qb_version": [],
+    "qb_set_pdl": [P, I],
+    "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
+    "qb_marlin_tune": [P, I, I, I, I, I],
+    "qb_row_order": [I, I, P],
+    "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
+    "qb_pack_f16": [P, I, I, P, I, P],
+    "qb_split_for": [I, I, I, I],
+}
+_RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m qwenny_b200.build` (there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.argtypes = args
+            fn.restype = _RESTYPE.get(name, I)
+    return _lib
+
+
+class QbError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise QbError(f"{what} failed with code {rc}")

@@ -1,0 +1,27 @@
+// The library context: what the reference's Gemm::load allocates once per model (src/cuda/core.rs:437-464) — the SM
+// count and the scratch its blocks reduce through — plus the device error word of the bounded waits.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/qwenny_b200.h"
+
+struct qb_ctx {
+    int device = 0;
+    int sms = 0;
+    // split-K partial sums of the skinny int4 products (L2 resident) and the per-64-output arrival tickets
+    float* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    int* counters = nullptr;
+    size_t ncounters = 0;
+    int* err = nullptr;  // device word
+    // measurement override of the GEMV plan (0: built-in choice)
+    int tune_cg = 0, tune_kg = 0, tune_nsplit = 0, tune_nstages = 0, tune_ctas = 0;
+    // programmatic dependent launch on the launches that support it
+    bool pdl = false;
+};
+
+#define QB_CUDA(x)                         \
+    do {                                   \
+        cudaError_t e_ = (x);              \
+        if (e_ != cudaSuccess) return (int)e_; \
+    } while (0)

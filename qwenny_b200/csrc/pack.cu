@@ -1,0 +1,116 @@
+// Host-side weight packers: the layouts the reference's loader produces (src/cuda/core.rs) and every kernel here
+// reads. Load-time code, multi-threaded over the k16 steps / tiles as the reference's is.
+#include <cuda_fp16.h>
+#include <algorithm>
+#include <cstring>
+#include <thread>
+#include <vector>
+#include "ctx.h"
+
+namespace {
+
+inline uint16_t f16_bits(float v) {
+    __half h = __float2half_rn(v);
+    uint16_t b;
+    std::memcpy(&b, &h, 2);
+    return b;
+}
+
+template <class F>
+void parallel_for(int n, F f) {
+    int threads = (int)std::max(1u, std::thread::hardware_concurrency());
+    threads = std::min(threads, std::max(1, n));
+    int per = (n + threads - 1) / threads;
+    std::vector<std::thread> pool;
+    for (int i = 0; i < threads; i++) {
+        int a = i * per, b = std::min(n, a + per);
+        if (a >= b) break;
+        pool.emplace_back([=] { for (int j = a; j < b; j++) f(j); });
+    }
+    for (auto& t : pool) t.join();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Packed row i holds source row order[i]; SwiGLU matrices interleave 8 gate rows with their 8 up rows per 16-row
+// block (row_order, src/cuda/core.rs:106-114).
+int qb_row_order(int rows, int silu, int* h_order) {
+    if (rows < 0 || !h_order || (silu && rows % 16)) return QB_ERR_ARG;
+    for (int i = 0; i < rows; i++)
+        h_order[i] = silu ? (i / 16) * 8 + i % 8 + (i % 16 >= 8 ? rows / 2 : 0) : i;
+    return QB_OK;
+}
+
+// A stored int4 matrix -> Marlin's layout (pack_marlin, src/cuda/core.rs:262-311; marlin_word :244-253).
+//   h_q      u32 [rows][cols/8], value of column c at bits (c % 8) * 4, stored q + 8 (Quant, src/checkpoint.rs:20-31)
+//   h_scales f32 [rows][cols/group], group a multiple of 128
+//   h_order  n packed rows -> source row (n a multiple of 64)
+//   h_words  out: u32 [cols/16][2n]; h_sc out: f16 bits [cols/128][n], output o of a 64-group at 8 (o % 8) + o / 8
+int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int cols, int group, const int* h_order, int n,
+                   uint32_t* h_words, uint16_t* h_sc) {
+    if (!h_q || !h_scales || !h_order || !h_words || !h_sc) return QB_ERR_ARG;
+    if (n % 64 || cols % 128 || group % 128 || cols % group) return QB_ERR_ARG;
+    for (int i = 0; i < n; i++)
+        if (h_order[i] < 0 || h_order[i] >= rows) return QB_ERR_ARG;
+    const int words = cols / 8, groups = cols / 128, qgroups = cols / group;
+    for (int o = 0; o < n; o++) {
+        int c64 = o / 64, c = o % 64, at = c64 * 64 + 8 * (c % 8) + c / 8;
+        for (int gi = 0; gi < groups; gi++)
+            h_sc[(size_t)gi * n + at] = f16_bits(h_scales[(size_t)h_order[o] * qgroups + gi * 128 / group]);
+    }
+    parallel_for(cols / 16, [&](int k16) {
+        uint32_t* ws = h_words + (size_t)k16 * 2 * n;
+        int k0 = k16 * 16;
+        for (int c64 = 0; c64 < n / 64; c64++)
+            for (int lane = 0; lane < 32; lane++) {
+                int g = lane / 4, t = lane % 4;
+                for (int blk = 0; blk < 4; blk++) {
+                    const int* rws = h_order + c64 * 64 + blk * 16;
+                    uint32_t word = 0;
+                    for (int x = 0; x < 8; x++) {
+                        int row = rws[g + 8 * ((x >> 1) & 1)], c = k0 + 2 * t + 8 * (x & 1) + (x >> 2);
+                        uint32_t v = (h_q[(size_t)row * words + c / 8] >> ((c % 8) * 4)) & 15u;
+                        word |= v << (4 * x);
+                    }
+                    ws[(c64 * 32 + lane) * 4 + blk] = word;
+                }
+            }
+    });
+    return QB_OK;
+}
+
+// A dense matrix (f32 [rows][cols]) -> f16 tiles of 16 rows in mma A-fragment order, [tile][cols/16][32 lanes][8]
+// (pack, src/cuda/core.rs:337-391, the f16 branch; frag :222-227). rows = n packed rows through h_order.
+int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n, uint16_t* h_out) {
+    if (!h_w || !h_out || n % 16 || cols % 16) return QB_ERR_ARG;
+    parallel_for(n / 16, [&](int tile) {
+        uint16_t* o = h_out + (size_t)tile * 16 * cols;
+        for (int k16 = 0; k16 < cols / 16; k16++)
+            for (int lane = 0; lane < 32; lane++) {
+                int g = lane / 4, t = lane % 4, c = k16 * 16 + 2 * t;
+                int rc[8][2] = {{g, c}, {g, c + 1}, {g + 8, c}, {g + 8, c + 1},
+                                {g, c + 8}, {g, c + 9}, {g + 8, c + 8}, {g + 8, c + 9}};
+                for (int e = 0; e < 8; e++) {
+                    int pr = tile * 16 + rc[e][0];
+                    int row = h_order ? h_order[pr] : pr;
+                    *o++ = f16_bits(h_w[(size_t)row * cols + rc[e][1]]);
+                }
+            }
+    });
+    (void)rows;
+    return QB_OK;
+}
+
+// Split-K factor of the dense decode products (split_for, src/cuda/core.rs:393-398).
+int qb_split_for(int tiles, int cols, int bits, int kd) {
+    const int UNITS = 1024;
+    int stage_cols = 2048 / bits, chunks = cols / stage_cols;
+    int want = std::max((UNITS + tiles - 1) / tiles, (cols + kd - 1) / kd);
+    for (int d = 1; d <= chunks; d++)
+        if (chunks % d == 0 && d >= want) return d;
+    return chunks;
+}
+
+}  // extern "C"

@@ -1,0 +1,349 @@
+// W4A16 skinny matrix product for decode / verify steps (1..16 token rows): Y = X . W^T with W int4 (symmetric,
+// groups of 128 columns, f16 scales) in the reference's Marlin layout, X f16, f32 accumulation.
+//
+// Replaces marlin::mul<1,8,8,*> (kernels/marlin.cuh:171-582 of the reference) for steps of up to 16 tokens. It is a
+// bandwidth-bound GEMV, organised around the HBM stream rather than around the tensor pipe:
+//  * a producer warp streams the weights with descriptor-free bulk async copies (cp.async.bulk, the TMA engine)
+//    into a ring of shared-memory stages; a stage is TN = 64 CG outputs x TK = 128 KG columns of packed int4
+//    (4 KB per consumer warp), its group scales and the matching slice of X; full/empty mbarriers, no __syncthreads
+//    in the stream;
+//  * consumer warp (cg, kg) owns 64 outputs x one scale group of the stage. The Marlin word of lane (g, t) holds
+//    outputs {g, g + 8} x columns {2t, 2t+1, 2t+8, 2t+9} of a 16-output block: exactly the A fragment of
+//    mma.m16n8k16 when the WEIGHTS are the A operand and the tokens the n = 8 side, so the nibbles go from one
+//    128-bit shared load through four lop3 and four hsub2 straight into the tensor core, no shuffles, no
+//    re-layout. The group scale is applied in f32 to the group's partial sum (exact, and 8x fewer multiplies
+//    than scaling every weight);
+//  * work is split into units (TN outputs x kper columns), dealt round-robin to a persistent grid, so the copy
+//    pipeline never drains between units. The KG warps of a column group add up in shared memory in a fixed order;
+//    with split K the units of a column group leave f32 partials in an L2-resident scratch and the LAST unit to
+//    arrive (an atomic ticket, no waiting) adds them in split order and runs the epilogue. Every sum has a fixed
+//    order that depends on the shape alone, never on the number of rows or on timing: a row's result is bit-identical
+//    alone or next to drafts.
+// Epilogues as the reference's: plain f32 [m][n]; SwiGLU of interleaved gate/up blocks -> f16 [m][n/2]
+// (kernels/marlin.cuh:472-498); plain + argmax keys over the first n_valid outputs (:499-517).
+#pragma once
+#include "common.cuh"
+
+namespace qb {
+
+enum { EPI_PLAIN = 0, EPI_SILU = 1, EPI_ARGMAX = 2 };
+
+struct GemvArgs {
+    const __half* X;      // [rows][K] f16
+    const int* xrows;     // X row of token t (null: row0 + t)
+    const uint32_t* B;    // Marlin words [K/16][2N]
+    const __half* S;      // scales [K/128][N], permuted per 64 outputs
+    void* Y;              // plain/argmax: f32 [.][N]; silu: f16 [.][N/2]; rows row0 .. row0 + m - 1
+    int m, N, K, row0;
+    int kper, nsplit;     // K = kper * nsplit, kper a multiple of TK
+    int nstages;          // ring depth
+    float4* scratch;      // split-K partials: [N/64][nsplit][4][32] float4 (x NT)
+    int* counters;        // [N/64] tickets, zero between launches
+    unsigned long long* keys;
+    int n_valid;
+    int* err;             // set non-zero when a bounded wait ran out
+};
+
+constexpr int GEMV_MAX_STAGES = 8;
+
+template <int CG, int KG, int NT>
+struct GemvCfg {
+    static constexpr int NW = CG * KG;               // consumer warps
+    static constexpr int THREADS = (NW + 1) * 32;    // + the producer warp
+    static constexpr int TN = CG * 64, TK = KG * 128;
+    static constexpr int W_BYTES = NW * 4096;        // TK/16 k16-steps x CG x 512 B
+    static constexpr int XROW = TK + 8;              // halves; the pad spreads the 8 token rows over the banks
+    static constexpr int X_BYTES = 8 * NT * XROW * 2;
+    static constexpr int S_BYTES = KG * TN * 2;
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + S_BYTES;
+    static constexpr int RED_BYTES = (KG - 1) * CG * NT * 2048;
+    static constexpr int BAR_BYTES = 128;
+    static constexpr int smem(int nstages) { return BAR_BYTES + nstages * STAGE_BYTES + RED_BYTES; }
+};
+
+// One Marlin word (8 nibbles q + 8) -> the four A-fragment registers of signed values q - 8, exactly:
+// 0x6400 | n is the half 1024 + n (nibbles 0, 4), 0x5400 | (n << 4) the half 64 + n (nibbles 1, 5).
+__device__ __forceinline__ void dequant_word(uint32_t q, uint32_t* a) {
+    uint32_t lo0, hi0, lo1, hi1;
+    asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo0) : "r"(q));
+    asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi0) : "r"(q));
+    uint32_t q8 = q >> 8;
+    asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo1) : "r"(q8));
+    asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi1) : "r"(q8));
+    const uint32_t SUB_LO = 0x64086408u, SUB_HI = 0x54805480u;  // 1032, 72
+    __half2 r0 = __hsub2(*(__half2*)&lo0, *(const __half2*)&SUB_LO);  // outputs g,     columns 2t, 2t+1
+    __half2 r1 = __hsub2(*(__half2*)&lo1, *(const __half2*)&SUB_LO);  // outputs g + 8, columns 2t, 2t+1
+    __half2 r2 = __hsub2(*(__half2*)&hi0, *(const __half2*)&SUB_HI);  // outputs g,     columns 2t+8, 2t+9
+    __half2 r3 = __hsub2(*(__half2*)&hi1, *(const __half2*)&SUB_HI);  // outputs g + 8, columns 2t+8, 2t+9
+    a[0] = *(uint32_t*)&r0; a[1] = *(uint32_t*)&r1; a[2] = *(uint32_t*)&r2; a[3] = *(uint32_t*)&r3;
+}
+
+template <int CG, int KG, int NT, int EPI>
+__global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kernel(const GemvArgs a) {
+    using C = GemvCfg<CG, KG, NT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + GEMV_MAX_STAGES;
+    uint8_t* stages = smem + C::BAR_BYTES;
+    float4* red = (float4*)(stages + (size_t)a.nstages * C::STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nstages = a.nstages;
+    const int ncb = a.N / C::TN, nunits = ncb * a.nsplit, nst = a.kper / C::TK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < nstages; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], C::NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == C::NW) {
+        // ------------------------------------------------------------ producer
+        const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+        int my_units = blockIdx.x < nunits ? (nunits - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+        const uint32_t total = (uint32_t)my_units * nst;
+        const uint32_t tx = C::W_BYTES + C::S_BYTES + a.m * C::TK * 2;
+        // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
+        auto issue = [&](uint32_t it, int what) {
+            int ui = it / nst, st = it - ui * nst, u = blockIdx.x + ui * gridDim.x;
+            int cb = u / a.nsplit, sp = u - cb * a.nsplit;
+            int n0 = cb * C::TN, k0 = sp * a.kper + st * C::TK;
+            int slot = it % nstages;
+            uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
+            if (what != 1) {
+                if (lane == 0) mbar_expect_tx(&full[slot], tx);
+                __syncwarp();
+                const uint8_t* wsrc = (const uint8_t*)a.B + ((size_t)(k0 / 16) * 2 * a.N + (size_t)(n0 / 64) * 128) * 4;
+                for (int c = lane; c < C::TK / 16; c += 32)
+                    bulk_g2s(base + c * (CG * 512), wsrc + (size_t)c * 8 * a.N, CG * 512, &full[slot], pol_w);
+                if (lane < KG)
+                    bulk_g2s(base + C::W_BYTES + C::X_BYTES + lane * (C::TN * 2),
+                             a.S + (size_t)(k0 / 128 + lane) * a.N + n0, C::TN * 2, &full[slot], pol_w);
+            }
+            if (what != 0) {
+                if (lane < a.m) {
+                    int row = a.xrows ? a.xrows[lane] : a.row0 + lane;
+                    bulk_g2s(base + C::W_BYTES + lane * (C::XROW * 2), a.X + (size_t)row * a.K + k0, C::TK * 2,
+                             &full[slot], pol_x);
+                }
+            }
+        };
+        // the weights of the first ring-full of stages do not depend on the previous kernel: start them, then wait
+        // for it (its activations are this kernel's X)
+        uint32_t pre = total < (uint32_t)nstages ? total : (uint32_t)nstages;
+        for (uint32_t it = 0; it < pre; it++) issue(it, 0);
+        pdl_wait();
+        for (uint32_t it = 0; it < pre; it++) issue(it, 1);
+        bool ok = true;
+        for (uint32_t it = pre; it < total && ok; it++) {
+            int slot = it % nstages;
+            uint32_t par = ((it / nstages) & 1) ^ 1;
+            if (lane == 0) ok = mbar_wait(&empty[slot], par);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            issue(it, 2);
+        }
+        if (!ok && lane == 0) atomicExch(a.err, 1);
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    pdl_wait();
+    const int cg = warp % CG, kg = warp / CG, g = lane >> 2, t = lane & 3;
+    float acc[NT][4][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
+
+    uint32_t it = 0;
+    // A wait that runs out marks the warp dead: it records the error, then walks the rest of its schedule with
+    // short waits only (so that copies already in flight still land in a live block) and keeps meeting the block's
+    // barriers, and the kernel ends instead of hanging.
+    bool dead = false;
+    for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+        const int cb = u / a.nsplit, sp = u - cb * a.nsplit;
+        for (int st = 0; st < nst; st++, it++) {
+            int slot = it % nstages;
+            if (!dead) {
+                dead = !mbar_wait(&full[slot], (it / nstages) & 1);
+                if (dead && lane == 0) atomicExch(a.err, 2);
+            } else {
+                for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], (it / nstages) & 1); i++) {}
+            }
+            const uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
+            const uint4* wp = (const uint4*)(base + (size_t)(kg * 8 * CG + cg) * 512) + lane;
+            const __half* xs = (const __half*)(base + C::W_BYTES) + kg * 128 + 2 * t;
+            uint4 sc4 = *(const uint4*)(base + C::W_BYTES + C::X_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
+            float tmp[NT][4][4];
+#pragma unroll
+            for (int j = 0; j < NT; j++)
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) tmp[j][b][i] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                uint4 w = wp[ks * CG * 32];
+                uint32_t bx[NT][2];
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    const __half* xr = xs + (8 * j + g) * C::XROW + ks * 16;
+                    bool live = 8 * j + g < a.m;
+                    bx[j][0] = live ? *(const uint32_t*)xr : 0u;
+                    bx[j][1] = live ? *(const uint32_t*)(xr + 8) : 0u;
+                }
+                uint32_t wq[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    uint32_t af[4];
+                    dequant_word(wq[b], af);
+#pragma unroll
+                    for (int j = 0; j < NT; j++) mma16816(tmp[j][b], af, bx[j][0], bx[j][1]);
+                }
+            }
+            // the group's scales: half 2 b + h of the lane's 16 bytes is output 16 b + g + 8 h
+            const __half* sh = (const __half*)&sc4;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                float s0 = __half2float(sh[2 * b]), s1 = __half2float(sh[2 * b + 1]);
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    acc[j][b][0] += s0 * tmp[j][b][0]; acc[j][b][1] += s0 * tmp[j][b][1];
+                    acc[j][b][2] += s1 * tmp[j][b][2]; acc[j][b][3] += s1 * tmp[j][b][3];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+
+        // ---- the KG warps of a column group: kg > 0 hand their sums to kg = 0, which adds them in kg order
+        if (KG > 1) {
+            if (kg > 0) {
+                float4* r = red + (size_t)((kg - 1) * CG + cg) * NT * 4 * 32;
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++)
+                        r[(j * 4 + b) * 32 + lane] = make_float4(acc[j][b][0], acc[j][b][1], acc[j][b][2], acc[j][b][3]);
+            }
+            named_bar_sync(1, C::NW * 32);
+            if (kg == 0) {
+#pragma unroll
+                for (int kk = 1; kk < KG; kk++) {
+                    const float4* r = red + (size_t)((kk - 1) * CG + cg) * NT * 4 * 32;
+#pragma unroll
+                    for (int j = 0; j < NT; j++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            float4 v = r[(j * 4 + b) * 32 + lane];
+                            acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
+                        }
+                }
+            }
+            named_bar_sync(2, C::NW * 32);
+        }
+
+        if (kg == 0) {
+            const int colgrp = cb * CG + cg;  // 64 outputs
+            bool finish = true;
+            if (a.nsplit > 1) {
+                float4* mine = a.scratch + ((size_t)colgrp * a.nsplit + sp) * (NT * 4 * 32);
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++)
+                        __stcg(mine + (j * 4 + b) * 32 + lane,
+                               make_float4(acc[j][b][0], acc[j][b][1], acc[j][b][2], acc[j][b][3]));
+                __threadfence();
+                __syncwarp();
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(a.counters + colgrp, 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                finish = ticket == a.nsplit - 1;
+                if (finish) {
+                    __threadfence();
+                    const float4* p0 = a.scratch + (size_t)colgrp * a.nsplit * (NT * 4 * 32);
+#pragma unroll
+                    for (int j = 0; j < NT; j++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++)
+#pragma unroll
+                            for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
+                    for (int s = 0; s < a.nsplit; s++) {
+#pragma unroll
+                        for (int j = 0; j < NT; j++)
+#pragma unroll
+                            for (int b = 0; b < 4; b++) {
+                                float4 v = __ldcg(p0 + (size_t)s * (NT * 4 * 32) + (j * 4 + b) * 32 + lane);
+                                acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
+                            }
+                    }
+                    if (lane == 0) a.counters[colgrp] = 0;  // left zero for the next product
+                }
+            }
+            if (finish) {
+                const int col = colgrp * 64;
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        int tok = 8 * j + 2 * t + e;
+                        if (tok >= a.m) continue;
+                        if (EPI == EPI_SILU) {
+                            __half* y = (__half*)a.Y + (size_t)(a.row0 + tok) * (a.N / 2) + col / 2 + g;
+#pragma unroll
+                            for (int b = 0; b < 4; b++)
+                                y[8 * b] = __float2half_rn(silu(acc[j][b][e]) * acc[j][b][2 + e]);
+                        } else {
+                            float* y = (float*)a.Y + (size_t)(a.row0 + tok) * a.N + col + g;
+#pragma unroll
+                            for (int b = 0; b < 4; b++) {
+                                y[16 * b] = acc[j][b][e];
+                                y[16 * b + 8] = acc[j][b][2 + e];
+                            }
+                        }
+                    }
+                if (EPI == EPI_ARGMAX) {
+#pragma unroll
+                    for (int j = 0; j < NT; j++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            unsigned long long k = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; b++)
+#pragma unroll
+                                for (int h = 0; h < 2; h++) {
+                                    int o = col + 16 * b + g + 8 * h;
+                                    if (o < a.n_valid) {
+                                        unsigned long long kk = argmax_key(acc[j][b][2 * h + e], o);
+                                        k = kk > k ? kk : k;
+                                    }
+                                }
+#pragma unroll
+                            for (int o = 4; o < 32; o <<= 1) {
+                                unsigned long long kk = __shfl_xor_sync(0xffffffffu, k, o);
+                                k = kk > k ? kk : k;
+                            }
+                            int tok = 8 * j + 2 * t + e;
+                            if (g == 0 && tok < a.m && k) atomicMax(a.keys + a.row0 + tok, k);
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int b = 0; b < 4; b++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
+    }
+}
+
+}  // namespace qb

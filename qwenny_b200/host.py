@@ -1,0 +1,64 @@
+"""Host-side mirror of the reference's loader functions for this path (src/cuda/core.rs): numpy in, numpy out, the
+work done by the library's C++ packers."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+
+QG = 128
+
+
+def _np(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def row_order(rows: int, silu: bool) -> np.ndarray:
+    out = np.empty(rows, dtype=np.int32)
+    check(lib().qb_row_order(rows, int(silu), _np(out)), "qb_row_order")
+    return out
+
+
+def quant_words(codes: np.ndarray) -> np.ndarray:
+    """uint8 codes [rows][cols] (q + 8) -> the stored form u32 [rows][cols/8], column c at bits (c % 8) * 4."""
+    rows, cols = codes.shape
+    c = codes.reshape(rows, cols // 8, 8).astype(np.uint32)
+    w = np.zeros((rows, cols // 8), dtype=np.uint32)
+    for i in range(8):
+        w |= c[:, :, i] << np.uint32(4 * i)
+    return w
+
+
+def pack_marlin(codes: np.ndarray, scales: np.ndarray, silu: bool = False, order: np.ndarray | None = None,
+                group: int = QG):
+    """codes uint8 [rows][cols] (q + 8), scales f32 [rows][cols/group] -> (words uint32 [cols/16][2n],
+    scales float16 [cols/128][n]) as Mat::marlin does (src/cuda/core.rs:160-164)."""
+    rows, cols = codes.shape
+    if order is None:
+        order = row_order(rows, silu)
+    order = np.ascontiguousarray(order, dtype=np.int32)
+    n = len(order)
+    q = np.ascontiguousarray(quant_words(codes))
+    sc = np.ascontiguousarray(scales, dtype=np.float32)
+    words = np.empty((cols // 16, 2 * n), dtype=np.uint32)
+    s16 = np.empty((cols // 128, n), dtype=np.uint16)
+    check(lib().qb_pack_marlin(_np(q), _np(sc), rows, cols, group, _np(order), n, _np(words), _np(s16)),
+          "qb_pack_marlin")
+    return words, s16.view(np.float16)
+
+
+def pack_f16(w: np.ndarray, order: np.ndarray | None = None) -> np.ndarray:
+    """f32 [rows][cols] -> float16 [rows/16][cols/16][32][8] (mma A-fragment order)."""
+    rows, cols = w.shape
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n = rows if order is None else len(order)
+    out = np.empty((n // 16, cols // 16, 32, 8), dtype=np.uint16)
+    o = None if order is None else np.ascontiguousarray(order, dtype=np.int32)
+    check(lib().qb_pack_f16(_np(w), rows, cols, C.c_void_p(0) if o is None else _np(o), n, _np(out)), "qb_pack_f16")
+    return out.view(np.float16)
+
+
+def split_for(tiles: int, cols: int, bits: int, kd: int) -> int:
+    return lib().qb_split_for(tiles, cols, bits, kd)

@@ -1,0 +1,150 @@
+"""Parity of the W4A16 skinny product (qb_marlin_gemm) on the GPU: against the CPU oracle, against the reference's
+own Marlin kernels on the same device buffers, and its invariants (bit-exact unpack, row-count invariance)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_ops as R
+from qwenny_b200 import host, synth
+
+pytestmark = pytest.mark.gpu
+
+# BASELINE tolerance for matrix-product outputs: 1e-2 relative / 2e-3 absolute after rounding both sides to bf16
+RTOL, ATOL = 1e-2, 2e-3
+
+
+def bf16(a):
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def close(a, b):
+    a, b = bf16(a), bf16(b)
+    return np.abs(a - b) <= ATOL + RTOL * np.abs(b)
+
+
+def make(rows, cols, silu, seed, m):
+    g = synth.gen(seed)
+    x = synth.activations(m, cols, g)
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    words, s16 = host.pack_marlin(codes, sc, silu=silu)
+    wdq = R.dequant(codes, sc.astype(np.float16))[R.row_order(rows, silu)]
+    dev = lambda a: torch.from_numpy(a).cuda()
+    return x, wdq, dev(x), dev(words.view(np.int32)), dev(s16.view(np.int16)).view(torch.float16)
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 13, 16])
+@pytest.mark.parametrize("rows,cols", [(512, 1024), (2560, 512), (256, 128)])
+def test_plain_vs_oracle(ctx, m, rows, cols):
+    x, wdq, xd, wd, sd = make(rows, cols, False, 10 + m, m)
+    y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+    want = R.marlin_gemm(x, wdq)
+    assert close(y, want).all()
+    assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("cfg", [(2, 4, 1), (2, 4, 2), (4, 2, 1), (4, 2, 4), (8, 1, 2), (8, 1, 8), (1, 8, 1)])
+def test_every_tile_shape_and_split(ctx, cfg):
+    cg, kg, nsplit = cfg
+    x, wdq, xd, wd, sd = make(1024, 2048, False, 3, 5)
+    ctx.tune(cg=cg, kg=kg, nsplit=nsplit)
+    try:
+        y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+        y2 = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()  # tickets left at zero: a second product works
+    finally:
+        ctx.tune()
+    want = R.marlin_gemm(x, wdq)
+    assert close(y, want).all()
+    assert np.array_equal(y, y2)
+
+
+def test_unpack_bit_exact(ctx):
+    """X = identity rows: row t of Y is column t of the dequantised matrix, exactly (bf16 scales: (q-8)*s is exact)."""
+    rows, cols = 512, 256
+    g = synth.gen(5)
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    words, s16 = host.pack_marlin(codes, sc)
+    wd = torch.from_numpy(words.view(np.int32)).cuda()
+    sd = torch.from_numpy(s16.view(np.int16)).cuda().view(torch.float16)
+    wdq = R.dequant(codes, sc.astype(np.float16)).astype(np.float32)
+    for c0 in range(0, cols, 16):
+        x = np.zeros((16, cols), dtype=np.float16)
+        x[np.arange(16), c0 + np.arange(16)] = 1
+        y = ctx.marlin_gemm(torch.from_numpy(x).cuda(), wd, sd).cpu().numpy()
+        assert np.array_equal(y, wdq[:, c0:c0 + 16].T)
+
+
+def test_row_count_invariance(ctx):
+    """A row's result is bit-identical alone, among 5 rows, or among 16 (the reference's speccheck property)."""
+    x, wdq, xd, wd, sd = make(1024, 5120, False, 7, 16)
+    y16 = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+    y5 = ctx.marlin_gemm(xd[:5].contiguous(), wd, sd).cpu().numpy()
+    assert np.array_equal(y5, y16[:5])
+    for t in (0, 3, 15):
+        y1 = ctx.marlin_gemm(xd[t:t + 1].contiguous(), wd, sd).cpu().numpy()
+        assert np.array_equal(y1[0], y16[t])
+    # row0: rows 4..8 of X written to rows 4..8 of Y
+    y = torch.zeros(16, 1024, device="cuda")
+    ctx.marlin_gemm(xd, wd, sd, y=y, row0=4, m=5)
+    assert np.array_equal(y.cpu().numpy()[4:9], y16[4:9]) and float(y[:4].abs().max()) == 0
+
+
+def test_silu_vs_oracle_and_reference(ctx, ref):
+    rows, cols, m = 1024, 1024, 5
+    x, wdq, xd, wd, sd = make(rows, cols, True, 11, m)
+    y = ctx.marlin_gemm(xd, wd, sd, epi="silu")
+    want = R.marlin_gemm(x, wdq, "silu")
+    assert y.shape == (m, rows // 2)
+    assert close(y.float().cpu().numpy(), want.astype(np.float32)).all()
+    yr = torch.zeros_like(y)
+    ref.marlin(m, wd, sd, xd, yr, "silu")
+    assert close(y.float().cpu().numpy(), yr.float().cpu().numpy()).all()
+
+
+def test_argmax_vs_oracle_and_reference(ctx, ref):
+    rows, cols, valid = 2048, 512, 1936
+    g = synth.gen(12)
+    xall = synth.activations(9, cols, g)
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    words, s16 = host.pack_marlin(codes, sc)
+    wdq = R.dequant(codes, sc.astype(np.float16))
+    xd = torch.from_numpy(xall).cuda()
+    wd = torch.from_numpy(words.view(np.int32)).cuda()
+    sd = torch.from_numpy(s16.view(np.int16)).cuda().view(torch.float16)
+    out_rows = torch.tensor([8, 2, 5], dtype=torch.int32, device="cuda")
+    keys = torch.zeros(8, dtype=torch.int64, device="cuda")
+    y = ctx.marlin_gemm(xd, wd, sd, epi="argmax", xrows=out_rows, keys=keys, n_valid=valid).cpu().numpy()
+    want, wkeys = R.marlin_gemm(xall[[8, 2, 5]], wdq, "argmax", valid)
+    assert close(y, want).all()
+    got = keys.cpu().numpy().view(np.uint64)[:3]
+    assert np.array_equal(R.key_token(got), R.key_token(wkeys))
+    assert all(int(t) < valid for t in R.key_token(got))
+    # the reference: marlin_gather + marlin argmax
+    xg = torch.zeros(3, cols, dtype=torch.float16, device="cuda")
+    ref.marlin_gather(xd, out_rows, xg, cols)
+    rkeys = torch.zeros(8, dtype=torch.int64, device="cuda")
+    yr = torch.zeros(3, rows, device="cuda")
+    ref.marlin(3, wd, sd, xg, yr, "argmax", keys=rkeys, valid=valid)
+    assert close(y, yr.cpu().numpy()).all()
+    assert np.array_equal(R.key_token(got), R.key_token(rkeys.cpu().numpy().view(np.uint64)[:3]))
+
+
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_config0_vs_reference_kernel(ctx, ref, m):
+    """BASELINE config 0: N=17408 x K=5120, g128, against the reference's marlin_m1_n8_plain on the same buffers."""
+    x, wdq, xd, wd, sd = make(17408, 5120, False, 0, m)
+    y = ctx.marlin_gemm(xd, wd, sd)
+    yr = torch.zeros_like(y)
+    ref.marlin(m, wd, sd, xd, yr, "plain")
+    torch.cuda.synchronize()
+    a, b = y.cpu().numpy(), yr.cpu().numpy()
+    assert close(a, b).all()
+    want = R.marlin_gemm(x, wdq)
+    assert close(a, want).all() and close(b, want).all()
+    # both are f32 sums of exact products in different orders: far inside the tolerance
+    assert np.abs(a - b).max() < 1e-4 * np.abs(want).max()
+
+
+def test_many_rows_fall_back_to_slabs(ctx):
+    x, wdq, xd, wd, sd = make(512, 512, False, 21, 40)
+    y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+    assert close(y, R.marlin_gemm(x, wdq)).all()
