@@ -50,9 +50,9 @@ const char* qb_version(void);
 int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                    int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 
-/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), split-K factor, ring depth and
- * blocks per SM of the next qb_marlin_gemm calls; zeros restore the built-in choice. */
-int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nsplit, int nstages, int ctas_per_sm);
+/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
+ * next qb_marlin_gemm calls; zeros restore the built-in choice. */
+int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
 /* ---- host-side weight packers (load time; host pointers). They produce the layouts the reference's loader
  * produces, which every kernel here reads unchanged.

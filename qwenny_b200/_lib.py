@@ -22,7 +22,7 @@ SIGNATURES = {
     "qb_version": [],
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
-    "qb_marlin_tune": [P, I, I, I, I, I],
+    "qb_marlin_tune": [P, I, I, I, I],
     "qb_row_order": [I, I, P],
     "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],

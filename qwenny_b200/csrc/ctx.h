@@ -15,7 +15,7 @@ struct qb_ctx {
     size_t ncounters = 0;
     int* err = nullptr;  // device word
     // measurement override of the GEMV plan (0: built-in choice)
-    int tune_cg = 0, tune_kg = 0, tune_nsplit = 0, tune_nstages = 0, tune_ctas = 0;
+    int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
     // programmatic dependent launch on the launches that support it
     bool pdl = false;
 };

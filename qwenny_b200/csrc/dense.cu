@@ -1,0 +1,182 @@
+// The small per-token kernels of a step: embedding lookup, RMSNorm, residual + split sum + RMSNorm, f32 -> f16 cast,
+// split sum, the seen-token bitsets, row gather. One entry point per kernel of the reference
+// (kernels/dense.cuh, kernels/qwen.cu:57-80,136-143, kernels/sampling.cuh:14-26, kernels/marlin.cuh:605-608).
+// They move kilobytes; what matters is latency, so each token row is spread over a whole block with 128-bit
+// accesses and every kernel can be launched ahead of its predecessor (pdl_wait guards the first dependent read).
+#include "common.cuh"
+#include "launch.h"
+
+namespace qb {
+
+constexpr int ROW_THREADS = 640;         // H / 8: one 8-element vector per thread
+static_assert(H % 8 == 0 && H / 8 == ROW_THREADS, "a row of H is one vector of 8 per thread");
+
+// out[t] = E[ids[t]] (bf16 -> f32); the first nkeys blocks clear the step's argmax keys
+__global__ void __launch_bounds__(ROW_THREADS) embed_kernel(const __nv_bfloat16* E, const int* ids, float* out,
+                                                            unsigned long long* keys, int nkeys) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int t = blockIdx.x;
+    if (threadIdx.x == 0 && t < nkeys) keys[t] = 0;
+    const uint4* row = (const uint4*)(E + (size_t)ids[t] * H);
+    uint4 v = row[threadIdx.x];
+    const __nv_bfloat162* b = (const __nv_bfloat162*)&v;
+    float4* o = (float4*)(out + (size_t)t * H) + 2 * threadIdx.x;
+    float2 a0 = __bfloat1622float2(b[0]), a1 = __bfloat1622float2(b[1]), a2 = __bfloat1622float2(b[2]),
+           a3 = __bfloat1622float2(b[3]);
+    o[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
+    o[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
+}
+
+__device__ __forceinline__ void store_norm8(__half* y, const float* v, const float* w, float r) {
+    uint4 o;
+    o.x = pack_half2(w[0] * (v[0] * r), w[1] * (v[1] * r));
+    o.y = pack_half2(w[2] * (v[2] * r), w[3] * (v[3] * r));
+    o.z = pack_half2(w[4] * (v[4] * r), w[5] * (v[5] * r));
+    o.w = pack_half2(w[6] * (v[6] * r), w[7] * (v[7] * r));
+    *(uint4*)y = o;
+}
+
+// y = w * x / rms(x) -> f16, one block per token
+__global__ void __launch_bounds__(ROW_THREADS) rmsnorm_kernel(const float* x, const float* w, __half* y, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    float wv[8];
+    *(float4*)&wv[0] = ((const float4*)w)[2 * threadIdx.x];
+    *(float4*)&wv[4] = ((const float4*)w)[2 * threadIdx.x + 1];
+    pdl_wait();
+    const float4* xr = (const float4*)(x + (size_t)blockIdx.x * H) + 2 * threadIdx.x;
+    float v[8];
+    *(float4*)&v[0] = xr[0];
+    *(float4*)&v[4] = xr[1];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) ss += v[i] * v[i];
+    float r = rsqrtf(block_sum(ss, sh) / H + eps);
+    store_norm8(y + (size_t)blockIdx.x * H + 8 * threadIdx.x, v, wv, r);
+}
+
+// h += sum over splits of x [split][n][H]; y = w_next * h / rms(h) -> f16
+__global__ void __launch_bounds__(ROW_THREADS) add_rmsnorm_kernel(float* h, const float* x, int splits, int n,
+                                                                  const float* w_next, __half* y, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    float wv[8];
+    *(float4*)&wv[0] = ((const float4*)w_next)[2 * threadIdx.x];
+    *(float4*)&wv[4] = ((const float4*)w_next)[2 * threadIdx.x + 1];
+    pdl_wait();
+    size_t base = (size_t)blockIdx.x * H + 8 * threadIdx.x;
+    float v[8];
+    *(float4*)&v[0] = *(const float4*)(h + base);
+    *(float4*)&v[4] = *(const float4*)(h + base + 4);
+    for (int s = 0; s < splits; s++) {
+        const float* p = x + (size_t)s * n * H + base;
+        float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    }
+    *(float4*)(h + base) = *(float4*)&v[0];
+    *(float4*)(h + base + 4) = *(float4*)&v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) ss += v[i] * v[i];
+    float r = rsqrtf(block_sum(ss, sh) / H + eps);
+    store_norm8(y + base, v, wv, r);
+}
+
+__global__ void __launch_bounds__(256) to_xin_kernel(const float* x, __half* y, int len) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    for (; i + 3 < len; i += gridDim.x * blockDim.x * 4) {
+        float4 v = *(const float4*)(x + i);
+        *(uint2*)(y + i) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (len & 3)) y[(len & ~3) + threadIdx.x] = __float2half_rn(x[(len & ~3) + threadIdx.x]);
+}
+
+__global__ void __launch_bounds__(256) sum_parts_kernel(const float* x, int splits, int n, int ld, float* y) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int c = threadIdx.x; c < ld; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += x[((size_t)s * n + blockIdx.x) * ld + c];
+        y[(size_t)blockIdx.x * ld + c] = v;
+    }
+}
+
+// One block per segment: a segment at position 0 clears its slot's set, then its marked tokens are set
+__global__ void __launch_bounds__(256) mark_seen_kernel(unsigned* seen, const int* mark, const int* mark_at,
+                                                        const int* seg_slot, const int* seg_pos0, int seen_words) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int sg = blockIdx.x;
+    unsigned* sb = seen + (size_t)seg_slot[sg] * seen_words;
+    if (seg_pos0[sg] == 0) {
+        for (int i = threadIdx.x; i < seen_words; i += blockDim.x) sb[i] = 0;
+        __syncthreads();
+    }
+    for (int i = mark_at[sg] + threadIdx.x; i < mark_at[sg + 1]; i += blockDim.x) {
+        int id = mark[i];
+        atomicOr(sb + (id >> 5), 1u << (id & 31));
+    }
+}
+
+__global__ void __launch_bounds__(128) gather_rows_kernel(const uint4* x, const int* rows, uint4* out, int k8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint4* row = x + (size_t)rows[blockIdx.x] * k8;
+    for (int c = threadIdx.x; c < k8; c += blockDim.x) out[(size_t)blockIdx.x * k8 + c] = row[c];
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" {
+
+int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
+             int nkeys, int n) {
+    if (!ctx || !E || !ids || !out || n <= 0 || nkeys > n || (nkeys > 0 && !keys)) return QB_ERR_ARG;
+    return launch(ctx, embed_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, (const __nv_bfloat16*)E, ids,
+                  out, keys, nkeys);
+}
+
+int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n) {
+    if (!ctx || !x || !w || !y || n <= 0) return QB_ERR_ARG;
+    return launch(ctx, rmsnorm_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, x, w, (__half*)y, eps);
+}
+
+int qb_add_rmsnorm(qb_ctx* ctx, void* stream, float* h, const float* x, int splits, int n, const float* w_next,
+                   void* y, float eps) {
+    if (!ctx || !h || !x || !w_next || !y || n <= 0 || splits < 1) return QB_ERR_ARG;
+    return launch(ctx, add_rmsnorm_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, h, x, splits, n,
+                  w_next, (__half*)y, eps);
+}
+
+int qb_to_xin(qb_ctx* ctx, void* stream, const float* x, void* y, int len) {
+    if (!ctx || !x || !y || len <= 0) return QB_ERR_ARG;
+    int blocks = (len + 1023) / 1024;
+    if (blocks > 1024) blocks = 1024;
+    return launch(ctx, to_xin_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (__half*)y, len);
+}
+
+int qb_sum_parts(qb_ctx* ctx, void* stream, const float* x, int splits, int n, int ld, float* y) {
+    if (!ctx || !x || !y || n <= 0 || ld <= 0 || splits < 1) return QB_ERR_ARG;
+    return launch(ctx, sum_parts_kernel, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, splits, n, ld, y);
+}
+
+int qb_mark_seen(qb_ctx* ctx, void* stream, unsigned* seen, const int* mark, const int* mark_at, const int* seg_slot,
+                 const int* seg_pos0, int segs, int vocab) {
+    if (!ctx || !seen || !mark || !mark_at || !seg_slot || !seg_pos0 || segs <= 0 || vocab % 32) return QB_ERR_ARG;
+    return launch(ctx, mark_seen_kernel, dim3(segs), dim3(256), 0, (cudaStream_t)stream, seen, mark, mark_at, seg_slot,
+                  seg_pos0, vocab / 32);
+}
+
+int qb_marlin_gather(qb_ctx* ctx, void* stream, const void* x, const int* rows, void* out, int k8, int n) {
+    if (!ctx || !x || !rows || !out || n <= 0 || k8 <= 0) return QB_ERR_ARG;
+    return launch(ctx, gather_rows_kernel, dim3(n), dim3(128), 0, (cudaStream_t)stream, (const uint4*)x, rows,
+                  (uint4*)out, k8);
+}
+
+}  // extern "C"

@@ -5,8 +5,24 @@
 namespace qb {
 
 struct GemvPlan {
-    int cg, kg, nsplit, nstages, ctas;
+    int cg, kg, nstages, ctas;
 };
+
+static int smem_of(int cg, int kg, int nt, int nstages) {
+    int nw = cg * kg, tk = kg * 128, tn = cg * 64;
+    return 128 + nstages * (nw * 4096 + 8 * nt * (tk + 8) * 2 + kg * tn * 2) + (kg - 1) * cg * nt * 2048;
+}
+
+// Blocks of the persistent grid and the most of them that can share one column block (the scratch stride).
+static void grid_of(const qb_ctx* ctx, const GemvPlan& p, int n, int k, int* grid, int* maxc) {
+    long long total = (long long)(n / (p.cg * 64)) * (k / (p.kg * 128));
+    long long g = (long long)ctx->sms * p.ctas;
+    if (g > total) g = total;
+    int kst = k / (p.kg * 128);
+    long long per = total / g;  // the shortest range
+    *grid = (int)g;
+    *maxc = (int)((kst + per - 1) / per) + 1;
+}
 
 template <int CG, int KG, int NT, int EPI>
 static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& p) {
@@ -18,9 +34,10 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
         QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         opted = smem;
     }
-    int nunits = (a.N / C::TN) * a.nsplit;
-    int grid = ctx->sms * p.ctas;
-    if (grid > nunits) grid = nunits;
+    int grid, maxc;
+    grid_of(ctx, p, a.N, a.K, &grid, &maxc);
+    a.maxc = maxc;
+    if ((size_t)(a.N / 64) * maxc * NT * 4 * 32 * 16 > ctx->scratch_bytes) return QB_ERR_ARG;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(grid);
     lc.blockDim = dim3(C::THREADS);
@@ -41,34 +58,25 @@ static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const G
     if (p.cg == 4 && p.kg == 2) return launch_cfg<4, 2, NT, EPI>(ctx, st, a, p);
     if (p.cg == 8 && p.kg == 1) return launch_cfg<8, 1, NT, EPI>(ctx, st, a, p);
     if (p.cg == 1 && p.kg == 8) return launch_cfg<1, 8, NT, EPI>(ctx, st, a, p);
+    if (p.cg == 4 && p.kg == 1) return launch_cfg<4, 1, NT, EPI>(ctx, st, a, p);
     return QB_ERR_ARG;
 }
 
-static int smem_of(int cg, int kg, int nt, int nstages) {
-    int nw = cg * kg, tk = kg * 128, tn = cg * 64;
-    return 128 + nstages * (nw * 4096 + 8 * nt * (tk + 8) * 2 + kg * tn * 2) + (kg - 1) * cg * nt * 2048;
-}
-
-// The built-in choice. Wide matrices (n >= 8192) take 256 x 256 tiles, narrow ones 128 x 512 so that enough column
-// blocks exist; split K until the units fill about two blocks per SM; the ring as deep as two blocks per SM allow.
-static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt) {
+// The built-in choice: wide matrices take 256 x 256 tiles (fewer, larger copies; a block's range crosses few column
+// blocks), narrow ones 128 x 512 so that a column block is shared by few blocks; the ring as deep as the blocks per
+// SM allow.
+static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt, int cg, int kg, int ctas) {
     GemvPlan p;
-    if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
+    if (cg) { p.cg = cg; p.kg = kg; }
+    else if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
     else if (k % 512 == 0 && n % 128 == 0) { p.cg = 2; p.kg = 4; }
     else if (k % 256 == 0) { p.cg = 4; p.kg = 2; }
-    else { p.cg = 8; p.kg = 1; if (n % 512) { p.cg = 4; p.kg = 2; } }
-    p.ctas = 2;
-    int slots = ctx->sms * p.ctas;
-    int ncb = n / (p.cg * 64), kst = k / (p.kg * 128);
-    p.nsplit = 1;
-    for (int s = 1; s <= kst; s++) {
-        if (kst % s) continue;
-        p.nsplit = s;
-        if (ncb * s >= slots) break;
-    }
+    else { p.cg = 4; p.kg = 1; }
+    p.ctas = ctas ? ctas : 2;
     const int budget = (228 * 1024) / p.ctas - 1024;
     p.nstages = 2;
     while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, nt, p.nstages + 1) <= budget) p.nstages++;
+    (void)ctx;
     return p;
 }
 
@@ -76,38 +84,23 @@ static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt) {
 
 using namespace qb;
 
-extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nsplit, int nstages, int ctas) {
-    ctx->tune_cg = cg; ctx->tune_kg = kg; ctx->tune_nsplit = nsplit; ctx->tune_nstages = nstages; ctx->tune_ctas = ctas;
+extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas) {
+    ctx->tune_cg = cg; ctx->tune_kg = kg; ctx->tune_nstages = nstages; ctx->tune_ctas = ctas;
     return QB_OK;
 }
 
 static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m,
                      int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid) {
     int nt = m <= 8 ? 1 : 2;
-    GemvPlan p = pick(ctx, n, k, nt);
-    if (ctx->tune_cg) { p.cg = ctx->tune_cg; p.kg = ctx->tune_kg; }
-    if (ctx->tune_ctas) p.ctas = ctx->tune_ctas;
-    if (ctx->tune_cg || ctx->tune_ctas) {  // re-derive what depends on the tile
-        GemvPlan q = p;
-        int slots = ctx->sms * q.ctas, ncb = n / (q.cg * 64), kst = k / (q.kg * 128);
-        q.nsplit = 1;
-        for (int s = 1; s <= kst; s++) { if (kst % s) continue; q.nsplit = s; if (ncb * s >= slots) break; }
-        int budget = (228 * 1024) / q.ctas - 1024;
-        q.nstages = 2;
-        while (q.nstages < GEMV_MAX_STAGES && smem_of(q.cg, q.kg, nt, q.nstages + 1) <= budget) q.nstages++;
-        p = q;
-    }
-    if (ctx->tune_nsplit) p.nsplit = ctx->tune_nsplit;
+    GemvPlan p = pick(ctx, n, k, nt, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas);
     if (ctx->tune_nstages) p.nstages = ctx->tune_nstages;
     int tn = p.cg * 64, tk = p.kg * 128;
-    if (n % tn || k % tk || (k / tk) % p.nsplit || p.nstages < 2 || p.nstages > GEMV_MAX_STAGES) return QB_ERR_ARG;
-    if (smem_of(p.cg, p.kg, nt, p.nstages) > 227 * 1024) return QB_ERR_ARG;
-    if ((size_t)(n / 64) * p.nsplit * nt * 4 * 32 * 16 > ctx->scratch_bytes || (size_t)(n / 64) > ctx->ncounters)
-        return QB_ERR_ARG;
+    if (n % tn || k % tk || p.nstages < 2 || p.nstages > GEMV_MAX_STAGES) return QB_ERR_ARG;
+    if (smem_of(p.cg, p.kg, nt, p.nstages) > 227 * 1024 || (size_t)(n / 64) > ctx->ncounters) return QB_ERR_ARG;
     GemvArgs a;
     a.X = (const __half*)X; a.xrows = xrows; a.B = (const uint32_t*)B; a.S = (const __half*)S; a.Y = Y;
     a.m = m; a.N = n; a.K = k; a.row0 = row0;
-    a.kper = k / p.nsplit; a.nsplit = p.nsplit; a.nstages = p.nstages;
+    a.nstages = p.nstages; a.maxc = 1;
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
 #define QB_GO(NT)                                                              \
     switch (epi) {                                                             \

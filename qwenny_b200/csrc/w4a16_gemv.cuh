@@ -13,12 +13,13 @@
 //    128-bit shared load through four lop3 and four hsub2 straight into the tensor core, no shuffles, no
 //    re-layout. The group scale is applied in f32 to the group's partial sum (exact, and 8x fewer multiplies
 //    than scaling every weight);
-//  * work is split into units (TN outputs x kper columns), dealt round-robin to a persistent grid, so the copy
-//    pipeline never drains between units. The KG warps of a column group add up in shared memory in a fixed order;
-//    with split K the units of a column group leave f32 partials in an L2-resident scratch and the LAST unit to
-//    arrive (an atomic ticket, no waiting) adds them in split order and runs the epilogue. Every sum has a fixed
-//    order that depends on the shape alone, never on the number of rows or on timing: a row's result is bit-identical
-//    alone or next to drafts.
+//  * the stages of the whole matrix, numbered column block by column block, are cut into one equal contiguous
+//    range per block of a persistent grid (stream-K), so every SM streams the same number of bytes whatever the
+//    shape and the copy pipeline never drains between column blocks. The KG warps of a column group add up in
+//    shared memory in a fixed order; a column block that several blocks share gets their f32 partials in an
+//    L2-resident scratch, and the LAST block to arrive (an atomic ticket, no waiting) adds them in k order and runs
+//    the epilogue. Every sum has a fixed order that depends on the shape and the grid alone, never on the number of
+//    rows or on timing: a row's result is bit-identical alone or next to drafts.
 // Epilogues as the reference's: plain f32 [m][n]; SwiGLU of interleaved gate/up blocks -> f16 [m][n/2]
 // (kernels/marlin.cuh:472-498); plain + argmax keys over the first n_valid outputs (:499-517).
 #pragma once
@@ -35,9 +36,9 @@ struct GemvArgs {
     const __half* S;      // scales [K/128][N], permuted per 64 outputs
     void* Y;              // plain/argmax: f32 [.][N]; silu: f16 [.][N/2]; rows row0 .. row0 + m - 1
     int m, N, K, row0;
-    int kper, nsplit;     // K = kper * nsplit, kper a multiple of TK
     int nstages;          // ring depth
-    float4* scratch;      // split-K partials: [N/64][nsplit][4][32] float4 (x NT)
+    int maxc;             // most blocks that share a column block (scratch stride)
+    float4* scratch;      // partials of shared column blocks: [N/64][maxc][NT][4][32] float4
     int* counters;        // [N/64] tickets, zero between launches
     unsigned long long* keys;
     int n_valid;
@@ -65,11 +66,11 @@ struct GemvCfg {
 // 0x6400 | n is the half 1024 + n (nibbles 0, 4), 0x5400 | (n << 4) the half 64 + n (nibbles 1, 5).
 __device__ __forceinline__ void dequant_word(uint32_t q, uint32_t* a) {
     uint32_t lo0, hi0, lo1, hi1;
-    asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo0) : "r"(q));
-    asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi0) : "r"(q));
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo0) : "r"(q));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi0) : "r"(q));
     uint32_t q8 = q >> 8;
-    asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo1) : "r"(q8));
-    asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi1) : "r"(q8));
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;\n" : "=r"(lo1) : "r"(q8));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xea;\n" : "=r"(hi1) : "r"(q8));
     const uint32_t SUB_LO = 0x64086408u, SUB_HI = 0x54805480u;  // 1032, 72
     __half2 r0 = __hsub2(*(__half2*)&lo0, *(const __half2*)&SUB_LO);  // outputs g,     columns 2t, 2t+1
     __half2 r1 = __hsub2(*(__half2*)&lo1, *(const __half2*)&SUB_LO);  // outputs g + 8, columns 2t, 2t+1
@@ -89,7 +90,12 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = a.nstages;
-    const int ncb = a.N / C::TN, nunits = ncb * a.nsplit, nst = a.kper / C::TK;
+    // stream-K: stage x of the matrix is (column block x / kst, k stage x % kst); block i owns [b(i), b(i+1))
+    const int kst = a.K / C::TK;
+    const long long total = (long long)(a.N / C::TN) * kst, G = gridDim.x;
+    const int beg = (int)((long long)blockIdx.x * total / G), end = (int)((long long)(blockIdx.x + 1) * total / G);
+    // the block that owns stage x: the largest i with b(i) <= x
+    auto owner = [&](long long x) { return (int)(((x + 1) * G + total - 1) / total - 1); };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; i++) {
@@ -98,21 +104,23 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         }
         mbar_fence_init();
     }
+    // the token rows the copies never write (m .. 8 NT - 1) read as zeros
+    for (int i = threadIdx.x; i < nstages * (C::X_BYTES / 16); i += C::THREADS) {
+        int sgi = i / (C::X_BYTES / 16), o = i % (C::X_BYTES / 16);
+        if (o * 16 >= a.m * C::XROW * 2)
+            *(uint4*)(stages + (size_t)sgi * C::STAGE_BYTES + C::W_BYTES + o * 16) = make_uint4(0, 0, 0, 0);
+    }
     __syncthreads();
     pdl_launch_dependents();
 
     if (warp == C::NW) {
         // ------------------------------------------------------------ producer
         const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
-        int my_units = blockIdx.x < nunits ? (nunits - 1 - blockIdx.x) / gridDim.x + 1 : 0;
-        const uint32_t total = (uint32_t)my_units * nst;
+        const uint32_t mine = (uint32_t)(end - beg);
         const uint32_t tx = C::W_BYTES + C::S_BYTES + a.m * C::TK * 2;
         // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
-        auto issue = [&](uint32_t it, int what) {
-            int ui = it / nst, st = it - ui * nst, u = blockIdx.x + ui * gridDim.x;
-            int cb = u / a.nsplit, sp = u - cb * a.nsplit;
-            int n0 = cb * C::TN, k0 = sp * a.kper + st * C::TK;
-            int slot = it % nstages;
+        auto issue = [&](int cb, int st, int slot, int what) {
+            int n0 = cb * C::TN, k0 = st * C::TK;
             uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
             if (what != 1) {
                 if (lane == 0) mbar_expect_tx(&full[slot], tx);
@@ -134,18 +142,23 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         };
         // the weights of the first ring-full of stages do not depend on the previous kernel: start them, then wait
         // for it (its activations are this kernel's X)
-        uint32_t pre = total < (uint32_t)nstages ? total : (uint32_t)nstages;
-        for (uint32_t it = 0; it < pre; it++) issue(it, 0);
+        uint32_t pre = mine < (uint32_t)nstages ? mine : (uint32_t)nstages;
+        const int cb0 = beg / kst, st0 = beg - cb0 * kst;
+        int cb = cb0, st = st0;
+        auto next = [&]() { if (++st == kst) { st = 0; cb++; } };
+        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, 0);
         pdl_wait();
-        for (uint32_t it = 0; it < pre; it++) issue(it, 1);
+        cb = cb0; st = st0;
+        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, 1);
         bool ok = true;
-        for (uint32_t it = pre; it < total && ok; it++) {
-            int slot = it % nstages;
-            uint32_t par = ((it / nstages) & 1) ^ 1;
+        int slot = 0;
+        uint32_t par = 0;  // parity of the consumers' release this slot is waiting for
+        for (uint32_t it = pre; it < mine && ok; it++, next()) {
             if (lane == 0) ok = mbar_wait(&empty[slot], par);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            issue(it, 2);
+            issue(cb, st, slot, 2);
+            if (++slot == nstages) { slot = 0; par ^= 1; }
         }
         if (!ok && lane == 0) atomicExch(a.err, 1);
         return;
@@ -162,42 +175,35 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
 
-    uint32_t it = 0;
     // A wait that runs out marks the warp dead: it records the error, then walks the rest of its schedule with
     // short waits only (so that copies already in flight still land in a live block) and keeps meeting the block's
     // barriers, and the kernel ends instead of hanging.
     bool dead = false;
-    for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
-        const int cb = u / a.nsplit, sp = u - cb * a.nsplit;
-        for (int st = 0; st < nst; st++, it++) {
-            int slot = it % nstages;
+    int cb = beg / kst, st = beg - cb * kst, slot = 0;
+    uint32_t par = 0;
+    for (int x = beg; x < end; x++) {
+        {
             if (!dead) {
-                dead = !mbar_wait(&full[slot], (it / nstages) & 1);
+                dead = !mbar_wait(&full[slot], par);
                 if (dead && lane == 0) atomicExch(a.err, 2);
             } else {
-                for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], (it / nstages) & 1); i++) {}
+                for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], par); i++) {}
             }
             const uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
             const uint4* wp = (const uint4*)(base + (size_t)(kg * 8 * CG + cg) * 512) + lane;
-            const __half* xs = (const __half*)(base + C::W_BYTES) + kg * 128 + 2 * t;
+            // ldmatrix row address of this lane: token row lane % 8 (+ 8 j), columns 8 (lane / 8) of each pair of k16 steps
+            const uint32_t xs = smem_u32(base + C::W_BYTES) + ((lane & 7) * C::XROW + kg * 128 + 8 * (lane >> 3)) * 2;
             uint4 sc4 = *(const uint4*)(base + C::W_BYTES + C::X_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
             float tmp[NT][4][4];
-#pragma unroll
-            for (int j = 0; j < NT; j++)
-#pragma unroll
-                for (int b = 0; b < 4; b++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) tmp[j][b][i] = 0.f;
+            uint32_t bx[NT][2][2];  // [token tile][k16 step of the pair][b0, b1]
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
                 uint4 w = wp[ks * CG * 32];
-                uint32_t bx[NT][2];
+                if ((ks & 1) == 0) {
 #pragma unroll
-                for (int j = 0; j < NT; j++) {
-                    const __half* xr = xs + (8 * j + g) * C::XROW + ks * 16;
-                    bool live = 8 * j + g < a.m;
-                    bx[j][0] = live ? *(const uint32_t*)xr : 0u;
-                    bx[j][1] = live ? *(const uint32_t*)(xr + 8) : 0u;
+                    for (int j = 0; j < NT; j++)
+                        ldsm_x4(bx[j][0][0], bx[j][0][1], bx[j][1][0], bx[j][1][1],
+                                xs + (8 * j * C::XROW + ks * 16) * 2);
                 }
                 uint32_t wq[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -205,7 +211,10 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     uint32_t af[4];
                     dequant_word(wq[b], af);
 #pragma unroll
-                    for (int j = 0; j < NT; j++) mma16816(tmp[j][b], af, bx[j][0], bx[j][1]);
+                    for (int j = 0; j < NT; j++) {
+                        if (ks == 0) mma16816_zero(tmp[j][b], af, bx[j][0][0], bx[j][0][1]);
+                        else mma16816(tmp[j][b], af, bx[j][ks & 1][0], bx[j][ks & 1][1]);
+                    }
                 }
             }
             // the group's scales: half 2 b + h of the lane's 16 bytes is output 16 b + g + 8 h
@@ -221,7 +230,12 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[slot]);
+            if (++slot == nstages) { slot = 0; par ^= 1; }
         }
+        // the piece (this block's stages of column block cb) goes on
+        const int pcb = cb;
+        if (++st == kst) { st = 0; cb++; }
+        if (x + 1 < end && st != 0) continue;
 
         // ---- the KG warps of a column group: kg > 0 hand their sums to kg = 0, which adds them in kg order
         if (KG > 1) {
@@ -251,10 +265,12 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         }
 
         if (kg == 0) {
-            const int colgrp = cb * CG + cg;  // 64 outputs
+            const int colgrp = pcb * CG + cg;  // 64 outputs
             bool finish = true;
-            if (a.nsplit > 1) {
-                float4* mine = a.scratch + ((size_t)colgrp * a.nsplit + sp) * (NT * 4 * 32);
+            // the blocks that share column block cb, in k order: first .. last
+            const int first = owner((long long)pcb * kst), nshare = owner((long long)pcb * kst + kst - 1) - first + 1;
+            if (nshare > 1) {
+                float4* mine = a.scratch + ((size_t)colgrp * a.maxc + (blockIdx.x - first)) * (NT * 4 * 32);
 #pragma unroll
                 for (int j = 0; j < NT; j++)
 #pragma unroll
@@ -266,17 +282,17 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 int ticket = 0;
                 if (lane == 0) ticket = atomicAdd(a.counters + colgrp, 1);
                 ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                finish = ticket == a.nsplit - 1;
+                finish = ticket == nshare - 1;
                 if (finish) {
                     __threadfence();
-                    const float4* p0 = a.scratch + (size_t)colgrp * a.nsplit * (NT * 4 * 32);
+                    const float4* p0 = a.scratch + (size_t)colgrp * a.maxc * (NT * 4 * 32);
 #pragma unroll
                     for (int j = 0; j < NT; j++)
 #pragma unroll
                         for (int b = 0; b < 4; b++)
 #pragma unroll
                             for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
-                    for (int s = 0; s < a.nsplit; s++) {
+                    for (int s = 0; s < nshare; s++) {
 #pragma unroll
                         for (int j = 0; j < NT; j++)
 #pragma unroll

@@ -52,8 +52,8 @@ class Context:
     def set_pdl(self, on: bool):
         check(lib().qb_set_pdl(self.h, int(on)), "qb_set_pdl")
 
-    def tune(self, cg=0, kg=0, nsplit=0, nstages=0, ctas=0):
-        check(lib().qb_marlin_tune(self.h, cg, kg, nsplit, nstages, ctas), "qb_marlin_tune")
+    def tune(self, cg=0, kg=0, nstages=0, ctas=0):
+        check(lib().qb_marlin_tune(self.h, cg, kg, nstages, ctas), "qb_marlin_tune")
 
     # ---- products
     def marlin_gemm(self, x, words, scales, epi="plain", y=None, row0=0, m=None, xrows=None, keys=None,

@@ -1,5 +1,6 @@
-"""Parity of the W4A16 skinny product (qb_marlin_gemm) on the GPU: against the CPU oracle, against the reference's
-own Marlin kernels on the same device buffers, and its invariants (bit-exact unpack, row-count invariance)."""
+"""Parity of the W4A16 skinny product (qb_marlin_gemm) on the GPU: against the CPU oracle (exact dequantisation,
+f64 product) and its invariants (bit-exact unpack, row-count invariance). The reference's own Marlin kernels are not
+run next to it: they end with an illegal-instruction fault on B200 (see oracle/ref_cuda.py RefModule.marlin)."""
 import numpy as np
 import pytest
 import torch
@@ -42,11 +43,11 @@ def test_plain_vs_oracle(ctx, m, rows, cols):
     assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("cfg", [(2, 4, 1), (2, 4, 2), (4, 2, 1), (4, 2, 4), (8, 1, 2), (8, 1, 8), (1, 8, 1)])
-def test_every_tile_shape_and_split(ctx, cfg):
-    cg, kg, nsplit = cfg
+@pytest.mark.parametrize("cfg", [(2, 4, 1), (2, 4, 2), (4, 2, 1), (4, 2, 3), (8, 1, 2), (8, 1, 1), (1, 8, 1), (4, 1, 2)])
+def test_every_tile_shape(ctx, cfg):
+    cg, kg, ctas = cfg
     x, wdq, xd, wd, sd = make(1024, 2048, False, 3, 5)
-    ctx.tune(cg=cg, kg=kg, nsplit=nsplit)
+    ctx.tune(cg=cg, kg=kg, ctas=ctas)
     try:
         y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
         y2 = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()  # tickets left at zero: a second product works
@@ -88,19 +89,16 @@ def test_row_count_invariance(ctx):
     assert np.array_equal(y.cpu().numpy()[4:9], y16[4:9]) and float(y[:4].abs().max()) == 0
 
 
-def test_silu_vs_oracle_and_reference(ctx, ref):
-    rows, cols, m = 1024, 1024, 5
+@pytest.mark.parametrize("rows,cols,m", [(1024, 1024, 5), (34816, 5120, 5), (512, 256, 16)])
+def test_silu_vs_oracle(ctx, rows, cols, m):
     x, wdq, xd, wd, sd = make(rows, cols, True, 11, m)
     y = ctx.marlin_gemm(xd, wd, sd, epi="silu")
     want = R.marlin_gemm(x, wdq, "silu")
     assert y.shape == (m, rows // 2)
     assert close(y.float().cpu().numpy(), want.astype(np.float32)).all()
-    yr = torch.zeros_like(y)
-    ref.marlin(m, wd, sd, xd, yr, "silu")
-    assert close(y.float().cpu().numpy(), yr.float().cpu().numpy()).all()
 
 
-def test_argmax_vs_oracle_and_reference(ctx, ref):
+def test_argmax_vs_oracle(ctx):
     rows, cols, valid = 2048, 512, 1936
     g = synth.gen(12)
     xall = synth.activations(9, cols, g)
@@ -118,30 +116,30 @@ def test_argmax_vs_oracle_and_reference(ctx, ref):
     got = keys.cpu().numpy().view(np.uint64)[:3]
     assert np.array_equal(R.key_token(got), R.key_token(wkeys))
     assert all(int(t) < valid for t in R.key_token(got))
-    # the reference: marlin_gather + marlin argmax
-    xg = torch.zeros(3, cols, dtype=torch.float16, device="cuda")
-    ref.marlin_gather(xd, out_rows, xg, cols)
-    rkeys = torch.zeros(8, dtype=torch.int64, device="cuda")
-    yr = torch.zeros(3, rows, device="cuda")
-    ref.marlin(3, wd, sd, xg, yr, "argmax", keys=rkeys, valid=valid)
-    assert close(y, yr.cpu().numpy()).all()
-    assert np.array_equal(R.key_token(got), R.key_token(rkeys.cpu().numpy().view(np.uint64)[:3]))
+    # the key's value half is the ordered logit of that token
+    for r in range(3):
+        tok = int(R.key_token(got)[r])
+        assert int(got[r] >> np.uint64(32)) == int(R.ordered_u32(y[r:r + 1, tok:tok + 1])[0, 0])
 
 
 @pytest.mark.parametrize("m", [1, 5, 16])
-def test_config0_vs_reference_kernel(ctx, ref, m):
-    """BASELINE config 0: N=17408 x K=5120, g128, against the reference's marlin_m1_n8_plain on the same buffers."""
+def test_config0_vs_oracle(ctx, m):
+    """BASELINE config 0: N=17408 x K=5120, g128, seed 0."""
     x, wdq, xd, wd, sd = make(17408, 5120, False, 0, m)
-    y = ctx.marlin_gemm(xd, wd, sd)
-    yr = torch.zeros_like(y)
-    ref.marlin(m, wd, sd, xd, yr, "plain")
-    torch.cuda.synchronize()
-    a, b = y.cpu().numpy(), yr.cpu().numpy()
-    assert close(a, b).all()
+    a = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
     want = R.marlin_gemm(x, wdq)
-    assert close(a, want).all() and close(b, want).all()
-    # both are f32 sums of exact products in different orders: far inside the tolerance
-    assert np.abs(a - b).max() < 1e-4 * np.abs(want).max()
+    assert close(a, want).all()
+    # f32 sums of exact products against the f64 product: far inside the tolerance
+    assert np.abs(a - want).max() < 1e-4 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("n,k", [(16384, 5120), (14336, 5120), (5120, 6144), (5120, 17408)])
+def test_model_shapes_vs_oracle(ctx, n, k):
+    x, wdq, xd, wd, sd = make(n, k, False, n + k, 5)
+    a = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+    want = R.marlin_gemm(x, wdq)
+    assert close(a, want).all()
+    assert np.abs(a - want).max() < 1e-4 * np.abs(want).max()
 
 
 def test_many_rows_fall_back_to_slabs(ctx):
