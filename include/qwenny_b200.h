@@ -54,6 +54,67 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
  * next qb_marlin_gemm calls; zeros restore the built-in choice. */
 int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
+/* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
+ * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it
+ * (src/cuda/core.rs:532-560): W in mma A-fragment order (qb_pack_f16), X f16 [.][K] (rows xrows[t] if given),
+ * Y f32 [K/kper splits][n][ldy] partial products which the consumer sums; n <= 32. */
+int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
+                      int n, int kper, float* Y, int ldy);
+
+/* ---- per-token kernels. n = tokens of the step (grid size in the reference's launches).
+ * qb_embed        embed, kernels/dense.cuh:6-11 (src/cuda/qwen/mod.rs:612-621): out f32 [n][5120] = E bf16 rows;
+ *                 clears keys[0..nkeys)
+ * qb_rmsnorm      rmsnorm, kernels/dense.cuh:14-26: y f16 = w * x / rms(x)
+ * qb_add_rmsnorm  add_rmsnorm, kernels/qwen.cu:57-80: h += sum of x [splits][n][5120]; y f16 = w_next * h / rms(h)
+ * qb_to_xin       to_xin, kernels/qwen.cu:136-138
+ * qb_sum_parts    sum_parts, kernels/qwen.cu:141-143
+ * qb_mark_seen    mark_seen, kernels/sampling.cuh:14-26 (src/cuda/core.rs:949-960); vocab = bits per slot
+ * qb_marlin_gather marlin_gather, kernels/marlin.cuh:605-608 (qb_marlin_gemm's xrows makes it unnecessary) */
+int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
+             int nkeys, int n);
+int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n);
+int qb_add_rmsnorm(qb_ctx* ctx, void* stream, float* h, const float* x, int splits, int n, const float* w_next,
+                   void* y, float eps);
+int qb_to_xin(qb_ctx* ctx, void* stream, const float* x, void* y, int len);
+int qb_sum_parts(qb_ctx* ctx, void* stream, const float* x, int splits, int n, int ld, float* y);
+int qb_mark_seen(qb_ctx* ctx, void* stream, unsigned* seen, const int* mark, const int* mark_at, const int* seg_slot,
+                 const int* seg_pos0, int segs, int vocab);
+int qb_marlin_gather(qb_ctx* ctx, void* stream, const void* x, const int* rows, void* out, int k8, int n);
+
+/* ---- gated attention over the int8 KV cache.
+ * qb_attn_prep    attn_prep + kv_store, kernels/qwen.cu:156-202, kernels/attn.cuh:50-64 (launched by Attn::run,
+ *                 src/cuda/qwen/attn.rs:285-302). Cache layout and quantisation are the reference's: K rows of 256
+ *                 bytes in kslot order, V in 16-position blocks in vslot order, byte = code + 128, f32 scale per
+ *                 (slot, kv head, position); cap a multiple of 64.
+ * qb_attn_decode  attn_mq{1,2,3} + attn_combine (+ to_xin when mix_f16 != NULL), kernels/attn.cuh:77-325 as
+ *                 Attn::run launches them (src/cuda/qwen/attn.rs:303-336,370-375). `out` holds the gate on entry and
+ *                 the gated attention output on return. part_ml / part_acc: scratch for ndec * 24 * 64 (m, l) pairs
+ *                 and accumulators of 256 floats. The split size is a function of the key count alone
+ *                 (qb_attn_dec_splits), as the reference's dchunk is (kernels/attn.cuh:41-46). */
+int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n, const float* q_norm,
+                 const float* k_norm, const float* inv_freq, float qscale, float* q, float* out, void* kc, void* vc,
+                 float* ks, float* vs, const int* tok_slot, const int* tok_pos, int cap);
+int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, const void* vc, const float* ks,
+                   const float* vs, const int* dseg, const int* dtok, const int* dkeys, const int* tok_slot,
+                   const int* tok_pos, int cap, int ndseg, int ndec, int dmax, int max_keys, float* part_ml,
+                   float* part_acc, float* out, void* mix_f16);
+int qb_attn_dec_splits(int keys);
+
+/* ---- Gated DeltaNet. Slot memory (sst floats per slot), metadata and the rollback plan are the reference's
+ * (kernels/qwen_deltanet.cuh:12-82; host side src/cuda/qwen/deltanet.rs:83-104,181-226).
+ * qb_delta_conv   delta_conv, kernels/qwen_deltanet.cuh:84-131
+ * qb_delta_rule   delta_rule, kernels/qwen_deltanet.cuh:172-288
+ * qb_delta_norm   delta_norm, kernels/qwen_deltanet.cuh:295-315
+ * launched in this order by DeltaNet::run (src/cuda/qwen/deltanet.rs:109-160). */
+int qb_delta_conv(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* ba, int ba_splits,
+                  const float* cw, const float* a_log, const float* dt_bias, const float* mem, long long sst,
+                  float* cv, const int* tok_slot, const int* tok_pos);
+int qb_delta_rule(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* cv, float* mem,
+                  long long sst, const int* meta, float* out, const int* seg_start, const int* seg_len,
+                  const int* seg_slot, const int* seg_pos0, int segs);
+int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* nw, const float* out,
+                  void* y, int* meta, const int* seg_len, const int* seg_slot, const int* seg_pos0, int segs);
+
 /* ---- host-side weight packers (load time; host pointers). They produce the layouts the reference's loader
  * produces, which every kernel here reads unchanged.
  * qb_row_order    row_order, src/cuda/core.rs:106-114

@@ -23,6 +23,20 @@ SIGNATURES = {
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_tune": [P, I, I, I, I],
+    "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
+    "qb_embed": [P, P, P, P, P, P, I, I],
+    "qb_rmsnorm": [P, P, P, P, P, F, I],
+    "qb_add_rmsnorm": [P, P, P, P, I, I, P, P, F],
+    "qb_to_xin": [P, P, P, P, I],
+    "qb_sum_parts": [P, P, P, I, I, I, P],
+    "qb_mark_seen": [P, P, P, P, P, P, P, I, I],
+    "qb_marlin_gather": [P, P, P, P, P, I, I],
+    "qb_attn_prep": [P, P, P, I, I, P, P, P, F, P, P, P, P, P, P, P, P, I],
+    "qb_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P, P, P],
+    "qb_attn_dec_splits": [I],
+    "qb_delta_conv": [P, P, P, I, I, P, I, P, P, P, P, LL, P, P, P],
+    "qb_delta_rule": [P, P, P, I, I, P, P, LL, P, P, P, P, P, P, I],
+    "qb_delta_norm": [P, P, P, I, I, P, P, P, P, P, P, P, I],
     "qb_row_order": [I, I, P],
     "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],

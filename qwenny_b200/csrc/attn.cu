@@ -1,0 +1,472 @@
+// Gated GQA attention of a decode / verify step over the int8 KV cache.
+//  attn_prep    per token: sum of the in-projection parts, q/k RMSNorm(1+w), partial RoPE, q scaled to base-2 scores,
+//               sigmoid gate -> out, k and v quantised into the cache in the reference's byte order
+//               (replaces attn_prep + kv_store, kernels/qwen.cu:156-202, kernels/attn.cuh:50-64)
+//  attn_decode  split-K flash-decode: block (segment, kv head, key split) streams its run of keys and values with
+//               bulk async copies into a shared-memory ring (keys are [pos][256] and values [pos/16][256][16] bytes
+//               per head, both contiguous per run) while RT x 2 warps compute S = Q K^T and O += P V on tensor cores
+//               with a warp-level base-2 online softmax, straight from the int8 bytes (prmt to 1152 + q halves, the
+//               offset folded out through the row sums as the reference does, kernels/attn.cuh:38-40,198-234)
+//               (replaces attn_mq_tc<RT>, kernels/attn.cuh:77-261)
+//  attn_combine merges the splits of a (token, head) in split order, multiplies into the gated output and can write
+//               the f16 copy the out-projection reads (replaces attn_combine + to_xin, kernels/attn.cuh:271-325,
+//               kernels/qwen.cu:136-138)
+// The size of a key split is a function of the key count alone (dec_chunk), so a token's sums are the same whether
+// it runs alone or with drafts.
+#include "common.cuh"
+#include "launch.h"
+
+namespace qb {
+
+constexpr float KV_OFF = 1152.f;
+constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
+constexpr int SK = 32;         // keys per ring stage
+constexpr int NSTG = 4;        // ring depth
+constexpr int KWARPS = 2;      // warps that share a row tile, one 16-key block of a stage each
+constexpr int STG_BYTES = SK * HD * 2 + SK * 4 * 2;  // keys, values, key scales, value scales
+constexpr int DSPLITS = 64;    // most key splits of a decode token
+
+__host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
+__host__ __device__ inline size_t scale_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap; }
+
+// Byte of dim d in a key row / of (position, dim) in a head's values: the reference's fragment orders
+// (kslot, vslot: kernels/attn.cuh:23-37)
+__device__ __forceinline__ int kslot(int d) {
+    int b = d >> 6, w = d & 15, t4 = (w & 7) >> 1, e = (w & 1) | ((w >> 3) << 1);
+    return b * 64 + t4 * 16 + ((d & 63) >> 4) * 4 + e;
+}
+__device__ __forceinline__ size_t vslot(int pos, int d) {
+    int j = pos & 15, t4 = (j & 7) >> 1, e = (j & 1) | ((j >> 3) << 1);
+    return ((size_t)(pos >> 4) * HD + d) * 16 + t4 * 4 + e;
+}
+
+// Keys per split of a token with `keys` keys: a multiple of 64, at most DSPLITS splits; changes only where keys
+// crosses a multiple of 64 * DSPLITS = 4096 (the host cuts short segments at multiples of 2048 keys, so the tokens
+// of a segment always agree).
+__host__ __device__ inline int dec_chunk(int keys) { return max(64, ((keys + DSPLITS - 1) / DSPLITS + 63) / 64 * 64); }
+__host__ __device__ inline int dec_splits(int keys) { int c = dec_chunk(keys); return (keys + c - 1) / c; }
+
+// ------------------------------------------------------------------------------------------------ attn_prep
+constexpr int PREP_WARPS = NH + 2 * NKV;
+
+__global__ void __launch_bounds__(32 * PREP_WARPS)
+attn_prep_kernel(const float* part, int splits, int n, const float* q_norm, const float* k_norm, const float* inv_freq,
+                 float qscale, float* q, float* out, uint8_t* kc, uint8_t* vc, float* ks, float* vs,
+                 const int* tok_slot, const int* tok_pos, int cap) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp w: query head w (its q and gate), then the key heads, then the value heads
+    int col;
+    const float* nw;
+    if (w < NH) { col = w * 2 * HD; nw = q_norm; }
+    else if (w < NH + NKV) { col = QG_ROWS + (w - NH) * HD; nw = k_norm; }
+    else { col = QG_ROWS + NKV * HD + (w - NH - NKV) * HD; nw = nullptr; }
+    float nv[HD / 32];
+    if (nw) {
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) nv[j] = nw[lane + 32 * j];
+    }
+    float fr = inv_freq[lane];
+    pdl_wait();
+    const int pos = tok_pos[t];
+    // the lane owns dims lane + 32 j: the RoPE pair (d, d + 32), d < 32, is j = 0 and 1 of one lane
+    float v[HD / 32], gl[HD / 32];
+#pragma unroll
+    for (int j = 0; j < HD / 32; j++) v[j] = gl[j] = 0.f;
+    for (int sp = 0; sp < splits; sp++) {
+        const float* p = part + ((size_t)sp * n + t) * ATTN_IN + col + lane;
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) v[j] += p[32 * j];
+        if (w < NH) {
+#pragma unroll
+            for (int j = 0; j < HD / 32; j++) gl[j] += p[HD + 32 * j];
+        }
+    }
+    if (nw) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) ss += v[j] * v[j];
+        float r = rsqrtf(warp_sum(ss) / HD + EPS);
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) v[j] = nv[j] * (v[j] * r);
+        float sn, cs;
+        sincosf((float)pos * fr, &sn, &cs);
+        float a = v[0], b = v[1];
+        v[0] = a * cs - b * sn;
+        v[1] = b * cs + a * sn;
+    }
+    if (w < NH) {
+        float* qo = q + ((size_t)t * NH + w) * HD;
+        float* go = out + (size_t)t * MIX + w * HD;
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) {
+            qo[lane + 32 * j] = v[j] * qscale;
+            go[lane + 32 * j] = 1.f / (1.f + expf(-gl[j]));
+        }
+    } else {
+        // int8 with one scale per (position, head): code = round(v * 127 / max) + 128, scale = max / 127
+        const bool key = w < NH + NKV;
+        const int g = (w - NH) % NKV, slot = tok_slot[t];
+        uint8_t* c = (key ? kc : vc) + cache_head(slot, g, cap);
+        float mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) mx = fmaxf(mx, fabsf(v[j]));
+        mx = warp_max(mx);
+        float inv = mx > 0.f ? 127.f / mx : 0.f;
+#pragma unroll
+        for (int j = 0; j < HD / 32; j++) {
+            int d = lane + 32 * j;
+            c[key ? (size_t)pos * HD + kslot(d) : vslot(pos, d)] = (uint8_t)(__float2int_rn(v[j] * inv) + 128);
+        }
+        if (lane == 0) (key ? ks : vs)[scale_head(slot, g, cap) + pos] = mx / 127.f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ attn_decode
+__device__ __forceinline__ uint32_t kv_half2(uint32_t w, uint32_t sel) { return __byte_perm(w, 0x64646464u, sel); }
+
+template <int RT>
+struct DecCfg {
+    static constexpr int CW = RT * KWARPS;            // compute warps
+    static constexpr int THREADS = (CW + 1) * 32;     // + the copy warp
+    static constexpr int Q_BYTES = RT * 16 * SROW * 2;
+    static constexpr int BAR_BYTES = 128;
+    static constexpr int SMEM = BAR_BYTES + Q_BYTES + NSTG * STG_BYTES;
+    static constexpr int MERGE_FLOATS = 32 * (HD / 8 * 4 + 6);  // per row tile: o, m, l, ps of 32 lanes
+    static_assert(RT * MERGE_FLOATS * 4 <= NSTG * STG_BYTES, "the merge buffers reuse the ring");
+};
+
+template <int RT>
+__global__ void __launch_bounds__(DecCfg<RT>::THREADS)
+attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs,
+                   const int* dseg, const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z,
+                   float* part_ml, float* part_acc, float* out, int* err) {
+    using C = DecCfg<RT>;
+    constexpr int NTD = HD / 8;  // n8 dim tiles of the output
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + NSTG;
+    __half* qsh = (__half*)(smem + C::BAR_BYTES);
+    uint8_t* ring = smem + C::BAR_BYTES + C::Q_BYTES;
+
+    const int seg = blockIdx.x, g = blockIdx.y, s = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSTG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], C::CW); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();  // the step's own keys and values are written by attn_prep just before
+
+    const int first = dseg[2 * seg], nt = dseg[2 * seg + 1];
+    const int tlast = dtok[first + nt - 1], keys = tok_pos[tlast] + 1;
+    const int chunk = dec_chunk(keys), ns = (keys + chunk - 1) / chunk;
+    if (s >= ns) return;
+    const int kbeg = s * chunk, ke = min(keys, kbeg + chunk), nstg = (ke - kbeg + SK - 1) / SK;
+    const int slot = tok_slot[tlast];
+
+    if (warp == C::CW) {
+        // ------------------------------------------------------------ copy warp: one lane per region of a stage
+        const uint64_t pol = policy_evict_first();
+        const uint8_t* kh = kc + cache_head(slot, g, cap);
+        const uint8_t* vh = vc + cache_head(slot, g, cap);
+        const float* ksh = ks + scale_head(slot, g, cap);
+        const float* vsh = vs + scale_head(slot, g, cap);
+        int sl = 0;
+        uint32_t par = 1;  // a fresh barrier passes a wait on the phase before its first
+        bool ok = true;
+        for (int i = 0; i < nstg && ok; i++) {
+            if (lane == 0) ok = mbar_wait(&empty[sl], par);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            uint8_t* base = ring + sl * STG_BYTES;
+            const int kb = kbeg + i * SK;
+            if (lane == 0) mbar_expect_tx(&full[sl], STG_BYTES);
+            __syncwarp();
+            if (lane == 0) bulk_g2s(base, kh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+            if (lane == 1) bulk_g2s(base + SK * HD, vh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+            if (lane == 2) bulk_g2s(base + 2 * SK * HD, ksh + kb, SK * 4, &full[sl], pol);
+            if (lane == 3) bulk_g2s(base + 2 * SK * HD + SK * 4, vsh + kb, SK * 4, &full[sl], pol);
+            if (++sl == NSTG) { sl = 0; par ^= 1; }
+        }
+        if (!ok && lane == 0) atomicExch(err, 3);
+        return;
+    }
+
+    // ---------------------------------------------------------------- compute warps
+    const int wt = warp / KWARPS, kw = warp % KWARPS, r = lane >> 2, t4 = lane & 3;
+    // Q of the segment's rows (row = token * GROUP + head) as f16
+    for (int x = threadIdx.x; x < RT * 16 * HD / 4; x += C::CW * 32) {
+        int row = x / (HD / 4), d = (x % (HD / 4)) * 4, tok = row / GROUP;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tok < nt) v = *(const float4*)(q + ((size_t)dtok[first + tok] * NH + g * GROUP + row % GROUP) * HD + d);
+        *(uint2*)&qsh[row * SROW + d] = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    }
+    named_bar_sync(1, C::CW * 32);
+    // this lane's rows wt * 16 + r and + 8: the keys they may see end at lim; KV_OFF times the sums of their Q
+    int lim[2];
+    float qoff[2];
+    {
+        float qs = 0.f;
+        const __half* qr = qsh + (wt * 16 + (lane & 15)) * SROW + (lane >> 4) * (HD / 2);
+        for (int d = 0; d < HD / 2; d += 2) {
+            float2 f = __half22float2(*(const __half2*)(qr + d));
+            qs += f.x + f.y;
+        }
+        qs += __shfl_xor_sync(0xffffffffu, qs, 16);
+        qoff[0] = KV_OFF * __shfl_sync(0xffffffffu, qs, r);
+        qoff[1] = KV_OFF * __shfl_sync(0xffffffffu, qs, r + 8);
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; h2++) {
+        int tok = (wt * 16 + r + 8 * h2) / GROUP;
+        lim[h2] = tok < nt ? min(ke, tok_pos[dtok[first + tok]] + 1) : 0;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, ps[2] = {0.f, 0.f}, o[NTD][4];
+#pragma unroll
+    for (int j = 0; j < NTD; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const uint32_t qa = smem_u32(qsh + (wt * 16 + (lane & 15)) * SROW + (lane >> 4) * 8);
+
+    int sl = 0;
+    uint32_t par = 0;
+    bool dead = false;
+    for (int i = 0; i < nstg; i++) {
+        if (!dead) {
+            dead = !mbar_wait(&full[sl], par);
+            if (dead && lane == 0) atomicExch(err, 4);
+        } else {
+            for (int k = 0; k < 1024 && !mbar_try_wait(&full[sl], par); k++) {}
+        }
+        const uint8_t* base = ring + sl * STG_BYTES;
+        const int kb = kbeg + i * SK + 16 * kw;  // this warp's 16 keys of the stage
+        if (kb < ke) {
+            const uint8_t* kp = base + (16 * kw + r) * HD + 16 * t4;
+            const uint8_t* vp = base + SK * HD + kw * 16 * HD + r * 16 + t4 * 4;
+            const float* ksc_s = (const float*)(base + 2 * SK * HD) + 16 * kw;
+            const float* vsc_s = ksc_s + SK;
+            float ksc[2][2], vsc[2][2];
+#pragma unroll
+            for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    int kk = 8 * nn + 2 * t4 + e;
+                    bool in = kb + kk < ke;
+                    ksc[nn][e] = in ? ksc_s[kk] : 0.f;
+                    vsc[nn][e] = in ? vsc_s[kk] : 0.f;
+                }
+            // S = Q K^T
+            float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int b = 0; b < HD / 64; b++) {
+                uint4 kf0 = *(const uint4*)(kp + 64 * b), kf1 = *(const uint4*)(kp + 8 * HD + 64 * b);
+                uint32_t w0[4] = {kf0.x, kf0.y, kf0.z, kf0.w}, w1[4] = {kf1.x, kf1.y, kf1.z, kf1.w};
+#pragma unroll
+                for (int st = 0; st < 4; st++) {
+                    uint32_t a[4];
+                    ldsm_x4(a[0], a[1], a[2], a[3], qa + (b * 64 + st * 16) * 2);
+                    mma16816(sacc[0], a, kv_half2(w0[st], 0x4140), kv_half2(w0[st], 0x4342));
+                    mma16816(sacc[1], a, kv_half2(w1[st], 0x4140), kv_half2(w1[st], 0x4342));
+                }
+            }
+            // scale, mask, online softmax per row; P times the value scales as the A fragments of P V
+            float pv[2][4];
+            bool grew = false;
+            float corr[2];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                float v[2][2], mx = -INFINITY;
+#pragma unroll
+                for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        int k = kb + 8 * nn + 2 * t4 + e;
+                        v[nn][e] = k < lim[h2] ? (sacc[nn][2 * h2 + e] - qoff[h2]) * ksc[nn][e] : -INFINITY;
+                        mx = fmaxf(mx, v[nn][e]);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                float mn = fmaxf(m[h2], mx);
+                corr[h2] = mn == -INFINITY ? 1.f : exp2f(m[h2] - mn);
+                m[h2] = mn;
+                float sum = 0.f;
+#pragma unroll
+                for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        float p = v[nn][e] == -INFINITY ? 0.f : exp2f(v[nn][e] - mn);
+                        sum += p;
+                        pv[nn][2 * h2 + e] = p * vsc[nn][e];
+                    }
+                l[h2] = l[h2] * corr[h2] + sum;
+                ps[h2] *= corr[h2];
+                grew |= corr[h2] != 1.f;
+            }
+            if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+                for (int j = 0; j < NTD; j++) {
+                    o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                    o[j][2] *= corr[1]; o[j][3] *= corr[1];
+                }
+            }
+            uint32_t pa[4] = {pack_half2(pv[0][0], pv[0][1]), pack_half2(pv[0][2], pv[0][3]),
+                              pack_half2(pv[1][0], pv[1][1]), pack_half2(pv[1][2], pv[1][3])};
+            // the P the products see (f16): rows r (words 0, 2) and r + 8 (1, 3)
+            float2 f0 = __half22float2(*(__half2*)&pa[0]), f2 = __half22float2(*(__half2*)&pa[2]);
+            float2 f1 = __half22float2(*(__half2*)&pa[1]), f3 = __half22float2(*(__half2*)&pa[3]);
+            ps[0] += f0.x + f0.y + f2.x + f2.y;
+            ps[1] += f1.x + f1.y + f3.x + f3.y;
+            // O += P V
+#pragma unroll
+            for (int j = 0; j < NTD; j++) {
+                uint32_t vw = *(const uint32_t*)(vp + j * 8 * 16);
+                mma16816(o[j], pa, kv_half2(vw, 0x4140), kv_half2(vw, 0x4342));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[sl]);
+        if (++sl == NSTG) { sl = 0; par ^= 1; }
+    }
+
+    // ---- the two warps of a row tile merge (the ring is free: every stage was consumed)
+    named_bar_sync(1, C::CW * 32);
+    float* mb = (float*)ring + (size_t)wt * C::MERGE_FLOATS;
+    if (kw == 1) {
+#pragma unroll
+        for (int j = 0; j < NTD; j++)
+            *(float4*)(mb + (j * 32 + lane) * 4) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        float* t = mb + NTD * 32 * 4 + lane * 6;
+        t[0] = m[0]; t[1] = m[1]; t[2] = l[0]; t[3] = l[1]; t[4] = ps[0]; t[5] = ps[1];
+    }
+    named_bar_sync(1, C::CW * 32);
+    if (kw == 1) return;
+    {
+        const float* t = mb + NTD * 32 * 4 + lane * 6;
+        float c0[2], c1[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            float m1 = t[h2], mn = fmaxf(m[h2], m1);
+            c0[h2] = mn == -INFINITY ? 1.f : exp2f(m[h2] - mn);
+            c1[h2] = mn == -INFINITY ? 1.f : exp2f(m1 - mn);
+            m[h2] = mn;
+            l[h2] = l[h2] * c0[h2] + t[2 + h2] * c1[h2];
+            ps[h2] = ps[h2] * c0[h2] + t[4 + h2] * c1[h2];
+        }
+#pragma unroll
+        for (int j = 0; j < NTD; j++) {
+            float4 v = *(const float4*)(mb + (j * 32 + lane) * 4);
+            o[j][0] = o[j][0] * c0[0] + v.x * c1[0]; o[j][1] = o[j][1] * c0[0] + v.y * c1[0];
+            o[j][2] = o[j][2] * c0[1] + v.z * c1[1]; o[j][3] = o[j][3] * c0[1] + v.w * c1[1];
+        }
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; h2++) {
+        float L = l[h2], P = ps[h2];
+        L += __shfl_xor_sync(0xffffffffu, L, 1);
+        L += __shfl_xor_sync(0xffffffffu, L, 2);
+        P += __shfl_xor_sync(0xffffffffu, P, 1);
+        P += __shfl_xor_sync(0xffffffffu, P, 2);
+        int row = wt * 16 + r + 8 * h2, tok = row / GROUP;
+        if (tok >= nt) continue;
+        int i = first + tok, t = dtok[i], head = g * GROUP + row % GROUP;
+        if (ns == 1) {
+            float f = 1.f / L;
+            float* op = out + (size_t)t * MIX + head * HD + 2 * t4;
+#pragma unroll
+            for (int j = 0; j < NTD; j++) {
+                float2 gt = *(float2*)(op + j * 8);
+                *(float2*)(op + j * 8) = make_float2(gt.x * (o[j][2 * h2] - KV_OFF * P) * f,
+                                                     gt.y * (o[j][2 * h2 + 1] - KV_OFF * P) * f);
+            }
+        } else {
+            size_t pi = ((size_t)i * NH + head) * z + s;
+            float* pp = part_acc + pi * HD + 2 * t4;
+#pragma unroll
+            for (int j = 0; j < NTD; j++)
+                *(float2*)(pp + j * 8) = make_float2(o[j][2 * h2] - KV_OFF * P, o[j][2 * h2 + 1] - KV_OFF * P);
+            if (t4 == 0) { part_ml[pi * 2] = m[h2]; part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
+// Merge the key splits of one (decode token, head) in split order; out *= result (the gate is there); optionally also
+// the f16 copy of the product. HD threads, thread d owns dim d.
+__global__ void __launch_bounds__(HD)
+attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, float* out,
+                    __half* mix) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x, h = blockIdx.y, t = dtok[i], d = threadIdx.x;
+    const int ns = dec_splits(dkeys[i]);
+    float* op = out + (size_t)t * MIX + h * HD + d;
+    float res;
+    if (ns == 1) {
+        res = *op;  // attn_decode finished it
+    } else {
+        const size_t base = ((size_t)i * NH + h) * z;
+        float M = -INFINITY;
+        for (int s = 0; s < ns; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
+        float L = 0.f, A = 0.f;
+        for (int s = 0; s < ns; s++) {
+            float ms = part_ml[(base + s) * 2];
+            float e = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            L += e * part_ml[(base + s) * 2 + 1];
+            A += e * part_acc[(base + s) * HD + d];
+        }
+        res = *op * A * (1.f / L);
+        *op = res;
+    }
+    if (mix) mix[(size_t)t * MIX + h * HD + d] = __float2half_rn(res);
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" {
+
+int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n, const float* q_norm,
+                 const float* k_norm, const float* inv_freq, float qscale, float* q, float* out, void* kc, void* vc,
+                 float* ks, float* vs, const int* tok_slot, const int* tok_pos, int cap) {
+    if (!ctx || !part || !q_norm || !k_norm || !inv_freq || !q || !out || !kc || !vc || !ks || !vs || !tok_slot ||
+        !tok_pos || n <= 0 || splits < 1 || cap <= 0 || cap % 64)
+        return QB_ERR_ARG;
+    return launch(ctx, attn_prep_kernel, dim3(n), dim3(32 * PREP_WARPS), 0, (cudaStream_t)stream, part, splits, n,
+                  q_norm, k_norm, inv_freq, qscale, q, out, (uint8_t*)kc, (uint8_t*)vc, ks, vs, tok_slot, tok_pos, cap);
+}
+
+int qb_attn_dec_splits(int keys) { return keys > 0 ? dec_splits(keys) : 0; }
+
+// ndseg short segments (dseg: first index into dtok, token count; at most 8 tokens each), ndec = their tokens in
+// all, dmax = the longest segment's tokens, max_keys = the largest key count among them (sizes the grid).
+int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, const void* vc, const float* ks,
+                   const float* vs, const int* dseg, const int* dtok, const int* dkeys, const int* tok_slot,
+                   const int* tok_pos, int cap, int ndseg, int ndec, int dmax, int max_keys, float* part_ml,
+                   float* part_acc, float* out, void* mix_f16) {
+    if (!ctx || !q || !kc || !vc || !ks || !vs || !dseg || !dtok || !dkeys || !tok_slot || !tok_pos || !part_ml ||
+        !part_acc || !out || ndseg <= 0 || ndec <= 0 || dmax <= 0 || dmax > 8 || max_keys <= 0 || cap % 64 ||
+        max_keys > cap)
+        return QB_ERR_ARG;
+    const int z = dec_splits(max_keys), rt = (dmax * GROUP + 15) / 16;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(ndseg, NKV, z);
+    int rc;
+#define QB_DEC(RT)                                                                                              \
+    {                                                                                                           \
+        static bool opted = false;                                                                              \
+        if (!opted) {                                                                                           \
+            QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                         DecCfg<RT>::SMEM));                                                    \
+            opted = true;                                                                                       \
+        }                                                                                                       \
+        rc = launch(ctx, attn_decode_kernel<RT>, grid, dim3(DecCfg<RT>::THREADS), DecCfg<RT>::SMEM, st, q,     \
+                    (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, part_ml, \
+                    part_acc, out, ctx->err);                                                                   \
+    }
+    if (rt == 1) QB_DEC(1) else if (rt == 2) QB_DEC(2) else QB_DEC(3)
+#undef QB_DEC
+    if (rc) return rc;
+    return launch(ctx, attn_combine_kernel, dim3(ndec, NH), dim3(HD), 0, st, (const float*)part_ml,
+                  (const float*)part_acc, dtok, dkeys, z, out, (__half*)mix_f16);
+}
+
+}  // extern "C"

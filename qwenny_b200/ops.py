@@ -70,3 +70,65 @@ class Context:
         check(lib().qb_marlin_gemm(self.h, _stream(), _p(x), _p(words), _p(y), _p(scales), m, n, k, row0, EPI[epi],
                                    _p(xrows), _p(keys), n if n_valid is None else n_valid), "qb_marlin_gemm")
         return y
+
+    def gemm_f16_plain(self, w_packed, x, n, K, ntiles, kper, y=None, xrows=None):
+        """w_packed f16 [ntiles][K/16][32][8]; x f16 [.][K]. Returns y f32 [K/kper][n][ntiles*16] partial products."""
+        split = -(-K // kper)
+        if y is None:
+            y = torch.zeros((split, n, ntiles * 16), dtype=torch.float32, device=x.device)
+        check(lib().qb_gemm_f16_plain(self.h, _stream(), _p(w_packed), _p(x), _p(xrows), K, ntiles, n, kper, _p(y),
+                                      ntiles * 16), "qb_gemm_f16_plain")
+        return y
+
+    # ---- per-token kernels
+    def embed(self, table, ids, out, keys, nkeys, n):
+        check(lib().qb_embed(self.h, _stream(), _p(table), _p(ids), _p(out), _p(keys), nkeys, n), "qb_embed")
+
+    def rmsnorm(self, x, w, y, n, eps=1e-6):
+        check(lib().qb_rmsnorm(self.h, _stream(), _p(x), _p(w), _p(y), eps, n), "qb_rmsnorm")
+
+    def add_rmsnorm(self, h, x, splits, n, w_next, y, eps=1e-6):
+        check(lib().qb_add_rmsnorm(self.h, _stream(), _p(h), _p(x), splits, n, _p(w_next), _p(y), eps),
+              "qb_add_rmsnorm")
+
+    def to_xin(self, x, y, length):
+        check(lib().qb_to_xin(self.h, _stream(), _p(x), _p(y), length), "qb_to_xin")
+
+    def sum_parts(self, x, splits, n, ld, y):
+        check(lib().qb_sum_parts(self.h, _stream(), _p(x), splits, n, ld, _p(y)), "qb_sum_parts")
+
+    def mark_seen(self, seen, mark, mark_at, seg_slot, seg_pos0, segs, vocab):
+        check(lib().qb_mark_seen(self.h, _stream(), _p(seen), _p(mark), _p(mark_at), _p(seg_slot), _p(seg_pos0), segs,
+                                 vocab), "qb_mark_seen")
+
+    def marlin_gather(self, x, rows, out, k, n):
+        check(lib().qb_marlin_gather(self.h, _stream(), _p(x), _p(rows), _p(out), k // 8, n), "qb_marlin_gather")
+
+    # ---- attention
+    def attn_prep(self, part, splits, n, q_norm, k_norm, inv_freq, qscale, q, out, kc, vc, ks, vs, tok_slot, tok_pos,
+                  cap):
+        check(lib().qb_attn_prep(self.h, _stream(), _p(part), splits, n, _p(q_norm), _p(k_norm), _p(inv_freq), qscale,
+                                 _p(q), _p(out), _p(kc), _p(vc), _p(ks), _p(vs), _p(tok_slot), _p(tok_pos), cap),
+              "qb_attn_prep")
+
+    def attn_decode(self, q, kc, vc, ks, vs, dev, st, cap, part_ml, part_acc, out, mix=None):
+        """dev: the step's device arrays (dseg, dtok, dkeys, tok_slot, tok_pos); st: its host counts."""
+        check(lib().qb_attn_decode(self.h, _stream(), _p(q), _p(kc), _p(vc), _p(ks), _p(vs), _p(dev["dseg"]),
+                                   _p(dev["dtok"]), _p(dev["dkeys"]), _p(dev["tok_slot"]), _p(dev["tok_pos"]), cap,
+                                   st["ndseg"], st["ndec"], st["dmax"], st["dec_max_pos"] + 1, _p(part_ml),
+                                   _p(part_acc), _p(out), _p(mix)), "qb_attn_decode")
+
+    # ---- DeltaNet
+    def delta_conv(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, mem, sst, cv, dev):
+        check(lib().qb_delta_conv(self.h, _stream(), _p(part), splits, n, _p(ba), ba_splits, _p(conv_w), _p(a_log),
+                                  _p(dt_bias), _p(mem), sst, _p(cv), _p(dev["tok_slot"]), _p(dev["tok_pos"])),
+              "qb_delta_conv")
+
+    def delta_rule(self, part, splits, n, cv, mem, sst, meta, out, dev, segs):
+        check(lib().qb_delta_rule(self.h, _stream(), _p(part), splits, n, _p(cv), _p(mem), sst, _p(meta), _p(out),
+                                  _p(dev["seg_start"]), _p(dev["seg_len"]), _p(dev["seg_slot"]), _p(dev["seg_pos0"]),
+                                  segs), "qb_delta_rule")
+
+    def delta_norm(self, part, splits, n, norm_w, out, y, meta, dev, segs):
+        check(lib().qb_delta_norm(self.h, _stream(), _p(part), splits, n, _p(norm_w), _p(out), _p(y), _p(meta),
+                                  _p(dev["seg_len"]), _p(dev["seg_slot"]), _p(dev["seg_pos0"]), segs), "qb_delta_norm")
