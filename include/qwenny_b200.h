@@ -115,6 +115,64 @@ int qb_delta_rule(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
 int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* nw, const float* out,
                   void* y, int* meta, const int* seg_len, const int* seg_slot, const int* seg_pos0, int segs);
 
+/* ---- the step: the host side of Model::step for this path (src/cuda/qwen/mod.rs:1125-1143).
+ * A model is the layer stack's device pointers (owned by the caller, valid for the model's life, at fixed addresses
+ * as the reference's regions are: src/cuda/vmm.rs:1-4) plus the step buffers allocated by qb_model_create
+ * (Bufs and Step of the reference: src/cuda/qwen/mod.rs:286-305, src/cuda/core.rs:699-760). */
+typedef struct qb_model qb_model;
+enum { QB_LAYER_DELTA = 0, QB_LAYER_ATTN = 1 };
+
+/* One layer (Layer + Mixer, src/cuda/qwen/mod.rs:178-196): Marlin matrices as (words, scales) pairs, norms pre-biased
+ * 1 + w, then the mixer's own tensors and per-slot caches. */
+typedef struct qb_layer {
+    int kind;                               /* QB_LAYER_DELTA | QB_LAYER_ATTN */
+    const void *in_proj_w, *in_proj_s;      /* [in_proj_qkv; in_proj_z] 16384 x 5120 | [q; k; v] 14336 x 5120 */
+    const void* in_ba;                      /* DeltaNet: [in_proj_b; in_proj_a] 96 x 5120, f16 fragment order */
+    const void *out_w, *out_s;              /* out_proj | o_proj, 5120 x 6144 */
+    const float *input_norm, *post_norm;
+    const void *gate_up_w, *gate_up_s;      /* [gate; up] 34816 x 5120, row_order(silu) */
+    const void *down_w, *down_s;            /* 5120 x 17408 */
+    /* DeltaNet (src/cuda/qwen/deltanet.rs:50-70) */
+    const float *conv_w, *a_log, *dt_bias, *norm_w;
+    float* mem;                             /* slots x sst floats: states, banks, ring */
+    long long sst;
+    int* meta;                              /* slots x 4: end (-1: none), ck, ebuf, _ */
+    /* attention (src/cuda/qwen/attn.rs:96-111) */
+    const float *q_norm, *k_norm, *inv_freq;
+    void *kc, *vc;                          /* int8 [slot][4][cap][256] */
+    float *ks, *vs;                         /* f32 [slot][4][cap] */
+    int cap;
+} qb_layer;
+
+/* A token of a step (Tok, src/engine.rs:90-95) */
+typedef struct qb_tok {
+    uint32_t id, slot, pos;
+} qb_tok;
+
+int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_rows, int vocab_valid,
+                    qb_model** out);
+void qb_model_destroy(qb_model* m);
+int qb_model_set_layer(qb_model* m, int i, const qb_layer* l);
+/* embedding bf16 [vocab][5120], final norm (1 + w), lm_head as a Marlin matrix of vocab_rows rows of which the first
+ * vocab_valid count (Mat::marlin_rows, src/cuda/core.rs:137-152) */
+int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_norm, const void* lm_w,
+                      const void* lm_s);
+/* Model::step = Step::upload (src/cuda/core.rs:835-926) + Graphs::run (:1151-1192) of launch_step
+ * (src/cuda/qwen/mod.rs:744-766). h_toks, h_out: host arrays; sequences contiguous and in order; errors as the
+ * reference's ensure!s (QB_ERR_ARG). Steps of up to 32 tokens are captured once per shape and replayed as a CUDA
+ * graph. Steps with segments longer than 8 tokens (prompt attention) return QB_ERR_UNSUPPORTED. */
+int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
+int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
+int qb_model_run(qb_model* m, void* stream);
+int qb_model_use_graphs(qb_model* m, int on);
+/* Engine::argmax (src/cuda/core.rs:1100-1103): greedy token per logit row of the last step; synchronises the stream */
+int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);
+float* qb_model_logits(qb_model* m);   /* device f32 [n_out][vocab_rows] */
+float* qb_model_hidden(qb_model* m);   /* device f32 [n][5120], the residual stream after the last layer */
+void* qb_model_xn(qb_model* m);        /* device f16 [n][5120], the final norm's output */
+long long qb_model_launches(const qb_model* m);  /* kernels launched or replayed so far */
+int qb_model_step_kernels(const qb_model* m);    /* kernels of one step of the last shape */
+
 /* ---- host-side weight packers (load time; host pointers). They produce the layouts the reference's loader
  * produces, which every kernel here reads unchanged.
  * qb_row_order    row_order, src/cuda/core.rs:106-114

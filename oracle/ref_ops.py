@@ -91,9 +91,11 @@ def unpack_marlin(words: np.ndarray, sc: np.ndarray):
     n, k = n2 // 2, k16 * 16
     w = words.reshape(k16, n // 64, 32, 4).transpose(0, 1, 3, 2)     # [k16][c64][blk][lane]
     r, c = _marlin_lane_maps()
-    a = np.zeros((k16, n // 64, 4, 16, 16), dtype=np.uint8)
-    for x in range(8):
-        a[:, :, :, r[:, x], c[:, x]] = ((w >> np.uint32(4 * x)) & 15).astype(np.uint8)
+    # (lane, nibble) -> (row, col) of the 16 x 16 block is a bijection: gather through its inverse
+    inv = np.zeros(256, dtype=np.int64)
+    inv[(r * 16 + c).reshape(-1)] = np.arange(256)
+    nib = np.stack([((w >> np.uint32(4 * x)) & 15).astype(np.uint8) for x in range(8)], axis=-1)  # [..][lane][x]
+    a = nib.reshape(k16, n // 64, 4, 256)[..., inv].reshape(k16, n // 64, 4, 16, 16)
     q = a.transpose(1, 2, 3, 0, 4).reshape(n, k)
     o = np.arange(n)
     at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8

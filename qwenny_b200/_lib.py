@@ -37,12 +37,42 @@ SIGNATURES = {
     "qb_delta_conv": [P, P, P, I, I, P, I, P, P, P, P, LL, P, P, P],
     "qb_delta_rule": [P, P, P, I, I, P, P, LL, P, P, P, P, P, P, I],
     "qb_delta_norm": [P, P, P, I, I, P, P, P, P, P, P, P, I],
+    "qb_model_create": [P, I, I, I, I, I, C.POINTER(P)],
+    "qb_model_destroy": [P],
+    "qb_model_set_layer": [P, I, P],
+    "qb_model_set_head": [P, P, P, P, P],
+    "qb_model_step": [P, P, P, I, P, I],
+    "qb_model_upload": [P, P, P, I, P, I],
+    "qb_model_run": [P, P],
+    "qb_model_use_graphs": [P, I],
+    "qb_model_argmax": [P, P, P, I],
+    "qb_model_logits": [P],
+    "qb_model_hidden": [P],
+    "qb_model_xn": [P],
+    "qb_model_launches": [P],
+    "qb_model_step_kernels": [P],
     "qb_row_order": [I, I, P],
     "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],
     "qb_split_for": [I, I, I, I],
 }
-_RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None}
+_RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
+            "qb_model_hidden": P, "qb_model_xn": P, "qb_model_launches": LL}
+
+
+class QbLayer(C.Structure):
+    """qb_layer of include/qwenny_b200.h."""
+    _fields_ = [
+        ("kind", I),
+        ("in_proj_w", P), ("in_proj_s", P), ("in_ba", P), ("out_w", P), ("out_s", P),
+        ("input_norm", P), ("post_norm", P), ("gate_up_w", P), ("gate_up_s", P), ("down_w", P), ("down_s", P),
+        ("conv_w", P), ("a_log", P), ("dt_bias", P), ("norm_w", P), ("mem", P), ("sst", LL), ("meta", P),
+        ("q_norm", P), ("k_norm", P), ("inv_freq", P), ("kc", P), ("vc", P), ("ks", P), ("vs", P), ("cap", I),
+    ]
+
+
+class QbTok(C.Structure):
+    _fields_ = [("id", C.c_uint32), ("slot", C.c_uint32), ("pos", C.c_uint32)]
 
 _lib = None
 

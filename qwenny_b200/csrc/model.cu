@@ -1,0 +1,348 @@
+// Host side of a decode / verify step: what the reference's Rust host does around its kernels, restated in C++ for
+// this path only.
+//   qb_model_create / set_layer / set_head   the layer stack's pointers and the step buffers
+//                                            (Stack::load, Bufs: src/cuda/qwen/mod.rs:286-419)
+//   qb_model_step                            Model::step (src/cuda/qwen/mod.rs:1125-1143): Step::upload
+//                                            (src/cuda/core.rs:835-926), then Graphs::run (:1151-1192) of launch_step
+//                                            (src/cuda/qwen/mod.rs:744-766): the step's kernels captured once per
+//                                            step shape into a CUDA graph and replayed
+//   qb_model_argmax                          Engine::argmax (src/cuda/core.rs:1100-1103): the greedy tokens
+// Weights and per-slot caches belong to the caller (device pointers that stay valid for the model's life, as the
+// reference's fixed-address regions do); activations and step arrays are allocated here once.
+#include <cstring>
+#include <map>
+#include <vector>
+#include "common.cuh"
+#include "ctx.h"
+
+using namespace qb;
+
+namespace {
+
+constexpr int MAX_TOK = 2048, MAX_OUT = 64;     // src/cuda/core.rs:16-19
+constexpr int SHORT_SEG = 8, MAX_DEC = 64;      // attn::segments, src/cuda/qwen/attn.rs:17-19
+constexpr int DCUT = 2048;                      // short segments are cut where pos / DCUT changes (attn.rs:27)
+constexpr int GRAPH_TOK = 32;                   // steps of up to this many tokens are replayed as graphs (core.rs:27)
+constexpr int PAIRS = 64 * 128;                 // (decode token, split) pairs of the partial buffers (attn.rs:29)
+
+struct Layer {
+    qb_layer w;
+    bool set = false;
+};
+
+struct GraphKey {
+    int v[9];
+    bool operator<(const GraphKey& o) const { return std::memcmp(v, o.v, sizeof v) < 0; }
+};
+
+}  // namespace
+
+struct qb_model {
+    qb_ctx* ctx = nullptr;
+    int nlayers = 0, slots = 0, max_ctx = 0, vocab_rows = 0, vocab_valid = 0;
+    std::vector<Layer> layers;
+    const void* embed = nullptr;
+    const float* final_norm = nullptr;
+    const void *lm_w = nullptr, *lm_s = nullptr;
+    // activations (Bufs)
+    float *h = nullptr, *part = nullptr, *ba = nullptr, *o = nullptr, *cv = nullptr, *q = nullptr, *ml = nullptr,
+          *acc = nullptr, *logits = nullptr;
+    __half *xn = nullptr, *mix = nullptr, *mid = nullptr;
+    unsigned long long* keys = nullptr;
+    unsigned* seen = nullptr;
+    // step arrays (Step), one device allocation and one pinned host mirror: a single copy per step
+    int *d_step = nullptr, *h_step = nullptr;
+    size_t step_ints = 0;
+    int *ids, *tok_slot, *tok_pos, *seg_start, *seg_len, *seg_slot, *seg_pos0, *dtok, *dseg, *dkeys, *out_rows, *mark,
+        *mark_at;
+    unsigned long long* h_keys = nullptr;  // pinned
+    // host-side shape of the uploaded step
+    int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0;
+    std::map<GraphKey, cudaGraphExec_t> graphs;
+    bool use_graphs = true;
+    long long launches = 0;  // kernels launched (or replayed) since creation
+    int step_kernels = 0;    // kernels of the last step
+};
+
+namespace {
+
+struct StepLayout {
+    // offsets (ints) of the step arrays inside the single step allocation
+    size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, out_rows, mark, mark_at,
+        total;
+    StepLayout() {
+        size_t o = 0;
+        auto take = [&](size_t n) { size_t r = o; o += (n + 3) / 4 * 4; return r; };
+        ids = take(MAX_TOK); tok_slot = take(MAX_TOK); tok_pos = take(MAX_TOK);
+        seg_start = take(MAX_TOK); seg_len = take(MAX_TOK); seg_slot = take(MAX_TOK); seg_pos0 = take(MAX_TOK);
+        dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); out_rows = take(MAX_OUT);
+        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1);
+        total = o;
+    }
+};
+
+template <class T>
+int dalloc(T** p, size_t n) {
+    QB_CUDA(cudaMalloc((void**)p, n * sizeof(T)));
+    QB_CUDA(cudaMemset(*p, 0, n * sizeof(T)));
+    return QB_OK;
+}
+
+#define QB_TRY(x)            \
+    do {                     \
+        int rc_ = (x);       \
+        if (rc_) return rc_; \
+    } while (0)
+
+// The kernels of one step over the uploaded tokens, in the reference's order (launch_step)
+int launch_step(qb_model* m, cudaStream_t st) {
+    qb_ctx* c = m->ctx;
+    const int n = m->n;
+    int k = 0;
+    void* s = (void*)st;
+    QB_TRY(qb_mark_seen(c, s, m->seen, m->mark, m->mark_at, m->seg_slot, m->seg_pos0, m->segs, m->vocab_rows)); k++;
+    QB_TRY(qb_embed(c, s, m->embed, m->ids, m->h, m->keys, m->n_out, n)); k++;
+    QB_TRY(qb_rmsnorm(c, s, m->h, m->layers[0].w.input_norm, m->xn, EPS, n)); k++;
+    for (int i = 0; i < m->nlayers; i++) {
+        const qb_layer& L = m->layers[i].w;
+        const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
+        if (L.kind == QB_LAYER_DELTA) {
+            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
+                                  nullptr, nullptr, 0)); k++;
+            const int ba_tiles = 2 * LV_HEADS / 16;
+            const int kper = H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
+            QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, kper, m->ba, 2 * LV_HEADS)); k++;
+            QB_TRY(qb_delta_conv(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.mem, L.sst,
+                                 m->cv, m->tok_slot, m->tok_pos)); k++;
+            QB_TRY(qb_delta_rule(c, s, m->part, 1, n, m->cv, L.mem, L.sst, L.meta, m->o, m->seg_start, m->seg_len,
+                                 m->seg_slot, m->seg_pos0, m->segs)); k++;
+            QB_TRY(qb_delta_norm(c, s, m->part, 1, n, L.norm_w, m->o, m->mix, L.meta, m->seg_len, m->seg_slot,
+                                 m->seg_pos0, m->segs)); k++;
+        } else {
+            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, ATTN_IN, H, 0, QB_EPI_PLAIN,
+                                  nullptr, nullptr, 0)); k++;
+            const float qscale = 1.4426950408889634f / 16.f;  // scores in base 2, over sqrt(HD)
+            QB_TRY(qb_attn_prep(c, s, m->part, 1, n, L.q_norm, L.k_norm, L.inv_freq, qscale, m->q, m->o, L.kc, L.vc,
+                                L.ks, L.vs, m->tok_slot, m->tok_pos, L.cap)); k++;
+            QB_TRY(qb_attn_decode(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->dseg, m->dtok, m->dkeys, m->tok_slot,
+                                  m->tok_pos, L.cap, m->ndseg, m->ndec, m->dmax, m->dec_max_pos + 1, m->ml, m->acc,
+                                  m->o, m->mix)); k += 2;
+        }
+        QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+        QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr,
+                              nullptr, 0)); k++;
+        QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+        QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, w_next, m->xn, EPS)); k++;
+    }
+    if (m->n_out > 0) {
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, 0, QB_EPI_ARGMAX,
+                              m->out_rows, m->keys, m->vocab_valid)); k++;
+    }
+    m->step_kernels = k;
+    return QB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_rows, int vocab_valid,
+                    qb_model** out) {
+    if (!ctx || !out || nlayers <= 0 || slots <= 0 || max_ctx <= 0 || vocab_rows % 256 || vocab_valid > vocab_rows ||
+        vocab_valid <= 0)
+        return QB_ERR_ARG;
+    QB_CUDA(cudaSetDevice(ctx->device));
+    qb_model* m = new qb_model();
+    m->ctx = ctx; m->nlayers = nlayers; m->slots = slots; m->max_ctx = max_ctx;
+    m->vocab_rows = vocab_rows; m->vocab_valid = vocab_valid;
+    m->layers.resize(nlayers);
+    const size_t T = MAX_TOK;
+    QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
+    QB_TRY(dalloc(&m->part, T * (size_t)DELTA_IN));
+    QB_TRY(dalloc(&m->ba, (size_t)40 * 32 * 2 * LV_HEADS + T * 2 * LV_HEADS));
+    QB_TRY(dalloc(&m->o, T * MIX)); QB_TRY(dalloc(&m->mix, T * MIX)); QB_TRY(dalloc(&m->mid, T * FF));
+    QB_TRY(dalloc(&m->cv, T * CVW)); QB_TRY(dalloc(&m->q, T * NH * HD));
+    QB_TRY(dalloc(&m->ml, (size_t)PAIRS * NH * 2)); QB_TRY(dalloc(&m->acc, (size_t)PAIRS * NH * HD));
+    QB_TRY(dalloc(&m->logits, (size_t)MAX_OUT * vocab_rows)); QB_TRY(dalloc(&m->keys, (size_t)MAX_OUT));
+    QB_TRY(dalloc(&m->seen, (size_t)slots * vocab_rows / 32));
+    StepLayout L;
+    m->step_ints = L.total;
+    QB_TRY(dalloc(&m->d_step, L.total));
+    QB_CUDA(cudaMallocHost((void**)&m->h_step, L.total * sizeof(int)));
+    QB_CUDA(cudaMallocHost((void**)&m->h_keys, MAX_OUT * sizeof(unsigned long long)));
+    std::memset(m->h_step, 0, L.total * sizeof(int));
+    int* d = m->d_step;
+    m->ids = d + L.ids; m->tok_slot = d + L.tok_slot; m->tok_pos = d + L.tok_pos; m->seg_start = d + L.seg_start;
+    m->seg_len = d + L.seg_len; m->seg_slot = d + L.seg_slot; m->seg_pos0 = d + L.seg_pos0; m->dtok = d + L.dtok;
+    m->dseg = d + L.dseg; m->dkeys = d + L.dkeys; m->out_rows = d + L.out_rows; m->mark = d + L.mark;
+    m->mark_at = d + L.mark_at;
+    *out = m;
+    return QB_OK;
+}
+
+void qb_model_destroy(qb_model* m) {
+    if (!m) return;
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    void* bufs[] = {m->h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
+                    m->seen, m->d_step};
+    for (void* b : bufs) cudaFree(b);
+    cudaFreeHost(m->h_step);
+    cudaFreeHost(m->h_keys);
+    delete m;
+}
+
+int qb_model_set_layer(qb_model* m, int i, const qb_layer* l) {
+    if (!m || !l || i < 0 || i >= m->nlayers) return QB_ERR_ARG;
+    if (!l->in_proj_w || !l->in_proj_s || !l->out_w || !l->out_s || !l->gate_up_w || !l->gate_up_s || !l->down_w ||
+        !l->down_s || !l->input_norm || !l->post_norm)
+        return QB_ERR_ARG;
+    if (l->kind == QB_LAYER_DELTA) {
+        if (!l->in_ba || !l->conv_w || !l->a_log || !l->dt_bias || !l->norm_w || !l->mem || !l->meta ||
+            l->sst < (long long)SLOT_RING + CR * LQKV)
+            return QB_ERR_ARG;
+    } else if (l->kind == QB_LAYER_ATTN) {
+        if (!l->q_norm || !l->k_norm || !l->inv_freq || !l->kc || !l->vc || !l->ks || !l->vs || l->cap < m->max_ctx ||
+            l->cap % 64)
+            return QB_ERR_ARG;
+    } else {
+        return QB_ERR_ARG;
+    }
+    m->layers[i].w = *l;
+    m->layers[i].set = true;
+    return QB_OK;
+}
+
+int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_norm, const void* lm_w,
+                      const void* lm_s) {
+    if (!m || !embed_bf16 || !final_norm || !lm_w || !lm_s) return QB_ERR_ARG;
+    m->embed = embed_bf16; m->final_norm = final_norm; m->lm_w = lm_w; m->lm_s = lm_s;
+    return QB_OK;
+}
+
+int qb_model_use_graphs(qb_model* m, int on) {
+    if (!m) return QB_ERR_ARG;
+    m->use_graphs = on != 0;
+    return QB_OK;
+}
+
+// Step::upload: the step's tokens (each sequence's contiguous and in order), the rows whose logits are wanted.
+// Every token of a segment is added to its slot's seen set (the reference's `marks: None`).
+int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out) {
+    if (!m || !toks || n < 1 || n > MAX_TOK || n_out < 0 || n_out > MAX_OUT || (n_out && !out)) return QB_ERR_ARG;
+    for (int i = 0; i < n_out; i++)
+        if (out[i] < 0 || out[i] >= n) return QB_ERR_ARG;
+    StepLayout L;
+    int* h = m->h_step;
+    int segs = 0;
+    for (int i = 0; i < n; i++) {
+        const qb_tok& t = toks[i];
+        if ((int)t.slot >= m->slots || (int)t.pos >= m->max_ctx || (int)t.id >= m->vocab_valid) return QB_ERR_ARG;
+        h[L.ids + i] = (int)t.id; h[L.tok_slot + i] = (int)t.slot; h[L.tok_pos + i] = (int)t.pos;
+        if (i > 0 && toks[i - 1].slot == t.slot) {
+            if (toks[i - 1].pos + 1 != t.pos) return QB_ERR_ARG;  // positions of a slot not consecutive
+            h[L.seg_len + segs - 1]++;
+        } else {
+            for (int s = 0; s < segs; s++)
+                if (h[L.seg_slot + s] == (int)t.slot) return QB_ERR_ARG;  // a slot in two segments
+            h[L.seg_start + segs] = i; h[L.seg_len + segs] = 1; h[L.seg_slot + segs] = (int)t.slot;
+            h[L.seg_pos0 + segs] = (int)t.pos;
+            segs++;
+        }
+    }
+    int ndec = 0, ndseg = 0, ntile = 0, dmax = 0, max_seg = 0, dec_max_pos = 0, nmark = 0;
+    for (int s = 0; s < segs; s++) {
+        int st = h[L.seg_start + s], len = h[L.seg_len + s];
+        max_seg = len > max_seg ? len : max_seg;
+        if (len <= SHORT_SEG && ndec + len <= MAX_DEC) {
+            int a = st;
+            while (a < st + len) {
+                int part = (int)toks[a].pos / DCUT, e = a + 1;
+                while (e < st + len && (int)toks[e].pos / DCUT == part) e++;
+                h[L.dseg + 2 * ndseg] = ndec; h[L.dseg + 2 * ndseg + 1] = e - a;
+                for (int t = a; t < e; t++) {
+                    h[L.dtok + ndec] = t;
+                    h[L.dkeys + ndec] = (int)toks[e - 1].pos + 1;
+                    ndec++;
+                }
+                dmax = e - a > dmax ? e - a : dmax;
+                dec_max_pos = (int)toks[e - 1].pos > dec_max_pos ? (int)toks[e - 1].pos : dec_max_pos;
+                ndseg++;
+                a = e;
+            }
+        } else {
+            ntile += (len + 9) / 10;  // prompt tiles of 64 / GROUP tokens: the prompt attention is not built yet
+        }
+        h[L.mark_at + s] = nmark;
+        for (int t = st; t < st + len; t++) h[L.mark + nmark++] = (int)toks[t].id;
+    }
+    h[L.mark_at + segs] = nmark;
+    for (int i = 0; i < n_out; i++) h[L.out_rows + i] = out[i];
+    if (ntile > 0) return QB_ERR_UNSUPPORTED;
+    QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
+    m->max_seg = max_seg; m->dec_max_pos = dec_max_pos;
+    return QB_OK;
+}
+
+// Graphs::run: replay the step's graph, capturing it the first time its shape is seen; larger steps launch directly.
+int qb_model_run(qb_model* m, void* stream) {
+    if (!m || m->n <= 0 || !m->embed) return QB_ERR_ARG;
+    for (auto& l : m->layers)
+        if (!l.set) return QB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!m->use_graphs || m->n > GRAPH_TOK) {
+        QB_TRY(launch_step(m, st));
+        m->launches += m->step_kernels;
+        return QB_OK;
+    }
+    GraphKey key = {{m->n, m->n_out, m->segs, m->ndec, m->ntile, m->max_seg,
+                     m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0, m->ndseg, m->dmax}};
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        // a first uncaptured run sets the kernels' attributes (not allowed while capturing) and warms the caches
+        QB_TRY(launch_step(m, st));
+        m->launches += m->step_kernels;
+        QB_CUDA(cudaStreamSynchronize(st));
+        cudaGraph_t g = nullptr;
+        QB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        int rc = launch_step(m, st);
+        cudaError_t e = cudaStreamEndCapture(st, &g);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) return (int)e;
+        cudaGraphExec_t ex = nullptr;
+        e = cudaGraphInstantiate(&ex, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return (int)e;
+        it = m->graphs.emplace(key, ex).first;
+        return QB_OK;  // the uncaptured run above was this step
+    }
+    QB_CUDA(cudaGraphLaunch(it->second, st));
+    m->launches += m->step_kernels;
+    return QB_OK;
+}
+
+int qb_model_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out) {
+    QB_TRY(qb_model_upload(m, stream, toks, n, out, n_out));
+    return qb_model_run(m, stream);
+}
+
+// Engine::argmax: the greedy token of each logit row of the last step (waits for the step)
+int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out) {
+    if (!m || !h_tokens || n_out < 0 || n_out > m->n_out) return QB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    QB_CUDA(cudaMemcpyAsync(m->h_keys, m->keys, n_out * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    for (int i = 0; i < n_out; i++) h_tokens[i] = (int)(0xffffffffu - (uint32_t)(m->h_keys[i] & 0xffffffffu));
+    return QB_OK;
+}
+
+// Device pointers of the step's results and activations (tests, samplers): logits f32 [n_out][vocab_rows], the
+// residual stream h f32 [n][5120], the last matrix-product input xn f16 [n][5120]
+float* qb_model_logits(qb_model* m) { return m ? m->logits : nullptr; }
+float* qb_model_hidden(qb_model* m) { return m ? m->h : nullptr; }
+void* qb_model_xn(qb_model* m) { return m ? (void*)m->xn : nullptr; }
+long long qb_model_launches(const qb_model* m) { return m ? m->launches : 0; }
+int qb_model_step_kernels(const qb_model* m) { return m ? m->step_kernels : 0; }
+
+}  // extern "C"

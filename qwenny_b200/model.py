@@ -1,0 +1,232 @@
+"""Host-side mirror of the reference's `Model` for the decode / verify path: holds the layer stack's device tensors,
+hands their pointers to the library (qb_model_*), and exposes step / argmax with the reference's argument meaning
+(`Engine::step(toks, out)` and `Engine::argmax`, src/engine.rs:106-239). torch only owns device memory here.
+
+`synthetic()` builds the random-init 27B-shape model of the benchmark (there are no checkpoints in this environment):
+every int4 matrix gets uniform codes and group scales |N(0, 0.02)| / 7 + 1e-4 rounded to bf16, norms 1 + N(0, 0.02),
+embedding N(0, 0.02) bf16. Codes are drawn directly in Marlin's packed form (a uniform random word is a uniform random
+tile of codes), so nothing the size of the model ever exists on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import QbLayer, QbTok, check, lib
+
+H, NH, NKV, HD = 5120, 24, 4, 256
+LK_HEADS, LV_HEADS, LKD, LVD = 16, 48, 128, 128
+LQKV = 2 * LK_HEADS * LKD + LV_HEADS * LVD
+DELTA_IN = LQKV + LV_HEADS * LVD
+ATTN_IN = 2 * NH * HD + 2 * NKV * HD
+MIX, FF = NH * HD, 17408
+CR, KEEP = 32, 16
+REP = LK_HEADS * LKD + LV_HEADS * LVD + 2 * LV_HEADS
+SLOT_FLOATS = 2 * LV_HEADS * LVD * LKD + 2 * KEEP * REP + CR * LQKV
+THETA = 1e7
+ROT = 64
+LAYER_PATTERN = ("delta", "delta", "delta", "attn")  # three of four layers Gated DeltaNet, every fourth attention
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def inv_freq() -> torch.Tensor:
+    i = torch.arange(ROT // 2, dtype=torch.float64)
+    return (1.0 / (THETA ** (2 * i / ROT))).float()
+
+
+class Marlin:
+    """An int4 matrix in Marlin's layout on the device: words int32 [k/16][2n], scales f16 [k/128][n]."""
+
+    def __init__(self, words: torch.Tensor, scales: torch.Tensor):
+        self.words, self.scales = words, scales
+        self.n, self.k = words.shape[1] // 2, words.shape[0] * 16
+
+    @staticmethod
+    def random(n: int, k: int, g: torch.Generator, device="cuda") -> "Marlin":
+        words = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), generator=g, dtype=torch.int32, device=device)
+        sc = (torch.randn(k // 128, n, generator=g, device=device).abs() * (0.02 / 7) + 1e-4)
+        return Marlin(words, sc.to(torch.bfloat16).to(torch.float16))
+
+    def bytes(self) -> int:
+        return self.words.numel() * 4 + self.scales.numel() * 2
+
+
+class Model:
+    """The layer stack on one device. `layers`: list of dicts of device tensors (see synthetic())."""
+
+    def __init__(self, ctx, layers, embed, final_norm, lm_head: Marlin, vocab_valid, slots, max_ctx):
+        self.ctx, self.layers, self.embed, self.final_norm, self.lm_head = ctx, layers, embed, final_norm, lm_head
+        self.slots, self.max_ctx, self.vocab_valid = slots, max_ctx, vocab_valid
+        # the model's own stream: the legacy default stream cannot be captured into a graph (the reference opens one
+        # the same way, src/cuda/core.rs:42-46)
+        torch.cuda.synchronize()
+        self.stream = torch.cuda.Stream()
+        h = C.c_void_p()
+        check(lib().qb_model_create(ctx.h, len(layers), slots, max_ctx, lm_head.n, vocab_valid, C.byref(h)),
+              "qb_model_create")
+        self.h = h
+        for i, l in enumerate(layers):
+            q = QbLayer()
+            q.kind = 0 if l["kind"] == "delta" else 1
+            for name in ("in_proj", "out", "gate_up", "down"):
+                setattr(q, name + "_w", l[name].words.data_ptr())
+                setattr(q, name + "_s", l[name].scales.data_ptr())
+            q.input_norm, q.post_norm = l["input_norm"].data_ptr(), l["post_norm"].data_ptr()
+            if l["kind"] == "delta":
+                q.in_ba = l["in_ba"].data_ptr()
+                for name in ("conv_w", "a_log", "dt_bias", "norm_w", "mem", "meta"):
+                    setattr(q, name, l[name].data_ptr())
+                q.sst = l["sst"]
+            else:
+                for name in ("q_norm", "k_norm", "inv_freq", "kc", "vc", "ks", "vs"):
+                    setattr(q, name, l[name].data_ptr())
+                q.cap = l["cap"]
+            check(lib().qb_model_set_layer(self.h, i, C.byref(q)), f"qb_model_set_layer({i})")
+        check(lib().qb_model_set_head(self.h, _p(embed), _p(final_norm), _p(lm_head.words), _p(lm_head.scales)),
+              "qb_model_set_head")
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().qb_model_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- Engine::step / Engine::argmax
+    @staticmethod
+    def _toks(toks):
+        arr = (QbTok * len(toks))()
+        for i, (tid, slot, pos) in enumerate(toks):
+            arr[i].id, arr[i].slot, arr[i].pos = int(tid), int(slot), int(pos)
+        return arr
+
+    def step(self, toks, out):
+        """toks: [(id, slot, pos)], sequences contiguous and in order; out: indices whose logits are wanted."""
+        arr = self._toks(toks)
+        o = (C.c_int * max(1, len(out)))(*out)
+        s = C.c_void_p(self.stream.cuda_stream)
+        check(lib().qb_model_step(self.h, s, arr, len(toks), o, len(out)), "qb_model_step")
+        self._n, self._n_out = len(toks), len(out)
+
+    def argmax(self, n_out=None):
+        n_out = self._n_out if n_out is None else n_out
+        res = (C.c_int * max(1, n_out))()
+        s = C.c_void_p(self.stream.cuda_stream)
+        check(lib().qb_model_argmax(self.h, s, res, n_out), "qb_model_argmax")
+        return list(res)[:n_out]
+
+    def use_graphs(self, on: bool):
+        check(lib().qb_model_use_graphs(self.h, int(on)), "qb_model_use_graphs")
+
+    def logits(self) -> torch.Tensor:
+        """f32 [n_out][vocab_rows] of the last step (a copy)."""
+        self.stream.synchronize()
+        ptr = lib().qb_model_logits(self.h)
+        return _device_copy(ptr, (self._n_out, self.lm_head.n), torch.float32)
+
+    def hidden(self) -> torch.Tensor:
+        self.stream.synchronize()
+        return _device_copy(lib().qb_model_hidden(self.h), (self._n, H), torch.float32)
+
+    def xn(self) -> torch.Tensor:
+        self.stream.synchronize()
+        return _device_copy(lib().qb_model_xn(self.h), (self._n, H), torch.float16)
+
+    def run(self):
+        """Replays the uploaded step (Graphs::run) without a new upload: the device-resident timing path."""
+        check(lib().qb_model_run(self.h, C.c_void_p(self.stream.cuda_stream)), "qb_model_run")
+
+    @property
+    def step_kernels(self) -> int:
+        return lib().qb_model_step_kernels(self.h)
+
+    @property
+    def launches(self) -> int:
+        return lib().qb_model_launches(self.h)
+
+    # ---- bytes a step must move (the roofline's numerator)
+    def step_bytes(self, positions: int) -> int:
+        b = int(self.vocab_valid * H * 0.515625)  # the output layer's rows that count
+        for l in self.layers:
+            for name in ("in_proj", "out", "gate_up", "down"):
+                b += int(l[name].n * l[name].k * 0.515625)
+            if l["kind"] == "delta":
+                b += 2 * LV_HEADS * H * 2          # in_proj_b / in_proj_a kept in f16
+                b += 2 * LV_HEADS * LVD * LKD * 4  # the f32 state, read and written
+            else:
+                b += NKV * 520 * positions         # int8 keys and values + two f32 scales per position and head
+        return b
+
+
+def _device_copy(ptr: int, shape, dtype) -> torch.Tensor:
+    """A torch copy of library-owned device memory."""
+    n = int(np.prod(shape))
+    out = torch.empty(shape, dtype=dtype, device="cuda")
+    from cuda.bindings import runtime as rt
+    (err,) = rt.cudaMemcpy(out.data_ptr(), ptr, n * out.element_size(), rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice)
+    if int(err) != 0:
+        raise RuntimeError(f"cudaMemcpy failed: {err}")
+    return out
+
+
+def synthetic(ctx, nlayers=64, slots=1, max_ctx=32768, vocab=151936, seed=0, device="cuda", position=0,
+              pattern=LAYER_PATTERN):
+    """The random-init 27B-shape hybrid decoder. With position > 0 the caches are filled as if `position` tokens had
+    been processed: random int8 keys / values with scales |N(0, 0.05)|, DeltaNet state N(0, 0.01), metadata
+    {position, position, 0}."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    cap = (max_ctx + 63) // 64 * 64
+    sst = (SLOT_FLOATS + 1023) // 1024 * 1024
+    norm = lambda n: 1 + torch.randn(n, generator=g, device=device) * 0.02
+    layers = []
+    for i in range(nlayers):
+        kind = pattern[i % len(pattern)]
+        l = dict(kind=kind, input_norm=norm(H), post_norm=norm(H),
+                 out=Marlin.random(H, MIX, g, device), gate_up=Marlin.random(2 * FF, H, g, device),
+                 down=Marlin.random(H, FF, g, device))
+        if kind == "delta":
+            l["in_proj"] = Marlin.random(DELTA_IN, H, g, device)
+            # in_proj_b / in_proj_a stay 16-bit (96 x 5120, fragment order: any order of N(0, 0.02) values is one)
+            l["in_ba"] = (torch.randn(2 * LV_HEADS // 16, H // 16, 32, 8, generator=g, device=device) * 0.02).half()
+            l["conv_w"] = torch.randn(LQKV, 4, generator=g, device=device) * 0.3
+            l["a_log"] = torch.randn(LV_HEADS, generator=g, device=device) * 0.5
+            l["dt_bias"] = torch.randn(LV_HEADS, generator=g, device=device) * 0.5
+            l["norm_w"] = norm(LVD)
+            mem = torch.zeros(slots * sst, device=device)
+            meta = torch.tensor([[-1, 0, 0, 0]] * slots, dtype=torch.int32, device=device)
+            if position > 0:
+                mem.normal_(0, 0.01, generator=g)
+                meta = torch.tensor([[position, position, 0, 0]] * slots, dtype=torch.int32, device=device)
+            l["mem"], l["meta"], l["sst"] = mem, meta, sst
+        else:
+            l["in_proj"] = Marlin.random(ATTN_IN, H, g, device)
+            l["q_norm"], l["k_norm"] = norm(HD), norm(HD)
+            l["inv_freq"] = inv_freq().to(device)
+            nb = slots * NKV * cap
+            if position > 0:
+                l["kc"] = torch.randint(1, 256, (nb * HD,), generator=g, dtype=torch.uint8, device=device)
+                l["vc"] = torch.randint(1, 256, (nb * HD,), generator=g, dtype=torch.uint8, device=device)
+                l["ks"] = (torch.randn(nb, generator=g, device=device) * 0.05).abs()
+                l["vs"] = (torch.randn(nb, generator=g, device=device) * 0.05).abs()
+            else:
+                l["kc"] = torch.zeros(nb * HD, dtype=torch.uint8, device=device)
+                l["vc"] = torch.zeros(nb * HD, dtype=torch.uint8, device=device)
+                l["ks"], l["vs"] = torch.zeros(nb, device=device), torch.zeros(nb, device=device)
+            l["cap"] = cap
+        layers.append(l)
+    vocab_rows = (vocab + 255) // 256 * 256
+    embed = (torch.randn(vocab, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    lm_head = Marlin.random(vocab_rows, H, g, device)
+    return Model(ctx, layers, embed, norm(H), lm_head, vocab, slots, max_ctx)
