@@ -207,10 +207,8 @@ def run_ours(args):
             gemm_us = a.elapsed_time(b) * 1e3 / reps / ngemm
 
     # ---- max over ranks
-    t = torch.tensor([ms_dev, ms_e2e], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = float(t[0]), float(t[1])
+    from qwenny_b200 import replicas
+    ms_dev, ms_e2e = replicas.slowest_ms(ms_dev, "cuda"), replicas.slowest_ms(ms_e2e, "cuda")
     err = ctx.device_error()
     if err:
         raise SystemExit(f"a kernel gave up a bounded wait (code {err})")
@@ -221,7 +219,7 @@ def run_ours(args):
         bytes_per_launch = gemm_bytes / ngemm
         achieved = bytes_per_launch / gemm_us / 1e3  # GB/s
         line = {
-            "metric": METRIC, "value": world * ROWS / ms_dev * 1e3, "unit": "tok/s", "n_gpus": world,
+            "metric": METRIC, "value": replicas.job_throughput(ROWS, ms_dev, world), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_dev, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"full 27B-shape hybrid decoder verify step ({args.layers} layers, int4 g128 weights, "
@@ -231,7 +229,7 @@ def run_ours(args):
                        "cuda_graph": True, "programmatic_dependent_launch": not args.no_pdl,
                        "l2": "inputs larger than L2: 14.4 GB of weights, KV and state stream per step",
                        "tok": "verified rows; steps/s = tok/s / 5"},
-            "e2e": {"value": world * ROWS / ms_e2e * 1e3, "unit": "tok/s", "ms_per_step": ms_e2e,
+            "e2e": {"value": replicas.job_throughput(ROWS, ms_e2e, world), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": int(model_step_h2d_bytes()), "d2h_bytes_per_step": ROWS * 8},
             "gpu_launches": int(launches * args.steps),
             "launches_per_step": int(launches),

@@ -54,6 +54,10 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
  * next qb_marlin_gemm calls; zeros restore the built-in choice. */
 int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
+/* Measurement only: the following qb_marlin_gemm calls write per-block timestamps (ns of the global timer: start,
+ * first stage landed, last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`. */
+int qb_marlin_trace(qb_ctx* ctx, long long* buf);
+
 /* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
  * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it
  * (src/cuda/core.rs:532-560): W in mma A-fragment order (qb_pack_f16), X f16 [.][K] (rows xrows[t] if given),
@@ -115,6 +119,14 @@ int qb_delta_rule(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
 int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* nw, const float* out,
                   void* y, int* meta, const int* seg_len, const int* seg_slot, const int* seg_pos0, int segs);
 
+/* The three DeltaNet kernels of a step in one launch (same arguments; `out`, the raw output before the gated norm,
+ * may be NULL). Gives the same bits as qb_delta_conv + qb_delta_rule + qb_delta_norm. The reference has no fused
+ * counterpart; DeltaNet::run (src/cuda/qwen/deltanet.rs:109-160) would call this once instead of its three launches. */
+int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* ba, int ba_splits,
+                   const float* cw, const float* a_log, const float* dt_bias, const float* nw, float* mem,
+                   long long sst, int* meta, float* out, void* y, const int* seg_start, const int* seg_len,
+                   const int* seg_slot, const int* seg_pos0, int segs);
+
 /* ---- the step: the host side of Model::step for this path (src/cuda/qwen/mod.rs:1125-1143).
  * A model is the layer stack's device pointers (owned by the caller, valid for the model's life, at fixed addresses
  * as the reference's regions are: src/cuda/vmm.rs:1-4) plus the step buffers allocated by qb_model_create
@@ -165,6 +177,8 @@ int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const 
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
+/* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
+int qb_model_use_fused(qb_model* m, int on);
 /* Engine::argmax (src/cuda/core.rs:1100-1103): greedy token per logit row of the last step; synchronises the stream */
 int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);
 float* qb_model_logits(qb_model* m);   /* device f32 [n_out][vocab_rows] */

@@ -23,6 +23,7 @@ SIGNATURES = {
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_tune": [P, I, I, I, I],
+    "qb_marlin_trace": [P, P],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
     "qb_embed": [P, P, P, P, P, P, I, I],
     "qb_rmsnorm": [P, P, P, P, P, F, I],
@@ -37,6 +38,8 @@ SIGNATURES = {
     "qb_delta_conv": [P, P, P, I, I, P, I, P, P, P, P, LL, P, P, P],
     "qb_delta_rule": [P, P, P, I, I, P, P, LL, P, P, P, P, P, P, I],
     "qb_delta_norm": [P, P, P, I, I, P, P, P, P, P, P, P, I],
+    "qb_delta_mixer": [P, P, P, I, I, P, I, P, P, P, P, P, LL, P, P, P, P, P, P, P, I],
+    "qb_model_use_fused": [P, I],
     "qb_model_create": [P, I, I, I, I, I, C.POINTER(P)],
     "qb_model_destroy": [P],
     "qb_model_set_layer": [P, I, P],

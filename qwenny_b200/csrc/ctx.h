@@ -16,8 +16,10 @@ struct qb_ctx {
     int* err = nullptr;  // device word
     // measurement override of the GEMV plan (0: built-in choice)
     int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
+    bool no_cluster = false;
     // programmatic dependent launch on the launches that support it
     bool pdl = false;
+    long long* trace = nullptr;  // measurement: per-block timestamps of the next products
 };
 
 #define QB_CUDA(x)                         \

@@ -300,3 +300,205 @@ int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
 }
 
 }  // extern "C"
+
+// =================================================================================================== fused mixer
+// delta_conv + delta_rule + delta_norm of a step in ONE launch: block (value head h, segment), 512 threads. The head's
+// whole f32 state (128 x 128) lives in the block's registers (32 per thread: column tid / 4, rows 4 (tid % 4 + 4 j) + i,
+// the same layout and operation order as delta_rule_kernel, so both give the same bits); the block recomputes the conv
+// of the 384 channels it needs (its key head's q and k, its own v) from the in-projection rows or the ring, runs the
+// recurrence, and finishes the gated RMSNorm over its 128 value columns in shared memory. The conv ring is written by
+// the blocks in shares; the slot metadata by the LAST block of the launch to finish (an atomic ticket), because every
+// block reads the old metadata when it starts.
+namespace qb {
+
+constexpr int FNT = 512;
+constexpr int FCH = 3 * LKD;  // q, k, v channels of a block
+
+struct FusedRound {
+    float c[TCH][FCH];      // conv outputs: q [0,128), k [128,256), v [256,384)
+    float o[TCH][LVD];      // raw outputs of the round
+    float e[TCH], b[TCH], kq[TCH], rn[TCH];
+};
+
+__global__ void __launch_bounds__(FNT)
+delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_splits, const float* cw,
+                   const float* a_log, const float* dt_bias, const float* nw, float* mem, long long sst, int* meta,
+                   float* out, __half* y, const int* seg_start, const int* seg_len, const int* seg_slot,
+                   const int* seg_pos0, int segs, int* ticket) {
+    __shared__ __align__(16) FusedRound R;
+    pdl_launch_dependents();
+    const int h = blockIdx.x, sg = blockIdx.y, kh = h / (LV_HEADS / LK_HEADS);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = tid % LPC, col = tid / LPC;
+    const int t0 = seg_start[sg], len = seg_len[sg], slot = seg_slot[sg], p0 = seg_pos0[sg];
+    const Plan pl = make_plan(meta, slot, p0, len);
+    float* sm0 = mem + slot * sst;
+    auto sbuf = [&](int b) { return sm0 + (size_t)b * SLOT_STATE + ((size_t)h * LVD + col) * LKD; };
+    auto entry = [&](int b, int pos) { return sm0 + 2 * SLOT_STATE + (size_t)b * SLOT_BANK + (size_t)(pos % KEEP) * REP; };
+    // global conv channel of the block's channel ch
+    auto gchan = [&](int ch) {
+        return ch < LKD ? kh * LKD + ch : ch < 2 * LKD ? LK_HEADS * LKD + kh * LKD + (ch - LKD)
+                                                       : 2 * LK_HEADS * LKD + h * LVD + (ch - 2 * LKD);
+    };
+
+    float S[RPT];
+    if (pl.zero) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++) S[i] = 0.f;
+    } else {
+        ld_rows(S, sbuf(pl.in), rg);
+    }
+    const float nwc = nw[col];
+    for (int i = 0; i < pl.r; i++) {
+        const float* e = entry(pl.in, pl.from + i);
+        float k[RPT];
+        ld_rows(k, e + kh * LKD, rg);
+        float dk = dot_rows(S, k);
+        float ex = e[LK_HEADS * LKD + LV_HEADS * LVD + h], be = e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h];
+        float delta = (e[LK_HEADS * LKD + h * LVD + col] - ex * dk) * be;
+#pragma unroll
+        for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
+    }
+    pdl_wait();
+
+    for (int c0 = 0; c0 < len; c0 += TCH) {
+        const int m = min(TCH, len - c0);
+        // ---- conv + SiLU of the round's tokens
+        for (int x = tid; x < m * FCH; x += FNT) {
+            int tk = x / FCH, ch = x - tk * FCH, gc = gchan(ch), i = c0 + tk;
+            float4 w = ld4(cw + gc * CONV_K);
+            const float wt[4] = {w.x, w.y, w.z, w.w};
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < CONV_K; j++) {
+                int si = i - (CONV_K - 1) + j, qp = p0 + si;
+                float xin = 0.f;
+                if (qp >= 0) {
+                    if (si >= 0) {
+                        for (int s = 0; s < splits; s++) xin += p[((size_t)s * n + t0 + si) * DELTA_IN + gc];
+                    } else {
+                        xin = sm0[SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV + gc];
+                    }
+                }
+                acc += wt[j] * xin;
+            }
+            R.c[tk][ch] = silu(acc);
+        }
+        if (tid < 2 * m) {  // the gates of head h
+            int tk = tid >> 1, which = tid & 1, t = t0 + c0 + tk;
+            float v = 0.f;
+            for (int s = 0; s < ba_splits; s++) v += ba[((size_t)s * n + t) * (2 * LV_HEADS) + (which ? h : LV_HEADS + h)];
+            if (which) {
+                R.b[tk] = 1.f / (1.f + expf(-v));
+            } else {
+                float a = v + dt_bias[h];
+                float sp = a > 20.f ? a : log1pf(expf(a));
+                R.e[tk] = expf(-expf(a_log[h]) * sp);
+            }
+        }
+        __syncthreads();
+        // ---- L2 norm of q and k (a warp per (token, q | k), 4 channels per lane), q also / sqrt(128)
+        for (int task = warp; task < 2 * m; task += FNT / 32) {
+            int tk = task >> 1, which = task & 1;
+            float4* v4 = (float4*)&R.c[tk][which * LKD + lane * 4];
+            float4 v = *v4;
+            float sc = rsqrtf(warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w) + 1e-6f);
+            if (!which) sc *= rsqrtf((float)LKD);
+            *v4 = make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc);
+        }
+        __syncthreads();
+        for (int tk = warp; tk < m; tk += FNT / 32) {  // k . q
+            float4 a = ld4(&R.c[tk][lane * 4]), b = ld4(&R.c[tk][LKD + lane * 4]);
+            float x = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
+            if (lane == 0) R.kq[tk] = x;
+        }
+        // ---- the delta rule inputs from the new checkpoint on, for a later restart
+        for (int tk = max(0, pl.ck - (p0 + c0)); tk < m; tk++) {
+            float* e = entry(pl.cbuf, p0 + c0 + tk);
+            if (h % (LV_HEADS / LK_HEADS) == 0 && tid < LKD) e[kh * LKD + tid] = R.c[tk][LKD + tid];
+            if (tid >= LKD && tid < LKD + LVD) e[LK_HEADS * LKD + h * LVD + tid - LKD] = R.c[tk][2 * LKD + tid - LKD];
+            if (tid == 2 * LKD) {
+                e[LK_HEADS * LKD + LV_HEADS * LVD + h] = R.e[tk];
+                e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h] = R.b[tk];
+            }
+        }
+        __syncthreads();
+        // ---- the recurrence
+        for (int tk = 0; tk < m; tk++) {
+            if (pl.wck && p0 + c0 + tk == pl.ck) st_rows(sbuf(pl.cbuf), S, rg);
+            float k[RPT], q[RPT];
+            ld_rows(k, &R.c[tk][LKD], rg);
+            ld_rows(q, &R.c[tk][0], rg);
+            float dk = dot_rows(S, k), dq = dot_rows(S, q);
+            float ex = R.e[tk], delta = (R.c[tk][2 * LKD + col] - ex * dk) * R.b[tk];
+            if (rg == 0) R.o[tk][col] = ex * dq + delta * R.kq[tk];
+#pragma unroll
+            for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
+        }
+        __syncthreads();
+        // ---- gated RMSNorm over the head's 128 value columns (a warp per token), then y = w o r silu(z)
+        for (int tk = warp; tk < m; tk += FNT / 32) {
+            float4 v = ld4(&R.o[tk][lane * 4]);
+            float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+            if (lane == 0) R.rn[tk] = rsqrtf(ss / LVD + EPS);
+        }
+        __syncthreads();
+        for (int x = tid; x < m * LVD; x += FNT) {
+            int tk = x / LVD, c = x - tk * LVD, t = t0 + c0 + tk;
+            float z = 0.f;
+            for (int s = 0; s < splits; s++) z += p[((size_t)s * n + t) * DELTA_IN + LQKV + h * LVD + c];
+            float o = R.o[tk][c];
+            if (out) out[(size_t)t * MIX + h * LVD + c] = o;
+            y[(size_t)t * MIX + h * LVD + c] = __float2half_rn(nw[c] * (o * R.rn[tk]) * silu(z));
+        }
+        __syncthreads();
+    }
+    (void)nwc;
+    st_rows(sbuf(pl.ebuf), S, rg);
+    // ---- conv ring: the conv inputs of the segment's last CR tokens, this block's share of the channels
+    const int CH = (LQKV + LV_HEADS - 1) / LV_HEADS;
+    const int cb = h * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
+    for (int i = tid; i < mm * ch; i += FNT) {
+        int tk = len - mm + i / ch, c = cb + i % ch;
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + tk) * DELTA_IN + c];
+        sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
+    }
+    // ---- the last block of the launch records the segments' steps in the slot metadata
+    __syncthreads();
+    __shared__ int last;
+    if (tid == 0) {
+        __threadfence();
+        int tkt = atomicAdd(ticket, 1);
+        last = tkt == (int)(gridDim.x * gridDim.y) - 1;
+    }
+    __syncthreads();
+    if (last) {
+        for (int s = tid; s < segs; s += FNT) {
+            int sl = seg_slot[s], q0 = seg_pos0[s], ln = seg_len[s];
+            Plan q = make_plan(meta, sl, q0, ln);
+            meta[sl * META] = q0 + ln;
+            meta[sl * META + 1] = q.ck;
+            meta[sl * META + 2] = q.ebuf;
+        }
+        if (tid == 0) *ticket = 0;
+    }
+}
+
+}  // namespace qb
+
+// conv + rule + norm in one launch (same arguments as the three together); `out` (the raw output before the gated
+// norm, f32 [n][MIX]) may be NULL
+extern "C" int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* ba,
+                              int ba_splits, const float* cw, const float* a_log, const float* dt_bias,
+                              const float* nw, float* mem, long long sst, int* meta, float* out, void* y,
+                              const int* seg_start, const int* seg_len, const int* seg_slot, const int* seg_pos0,
+                              int segs) {
+    if (!ctx || !p || !ba || !cw || !a_log || !dt_bias || !nw || !mem || !meta || !y || !seg_start || !seg_len ||
+        !seg_slot || !seg_pos0 || n <= 0 || segs <= 0 || splits < 1 || ba_splits < 1)
+        return QB_ERR_ARG;
+    // the launch's ticket: the last int of the context's ticket array (the products use the first n / 64)
+    int* ticket = ctx->counters + ctx->ncounters - 1;
+    return qb::launch(ctx, qb::delta_fused_kernel, dim3(qb::LV_HEADS, segs), dim3(qb::FNT), 0, (cudaStream_t)stream, p,
+                      splits, n, ba, ba_splits, cw, a_log, dt_bias, nw, mem, sst, meta, out, (__half*)y, seg_start,
+                      seg_len, seg_slot, seg_pos0, segs, ticket);
+}

@@ -6,6 +6,7 @@ namespace qb {
 
 struct GemvPlan {
     int cg, kg, nstages, ctas;
+    int cluster_s;  // > 0: clustered split K with this many ranks per column block
 };
 
 static int smem_of(int cg, int kg, int nt, int nstages) {
@@ -32,22 +33,68 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
     static int opted = 0;  // per instantiation
     if (opted < smem) {
         QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         opted = smem;
     }
-    int grid, maxc;
-    grid_of(ctx, p, a.N, a.K, &grid, &maxc);
-    a.maxc = maxc;
-    if ((size_t)(a.N / 64) * maxc * NT * 4 * 32 * 16 > ctx->scratch_bytes) return QB_ERR_ARG;
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(grid);
+    cudaLaunchAttribute at[2];
+    int nat = 0;
+    // Clusters are placed inside one GPC each, so not every rank count packs the GPU in one wave: ask the driver how
+    // many clusters of a size can be resident (cached per kernel and size) and take the most ranks whose column
+    // blocks all fit, then as few as give the same longest share of k stages.
+    int cluster_s = 0;
+    if (p.cluster_s > 0) {
+        static int fits[9] = {0};  // per instantiation: resident clusters of size s (0: not asked yet)
+        const int ncb = a.N / C::TN, kst = a.K / C::TK;
+        int s = p.cluster_s;
+        for (; s > 1; s--) {
+            if (!fits[s]) {
+                cudaLaunchConfig_t q = {};
+                q.gridDim = dim3(s, ncb);
+                q.blockDim = dim3(C::THREADS);
+                q.dynamicSmemBytes = smem;
+                cudaLaunchAttribute ca[1];
+                ca[0].id = cudaLaunchAttributeClusterDimension;
+                ca[0].val.clusterDim.x = s; ca[0].val.clusterDim.y = 1; ca[0].val.clusterDim.z = 1;
+                q.attrs = ca; q.numAttrs = 1;
+                int nc = 0;
+                if (cudaOccupancyMaxActiveClusters(&nc, kern, &q) != cudaSuccess) nc = -1;
+                fits[s] = nc > 0 ? nc : -1;
+            }
+            if (fits[s] >= ncb) break;
+        }
+        if (s > kst) s = kst;
+        const int longest = (kst + s - 1) / s;
+        while (s > 1 && (kst + s - 2) / (s - 1) == longest) s--;
+        cluster_s = s;
+    }
+    a.cluster_s = cluster_s;
+    if (cluster_s > 0) {
+
+        a.maxc = 1;
+        lc.gridDim = dim3(cluster_s, a.N / C::TN);
+        at[nat].id = cudaLaunchAttributeClusterDimension;
+        at[nat].val.clusterDim.x = cluster_s;
+        at[nat].val.clusterDim.y = 1;
+        at[nat].val.clusterDim.z = 1;
+        nat++;
+    } else {
+        int grid, maxc;
+        grid_of(ctx, p, a.N, a.K, &grid, &maxc);
+        a.maxc = maxc;
+        if ((size_t)(a.N / 64) * maxc * NT * 4 * 32 * 16 > ctx->scratch_bytes) return QB_ERR_ARG;
+        lc.gridDim = dim3(grid);
+    }
     lc.blockDim = dim3(C::THREADS);
     lc.dynamicSmemBytes = smem;
     lc.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    if (ctx->pdl) {
+        at[nat].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[nat].val.programmaticStreamSerializationAllowed = 1;
+        nat++;
+    }
     lc.attrs = at;
-    lc.numAttrs = ctx->pdl ? 1 : 0;
+    lc.numAttrs = nat;
     QB_CUDA(cudaLaunchKernelEx(&lc, kern, a));
     return QB_OK;
 }
@@ -76,7 +123,17 @@ static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt, int cg, int kg, in
     const int budget = (228 * 1024) / p.ctas - 1024;
     p.nstages = 2;
     while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, nt, p.nstages + 1) <= budget) p.nstages++;
-    (void)ctx;
+    // Clustered split K when the column blocks x ranks fit one wave of blocks: the most ranks (at most 8, the
+    // portable cluster size) that fit, then as few as give the same longest share. The in-block reduction buffer
+    // doubles as the rank's parking space, so the tile must have kg > 1.
+    p.cluster_s = 0;
+    const int slots = ctx->sms * p.ctas, ncb = n / (p.cg * 64), kst = k / (p.kg * 128);
+    if (!ctx->no_cluster && p.kg > 1 && ncb <= slots) {
+        int s = slots / ncb;  // an upper bound; the launch asks the driver what really fits
+        if (s > 8) s = 8;
+        (void)kst;
+        p.cluster_s = s;
+    }
     return p;
 }
 
@@ -84,7 +141,17 @@ static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt, int cg, int kg, in
 
 using namespace qb;
 
+// Measurement only: the next products record per-block timestamps (4 x 1024 int64 each) into `buf` (device memory);
+// null switches it off.
+extern "C" int qb_marlin_trace(qb_ctx* ctx, long long* buf) {
+    ctx->trace = buf;
+    return QB_OK;
+}
+
 extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas) {
+    // ctas < 0: as -ctas, and stream-K only (no clustered split K)
+    ctx->no_cluster = ctas < 0;
+    if (ctas < 0) ctas = -ctas;
     ctx->tune_cg = cg; ctx->tune_kg = kg; ctx->tune_nstages = nstages; ctx->tune_ctas = ctas;
     return QB_OK;
 }
@@ -101,6 +168,8 @@ static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B,
     a.X = (const __half*)X; a.xrows = xrows; a.B = (const uint32_t*)B; a.S = (const __half*)S; a.Y = Y;
     a.m = m; a.N = n; a.K = k; a.row0 = row0;
     a.nstages = p.nstages; a.maxc = 1;
+    a.trace = ctx->trace;
+    if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
 #define QB_GO(NT)                                                              \
     switch (epi) {                                                             \

@@ -59,7 +59,7 @@ struct qb_model {
     // host-side shape of the uploaded step
     int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0;
     std::map<GraphKey, cudaGraphExec_t> graphs;
-    bool use_graphs = true;
+    bool use_graphs = true, fused = true;
     long long launches = 0;  // kernels launched (or replayed) since creation
     int step_kernels = 0;    // kernels of the last step
 };
@@ -110,14 +110,22 @@ int launch_step(qb_model* m, cudaStream_t st) {
             QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
                                   nullptr, nullptr, 0)); k++;
             const int ba_tiles = 2 * LV_HEADS / 16;
-            const int kper = H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
+            // the reference splits this small product 40 ways (split_for); 5 splits of 1024 columns leave its
+            // consumers 8x fewer partial sums to add
+            const int kper = m->fused ? 1024 : H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
             QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, kper, m->ba, 2 * LV_HEADS)); k++;
-            QB_TRY(qb_delta_conv(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.mem, L.sst,
-                                 m->cv, m->tok_slot, m->tok_pos)); k++;
-            QB_TRY(qb_delta_rule(c, s, m->part, 1, n, m->cv, L.mem, L.sst, L.meta, m->o, m->seg_start, m->seg_len,
-                                 m->seg_slot, m->seg_pos0, m->segs)); k++;
-            QB_TRY(qb_delta_norm(c, s, m->part, 1, n, L.norm_w, m->o, m->mix, L.meta, m->seg_len, m->seg_slot,
-                                 m->seg_pos0, m->segs)); k++;
+            if (m->fused) {
+                QB_TRY(qb_delta_mixer(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.norm_w,
+                                      L.mem, L.sst, L.meta, nullptr, m->mix, m->seg_start, m->seg_len, m->seg_slot,
+                                      m->seg_pos0, m->segs)); k++;
+            } else {
+                QB_TRY(qb_delta_conv(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.mem, L.sst,
+                                     m->cv, m->tok_slot, m->tok_pos)); k++;
+                QB_TRY(qb_delta_rule(c, s, m->part, 1, n, m->cv, L.mem, L.sst, L.meta, m->o, m->seg_start, m->seg_len,
+                                     m->seg_slot, m->seg_pos0, m->segs)); k++;
+                QB_TRY(qb_delta_norm(c, s, m->part, 1, n, L.norm_w, m->o, m->mix, L.meta, m->seg_len, m->seg_slot,
+                                     m->seg_pos0, m->segs)); k++;
+            }
         } else {
             QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, ATTN_IN, H, 0, QB_EPI_PLAIN,
                                   nullptr, nullptr, 0)); k++;
@@ -223,6 +231,16 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
 int qb_model_use_graphs(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     m->use_graphs = on != 0;
+    return QB_OK;
+}
+
+int qb_model_use_fused(qb_model* m, int on) {
+    if (!m) return QB_ERR_ARG;
+    if (m->fused != (on != 0)) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->fused = on != 0;
     return QB_OK;
 }
 

@@ -13,6 +13,10 @@
 //    128-bit shared load through four lop3 and four hsub2 straight into the tensor core, no shuffles, no
 //    re-layout. The group scale is applied in f32 to the group's partial sum (exact, and 8x fewer multiplies
 //    than scaling every weight);
+//  * two ways to deal the work. Matrices whose column blocks x k splits fit one wave of blocks run CLUSTERED: one
+//    thread-block cluster per column block, rank r takes the r-th equal share of its k stages, and the ranks' f32
+//    partials meet in rank 0 through distributed shared memory (no global traffic, no fences), added in rank order.
+//    Larger matrices run STREAM-K:
 //  * the stages of the whole matrix, numbered column block by column block, are cut into one equal contiguous
 //    range per block of a persistent grid (stream-K), so every SM streams the same number of bytes whatever the
 //    shape and the copy pipeline never drains between column blocks. The KG warps of a column group add up in
@@ -37,13 +41,22 @@ struct GemvArgs {
     void* Y;              // plain/argmax: f32 [.][N]; silu: f16 [.][N/2]; rows row0 .. row0 + m - 1
     int m, N, K, row0;
     int nstages;          // ring depth
+    int cluster_s;        // > 0: clustered split K, cluster_s ranks per column block (grid (cluster_s, N / TN))
     int maxc;             // most blocks that share a column block (scratch stride)
     float4* scratch;      // partials of shared column blocks: [N/64][maxc][NT][4][32] float4
     int* counters;        // [N/64] tickets, zero between launches
     unsigned long long* keys;
     int n_valid;
     int* err;             // set non-zero when a bounded wait ran out
+    long long* trace;     // measurement only (may be null): per block {start, first stage landed, last stage
+                          // consumed, end} in ns of the global timer
 };
+
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 constexpr int GEMV_MAX_STAGES = 8;
 
@@ -79,6 +92,57 @@ __device__ __forceinline__ void dequant_word(uint32_t q, uint32_t* a) {
     a[0] = *(uint32_t*)&r0; a[1] = *(uint32_t*)&r1; a[2] = *(uint32_t*)&r2; a[3] = *(uint32_t*)&r3;
 }
 
+// The epilogue of 64 finished outputs x 8 NT tokens held in the accumulator layout of the mma (acc[j][b][2h+e]:
+// output col + 16 b + g + 8 h, token 8 j + 2 t + e).
+template <int NT, int EPI>
+__device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT][4][4], const int col, const int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            int tok = 8 * j + 2 * t + e;
+            if (tok >= a.m) continue;
+            if (EPI == EPI_SILU) {
+                __half* y = (__half*)a.Y + (size_t)(a.row0 + tok) * (a.N / 2) + col / 2 + g;
+#pragma unroll
+                for (int b = 0; b < 4; b++) y[8 * b] = __float2half_rn(silu(acc[j][b][e]) * acc[j][b][2 + e]);
+            } else {
+                float* y = (float*)a.Y + (size_t)(a.row0 + tok) * a.N + col + g;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    y[16 * b] = acc[j][b][e];
+                    y[16 * b + 8] = acc[j][b][2 + e];
+                }
+            }
+        }
+    if (EPI == EPI_ARGMAX) {
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                unsigned long long k = 0;
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        int o = col + 16 * b + g + 8 * h;
+                        if (o < a.n_valid) {
+                            unsigned long long kk = argmax_key(acc[j][b][2 * h + e], o);
+                            k = kk > k ? kk : k;
+                        }
+                    }
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    unsigned long long kk = __shfl_xor_sync(0xffffffffu, k, o);
+                    k = kk > k ? kk : k;
+                }
+                int tok = 8 * j + 2 * t + e;
+                if (g == 0 && tok < a.m && k) atomicMax(a.keys + a.row0 + tok, k);
+            }
+    }
+}
+
 template <int CG, int KG, int NT, int EPI>
 __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kernel(const GemvArgs a) {
     using C = GemvCfg<CG, KG, NT>;
@@ -92,11 +156,21 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     const int nstages = a.nstages;
     // stream-K: stage x of the matrix is (column block x / kst, k stage x % kst); block i owns [b(i), b(i+1))
     const int kst = a.K / C::TK;
+    const bool clustered = a.cluster_s > 0;
     const long long total = (long long)(a.N / C::TN) * kst, G = gridDim.x;
-    const int beg = (int)((long long)blockIdx.x * total / G), end = (int)((long long)(blockIdx.x + 1) * total / G);
+    int beg, end;
+    if (clustered) {  // rank blockIdx.x of the cluster of column block blockIdx.y
+        beg = blockIdx.y * kst + (int)blockIdx.x * kst / a.cluster_s;
+        end = blockIdx.y * kst + ((int)blockIdx.x + 1) * kst / a.cluster_s;
+    } else {
+        beg = (int)((long long)blockIdx.x * total / G);
+        end = (int)((long long)(blockIdx.x + 1) * total / G);
+    }
     // the block that owns stage x: the largest i with b(i) <= x
     auto owner = [&](long long x) { return (int)(((x + 1) * G + total - 1) / total - 1); };
 
+    const int bid = blockIdx.y * gridDim.x + blockIdx.x;
+    if (a.trace && threadIdx.x == 0) a.trace[bid * 4] = global_ns();
     if (threadIdx.x == 0) {
         for (int i = 0; i < nstages; i++) {
             mbar_init(&full[i], 1);
@@ -189,6 +263,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             } else {
                 for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], par); i++) {}
             }
+            if (a.trace && threadIdx.x == 0 && x == beg) a.trace[bid * 4 + 1] = global_ns();
             const uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
             const uint4* wp = (const uint4*)(base + (size_t)(kg * 8 * CG + cg) * 512) + lane;
             // ldmatrix row address of this lane: token row lane % 8 (+ 8 j), columns 8 (lane / 8) of each pair of k16 steps
@@ -232,6 +307,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             if (lane == 0) mbar_arrive(&empty[slot]);
             if (++slot == nstages) { slot = 0; par ^= 1; }
         }
+        if (a.trace && threadIdx.x == 0 && x + 1 == end) a.trace[bid * 4 + 2] = global_ns();
         // the piece (this block's stages of column block cb) goes on
         const int pcb = cb;
         if (++st == kst) { st = 0; cb++; }
@@ -264,6 +340,37 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             named_bar_sync(2, C::NW * 32);
         }
 
+        if (clustered) {
+            // ---- the ranks of the cluster meet in rank 0. Every block's kg = 0 warps park their sums in their own
+            // shared memory (the in-block reduction buffer, free by now), the cluster synchronises, rank 0 reads the
+            // others' through distributed shared memory and adds them in rank order, and a second barrier keeps the
+            // others' shared memory alive until it has.
+            if (kg != 0) return;  // exited threads do not count in the cluster barrier
+            float4* mine = red + (size_t)cg * NT * 4 * 32;
+            if (blockIdx.x != 0) {
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++)
+                        mine[(j * 4 + b) * 32 + lane] = make_float4(acc[j][b][0], acc[j][b][1], acc[j][b][2], acc[j][b][3]);
+            }
+            cluster_sync();
+            if (blockIdx.x == 0) {
+                for (int r = 1; r < a.cluster_s; r++) {
+                    const uint32_t rem = cluster_map(mine, r);
+#pragma unroll
+                    for (int j = 0; j < NT; j++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            float4 v = cluster_ld4(rem + ((j * 4 + b) * 32 + lane) * 16);
+                            acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
+                        }
+                }
+                gemv_epilogue<NT, EPI>(a, acc, (pcb * CG + cg) * 64, lane);
+            }
+            cluster_sync();
+            return;
+        }
         if (kg == 0) {
             const int colgrp = pcb * CG + cg;  // 64 outputs
             bool finish = true;
@@ -304,54 +411,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     if (lane == 0) a.counters[colgrp] = 0;  // left zero for the next product
                 }
             }
-            if (finish) {
-                const int col = colgrp * 64;
-#pragma unroll
-                for (int j = 0; j < NT; j++)
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        int tok = 8 * j + 2 * t + e;
-                        if (tok >= a.m) continue;
-                        if (EPI == EPI_SILU) {
-                            __half* y = (__half*)a.Y + (size_t)(a.row0 + tok) * (a.N / 2) + col / 2 + g;
-#pragma unroll
-                            for (int b = 0; b < 4; b++)
-                                y[8 * b] = __float2half_rn(silu(acc[j][b][e]) * acc[j][b][2 + e]);
-                        } else {
-                            float* y = (float*)a.Y + (size_t)(a.row0 + tok) * a.N + col + g;
-#pragma unroll
-                            for (int b = 0; b < 4; b++) {
-                                y[16 * b] = acc[j][b][e];
-                                y[16 * b + 8] = acc[j][b][2 + e];
-                            }
-                        }
-                    }
-                if (EPI == EPI_ARGMAX) {
-#pragma unroll
-                    for (int j = 0; j < NT; j++)
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            unsigned long long k = 0;
-#pragma unroll
-                            for (int b = 0; b < 4; b++)
-#pragma unroll
-                                for (int h = 0; h < 2; h++) {
-                                    int o = col + 16 * b + g + 8 * h;
-                                    if (o < a.n_valid) {
-                                        unsigned long long kk = argmax_key(acc[j][b][2 * h + e], o);
-                                        k = kk > k ? kk : k;
-                                    }
-                                }
-#pragma unroll
-                            for (int o = 4; o < 32; o <<= 1) {
-                                unsigned long long kk = __shfl_xor_sync(0xffffffffu, k, o);
-                                k = kk > k ? kk : k;
-                            }
-                            int tok = 8 * j + 2 * t + e;
-                            if (g == 0 && tok < a.m && k) atomicMax(a.keys + a.row0 + tok, k);
-                        }
-                }
-            }
+            if (finish) gemv_epilogue<NT, EPI>(a, acc, colgrp * 64, lane);
         }
 #pragma unroll
         for (int j = 0; j < NT; j++)
@@ -360,6 +420,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
     }
+    if (a.trace && threadIdx.x == 0) a.trace[bid * 4 + 3] = global_ns();
 }
 
 }  // namespace qb

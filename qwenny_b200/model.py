@@ -126,6 +126,9 @@ class Model:
         check(lib().qb_model_argmax(self.h, s, res, n_out), "qb_model_argmax")
         return list(res)[:n_out]
 
+    def use_fused(self, on: bool):
+        check(lib().qb_model_use_fused(self.h, int(on)), "qb_model_use_fused")
+
     def use_graphs(self, on: bool):
         check(lib().qb_model_use_graphs(self.h, int(on)), "qb_model_use_graphs")
 

@@ -132,3 +132,10 @@ class Context:
     def delta_norm(self, part, splits, n, norm_w, out, y, meta, dev, segs):
         check(lib().qb_delta_norm(self.h, _stream(), _p(part), splits, n, _p(norm_w), _p(out), _p(y), _p(meta),
                                   _p(dev["seg_len"]), _p(dev["seg_slot"]), _p(dev["seg_pos0"]), segs), "qb_delta_norm")
+
+    def delta_mixer(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, norm_w, mem, sst, meta, out, y, dev,
+                    segs):
+        check(lib().qb_delta_mixer(self.h, _stream(), _p(part), splits, n, _p(ba), ba_splits, _p(conv_w), _p(a_log),
+                                   _p(dt_bias), _p(norm_w), _p(mem), sst, _p(meta), _p(out), _p(y),
+                                   _p(dev["seg_start"]), _p(dev["seg_len"]), _p(dev["seg_slot"]), _p(dev["seg_pos0"]),
+                                   segs), "qb_delta_mixer")

@@ -1,0 +1,39 @@
+"""The C ABI without a GPU: the library loads, exports every function include/qwenny_b200.h declares, the ctypes table
+covers them all, and argument checks answer before anything touches a device."""
+import os
+import re
+
+from qwenny_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared():
+    src = open(os.path.join(ROOT, "include", "qwenny_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(qb_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared()
+    assert len(names) >= 40
+    l = _lib.lib()
+    for n in names:
+        assert hasattr(l, n), f"{n} is declared but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    for n in _lib.SIGNATURES:
+        assert n in names, f"{n} is bound but not declared in the header"
+
+
+def test_version_and_host_only_calls():
+    l = _lib.lib()
+    assert b"sm_100a" in l.qb_version()
+    assert l.qb_split_for(6, 5120, 16, 1024) == 40
+    assert l.qb_attn_dec_splits(32005) == 63 and l.qb_attn_dec_splits(1) == 1 and l.qb_attn_dec_splits(4097) == 33
+
+
+def test_argument_errors_need_no_device():
+    l = _lib.lib()
+    assert l.qb_row_order(17, 1, None) == 1000          # QB_ERR_ARG
+    assert l.qb_marlin_gemm(None, None, None, None, None, None, 5, 256, 128, 0, 0, None, None, 0) == 1000
+    assert l.qb_model_step(None, None, None, 0, None, 0) == 1000

@@ -43,8 +43,10 @@ def test_plain_vs_oracle(ctx, m, rows, cols):
     assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("cfg", [(2, 4, 1), (2, 4, 2), (4, 2, 1), (4, 2, 3), (8, 1, 2), (8, 1, 1), (1, 8, 1), (4, 1, 2)])
+@pytest.mark.parametrize("cfg", [(2, 4, 1), (2, 4, 2), (4, 2, 1), (4, 2, 3), (8, 1, 2), (8, 1, 1), (1, 8, 1), (4, 1, 2),
+                                 (2, 4, -2), (4, 2, -2), (1, 8, -1)])
 def test_every_tile_shape(ctx, cfg):
+    """Every consumer-warp arrangement, clustered split K (ctas > 0, where the shape allows) and stream-K (ctas < 0)."""
     cg, kg, ctas = cfg
     x, wdq, xd, wd, sd = make(1024, 2048, False, 3, 5)
     ctx.tune(cg=cg, kg=kg, ctas=ctas)
