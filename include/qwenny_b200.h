@@ -120,7 +120,8 @@ int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
                   void* y, int* meta, const int* seg_len, const int* seg_slot, const int* seg_pos0, int segs);
 
 /* The three DeltaNet kernels of a step in one launch (same arguments; `out`, the raw output before the gated norm,
- * may be NULL). Gives the same bits as qb_delta_conv + qb_delta_rule + qb_delta_norm. The reference has no fused
+ * may be NULL). Same arithmetic as qb_delta_conv + qb_delta_rule + qb_delta_norm (values agree to an f32 ulp); steps
+ * of up to 29 tokens (QB_ERR_UNSUPPORTED beyond: use the three calls). The reference has no fused
  * counterpart; DeltaNet::run (src/cuda/qwen/deltanet.rs:109-160) would call this once instead of its three launches. */
 int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* ba, int ba_splits,
                    const float* cw, const float* a_log, const float* dt_bias, const float* nw, float* mem,

@@ -4,7 +4,7 @@
 //               (replaces attn_prep + kv_store, kernels/qwen.cu:156-202, kernels/attn.cuh:50-64)
 //  attn_decode  split-K flash-decode: block (segment, kv head, key split) streams its run of keys and values with
 //               bulk async copies into a shared-memory ring (keys are [pos][256] and values [pos/16][256][16] bytes
-//               per head, both contiguous per run) while RT x 2 warps compute S = Q K^T and O += P V on tensor cores
+//               per head, both contiguous per run) while RT x 4 warps compute S = Q K^T and O += P V on tensor cores
 //               with a warp-level base-2 online softmax, straight from the int8 bytes (prmt to 1152 + q halves, the
 //               offset folded out through the row sums as the reference does, kernels/attn.cuh:38-40,198-234)
 //               (replaces attn_mq_tc<RT>, kernels/attn.cuh:77-261)
@@ -20,11 +20,11 @@ namespace qb {
 
 constexpr float KV_OFF = 1152.f;
 constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
-constexpr int SK = 32;         // keys per ring stage
+constexpr int KWARPS = 4;      // warps that share a row tile, one 16-key block of a stage each
+constexpr int SK = 16 * KWARPS;  // keys per ring stage
 constexpr int NSTG = 4;        // ring depth
-constexpr int KWARPS = 2;      // warps that share a row tile, one 16-key block of a stage each
 constexpr int STG_BYTES = SK * HD * 2 + SK * 4 * 2;  // keys, values, key scales, value scales
-constexpr int DSPLITS = 64;    // most key splits of a decode token
+constexpr int DSPLITS = 32;    // most key splits of a decode token: 4 kv heads x 32 splits fill the SMs once
 
 __host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
 __host__ __device__ inline size_t scale_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap; }
@@ -41,8 +41,8 @@ __device__ __forceinline__ size_t vslot(int pos, int d) {
 }
 
 // Keys per split of a token with `keys` keys: a multiple of 64, at most DSPLITS splits; changes only where keys
-// crosses a multiple of 64 * DSPLITS = 4096 (the host cuts short segments at multiples of 2048 keys, so the tokens
-// of a segment always agree).
+// crosses a multiple of 64 * DSPLITS = 2048 (where the host cuts short segments, so the tokens of a segment always
+// agree).
 __host__ __device__ inline int dec_chunk(int keys) { return max(64, ((keys + DSPLITS - 1) / DSPLITS + 63) / 64 * 64); }
 __host__ __device__ inline int dec_splits(int keys) { int c = dec_chunk(keys); return (keys + c - 1) / c; }
 
@@ -127,17 +127,17 @@ __device__ __forceinline__ uint32_t kv_half2(uint32_t w, uint32_t sel) { return 
 
 template <int RT>
 struct DecCfg {
-    static constexpr int CW = RT * KWARPS;            // compute warps
-    static constexpr int THREADS = (CW + 1) * 32;     // + the copy warp
+    static constexpr int CW = RT * KWARPS;            // warps (warp 0 also issues the copies)
+    static constexpr int THREADS = CW * 32;
     static constexpr int Q_BYTES = RT * 16 * SROW * 2;
     static constexpr int BAR_BYTES = 128;
     static constexpr int SMEM = BAR_BYTES + Q_BYTES + NSTG * STG_BYTES;
-    static constexpr int MERGE_FLOATS = 32 * (HD / 8 * 4 + 6);  // per row tile: o, m, l, ps of 32 lanes
-    static_assert(RT * MERGE_FLOATS * 4 <= NSTG * STG_BYTES, "the merge buffers reuse the ring");
+    static constexpr int MERGE_FLOATS = 32 * (HD / 8 * 4 + 6);  // one warp's o, m, l, ps
+    static_assert(RT * (KWARPS / 2) * MERGE_FLOATS * 4 <= NSTG * STG_BYTES, "the merge buffers reuse the ring");
 };
 
 template <int RT>
-__global__ void __launch_bounds__(DecCfg<RT>::THREADS)
+__global__ void __launch_bounds__(DecCfg<RT>::THREADS, 1)
 attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs,
                    const int* dseg, const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z,
                    float* part_ml, float* part_acc, float* out, int* err) {
@@ -165,32 +165,38 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     const int kbeg = s * chunk, ke = min(keys, kbeg + chunk), nstg = (ke - kbeg + SK - 1) / SK;
     const int slot = tok_slot[tlast];
 
-    if (warp == C::CW) {
-        // ------------------------------------------------------------ copy warp: one lane per region of a stage
-        const uint64_t pol = policy_evict_first();
-        const uint8_t* kh = kc + cache_head(slot, g, cap);
-        const uint8_t* vh = vc + cache_head(slot, g, cap);
-        const float* ksh = ks + scale_head(slot, g, cap);
-        const float* vsh = vs + scale_head(slot, g, cap);
-        int sl = 0;
-        uint32_t par = 1;  // a fresh barrier passes a wait on the phase before its first
-        bool ok = true;
-        for (int i = 0; i < nstg && ok; i++) {
-            if (lane == 0) ok = mbar_wait(&empty[sl], par);
+    // ---- the copies: warp 0 issues stage j two stages ahead of its own consumption (three stages in flight, four
+    // slots: the slot it refills was released two iterations ago by everyone who keeps pace), one lane per region
+    const uint64_t pol = policy_evict_first();
+    const uint8_t* kh = kc + cache_head(slot, g, cap);
+    const uint8_t* vh = vc + cache_head(slot, g, cap);
+    const float* ksh = ks + scale_head(slot, g, cap);
+    const float* vsh = vs + scale_head(slot, g, cap);
+    bool copy_ok = true;
+    auto issue = [&](int j) {
+        const int sl = j % NSTG;
+        if (j >= NSTG) {
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&empty[sl], ((j / NSTG) - 1) & 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            uint8_t* base = ring + sl * STG_BYTES;
-            const int kb = kbeg + i * SK;
-            if (lane == 0) mbar_expect_tx(&full[sl], STG_BYTES);
-            __syncwarp();
-            if (lane == 0) bulk_g2s(base, kh + (size_t)kb * HD, SK * HD, &full[sl], pol);
-            if (lane == 1) bulk_g2s(base + SK * HD, vh + (size_t)kb * HD, SK * HD, &full[sl], pol);
-            if (lane == 2) bulk_g2s(base + 2 * SK * HD, ksh + kb, SK * 4, &full[sl], pol);
-            if (lane == 3) bulk_g2s(base + 2 * SK * HD + SK * 4, vsh + kb, SK * 4, &full[sl], pol);
-            if (++sl == NSTG) { sl = 0; par ^= 1; }
+            if (!ok) {
+                if (lane == 0 && copy_ok) atomicExch(err, 3);
+                copy_ok = false;
+                return;
+            }
         }
-        if (!ok && lane == 0) atomicExch(err, 3);
-        return;
+        uint8_t* base = ring + sl * STG_BYTES;
+        const int kb = kbeg + j * SK;
+        if (lane == 0) mbar_expect_tx(&full[sl], STG_BYTES);
+        __syncwarp();
+        if (lane == 0) bulk_g2s(base, kh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+        if (lane == 1) bulk_g2s(base + SK * HD, vh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+        if (lane == 2) bulk_g2s(base + 2 * SK * HD, ksh + kb, SK * 4, &full[sl], pol);
+        if (lane == 3) bulk_g2s(base + 2 * SK * HD + SK * 4, vsh + kb, SK * 4, &full[sl], pol);
+    };
+    if (warp == 0) {
+        issue(0);
+        if (nstg > 1) issue(1);
     }
 
     // ---------------------------------------------------------------- compute warps
@@ -231,6 +237,7 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     uint32_t par = 0;
     bool dead = false;
     for (int i = 0; i < nstg; i++) {
+        if (warp == 0 && i + 2 < nstg && copy_ok) issue(i + 2);
         if (!dead) {
             dead = !mbar_wait(&full[sl], par);
             if (dead && lane == 0) atomicExch(err, 4);
@@ -327,37 +334,42 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
         if (++sl == NSTG) { sl = 0; par ^= 1; }
     }
 
-    // ---- the two warps of a row tile merge (the ring is free: every stage was consumed)
+    // ---- the warps of a row tile merge pairwise in two rounds (1 -> 0 and 3 -> 2, then 2 -> 0) through the ring, which
+    // is free: every stage was consumed
     named_bar_sync(1, C::CW * 32);
-    float* mb = (float*)ring + (size_t)wt * C::MERGE_FLOATS;
-    if (kw == 1) {
+    for (int round = 1; round < KWARPS; round <<= 1) {
+        const bool sender = (kw & (2 * round - 1)) == round, receiver = (kw & (2 * round - 1)) == 0;
+        float* mb = (float*)ring + (size_t)(wt * (KWARPS / 2) + (kw >> 1) / round % (KWARPS / 2)) * C::MERGE_FLOATS;
+        if (sender) {
 #pragma unroll
-        for (int j = 0; j < NTD; j++)
-            *(float4*)(mb + (j * 32 + lane) * 4) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
-        float* t = mb + NTD * 32 * 4 + lane * 6;
-        t[0] = m[0]; t[1] = m[1]; t[2] = l[0]; t[3] = l[1]; t[4] = ps[0]; t[5] = ps[1];
-    }
-    named_bar_sync(1, C::CW * 32);
-    if (kw == 1) return;
-    {
-        const float* t = mb + NTD * 32 * 4 + lane * 6;
-        float c0[2], c1[2];
-#pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-            float m1 = t[h2], mn = fmaxf(m[h2], m1);
-            c0[h2] = mn == -INFINITY ? 1.f : exp2f(m[h2] - mn);
-            c1[h2] = mn == -INFINITY ? 1.f : exp2f(m1 - mn);
-            m[h2] = mn;
-            l[h2] = l[h2] * c0[h2] + t[2 + h2] * c1[h2];
-            ps[h2] = ps[h2] * c0[h2] + t[4 + h2] * c1[h2];
+            for (int j = 0; j < NTD; j++)
+                *(float4*)(mb + (j * 32 + lane) * 4) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            float* t = mb + NTD * 32 * 4 + lane * 6;
+            t[0] = m[0]; t[1] = m[1]; t[2] = l[0]; t[3] = l[1]; t[4] = ps[0]; t[5] = ps[1];
         }
+        named_bar_sync(1, C::CW * 32);
+        if (receiver) {
+            const float* t = mb + NTD * 32 * 4 + lane * 6;
+            float c0[2], c1[2];
 #pragma unroll
-        for (int j = 0; j < NTD; j++) {
-            float4 v = *(const float4*)(mb + (j * 32 + lane) * 4);
-            o[j][0] = o[j][0] * c0[0] + v.x * c1[0]; o[j][1] = o[j][1] * c0[0] + v.y * c1[0];
-            o[j][2] = o[j][2] * c0[1] + v.z * c1[1]; o[j][3] = o[j][3] * c0[1] + v.w * c1[1];
+            for (int h2 = 0; h2 < 2; h2++) {
+                float m1 = t[h2], mn = fmaxf(m[h2], m1);
+                c0[h2] = mn == -INFINITY ? 1.f : exp2f(m[h2] - mn);
+                c1[h2] = mn == -INFINITY ? 1.f : exp2f(m1 - mn);
+                m[h2] = mn;
+                l[h2] = l[h2] * c0[h2] + t[2 + h2] * c1[h2];
+                ps[h2] = ps[h2] * c0[h2] + t[4 + h2] * c1[h2];
+            }
+#pragma unroll
+            for (int j = 0; j < NTD; j++) {
+                float4 v = *(const float4*)(mb + (j * 32 + lane) * 4);
+                o[j][0] = o[j][0] * c0[0] + v.x * c1[0]; o[j][1] = o[j][1] * c0[0] + v.y * c1[0];
+                o[j][2] = o[j][2] * c0[1] + v.z * c1[1]; o[j][3] = o[j][3] * c0[1] + v.w * c1[1];
+            }
         }
+        named_bar_sync(1, C::CW * 32);
     }
+    if (kw != 0) return;
 #pragma unroll
     for (int h2 = 0; h2 < 2; h2++) {
         float L = l[h2], P = ps[h2];
@@ -389,10 +401,13 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
 }
 
 // Merge the key splits of one (decode token, head) in split order; out *= result (the gate is there); optionally also
-// the f16 copy of the product. HD threads, thread d owns dim d.
+// the f16 copy of the product. HD threads, thread d owns dim d; the splits' maxima and sums go through shared memory
+// once so that the accumulator loads of all splits are independent and in flight together.
 __global__ void __launch_bounds__(HD)
 attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, float* out,
                     __half* mix) {
+    __shared__ float se[DSPLITS];
+    __shared__ float sL;
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, h = blockIdx.y, t = dtok[i], d = threadIdx.x;
@@ -403,16 +418,23 @@ attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok
         res = *op;  // attn_decode finished it
     } else {
         const size_t base = ((size_t)i * NH + h) * z;
-        float M = -INFINITY;
-        for (int s = 0; s < ns; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
-        float L = 0.f, A = 0.f;
-        for (int s = 0; s < ns; s++) {
-            float ms = part_ml[(base + s) * 2];
+        if (d < 32) {  // DSPLITS <= 32: one split per lane
+            float ms = d < ns ? part_ml[(base + d) * 2] : -INFINITY;
+            float ls = d < ns ? part_ml[(base + d) * 2 + 1] : 0.f;
+            float M = warp_max(ms);
             float e = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            L += e * part_ml[(base + s) * 2 + 1];
-            A += e * part_acc[(base + s) * HD + d];
+            se[d] = e;
+            // the sum over splits in split order (not a tree: the same order whatever the lane count)
+            float L = 0.f;
+            for (int s = 0; s < ns; s++) L += __shfl_sync(0xffffffffu, e * ls, s);
+            if (d == 0) sL = L;
         }
-        res = *op * A * (1.f / L);
+        __syncthreads();
+        float A = 0.f;
+        const float* pa = part_acc + base * HD + d;
+#pragma unroll 8
+        for (int s = 0; s < ns; s++) A += se[s] * pa[(size_t)s * HD];
+        res = *op * A * (1.f / sL);
         *op = res;
     }
     if (mix) mix[(size_t)t * MIX + h * HD + d] = __float2half_rn(res);

@@ -315,8 +315,11 @@ constexpr int FNT = 512;
 constexpr int FCH = 3 * LKD;  // q, k, v channels of a block
 
 struct FusedRound {
-    float c[TCH][FCH];      // conv outputs: q [0,128), k [128,256), v [256,384)
-    float o[TCH][LVD];      // raw outputs of the round
+    float x[TCH + CONV_K - 1][FCH];  // conv inputs of the round's tokens and the 3 positions before them
+    float c[TCH][FCH];               // conv outputs: q [0,128), k [128,256), v [256,384)
+    float z[TCH][LVD];               // the gate input of the norm
+    float o[TCH][LVD];               // raw outputs of the round
+    float w[FCH][CONV_K];            // conv taps of the block's channels
     float e[TCH], b[TCH], kq[TCH], rn[TCH];
 };
 
@@ -325,7 +328,8 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
                    const float* a_log, const float* dt_bias, const float* nw, float* mem, long long sst, int* meta,
                    float* out, __half* y, const int* seg_start, const int* seg_len, const int* seg_slot,
                    const int* seg_pos0, int segs, int* ticket) {
-    __shared__ __align__(16) FusedRound R;
+    extern __shared__ __align__(16) uint8_t fsm[];
+    FusedRound& R = *(FusedRound*)fsm;
     pdl_launch_dependents();
     const int h = blockIdx.x, sg = blockIdx.y, kh = h / (LV_HEADS / LK_HEADS);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = tid % LPC, col = tid / LPC;
@@ -340,6 +344,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
                                                        : 2 * LK_HEADS * LKD + h * LVD + (ch - 2 * LKD);
     };
 
+    // ---- everything that does not depend on this step's earlier kernels: the state, the taps, the norm weight
     float S[RPT];
     if (pl.zero) {
 #pragma unroll
@@ -347,7 +352,8 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
     } else {
         ld_rows(S, sbuf(pl.in), rg);
     }
-    const float nwc = nw[col];
+    if (tid < FCH) *(float4*)R.w[tid] = ld4(cw + gchan(tid) * CONV_K);
+    const float nwv = nw[tid % LVD], alog = a_log[h], dtb = dt_bias[h];
     for (int i = 0; i < pl.r; i++) {
         const float* e = entry(pl.in, pl.from + i);
         float k[RPT];
@@ -360,28 +366,30 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
     }
     pdl_wait();
 
+    // the block's share of the conv ring: channels cb .. cb + ch of the segment's last CR tokens
+    const int CH = (LQKV + LV_HEADS - 1) / LV_HEADS;
+    const int cb = h * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
+
     for (int c0 = 0; c0 < len; c0 += TCH) {
         const int m = min(TCH, len - c0);
-        // ---- conv + SiLU of the round's tokens
-        for (int x = tid; x < m * FCH; x += FNT) {
-            int tk = x / FCH, ch = x - tk * FCH, gc = gchan(ch), i = c0 + tk;
-            float4 w = ld4(cw + gc * CONV_K);
-            const float wt[4] = {w.x, w.y, w.z, w.w};
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < CONV_K; j++) {
-                int si = i - (CONV_K - 1) + j, qp = p0 + si;
-                float xin = 0.f;
-                if (qp >= 0) {
-                    if (si >= 0) {
-                        for (int s = 0; s < splits; s++) xin += p[((size_t)s * n + t0 + si) * DELTA_IN + gc];
-                    } else {
-                        xin = sm0[SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV + gc];
-                    }
+        // ---- one round of independent loads: conv inputs (step rows or ring), z, gates
+        for (int x = tid; x < (m + CONV_K - 1) * FCH; x += FNT) {
+            int row = x / FCH, c = x - row * FCH, gc = gchan(c), si = c0 + row - (CONV_K - 1), qp = p0 + si;
+            float v = 0.f;
+            if (qp >= 0) {
+                if (si >= 0) {
+                    for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + si) * DELTA_IN + gc];
+                } else {
+                    v = sm0[SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV + gc];
                 }
-                acc += wt[j] * xin;
             }
-            R.c[tk][ch] = silu(acc);
+            R.x[row][c] = v;
+        }
+        for (int x = tid; x < m * LVD; x += FNT) {
+            int tk = x / LVD, c = x - tk * LVD;
+            float v = 0.f;
+            for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + c];
+            R.z[tk][c] = v;
         }
         if (tid < 2 * m) {  // the gates of head h
             int tk = tid >> 1, which = tid & 1, t = t0 + c0 + tk;
@@ -390,10 +398,19 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             if (which) {
                 R.b[tk] = 1.f / (1.f + expf(-v));
             } else {
-                float a = v + dt_bias[h];
+                float a = v + dtb;
                 float sp = a > 20.f ? a : log1pf(expf(a));
-                R.e[tk] = expf(-expf(a_log[h]) * sp);
+                R.e[tk] = expf(-expf(alog) * sp);
             }
+        }
+        __syncthreads();
+        // ---- conv + SiLU
+        for (int x = tid; x < m * FCH; x += FNT) {
+            int tk = x / FCH, c = x - tk * FCH;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < CONV_K; j++) acc += R.w[c][j] * R.x[tk + j][c];
+            R.c[tk][c] = silu(acc);
         }
         __syncthreads();
         // ---- L2 norm of q and k (a warp per (token, q | k), 4 channels per lane), q also / sqrt(128)
@@ -421,6 +438,14 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
                 e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h] = R.b[tk];
             }
         }
+        // ---- this round's rows of the conv ring (the block's channel share), from the in-projection rows
+        for (int i = tid; i < m * ch; i += FNT) {
+            int tk = c0 + i / ch, c = cb + i % ch;
+            if (tk < len - mm) continue;
+            float v = 0.f;
+            for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + tk) * DELTA_IN + c];
+            sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
+        }
         __syncthreads();
         // ---- the recurrence
         for (int tk = 0; tk < m; tk++) {
@@ -444,27 +469,14 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
         __syncthreads();
         for (int x = tid; x < m * LVD; x += FNT) {
             int tk = x / LVD, c = x - tk * LVD, t = t0 + c0 + tk;
-            float z = 0.f;
-            for (int s = 0; s < splits; s++) z += p[((size_t)s * n + t) * DELTA_IN + LQKV + h * LVD + c];
             float o = R.o[tk][c];
             if (out) out[(size_t)t * MIX + h * LVD + c] = o;
-            y[(size_t)t * MIX + h * LVD + c] = __float2half_rn(nw[c] * (o * R.rn[tk]) * silu(z));
+            y[(size_t)t * MIX + h * LVD + c] = __float2half_rn(nwv * (o * R.rn[tk]) * silu(R.z[tk][c]));
         }
         __syncthreads();
     }
-    (void)nwc;
     st_rows(sbuf(pl.ebuf), S, rg);
-    // ---- conv ring: the conv inputs of the segment's last CR tokens, this block's share of the channels
-    const int CH = (LQKV + LV_HEADS - 1) / LV_HEADS;
-    const int cb = h * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
-    for (int i = tid; i < mm * ch; i += FNT) {
-        int tk = len - mm + i / ch, c = cb + i % ch;
-        float v = 0.f;
-        for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + tk) * DELTA_IN + c];
-        sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
-    }
     // ---- the last block of the launch records the segments' steps in the slot metadata
-    __syncthreads();
     __shared__ int last;
     if (tid == 0) {
         __threadfence();
@@ -496,9 +508,18 @@ extern "C" int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int spl
     if (!ctx || !p || !ba || !cw || !a_log || !dt_bias || !nw || !mem || !meta || !y || !seg_start || !seg_len ||
         !seg_slot || !seg_pos0 || n <= 0 || segs <= 0 || splits < 1 || ba_splits < 1)
         return QB_ERR_ARG;
+    // Blocks read the conv ring's last 3 positions and write the step's own; with a segment of 30 tokens or more the
+    // two would touch the same ring rows from different blocks. Such steps take the three-kernel path.
+    if (n > qb::CR - qb::CONV_K + 1) return QB_ERR_UNSUPPORTED;
     // the launch's ticket: the last int of the context's ticket array (the products use the first n / 64)
     int* ticket = ctx->counters + ctx->ncounters - 1;
-    return qb::launch(ctx, qb::delta_fused_kernel, dim3(qb::LV_HEADS, segs), dim3(qb::FNT), 0, (cudaStream_t)stream, p,
+    static bool opted = false;
+    if (!opted) {
+        QB_CUDA(cudaFuncSetAttribute(qb::delta_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)sizeof(qb::FusedRound)));
+        opted = true;
+    }
+    return qb::launch(ctx, qb::delta_fused_kernel, dim3(qb::LV_HEADS, segs), dim3(qb::FNT), sizeof(qb::FusedRound), (cudaStream_t)stream, p,
                       splits, n, ba, ba_splits, cw, a_log, dt_bias, nw, mem, sst, meta, out, (__half*)y, seg_start,
                       seg_len, seg_slot, seg_pos0, segs, ticket);
 }

@@ -19,8 +19,15 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
     const int k0 = split * kper, k1 = min(K, k0 + kper);
     const uint4* wp = W + ((size_t)tile * (K / 16) + k0 / 16) * 32 + lane;
     const int steps = (k1 - k0) / 16;
-    // the weights do not depend on the previous kernel: fetch this warp's first fragments before waiting for it
-    uint4 w0 = warp < steps ? __ldg(wp + (size_t)warp * 32) : make_uint4(0, 0, 0, 0);
+    // the weights do not depend on the previous kernel: all of this warp's fragments (up to MAXF k16 steps) are in
+    // flight before it waits for that kernel; longer ranges fetch the rest as they go
+    constexpr int MAXF = 16;
+    uint4 wf[MAXF];
+#pragma unroll
+    for (int i = 0; i < MAXF; i++) {
+        int sidx = warp + 4 * i;
+        wf[i] = sidx < steps ? __ldg(wp + (size_t)sidx * 32) : make_uint4(0, 0, 0, 0);
+    }
     pdl_wait();
     float acc[NTT][4];
 #pragma unroll
@@ -31,8 +38,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
         int tok = 8 * j + g;
         xr[j] = tok < n ? X + (size_t)(xrows ? xrows[tok] : tok) * K + k0 + 2 * t : nullptr;
     }
-    for (int s = warp; s < steps; s += 4) {
-        uint4 w = s == warp ? w0 : __ldg(wp + (size_t)s * 32);
+    auto step = [&](int s, const uint4& w) {
         uint32_t a[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int j = 0; j < NTT; j++) {
@@ -43,7 +49,11 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
             }
             mma16816(acc[j], a, b0, b1);
         }
-    }
+    };
+#pragma unroll
+    for (int i = 0; i < MAXF; i++)
+        if (warp + 4 * i < steps) step(warp + 4 * i, wf[i]);
+    for (int s = warp + 4 * MAXF; s < steps; s += 4) step(s, __ldg(wp + (size_t)s * 32));
     if (warp > 0) {
 #pragma unroll
         for (int j = 0; j < NTT; j++) red[warp - 1][j][lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);

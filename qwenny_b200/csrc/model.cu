@@ -107,14 +107,15 @@ int launch_step(qb_model* m, cudaStream_t st) {
         const qb_layer& L = m->layers[i].w;
         const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
         if (L.kind == QB_LAYER_DELTA) {
-            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
-                                  nullptr, nullptr, 0)); k++;
             const int ba_tiles = 2 * LV_HEADS / 16;
             // the reference splits this small product 40 ways (split_for); 5 splits of 1024 columns leave its
             // consumers 8x fewer partial sums to add
             const int kper = m->fused ? 1024 : H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
+            // the small 16-bit product first: the big one's weight prefetch then overlaps it
             QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, kper, m->ba, 2 * LV_HEADS)); k++;
-            if (m->fused) {
+            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
+                                  nullptr, nullptr, 0)); k++;
+            if (m->fused && n <= CR - CONV_K + 1) {
                 QB_TRY(qb_delta_mixer(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.norm_w,
                                       L.mem, L.sst, L.meta, nullptr, m->mix, m->seg_start, m->seg_len, m->seg_slot,
                                       m->seg_pos0, m->segs)); k++;

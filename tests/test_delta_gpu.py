@@ -224,5 +224,5 @@ def test_fused_mixer_matches_the_three_kernels(ctx, case):
     assert torch.equal(meta1, meta2)
     assert torch.allclose(o1, o2, rtol=2e-6, atol=1e-7)
     assert torch.allclose(y1.float(), y2.float(), rtol=2e-3, atol=1e-6)
-    assert torch.allclose(mem1, mem2, rtol=2e-6, atol=1e-8)
-    assert torch.equal(mem1 != mem[: mem1.numel()], mem2 != mem[: mem2.numel()]) or True
+    assert torch.allclose(mem1, mem2, rtol=2e-6, atol=2e-6)   # far inside the 1e-4 bound on the f32 state
+    assert torch.equal(mem1 != mem, mem2 != mem)              # the same places were written
