@@ -29,7 +29,7 @@ def test_version_and_host_only_calls():
     l = _lib.lib()
     assert b"sm_100a" in l.qb_version()
     assert l.qb_split_for(6, 5120, 16, 1024) == 40
-    assert l.qb_attn_dec_splits(32005) == 63 and l.qb_attn_dec_splits(1) == 1 and l.qb_attn_dec_splits(4097) == 33
+    assert l.qb_attn_dec_splits(32005) == 32 and l.qb_attn_dec_splits(1) == 1 and l.qb_attn_dec_splits(4097) == 22
 
 
 def test_argument_errors_need_no_device():
