@@ -23,6 +23,7 @@ extern "C" {
 #define QB_ERR_ARG 1000      /* a shape or pointer the kernels cannot take */
 #define QB_ERR_DEVICE 1001   /* a bounded device-side wait ran out (see qb_device_error) */
 #define QB_ERR_UNSUPPORTED 1002
+#define QB_ERR_TOO_LARGE 1003 /* a size beyond a fixed capacity (qb_marlin_gemm_noalloc) */
 
 typedef struct qb_ctx qb_ctx;
 
@@ -53,6 +54,19 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
 /* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
  * next qb_marlin_gemm calls; zeros restore the built-in choice. */
 int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
+
+/* qb_marlin_gemm without a context and without any allocation, for callers that cannot call cudaMalloc (an engine
+ * that gave all free device memory to its cache pool, a plugin in a process whose allocator it does not own). It has
+ * no counterpart in the reference. Same arguments and results as qb_marlin_gemm for m <= 16 rows, always through the
+ * stream-K path, whose scratch (split-K partials, tickets) lives in a fixed array inside the library image: each GPU
+ * that loads the library holds qb_static_scratch_bytes() (about 4 MiB) until exit. Limits: n <= 262144 and
+ * n/64 x sharers x 2 KiB (4 KiB above 8 rows) <= 4 MiB, i.e. every shape of the 27B model; larger sizes return
+ * QB_ERR_TOO_LARGE before anything is enqueued. The first call on a device resolves the array's device address and
+ * the SM count for that device (make it before any stream capture, with the device current); calls on one device
+ * share the array, so two of them must not overlap on the GPU (same stream, or ordered by events). */
+int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n, int k,
+                           int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
+int qb_static_scratch_bytes(void);
 
 /* Measurement only: the following qb_marlin_gemm calls write per-block timestamps (ns of the global timer: start,
  * first stage landed, last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`. */

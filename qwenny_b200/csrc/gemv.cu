@@ -201,3 +201,68 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
     }
     return QB_OK;
 }
+
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// Some hosts can never call cudaMalloc once they are serving: an engine that has handed all free device memory to its
+// KV-cache page pool (the reference sizes that pool from what is left after loading, src/cuda/qwen/mod.rs:422-428), a
+// plugin loaded into a process whose allocator is owned by someone else, code running inside a stream capture. For
+// them the stream-K product's scratch (split-K partials, arrival tickets, error word) also exists as a fixed array
+// inside the library image: every GPU that loads the library holds these QB_STATIC_SCRATCH_BYTES until exit.
+namespace {
+
+constexpr size_t STATIC_PARTIAL_BYTES = 4u << 20;   // [n / 64][sharers][4][32] float4 of one product
+constexpr size_t STATIC_TICKETS = 4096;             // one per 64 outputs: n <= 262144
+constexpr size_t STATIC_BYTES = STATIC_PARTIAL_BYTES + STATIC_TICKETS * sizeof(int) + 256;
+
+static __device__ __align__(256) unsigned char qb_static_scratch[STATIC_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+// device address of the array on each device, resolved by the first call there (the array's name in host code is only
+// a handle for cudaGetSymbolAddress, not an address a kernel could use)
+unsigned char* g_static_ptr[MAX_DEVICES] = {nullptr};
+int g_static_sms[MAX_DEVICES] = {0};
+
+}  // namespace
+
+extern "C" int qb_static_scratch_bytes(void) { return (int)STATIC_BYTES; }
+
+extern "C" int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
+                                      int k, int row0, int epi, const int* xrows, unsigned long long* keys,
+                                      int n_valid) {
+    if (!X || !B || !Y || !S || m < 1 || m > 16 || n <= 0 || k <= 0 || n % 256 || k % 128) return QB_ERR_ARG;
+    if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
+    int dev = -1;
+    QB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return QB_ERR_ARG;
+    if (!g_static_ptr[dev]) {
+        // set-up, once per device, with that device current: the array's device address and the SM count
+        unsigned char* ptr = nullptr;
+        QB_CUDA(cudaGetSymbolAddress((void**)&ptr, qb_static_scratch));
+        QB_CUDA(cudaDeviceGetAttribute(&g_static_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+        g_static_ptr[dev] = ptr;
+    }
+    // a context on the stack that points into the static array; stream-K only (the path that needs the scratch)
+    qb_ctx c;
+    c.device = dev;
+    c.sms = g_static_sms[dev];
+    c.scratch = (float*)g_static_ptr[dev];
+    c.scratch_bytes = STATIC_PARTIAL_BYTES;
+    c.counters = (int*)(g_static_ptr[dev] + STATIC_PARTIAL_BYTES);
+    c.ncounters = STATIC_TICKETS;
+    c.err = (int*)(g_static_ptr[dev] + STATIC_PARTIAL_BYTES + STATIC_TICKETS * sizeof(int));
+    c.no_cluster = true;
+    // sizes beyond the fixed array: refuse before anything is enqueued
+    if ((size_t)(n / 64) > STATIC_TICKETS) return QB_ERR_TOO_LARGE;
+    {
+        int nt = m <= 8 ? 1 : 2;
+        GemvPlan p = pick(&c, n, k, nt, 0, 0, 0);
+        int grid, maxc;
+        grid_of(&c, p, n, k, &grid, &maxc);
+        if ((size_t)(n / 64) * maxc * nt * 4 * 32 * 16 > STATIC_PARTIAL_BYTES) return QB_ERR_TOO_LARGE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    // the tickets must start at zero; every call leaves them so, but the array is shared with whatever ran before
+    QB_CUDA(cudaMemsetAsync(c.counters, 0, (size_t)(n / 64) * sizeof(int), st));
+    return gemm_rows(&c, st, X, B, Y, S, m, n, k, xrows ? 0 : row0, epi, xrows, keys, n_valid);
+}

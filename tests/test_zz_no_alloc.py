@@ -1,0 +1,83 @@
+"""qb_marlin_gemm_noalloc: the product for callers that cannot allocate device memory (an engine whose page pool owns
+all that was free, a plugin inside someone else's process). It must give exactly what qb_marlin_gemm gives, call after
+call, out of the scratch array built into the library. Collected last on purpose: a run that stops at the first failure
+has then already run every other test."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from qwenny_b200 import host, synth
+from qwenny_b200._lib import lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def noalloc(x, words, scales, epi, y, keys=None, n_valid=0, xrows=None, row0=0, m=None):
+    k, n = x.shape[1], words.shape[1] // 2
+    m = x.shape[0] if m is None else m
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return lib().qb_marlin_gemm_noalloc(s, _p(x), _p(words), _p(y), _p(scales), m, n, k, row0,
+                                        {"plain": 0, "silu": 1, "argmax": 2}[epi], _p(xrows), _p(keys), n_valid)
+
+
+def test_noalloc_matches_the_context_product_twice_in_a_row(ctx):
+    g = synth.gen(77)
+    rows, cols, m = 5120, 6144, 5   # the 27B out-projection: its column blocks are shared by several blocks
+    x = torch.from_numpy(synth.activations(m, cols, g)).cuda()
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    words, s16 = host.pack_marlin(codes, sc)
+    wd = torch.from_numpy(words.view(np.int32)).cuda()
+    sd = torch.from_numpy(s16.view(np.int16)).cuda().view(torch.float16)
+    ctx.tune(ctas=-2)  # the context product on the same stream-K path
+    try:
+        want = ctx.marlin_gemm(x, wd, sd)
+    finally:
+        ctx.tune()
+    clustered = ctx.marlin_gemm(x, wd, sd)
+    for _ in range(2):
+        y = torch.full_like(want, float("nan"))
+        assert noalloc(x, wd, sd, "plain", y) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(y, want)                                    # same path, same bits
+        assert torch.allclose(y, clustered, rtol=1e-5, atol=1e-6)      # the default path sums in another order
+    # the other epilogues, and a second shape right after
+    rows2, cols2 = 2048, 1024
+    codes2, sc2 = synth.int4_matrix(rows2, cols2, g)
+    w2, s2 = host.pack_marlin(codes2, sc2, silu=True)
+    w2d = torch.from_numpy(w2.view(np.int32)).cuda()
+    s2d = torch.from_numpy(s2.view(np.int16)).cuda().view(torch.float16)
+    x2 = torch.from_numpy(synth.activations(16, cols2, g)).cuda()
+    want2 = ctx.marlin_gemm(x2, w2d, s2d, epi="silu")
+    y2 = torch.zeros_like(want2)
+    assert noalloc(x2, w2d, s2d, "silu", y2) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(y2.float(), want2.float(), rtol=2e-3, atol=1e-5)
+    keys_a = torch.zeros(16, dtype=torch.int64, device="cuda")
+    keys_b = torch.zeros(16, dtype=torch.int64, device="cuda")
+    la = ctx.marlin_gemm(x2, w2d, s2d, epi="argmax", keys=keys_a, n_valid=2000)
+    lb = torch.zeros_like(la)
+    assert noalloc(x2, w2d, s2d, "argmax", lb, keys=keys_b, n_valid=2000) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(la, lb, rtol=1e-5, atol=1e-6)
+    ta = 0xFFFFFFFF - (keys_a.cpu().numpy().view(np.uint64) & np.uint64(0xFFFFFFFF))
+    tb = 0xFFFFFFFF - (keys_b.cpu().numpy().view(np.uint64) & np.uint64(0xFFFFFFFF))
+    assert np.array_equal(ta, tb)
+
+
+def test_noalloc_refuses_what_does_not_fit():
+    assert lib().qb_static_scratch_bytes() < 5 << 20
+    x = torch.zeros(5, 128, dtype=torch.float16, device="cuda")
+    y = torch.zeros(8, device="cuda")
+    big_n = 64 * 4096 + 256   # more 64-output groups than the array has tickets
+    w = torch.zeros(8, dtype=torch.int32, device="cuda")  # never read: the call is refused first
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib().qb_marlin_gemm_noalloc(s, _p(x), _p(w), _p(y), _p(w), 5, big_n, 128, 0, 0, None, None, 0)
+    assert rc == 1003  # QB_ERR_TOO_LARGE
+    rc = lib().qb_marlin_gemm_noalloc(s, _p(x), _p(w), _p(y), _p(w), 17, 256, 128, 0, 0, None, None, 0)
+    assert rc == 1000  # more than 16 rows: QB_ERR_ARG
