@@ -71,6 +71,9 @@ int qb_static_scratch_bytes(void);
 /* Measurement only: the following qb_marlin_gemm calls write per-block timestamps (ns of the global timer: start,
  * first stage landed, last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`. */
 int qb_marlin_trace(qb_ctx* ctx, long long* buf);
+/* Measurement only: mode 1 makes the products' consumers release every stage unread, so a launch times the copy
+ * pipeline alone (its results are meaningless); 0 restores the product. */
+int qb_marlin_probe(qb_ctx* ctx, int mode);
 
 /* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
  * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it

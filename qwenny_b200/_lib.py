@@ -24,6 +24,7 @@ SIGNATURES = {
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_tune": [P, I, I, I, I],
     "qb_marlin_trace": [P, P],
+    "qb_marlin_probe": [P, I],
     "qb_marlin_gemm_noalloc": [P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_static_scratch_bytes": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],

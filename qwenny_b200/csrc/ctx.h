@@ -19,6 +19,7 @@ struct qb_ctx {
     bool no_cluster = false;
     // programmatic dependent launch on the launches that support it
     bool pdl = false;
+    int probe = 0;               // measurement: see qb_marlin_probe
     long long* trace = nullptr;  // measurement: per-block timestamps of the next products
 };
 

@@ -9,9 +9,9 @@ struct GemvPlan {
     int cluster_s;  // > 0: clustered split K with this many ranks per column block
 };
 
-static int smem_of(int cg, int kg, int nt, int nstages) {
+static int smem_of(int cg, int kg, int m, int nstages) {
     int nw = cg * kg, tk = kg * 128, tn = cg * 64;
-    return 128 + nstages * (nw * 4096 + 8 * nt * (tk + 8) * 2 + kg * tn * 2) + (kg - 1) * cg * nt * 2048;
+    return 128 + (tk + 8) * 2 + nstages * (nw * 4096 + kg * tn * 2 + m * (tk + 8) * 2);
 }
 
 // Blocks of the persistent grid and the most of them that can share one column block (the scratch stride).
@@ -29,7 +29,7 @@ template <int CG, int KG, int NT, int EPI>
 static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& p) {
     using C = GemvCfg<CG, KG, NT>;
     auto kern = w4a16_gemv_kernel<CG, KG, NT, EPI>;
-    int smem = C::smem(p.nstages);
+    int smem = C::smem(p.nstages, a.m);
     static int opted = 0;  // per instantiation
     if (opted < smem) {
         QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -112,7 +112,7 @@ static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const G
 // The built-in choice: wide matrices take 256 x 256 tiles (fewer, larger copies; a block's range crosses few column
 // blocks), narrow ones 128 x 512 so that a column block is shared by few blocks; the ring as deep as the blocks per
 // SM allow.
-static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt, int cg, int kg, int ctas) {
+static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int ctas) {
     GemvPlan p;
     if (cg) { p.cg = cg; p.kg = kg; }
     else if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
@@ -122,7 +122,7 @@ static GemvPlan pick(const qb_ctx* ctx, int n, int k, int nt, int cg, int kg, in
     p.ctas = ctas ? ctas : 2;
     const int budget = (228 * 1024) / p.ctas - 1024;
     p.nstages = 2;
-    while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, nt, p.nstages + 1) <= budget) p.nstages++;
+    while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, m, p.nstages + 1) <= budget) p.nstages++;
     // Clustered split K when the column blocks x ranks fit one wave of blocks: the most ranks (at most 8, the
     // portable cluster size) that fit, then as few as give the same longest share. The in-block reduction buffer
     // doubles as the rank's parking space, so the tile must have kg > 1.
@@ -148,6 +148,13 @@ extern "C" int qb_marlin_trace(qb_ctx* ctx, long long* buf) {
     return QB_OK;
 }
 
+// Measurement only: 1 makes the products' consumers release every stage unread, which times the copy pipeline alone
+// (results are then meaningless); 0 restores the product.
+extern "C" int qb_marlin_probe(qb_ctx* ctx, int mode) {
+    ctx->probe = mode;
+    return QB_OK;
+}
+
 extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas) {
     // ctas < 0: as -ctas, and stream-K only (no clustered split K)
     ctx->no_cluster = ctas < 0;
@@ -159,15 +166,16 @@ extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas
 static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m,
                      int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid) {
     int nt = m <= 8 ? 1 : 2;
-    GemvPlan p = pick(ctx, n, k, nt, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas);
+    GemvPlan p = pick(ctx, n, k, m, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas);
     if (ctx->tune_nstages) p.nstages = ctx->tune_nstages;
     int tn = p.cg * 64, tk = p.kg * 128;
     if (n % tn || k % tk || p.nstages < 2 || p.nstages > GEMV_MAX_STAGES) return QB_ERR_ARG;
-    if (smem_of(p.cg, p.kg, nt, p.nstages) > 227 * 1024 || (size_t)(n / 64) > ctx->ncounters) return QB_ERR_ARG;
+    if (smem_of(p.cg, p.kg, m, p.nstages) > 227 * 1024 || (size_t)(n / 64) > ctx->ncounters) return QB_ERR_ARG;
     GemvArgs a;
     a.X = (const __half*)X; a.xrows = xrows; a.B = (const uint32_t*)B; a.S = (const __half*)S; a.Y = Y;
     a.m = m; a.N = n; a.K = k; a.row0 = row0;
     a.nstages = p.nstages; a.maxc = 1;
+    a.probe = ctx->probe;
     a.trace = ctx->trace;
     if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
@@ -256,7 +264,7 @@ extern "C" int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B
     if ((size_t)(n / 64) > STATIC_TICKETS) return QB_ERR_TOO_LARGE;
     {
         int nt = m <= 8 ? 1 : 2;
-        GemvPlan p = pick(&c, n, k, nt, 0, 0, 0);
+        GemvPlan p = pick(&c, n, k, m, 0, 0, 0);
         int grid, maxc;
         grid_of(&c, p, n, k, &grid, &maxc);
         if ((size_t)(n / 64) * maxc * nt * 4 * 32 * 16 > STATIC_PARTIAL_BYTES) return QB_ERR_TOO_LARGE;

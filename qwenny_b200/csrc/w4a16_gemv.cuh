@@ -48,6 +48,7 @@ struct GemvArgs {
     unsigned long long* keys;
     int n_valid;
     int* err;             // set non-zero when a bounded wait ran out
+    int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone)
     long long* trace;     // measurement only (may be null): per block {start, first stage landed, last stage
                           // consumed, end} in ns of the global timer
 };
@@ -67,12 +68,13 @@ struct GemvCfg {
     static constexpr int TN = CG * 64, TK = KG * 128;
     static constexpr int W_BYTES = NW * 4096;        // TK/16 k16-steps x CG x 512 B
     static constexpr int XROW = TK + 8;              // halves; the pad spreads the 8 token rows over the banks
-    static constexpr int X_BYTES = 8 * NT * XROW * 2;
     static constexpr int S_BYTES = KG * TN * 2;
-    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + S_BYTES;
-    static constexpr int RED_BYTES = (KG - 1) * CG * NT * 2048;
+    static constexpr int RED_BYTES = (KG > 1 ? KG - 1 : 1) * CG * NT * 2048;  // lives in a consumed stage's weights
     static constexpr int BAR_BYTES = 128;
-    static constexpr int smem(int nstages) { return BAR_BYTES + nstages * STAGE_BYTES + RED_BYTES; }
+    // a stage holds the weights, the group scales and the m live rows of X; one zero row serves the other token rows
+    static constexpr int stage_bytes(int m) { return W_BYTES + S_BYTES + m * XROW * 2; }
+    static constexpr int smem(int nstages, int m) { return BAR_BYTES + XROW * 2 + nstages * stage_bytes(m); }
+    static_assert(RED_BYTES <= W_BYTES, "the reduction buffer fits a stage's weights");
 };
 
 // One Marlin word (8 nibbles q + 8) -> the four A-fragment registers of signed values q - 8, exactly:
@@ -149,8 +151,10 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + GEMV_MAX_STAGES;
-    uint8_t* stages = smem + C::BAR_BYTES;
-    float4* red = (float4*)(stages + (size_t)a.nstages * C::STAGE_BYTES);
+    uint8_t* zrow = smem + C::BAR_BYTES;              // XROW halves of zeros: the token rows m .. 8 NT - 1
+    uint8_t* stages = zrow + C::XROW * 2;
+    const int STAGE_BYTES = C::stage_bytes(a.m);      // weights | scales | m rows of X
+    const int X_OFF = C::W_BYTES + C::S_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = a.nstages;
@@ -178,12 +182,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         }
         mbar_fence_init();
     }
-    // the token rows the copies never write (m .. 8 NT - 1) read as zeros
-    for (int i = threadIdx.x; i < nstages * (C::X_BYTES / 16); i += C::THREADS) {
-        int sgi = i / (C::X_BYTES / 16), o = i % (C::X_BYTES / 16);
-        if (o * 16 >= a.m * C::XROW * 2)
-            *(uint4*)(stages + (size_t)sgi * C::STAGE_BYTES + C::W_BYTES + o * 16) = make_uint4(0, 0, 0, 0);
-    }
+    for (int i = threadIdx.x; i < C::XROW * 2 / 16; i += C::THREADS) ((uint4*)zrow)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -195,7 +194,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
         auto issue = [&](int cb, int st, int slot, int what) {
             int n0 = cb * C::TN, k0 = st * C::TK;
-            uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
+            uint8_t* base = stages + (size_t)slot * STAGE_BYTES;
             if (what != 1) {
                 if (lane == 0) mbar_expect_tx(&full[slot], tx);
                 __syncwarp();
@@ -203,13 +202,13 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 for (int c = lane; c < C::TK / 16; c += 32)
                     bulk_g2s(base + c * (CG * 512), wsrc + (size_t)c * 8 * a.N, CG * 512, &full[slot], pol_w);
                 if (lane < KG)
-                    bulk_g2s(base + C::W_BYTES + C::X_BYTES + lane * (C::TN * 2),
+                    bulk_g2s(base + C::W_BYTES + lane * (C::TN * 2),
                              a.S + (size_t)(k0 / 128 + lane) * a.N + n0, C::TN * 2, &full[slot], pol_w);
             }
             if (what != 0) {
                 if (lane < a.m) {
                     int row = a.xrows ? a.xrows[lane] : a.row0 + lane;
-                    bulk_g2s(base + C::W_BYTES + lane * (C::XROW * 2), a.X + (size_t)row * a.K + k0, C::TK * 2,
+                    bulk_g2s(base + X_OFF + lane * (C::XROW * 2), a.X + (size_t)row * a.K + k0, C::TK * 2,
                              &full[slot], pol_x);
                 }
             }
@@ -264,11 +263,19 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], par); i++) {}
             }
             if (a.trace && threadIdx.x == 0 && x == beg) a.trace[bid * 4 + 1] = global_ns();
-            const uint8_t* base = stages + (size_t)slot * C::STAGE_BYTES;
+            const uint8_t* base = stages + (size_t)slot * STAGE_BYTES;
             const uint4* wp = (const uint4*)(base + (size_t)(kg * 8 * CG + cg) * 512) + lane;
-            // ldmatrix row address of this lane: token row lane % 8 (+ 8 j), columns 8 (lane / 8) of each pair of k16 steps
-            const uint32_t xs = smem_u32(base + C::W_BYTES) + ((lane & 7) * C::XROW + kg * 128 + 8 * (lane >> 3)) * 2;
-            uint4 sc4 = *(const uint4*)(base + C::W_BYTES + C::X_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
+            // ldmatrix row addresses of this lane: token row lane % 8 (+ 8 j) of X, or the zero row past the m live
+            // rows; columns 8 (lane / 8) of each pair of k16 steps
+            uint32_t xs[NT];
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                const int row = 8 * j + (lane & 7);
+                xs[j] = (row < a.m ? smem_u32(base + X_OFF) + row * C::XROW * 2 : smem_u32(zrow)) +
+                        (kg * 128 + 8 * (lane >> 3)) * 2;
+            }
+            uint4 sc4 = *(const uint4*)(base + C::W_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
+            if (a.probe == 1) goto stage_done;
             float tmp[NT][4][4];
             uint32_t bx[NT][2][2];  // [token tile][k16 step of the pair][b0, b1]
 #pragma unroll
@@ -277,8 +284,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 if ((ks & 1) == 0) {
 #pragma unroll
                     for (int j = 0; j < NT; j++)
-                        ldsm_x4(bx[j][0][0], bx[j][0][1], bx[j][1][0], bx[j][1][1],
-                                xs + (8 * j * C::XROW + ks * 16) * 2);
+                        ldsm_x4(bx[j][0][0], bx[j][0][1], bx[j][1][0], bx[j][1][1], xs[j] + ks * 32);
                 }
                 uint32_t wq[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -303,18 +309,25 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     acc[j][b][2] += s1 * tmp[j][b][2]; acc[j][b][3] += s1 * tmp[j][b][3];
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
-            if (++slot == nstages) { slot = 0; par ^= 1; }
         }
+    stage_done:
         if (a.trace && threadIdx.x == 0 && x + 1 == end) a.trace[bid * 4 + 2] = global_ns();
-        // the piece (this block's stages of column block cb) goes on
-        const int pcb = cb;
+        // the piece (this block's stages of column block cb) goes on: release the stage and take the next
+        const int pcb = cb, pslot = slot;
         if (++st == kst) { st = 0; cb++; }
-        if (x + 1 < end && st != 0) continue;
+        if (++slot == nstages) { slot = 0; par ^= 1; }
+        if (x + 1 < end && st != 0) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[pslot]);
+            continue;
+        }
+        // The piece ends. Its last stage is not released yet: once every consumer warp is past it (the barrier below)
+        // its weight area is this block's reduction buffer, and the copy warp gets the slot back afterwards.
+        float4* red = (float4*)(stages + (size_t)pslot * STAGE_BYTES);
 
         // ---- the KG warps of a column group: kg > 0 hand their sums to kg = 0, which adds them in kg order
         if (KG > 1) {
+            named_bar_sync(1, C::NW * 32);  // every warp has finished reading the stage that becomes the buffer
             if (kg > 0) {
                 float4* r = red + (size_t)((kg - 1) * CG + cg) * NT * 4 * 32;
 #pragma unroll
@@ -323,7 +336,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     for (int b = 0; b < 4; b++)
                         r[(j * 4 + b) * 32 + lane] = make_float4(acc[j][b][0], acc[j][b][1], acc[j][b][2], acc[j][b][3]);
             }
-            named_bar_sync(1, C::NW * 32);
+            named_bar_sync(2, C::NW * 32);
             if (kg == 0) {
 #pragma unroll
                 for (int kk = 1; kk < KG; kk++) {
@@ -337,16 +350,18 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                         }
                 }
             }
-            named_bar_sync(2, C::NW * 32);
+            named_bar_sync(1, C::NW * 32);
         }
 
         if (clustered) {
             // ---- the ranks of the cluster meet in rank 0. Every block's kg = 0 warps park their sums in their own
-            // shared memory (the in-block reduction buffer, free by now), the cluster synchronises, rank 0 reads the
+            // shared memory, the cluster synchronises, rank 0 reads the
             // others' through distributed shared memory and adds them in rank order, and a second barrier keeps the
             // others' shared memory alive until it has.
             if (kg != 0) return;  // exited threads do not count in the cluster barrier
-            float4* mine = red + (size_t)cg * NT * 4 * 32;
+            // the block is done streaming (one piece per block here): every slot is free, and slot 0 is at the same
+            // shared-memory offset in every rank
+            float4* mine = (float4*)stages + (size_t)cg * NT * 4 * 32;
             if (blockIdx.x != 0) {
 #pragma unroll
                 for (int j = 0; j < NT; j++)
@@ -371,6 +386,8 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             cluster_sync();
             return;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[pslot]);  // the reduction buffer is read: the slot goes back to the copy warp
         if (kg == 0) {
             const int colgrp = pcb * CG + cg;  // 64 outputs
             bool finish = true;

@@ -1,0 +1,153 @@
+"""Small drivers for timing and profiling one kernel or a short step on one GPU.
+
+    python -m qwenny_b200.microbench gemv N K [--rows 5] [--epi plain|silu|argmax] [--reps 24] [--tune cg,kg,stages,ctas]
+    python -m qwenny_b200.microbench attn [--context 32000] [--rows 5] [--reps 20]
+    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--no-graph] [--no-pdl]
+
+Each prints CUDA-event timings (launches replayed from a CUDA graph, inputs larger than L2 where the shape allows)
+and is small enough to sit under `ncu` (-k <kernel> -s <warm-up launches> -c <few>). Synthetic inputs, seeded.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import numpy as np
+import torch
+
+from . import model as M
+from .ops import Context
+
+
+def _time_graph(fn, stream, reps):
+    with torch.cuda.stream(stream):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def gemv(args):
+    ctx = Context(0)
+    ctx.set_pdl(not args.no_pdl)
+    if args.tune:
+        ctx.tune(*[int(v) for v in args.tune.split(",")])
+    if args.probe:
+        from ._lib import lib
+        lib().qb_marlin_probe(ctx.h, args.probe)
+    n, k, m = args.n, args.k, args.rows
+    nbuf = max(2, min(8, int(300e6 / (n * k * 0.516)) + 1))  # weight buffers in rotation: more than L2 in total
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bufs = [M.Marlin.random(n, k, g) for _ in range(nbuf)]
+    x = torch.randn(m, k, generator=g, device="cuda").half()
+    y = torch.empty(m, n // 2, dtype=torch.float16, device="cuda") if args.epi == "silu" else torch.empty(m, n, device="cuda")
+    keys = torch.zeros(64, dtype=torch.int64, device="cuda")
+    i = [0]
+
+    def one():
+        w = bufs[i[0] % nbuf]
+        i[0] += 1
+        ctx.marlin_gemm(x, w.words, w.scales, epi=args.epi, y=y, keys=keys if args.epi == "argmax" else None)
+    if args.plain:
+        for _ in range(args.reps):
+            one()
+        torch.cuda.synchronize()
+        print(f"gemv N={n} K={k} rows={m} epi={args.epi}: {args.reps} plain launches done, device error {ctx.device_error()}")
+        return
+    us = _time_graph(one, torch.cuda.Stream(), args.reps)
+    by = n * k * 0.515625
+    print(f"gemv N={n} K={k} rows={m} epi={args.epi}: {us:.2f} us/launch, {by / us / 1e3:.0f} GB/s of {by / 1e6:.1f} MB; "
+          f"device error {ctx.device_error()}")
+
+
+def attn(args):
+    ctx = Context(0)
+    NH, NKV, HD, MIX = M.NH, M.NKV, M.HD, M.MIX
+    n, pos0 = args.rows, args.context
+    cap = (pos0 + n + 63) // 64 * 64
+    g = torch.Generator(device="cuda").manual_seed(75)
+    kc = torch.randint(1, 256, (NKV * cap * HD,), generator=g, dtype=torch.uint8, device="cuda")
+    vc = torch.randint(1, 256, (NKV * cap * HD,), generator=g, dtype=torch.uint8, device="cuda")
+    ks = (torch.randn(NKV * cap, generator=g, device="cuda") * 0.05).abs()
+    vs = (torch.randn(NKV * cap, generator=g, device="cuda") * 0.05).abs()
+    q = torch.randn(n, NH, HD, generator=g, device="cuda") * (math.log2(math.e) / 16)
+    gate = torch.sigmoid(torch.randn(n, MIX, generator=g, device="cuda"))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    dev = dict(dseg=i32([0, n]), dtok=i32(list(range(n))), dkeys=i32([pos0 + n] * n), tok_slot=i32([0] * n),
+               tok_pos=i32([pos0 + i for i in range(n)]))
+    st = dict(ndseg=1, ndec=n, dmax=n, dec_max_pos=pos0 + n - 1)
+    ml = torch.zeros(64 * 128 * NH * 2, device="cuda")
+    acc = torch.zeros(64 * 128 * NH * HD, device="cuda")
+    out = gate.clone()
+    mix = torch.zeros(n, MIX, dtype=torch.float16, device="cuda")
+
+    def one():
+        ctx.attn_decode(q, kc, vc, ks, vs, dev, st, cap, ml, acc, out, mix)
+    if args.plain:
+        for _ in range(args.reps):
+            one()
+        torch.cuda.synchronize()
+        print(f"attn context={pos0} rows={n}: {args.reps} plain launches done, device error {ctx.device_error()}")
+        return
+    us = _time_graph(one, torch.cuda.Stream(), args.reps)
+    by = NKV * 520 * (pos0 + n)
+    print(f"attn context={pos0} rows={n}: {us:.2f} us per decode + combine, {by / us / 1e3:.0f} GB/s of {by / 1e6:.1f} MB; "
+          f"device error {ctx.device_error()}")
+
+
+def step(args):
+    ctx = Context(0)
+    ctx.set_pdl(not args.no_pdl)
+    m = M.synthetic(ctx, nlayers=args.layers, position=args.context, max_ctx=32768)
+    m.use_graphs(not args.no_graph)
+    toks = [(1000 + i, 0, args.context + i) for i in range(args.rows)]
+    out = list(range(args.rows))
+    for _ in range(2):
+        m.step(toks, out)
+    m.argmax()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(m.stream)
+    for _ in range(args.steps):
+        m.step(toks, out)
+    e1.record(m.stream)
+    tok = m.argmax()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(f"step layers={args.layers} rows={args.rows} context={args.context}: {ms * 1e3:.1f} us/step, "
+          f"{m.step_kernels} kernels, greedy {tok}, device error {ctx.device_error()}")
+
+
+def main():
+    ap = argparse.ArgumentParser(prog="python -m qwenny_b200.microbench")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    a = sub.add_parser("gemv")
+    a.add_argument("n", type=int); a.add_argument("k", type=int)
+    a.add_argument("--rows", type=int, default=5); a.add_argument("--epi", default="plain")
+    a.add_argument("--reps", type=int, default=24); a.add_argument("--tune", default="")
+    a.add_argument("--no-pdl", action="store_true"); a.add_argument("--plain", action="store_true")
+    a.add_argument("--probe", type=int, default=0, help="1: time the copy pipeline alone (no arithmetic)")
+    a.set_defaults(fn=gemv)
+    b = sub.add_parser("attn")
+    b.add_argument("--context", type=int, default=32000); b.add_argument("--rows", type=int, default=5)
+    b.add_argument("--reps", type=int, default=20); b.add_argument("--plain", action="store_true")
+    b.set_defaults(fn=attn)
+    c = sub.add_parser("step")
+    c.add_argument("--layers", type=int, default=8); c.add_argument("--steps", type=int, default=3)
+    c.add_argument("--rows", type=int, default=5); c.add_argument("--context", type=int, default=32000)
+    c.add_argument("--no-graph", action="store_true"); c.add_argument("--no-pdl", action="store_true")
+    c.set_defaults(fn=step)
+    args = ap.parse_args()
+    args.fn(args)
+
+
+if __name__ == "__main__":
+    main()
