@@ -16,7 +16,7 @@ struct qb_ctx {
     int* err = nullptr;  // device word
     // measurement override of the GEMV plan (0: built-in choice)
     int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
-    bool no_cluster = false;
+    bool no_cluster = false, no_tc = false;
     // programmatic dependent launch on the launches that support it
     bool pdl = false;
     int probe = 0;               // measurement: see qb_marlin_probe
@@ -28,3 +28,7 @@ struct qb_ctx {
         cudaError_t e_ = (x);              \
         if (e_ != cudaSuccess) return (int)e_; \
     } while (0)
+
+// the prompt-sized W4A16 product on tcgen05 (w4a16_gemm_tc.cu); reached through qb_marlin_gemm for more than 16 rows
+int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m, int n,
+                      int k, int row0, int epi);

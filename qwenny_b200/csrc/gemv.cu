@@ -156,7 +156,10 @@ extern "C" int qb_marlin_probe(qb_ctx* ctx, int mode) {
 }
 
 extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas) {
-    // ctas < 0: as -ctas, and stream-K only (no clustered split K)
+    // ctas < 0: as -ctas, and stream-K only (no clustered split K); nstages < 0: as -nstages, and no tensor-core
+    // path for more than 16 rows (16-row slabs through the skinny kernel instead)
+    ctx->no_tc = nstages < 0;
+    if (nstages < 0) nstages = nstages == -1 ? 0 : -nstages;
     ctx->no_cluster = ctas < 0;
     if (ctas < 0) ctas = -ctas;
     ctx->tune_cg = cg; ctx->tune_kg = kg; ctx->tune_nstages = nstages; ctx->tune_ctas = ctas;
@@ -197,7 +200,10 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
     if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
     if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    // steps above 16 rows: 16-row slabs through the same kernel (the prompt-sized product has its own path)
+    // more than 16 rows: the tensor-core product (plain and SwiGLU epilogues, contiguous rows)
+    if (m > 16 && epi != QB_EPI_ARGMAX && !xrows && !ctx->no_tc)
+        return qb_gemm_tc_launch(ctx, st, X, B, Y, S, m, n, k, row0, epi);
+    // otherwise 16-row slabs through the skinny kernel
     for (int r = 0; r < m; r += 16) {
         int mm = m - r < 16 ? m - r : 16;
         int rc = gemm_rows(ctx, st, X, B, Y, S, mm, n, k, xrows ? 0 : row0 + r, epi, xrows ? xrows + r : nullptr,

@@ -66,8 +66,8 @@ def gemv(args):
         return
     us = _time_graph(one, torch.cuda.Stream(), args.reps)
     by = n * k * 0.515625
-    print(f"gemv N={n} K={k} rows={m} epi={args.epi}: {us:.2f} us/launch, {by / us / 1e3:.0f} GB/s of {by / 1e6:.1f} MB; "
-          f"device error {ctx.device_error()}")
+    print(f"gemv N={n} K={k} rows={m} epi={args.epi}: {us:.2f} us/launch, {by / us / 1e3:.0f} GB/s of {by / 1e6:.1f} MB, "
+          f"{2.0 * m * n * k / us / 1e6:.1f} TFLOP/s; device error {ctx.device_error()}")
 
 
 def attn(args):
