@@ -120,6 +120,16 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
                    const int* tok_pos, int cap, int ndseg, int ndec, int dmax, int max_keys, float* part_ml,
                    float* part_acc, float* out, void* mix_f16);
 int qb_attn_dec_splits(int keys);
+/* qb_attn_prefill  attn_prefill + attn_combine_tiles (+ to_xin when mix_f16 != NULL), kernels/attn.cuh:327-349,351-520,
+ *                  as Attn::run launches them (src/cuda/qwen/attn.rs:338-368): ntile tiles (ptile: first token,
+ *                  count; at most 64 / 6 = 10 consecutive tokens of one segment each), max_keys = tile_max_pos + 1.
+ *                  The key splits are the library's (qb_attn_tile_splits, one value per step like the reference's
+ *                  Attn::tile_splits, attn.rs:268-274); part_ml / part_acc hold n * 24 * splits partials, n = the
+ *                  step's tokens. */
+int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, const void* vc, const float* ks,
+                    const float* vs, const int* ptile, const int* tok_slot, const int* tok_pos, int cap, int ntile,
+                    int max_keys, float* part_ml, float* part_acc, float* out, void* mix_f16);
+int qb_attn_tile_splits(int ntile, int max_keys);
 
 /* ---- Gated DeltaNet. Slot memory (sst floats per slot), metadata and the rollback plan are the reference's
  * (kernels/qwen_deltanet.cuh:12-82; host side src/cuda/qwen/deltanet.rs:83-104,181-226).

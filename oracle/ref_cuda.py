@@ -185,6 +185,22 @@ class RefModule:
             self.launch("attn_combine", (st["ndec"], R.NH, 1), R.HD, 0, [
                 _ptr(part_ml), _ptr(part_acc), _ptr(dev["dtok"]), _ptr(dev["dkeys"]), C.c_int(z), _ptr(out)])
 
+    def attn_prefill(self, q, kc, vc, ks, vs, st, dev, cap, part_ml, part_acc, out):
+        """attn_prefill + attn_combine_tiles as Attn::run launches them (src/cuda/qwen/attn.rs:266-274,338-368)."""
+        ntile = st["ntile"]
+        most = 1 << (max(min(128, 256 // ntile), 1).bit_length() - 1)
+        want = -(-(st["tile_max_pos"] + 1) // (64 * ntile))
+        z = min(1 << (want - 1).bit_length(), most)
+        smem = 64 * (R.HD + 8) * 2 + 2 * 2 * 64 * R.HD
+        self.launch("attn_prefill", (ntile, R.NKV, z), 128, smem, [
+            _ptr(q), _ptr(kc), _ptr(vc), _ptr(ks), _ptr(vs), _ptr(dev["ptile"]), _ptr(dev["tok_slot"]),
+            _ptr(dev["tok_pos"]), C.c_int(cap), C.c_int(z), C.c_int(64 * ntile), _ptr(part_ml), _ptr(part_acc),
+            _ptr(out)])
+        if z > 1:
+            self.launch("attn_combine_tiles", (ntile * (64 // R.GROUP), R.NH, 1), R.HD, 0, [
+                _ptr(part_ml), _ptr(part_acc), _ptr(dev["ptile"]), _ptr(dev["tok_pos"]), C.c_int(z),
+                C.c_int(64 * ntile), _ptr(out)])
+
     # ------------------------------------------------------------------------------------------ DeltaNet
     def delta(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, norm_w, mem, sst, meta, cv, o, mix, st,
               dev, which=("conv", "rule", "norm")):

@@ -529,6 +529,7 @@ def build_step(toks, out_rows, short=8, max_dec=64, ptile=10, cut=16 * DSPLITS):
         n=n, n_out=len(out_rows), segs=len(seg[0]), ndec=len(dtok), ntile=len(ptl) // 2, ndseg=len(dseg) // 2,
         dmax=max([dseg[i] for i in range(1, len(dseg), 2)], default=0), max_seg=max(seg[1], default=0),
         dec_max_pos=max([pos(t) for t in dtok], default=0),
+        tile_max_pos=max([pos(ptl[i] + ptl[i + 1] - 1) for i in range(0, len(ptl), 2)], default=0),
         ids=i32([t[0] for t in toks]), tok_slot=i32([t[1] for t in toks]), tok_pos=i32([t[2] for t in toks]),
         seg_start=i32(seg[0]), seg_len=i32(seg[1]), seg_slot=i32(seg[2]), seg_pos0=i32(seg[3]),
         dtok=i32(dtok), dseg=i32(dseg), dkeys=i32(dkeys), ptile=i32(ptl), out_rows=i32(out_rows),

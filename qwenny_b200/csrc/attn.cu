@@ -20,10 +20,6 @@ namespace qb {
 
 constexpr float KV_OFF = 1152.f;
 constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
-constexpr int KWARPS = 4;      // warps that share a row tile, one 16-key block of a stage each
-constexpr int SK = 16 * KWARPS;  // keys per ring stage
-constexpr int NSTG = 4;        // ring depth
-constexpr int STG_BYTES = SK * HD * 2 + SK * 4 * 2;  // keys, values, key scales, value scales
 constexpr int DSPLITS = 32;    // most key splits of a decode token: 4 kv heads x 32 splits fill the SMs once
 
 __host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
@@ -125,23 +121,39 @@ attn_prep_kernel(const float* part, int splits, int n, const float* q_norm, cons
 // ------------------------------------------------------------------------------------------------ attn_decode
 __device__ __forceinline__ uint32_t kv_half2(uint32_t w, uint32_t sel) { return __byte_perm(w, 0x64646464u, sel); }
 
-template <int RT>
+// Prompt tiles: z key splits of a whole number of 64-key blocks (z from tile_splits on the host: one value per step).
+__host__ __device__ __forceinline__ int tile_chunk(int keys, int z) { return max(64, ((keys + z - 1) / z + 63) / 64 * 64); }
+__host__ inline int tile_splits(int ntile, int max_keys) {
+    int z = 1;  // fill about two blocks per SM, no split shorter than 256 keys
+    while (z < DSPLITS && ntile * NKV * z * 2 <= 2 * 148 && max_keys / (z * 2) >= 256) z *= 2;
+    return z;
+}
+
+// RT row tiles of 16 (token, head) rows; KW warps per row tile, one 16-key block of a stage each; NS ring stages
+template <int RT, int KW, int NS>
 struct DecCfg {
-    static constexpr int CW = RT * KWARPS;            // warps (warp 0 also issues the copies)
+    static constexpr int KWARPS = KW, NSTG = NS;
+    static constexpr int SK = 16 * KW;                // keys per ring stage
+    static constexpr int STG_BYTES = SK * HD * 2 + SK * 4 * 2;  // keys, values, key scales, value scales
+    static constexpr int CW = RT * KW;                // warps (warp 0 also issues the copies)
     static constexpr int THREADS = CW * 32;
     static constexpr int Q_BYTES = RT * 16 * SROW * 2;
     static constexpr int BAR_BYTES = 128;
-    static constexpr int SMEM = BAR_BYTES + Q_BYTES + NSTG * STG_BYTES;
+    static constexpr int SMEM = BAR_BYTES + Q_BYTES + NS * STG_BYTES;
     static constexpr int MERGE_FLOATS = 32 * (HD / 8 * 4 + 6);  // one warp's o, m, l, ps
-    static_assert(RT * (KWARPS / 2) * MERGE_FLOATS * 4 <= NSTG * STG_BYTES, "the merge buffers reuse the ring");
+    static_assert(RT * (KW / 2) * MERGE_FLOATS * 4 <= NS * STG_BYTES, "the merge buffers reuse the ring");
 };
 
-template <int RT>
-__global__ void __launch_bounds__(DecCfg<RT>::THREADS, 1)
+// TILES = false: block (short segment, kv head, key split) of the decode attention (dseg / dtok name the tokens).
+// TILES = true: block (prompt tile, kv head): `dseg` is the host's ptile array (first token, count) of tiles of
+// consecutive tokens, each block takes all the keys of its tile (one split) and finishes its rows.
+template <int RT, int KW, int NS, bool TILES>
+__global__ void __launch_bounds__(DecCfg<RT, KW, NS>::THREADS, 1)
 attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs,
                    const int* dseg, const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z,
-                   float* part_ml, float* part_acc, float* out, int* err) {
-    using C = DecCfg<RT>;
+                   float* part_ml, float* part_acc, float* out, __half* mix, int* err) {
+    using C = DecCfg<RT, KW, NS>;
+    constexpr int KWARPS = C::KWARPS, NSTG = C::NSTG, SK = C::SK, STG_BYTES = C::STG_BYTES;
     constexpr int NTD = HD / 8;  // n8 dim tiles of the output
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;
@@ -149,7 +161,8 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     __half* qsh = (__half*)(smem + C::BAR_BYTES);
     uint8_t* ring = smem + C::BAR_BYTES + C::Q_BYTES;
 
-    const int seg = blockIdx.x, g = blockIdx.y, s = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = TILES ? gridDim.x - 1 - blockIdx.x : blockIdx.x;  // prompt tiles: the longest contexts first
+    const int g = blockIdx.y, s = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < NSTG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], C::CW); }
         mbar_fence_init();
@@ -159,8 +172,9 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     pdl_wait();  // the step's own keys and values are written by attn_prep just before
 
     const int first = dseg[2 * seg], nt = dseg[2 * seg + 1];
-    const int tlast = dtok[first + nt - 1], keys = tok_pos[tlast] + 1;
-    const int chunk = dec_chunk(keys), ns = (keys + chunk - 1) / chunk;
+    auto token = [&](int i) { return TILES ? first + i : dtok[first + i]; };
+    const int tlast = token(nt - 1), keys = tok_pos[tlast] + 1;
+    const int chunk = TILES ? tile_chunk(keys, z) : dec_chunk(keys), ns = (keys + chunk - 1) / chunk;
     if (s >= ns) return;
     const int kbeg = s * chunk, ke = min(keys, kbeg + chunk), nstg = (ke - kbeg + SK - 1) / SK;
     const int slot = tok_slot[tlast];
@@ -205,7 +219,7 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     for (int x = threadIdx.x; x < RT * 16 * HD / 4; x += C::CW * 32) {
         int row = x / (HD / 4), d = (x % (HD / 4)) * 4, tok = row / GROUP;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (tok < nt) v = *(const float4*)(q + ((size_t)dtok[first + tok] * NH + g * GROUP + row % GROUP) * HD + d);
+        if (tok < nt) v = *(const float4*)(q + ((size_t)token(tok) * NH + g * GROUP + row % GROUP) * HD + d);
         *(uint2*)&qsh[row * SROW + d] = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
     }
     named_bar_sync(1, C::CW * 32);
@@ -226,7 +240,7 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
 #pragma unroll
     for (int h2 = 0; h2 < 2; h2++) {
         int tok = (wt * 16 + r + 8 * h2) / GROUP;
-        lim[h2] = tok < nt ? min(ke, tok_pos[dtok[first + tok]] + 1) : 0;
+        lim[h2] = tok < nt ? min(ke, tok_pos[token(tok)] + 1) : 0;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, ps[2] = {0.f, 0.f}, o[NTD][4];
 #pragma unroll
@@ -379,15 +393,16 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
         P += __shfl_xor_sync(0xffffffffu, P, 2);
         int row = wt * 16 + r + 8 * h2, tok = row / GROUP;
         if (tok >= nt) continue;
-        int i = first + tok, t = dtok[i], head = g * GROUP + row % GROUP;
+        int i = first + tok, t = token(tok), head = g * GROUP + row % GROUP;
         if (ns == 1) {
             float f = 1.f / L;
             float* op = out + (size_t)t * MIX + head * HD + 2 * t4;
 #pragma unroll
             for (int j = 0; j < NTD; j++) {
                 float2 gt = *(float2*)(op + j * 8);
-                *(float2*)(op + j * 8) = make_float2(gt.x * (o[j][2 * h2] - KV_OFF * P) * f,
-                                                     gt.y * (o[j][2 * h2 + 1] - KV_OFF * P) * f);
+                float2 res = make_float2(gt.x * (o[j][2 * h2] - KV_OFF * P) * f, gt.y * (o[j][2 * h2 + 1] - KV_OFF * P) * f);
+                *(float2*)(op + j * 8) = res;
+                if (TILES && mix) *(__half2*)(mix + (size_t)t * MIX + head * HD + 2 * t4 + j * 8) = __floats2half2_rn(res.x, res.y);
             }
         } else {
             size_t pi = ((size_t)i * NH + head) * z + s;
@@ -400,24 +415,18 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     }
 }
 
-// Merge the key splits of one (decode token, head) in split order; out *= result (the gate is there); optionally also
-// the f16 copy of the product. HD threads, thread d owns dim d; the splits' maxima and sums go through shared memory
-// once so that the accumulator loads of all splits are independent and in flight together.
-__global__ void __launch_bounds__(HD)
-attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, float* out,
-                    __half* mix) {
+// Merge the ns key splits of one (token, head) in split order; *op *= result (the gate is there); optionally also the
+// f16 copy of the product. HD threads, thread d owns dim d; the splits' maxima and sums go through shared memory once
+// so that the accumulator loads of all splits are independent and in flight together.
+__device__ __forceinline__ void combine_row(const float* part_ml, const float* part_acc, size_t base, int ns, float* op,
+                                            __half* mp) {
     __shared__ float se[DSPLITS];
     __shared__ float sL;
-    pdl_launch_dependents();
-    pdl_wait();
-    const int i = blockIdx.x, h = blockIdx.y, t = dtok[i], d = threadIdx.x;
-    const int ns = dec_splits(dkeys[i]);
-    float* op = out + (size_t)t * MIX + h * HD + d;
+    const int d = threadIdx.x;
     float res;
     if (ns == 1) {
-        res = *op;  // attn_decode finished it
+        res = *op;  // the attention kernel finished it
     } else {
-        const size_t base = ((size_t)i * NH + h) * z;
         if (d < 32) {  // DSPLITS <= 32: one split per lane
             float ms = d < ns ? part_ml[(base + d) * 2] : -INFINITY;
             float ls = d < ns ? part_ml[(base + d) * 2 + 1] : 0.f;
@@ -437,7 +446,33 @@ attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok
         res = *op * A * (1.f / sL);
         *op = res;
     }
-    if (mix) mix[(size_t)t * MIX + h * HD + d] = __float2half_rn(res);
+    if (mp) *mp = __float2half_rn(res);
+}
+
+// block (decode token, head)
+__global__ void __launch_bounds__(HD)
+attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, float* out,
+                    __half* mix) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x, h = blockIdx.y, t = dtok[i], d = threadIdx.x;
+    const size_t o = (size_t)t * MIX + h * HD + d;
+    combine_row(part_ml, part_acc, ((size_t)i * NH + h) * z, dec_splits(dkeys[i]), out + o, mix ? mix + o : nullptr);
+}
+
+// block (prompt tile * PTILE + row, head)
+constexpr int PTILE = 64 / GROUP;  // tokens of a prompt tile at most
+__global__ void __launch_bounds__(HD)
+attn_combine_tiles_kernel(const float* part_ml, const float* part_acc, const int* ptile, const int* tok_pos, int z,
+                          float* out, __half* mix) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.x / PTILE, row = blockIdx.x % PTILE, h = blockIdx.y, d = threadIdx.x;
+    const int t0 = ptile[2 * tile], len = ptile[2 * tile + 1];
+    if (row >= len) return;
+    const int keys = tok_pos[t0 + len - 1] + 1, chunk = tile_chunk(keys, z), t = t0 + row;
+    const size_t o = (size_t)t * MIX + h * HD + d;
+    combine_row(part_ml, part_acc, ((size_t)t * NH + h) * z, (keys + chunk - 1) / chunk, out + o, mix ? mix + o : nullptr);
 }
 
 }  // namespace qb
@@ -474,21 +509,53 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
     int rc;
 #define QB_DEC(RT)                                                                                              \
     {                                                                                                           \
+        using C = DecCfg<RT, 4, 4>;                                                                             \
         static bool opted = false;                                                                              \
         if (!opted) {                                                                                           \
-            QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                         DecCfg<RT>::SMEM));                                                    \
+            QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<RT, 4, 4, false>,                                   \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));                \
             opted = true;                                                                                       \
         }                                                                                                       \
-        rc = launch(ctx, attn_decode_kernel<RT>, grid, dim3(DecCfg<RT>::THREADS), DecCfg<RT>::SMEM, st, q,     \
+        rc = launch(ctx, attn_decode_kernel<RT, 4, 4, false>, grid, dim3(C::THREADS), C::SMEM, st, q,          \
                     (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, part_ml, \
-                    part_acc, out, ctx->err);                                                                   \
+                    part_acc, out, (__half*)nullptr, ctx->err);                                                 \
     }
     if (rt == 1) QB_DEC(1) else if (rt == 2) QB_DEC(2) else QB_DEC(3)
 #undef QB_DEC
     if (rc) return rc;
     return launch(ctx, attn_combine_kernel, dim3(ndec, NH), dim3(HD), 0, st, (const float*)part_ml,
                   (const float*)part_acc, dtok, dkeys, z, out, (__half*)mix_f16);
+}
+
+int qb_attn_tile_splits(int ntile, int max_keys) { return ntile > 0 && max_keys > 0 ? tile_splits(ntile, max_keys) : 0; }
+
+// Prompt attention: ntile tiles of up to 10 consecutive tokens of one segment (the host's ptile array: first token,
+// count), each against all the keys up to its last token; max_keys = the largest key count among them. `out` holds
+// the gate on entry and the gated attention output on return; mix_f16 (optional) gets its f16 copy. One block per
+// (tile, kv head, key split); part_ml / part_acc: scratch for n * 24 * qb_attn_tile_splits(ntile, max_keys) (m, l)
+// pairs and accumulators of 256 floats, n = the step's tokens (unused with one split).
+int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, const void* vc, const float* ks,
+                    const float* vs, const int* ptile, const int* tok_slot, const int* tok_pos, int cap, int ntile,
+                    int max_keys, float* part_ml, float* part_acc, float* out, void* mix_f16) {
+    if (!ctx || !q || !kc || !vc || !ks || !vs || !ptile || !tok_slot || !tok_pos || !out || ntile <= 0 || cap % 64 ||
+        max_keys <= 0 || max_keys > cap)
+        return QB_ERR_ARG;
+    const int z = tile_splits(ntile, max_keys);
+    if (z > 1 && (!part_ml || !part_acc)) return QB_ERR_ARG;
+    using C = DecCfg<4, 2, 5>;  // 10 tokens x 6 heads = 60 rows: 4 row tiles; 2 warps each; 5 stages of 32 keys
+    static_assert(PTILE * GROUP <= 64, "a prompt tile fills at most 4 row tiles");
+    static bool opted = false;
+    if (!opted) {
+        QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<4, 2, 5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        opted = true;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = launch(ctx, attn_decode_kernel<4, 2, 5, true>, dim3(ntile, NKV, z), dim3(C::THREADS), C::SMEM, st, q,
+                    (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, ptile, (const int*)nullptr, tok_slot, tok_pos, cap, z,
+                    part_ml, part_acc, out, z == 1 ? (__half*)mix_f16 : (__half*)nullptr, ctx->err);
+    if (rc || z == 1) return rc;
+    return launch(ctx, attn_combine_tiles_kernel, dim3(ntile * PTILE, NH), dim3(HD), 0, st, (const float*)part_ml,
+                  (const float*)part_acc, ptile, tok_pos, z, out, (__half*)mix_f16);
 }
 
 }  // extern "C"

@@ -118,6 +118,12 @@ class Context:
                                    st["ndseg"], st["ndec"], st["dmax"], st["dec_max_pos"] + 1, _p(part_ml),
                                    _p(part_acc), _p(out), _p(mix)), "qb_attn_decode")
 
+    def attn_prefill(self, q, kc, vc, ks, vs, dev, st, cap, part_ml, part_acc, out, mix=None):
+        """The prompt tiles of a step (dev["ptile"], st["ntile"], st["tile_max_pos"])."""
+        check(lib().qb_attn_prefill(self.h, _stream(), _p(q), _p(kc), _p(vc), _p(ks), _p(vs), _p(dev["ptile"]),
+                                    _p(dev["tok_slot"]), _p(dev["tok_pos"]), cap, st["ntile"], st["tile_max_pos"] + 1,
+                                    _p(part_ml), _p(part_acc), _p(out), _p(mix)), "qb_attn_prefill")
+
     # ---- DeltaNet
     def delta_conv(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, mem, sst, cv, dev):
         check(lib().qb_delta_conv(self.h, _stream(), _p(part), splits, n, _p(ba), ba_splits, _p(conv_w), _p(a_log),

@@ -128,3 +128,75 @@ def test_attn_decode_row_invariance_and_two_slots(ctx):
         one = run_decode(ctx, q[t:t + 1].contiguous(), gate[t:t + 1].contiguous(), cache, st1,
                          ref_cuda.upload_step(st1), cap, 1)
         assert torch.equal(one[0], full[t])
+
+
+def run_prefill(impl, q, gate, cache, st, dv, cap, n, mix=False):
+    kc, vc, ks, vs = cache
+    out = gate.clone()
+    pairs = 256 * 16
+    ml = torch.zeros(pairs * R.NH * 2, device="cuda")
+    acc = torch.zeros(pairs * R.NH * R.HD, device="cuda")
+    if isinstance(impl, ref_cuda.RefModule):
+        impl.attn_prefill(q, kc, vc, ks, vs, st, dv, cap, ml, acc, out)
+        return out
+    m = torch.zeros(n, R.MIX, dtype=torch.float16, device="cuda") if mix else None
+    impl.attn_prefill(q, kc, vc, ks, vs, dv, st, cap, ml, acc, out, m)
+    return (out, m) if mix else out
+
+
+@pytest.mark.parametrize("pos0,n,cap,check", [
+    (0, 64, 512, 64),            # a prompt from position 0: the first tile sees 10 keys
+    (295, 23, 512, 23),          # ragged last tile, keys cross a 64-key block inside a tile
+    (4000, 100, 8192, 12),       # ten tiles, key splits
+    (32700, 17, 32768, 4),       # two tiles at the end of a long context: 32 splits
+    (0, 2048, 2048, 6),          # the benchmark's prompt chunk, first chunk
+    (30720, 2048, 32768, 3),     # ... and its last chunk of a 32768-token prompt
+])
+def test_attn_prefill(ctx, ref, pos0, n, cap, check):
+    """Prompt tiles against the reference's attn_prefill kernel (every row) and the CPU oracle (`check` rows spread
+    over the step: the oracle walks every key of every head in numpy)."""
+    g = synth.gen(90 + n)
+    cache = make_cache(1, cap, g, pos0 + n)
+    q = torch.randn(n, R.NH, R.HD, generator=g) * QSCALE
+    gate = torch.sigmoid(torch.randn(n, R.MIX, generator=g))
+    toks = [(0, 0, pos0 + i) for i in range(n)]
+    st = R.build_step(toks, list(range(n)), short=0)
+    assert st["ndec"] == 0 and st["ntile"] == -(-n // 10)
+    dv = ref_cuda.upload_step(st)
+    dc = [t.cuda() for t in cache]
+    mine, mix = run_prefill(ctx, q.cuda(), gate.cuda(), dc, st, dv, cap, n, mix=True)
+    theirs = run_prefill(ref, q.cuda(), gate.cuda(), dc, st, dv, cap, n)
+    assert ctx.device_error() == 0
+    a, b = mine.cpu().numpy(), theirs.cpu().numpy()
+    assert close(a, b).all()
+    assert np.array_equal(mix.cpu().numpy(), a.astype(np.float16))
+    rows = sorted(set(np.linspace(0, n - 1, check).astype(int).tolist()))
+    want = R.attn_decode(q.numpy()[rows], gate.numpy()[rows], *[t.numpy() for t in cache],
+                         st["tok_slot"][rows], st["tok_pos"][rows], cap)
+    assert close(a[rows], want).all() and close(b[rows], want).all()
+
+
+def test_attn_prefill_matches_decode_rows(ctx):
+    """A token's attention as part of a prompt tile and as a lone decode token agree within the output tolerance (different key
+    splits round P to f16 against different running maxima), and a mixed step (one short segment, one long) runs both kernels on one `out`."""
+    g = synth.gen(99)
+    cap = 4096
+    cache = [t.cuda() for t in make_cache(2, cap, g, 0)]
+    n = 3 + 40
+    q = (torch.randn(n, R.NH, R.HD, generator=g) * QSCALE).cuda()
+    gate = torch.sigmoid(torch.randn(n, R.MIX, generator=g)).cuda()
+    toks = [(0, 1, 2000 + i) for i in range(3)] + [(0, 0, 700 + i) for i in range(40)]
+    st = R.build_step(toks, list(range(n)))
+    assert st["ndec"] == 3 and st["ntile"] == 4
+    dv = ref_cuda.upload_step(st)
+    kc, vc, ks, vs = cache
+    out = gate.clone()
+    ml = torch.zeros(4096 * R.NH * 2, device="cuda")
+    acc = torch.zeros(4096 * R.NH * R.HD, device="cuda")
+    ctx.attn_decode(q, kc, vc, ks, vs, dv, st, cap, ml, acc, out, None)
+    ctx.attn_prefill(q, kc, vc, ks, vs, dv, st, cap, ml, acc, out, None)
+    for t in (0, 2, 3, 17, 42):
+        st1 = R.build_step([toks[t]], [0])
+        one = run_decode(ctx, q[t:t + 1].contiguous(), gate[t:t + 1].contiguous(), cache, st1,
+                         ref_cuda.upload_step(st1), cap, 1)
+        assert close(out[t].cpu().numpy(), one[0].cpu().numpy()).all()
