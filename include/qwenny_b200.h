@@ -78,7 +78,7 @@ int qb_marlin_probe(qb_ctx* ctx, int mode);
 /* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
  * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it
  * (src/cuda/core.rs:532-560): W in mma A-fragment order (qb_pack_f16), X f16 [.][K] (rows xrows[t] if given),
- * Y f32 [K/kper splits][n][ldy] partial products which the consumer sums; n <= 32. */
+ * Y f32 [K/kper splits][n][ldy] partial products which the consumer sums (any n: blocks of 32 tokens). */
 int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
                       int n, int kper, float* Y, int ldy);
 

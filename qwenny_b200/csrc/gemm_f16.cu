@@ -2,7 +2,7 @@
 // pair, 96 x 5120): Y[split][t][r] = W[r] . X[t] over the split's k range. Replaces gemm_dec<16, NTT, EPI_PLAIN>
 // (kernels/gemm.cuh:222-304 of the reference). W arrives in the reference's packed form: tiles of 16 rows, per k16
 // step the 32 lanes' mma A fragments (8 halves each), so a warp's 128-bit loads are the fragments themselves.
-// A block is one (tile, k split); its 4 warps take alternate k16 steps and add up in shared memory in warp order.
+// A block is one (tile, k split, block of 8 NTT tokens); its 4 warps take alternate k16 steps and add up in shared memory in warp order.
 #include "common.cuh"
 #include "launch.h"
 
@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
     __shared__ float4 red[3][NTT][32];
     pdl_launch_dependents();
     const int tile = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
+    const int g = lane >> 2, t = lane & 3, tok0 = blockIdx.z * (8 * NTT);
     const int k0 = split * kper, k1 = min(K, k0 + kper);
     const uint4* wp = W + ((size_t)tile * (K / 16) + k0 / 16) * 32 + lane;
     const int steps = (k1 - k0) / 16;
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
     const __half* xr[NTT];
 #pragma unroll
     for (int j = 0; j < NTT; j++) {
-        int tok = 8 * j + g;
+        int tok = tok0 + 8 * j + g;
         xr[j] = tok < n ? X + (size_t)(xrows ? xrows[tok] : tok) * K + k0 + 2 * t : nullptr;
     }
     auto step = [&](int s, const uint4& w) {
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                int tok = 8 * j + 2 * t + (i & 1), r = tile * 16 + g + (i >> 1) * 8;
+                int tok = tok0 + 8 * j + 2 * t + (i & 1), r = tile * 16 + g + (i >> 1) * 8;
                 if (tok < n) y[(size_t)tok * ldy + r] = acc[j][i];
             }
         }
@@ -83,11 +83,11 @@ using namespace qb;
 
 extern "C" int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K,
                                  int ntiles, int n, int kper, float* Y, int ldy) {
-    if (!ctx || !W || !X || !Y || K <= 0 || K % 16 || ntiles <= 0 || n <= 0 || n > 32 || kper <= 0 || kper % 16 ||
+    if (!ctx || !W || !X || !Y || K <= 0 || K % 16 || ntiles <= 0 || n <= 0 || n > 65535 * 32 || kper <= 0 || kper % 16 ||
         ldy < ntiles * 16)
         return QB_ERR_ARG;
     int split = (K + kper - 1) / kper;
-    dim3 grid(ntiles, split);
+    dim3 grid(ntiles, split, n <= 32 ? 1 : (n + 31) / 32);
     cudaStream_t st = (cudaStream_t)stream;
     if (n <= 8) return launch(ctx, gemm_f16_plain_kernel<1>, grid, dim3(128), 0, st, (const uint4*)W, (const __half*)X, xrows, K, ntiles, n, kper, Y, ldy);
     if (n <= 16) return launch(ctx, gemm_f16_plain_kernel<2>, grid, dim3(128), 0, st, (const uint4*)W, (const __half*)X, xrows, K, ntiles, n, kper, Y, ldy);

@@ -23,6 +23,7 @@ constexpr int MAX_TOK = 2048, MAX_OUT = 64;     // src/cuda/core.rs:16-19
 constexpr int SHORT_SEG = 8, MAX_DEC = 64;      // attn::segments, src/cuda/qwen/attn.rs:17-19
 constexpr int DCUT = 2048;                      // short segments are cut where pos / DCUT changes (attn.rs:27)
 constexpr int GRAPH_TOK = 32;                   // steps of up to this many tokens are replayed as graphs (core.rs:27)
+constexpr int PTILE = 64 / GROUP;                // tokens of a prompt tile (attn.rs:18)
 constexpr int PAIRS = 64 * 128;                 // (decode token, split) pairs of the partial buffers (attn.rs:29)
 
 struct Layer {
@@ -53,11 +54,12 @@ struct qb_model {
     // step arrays (Step), one device allocation and one pinned host mirror: a single copy per step
     int *d_step = nullptr, *h_step = nullptr;
     size_t step_ints = 0;
-    int *ids, *tok_slot, *tok_pos, *seg_start, *seg_len, *seg_slot, *seg_pos0, *dtok, *dseg, *dkeys, *out_rows, *mark,
-        *mark_at;
+    int *ids, *tok_slot, *tok_pos, *seg_start, *seg_len, *seg_slot, *seg_pos0, *dtok, *dseg, *dkeys, *ptile, *out_rows,
+        *mark, *mark_at;
     unsigned long long* h_keys = nullptr;  // pinned
     // host-side shape of the uploaded step
-    int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0;
+    int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0,
+        tile_max_pos = 0;
     std::map<GraphKey, cudaGraphExec_t> graphs;
     bool use_graphs = true, fused = true;
     long long launches = 0;  // kernels launched (or replayed) since creation
@@ -68,14 +70,14 @@ namespace {
 
 struct StepLayout {
     // offsets (ints) of the step arrays inside the single step allocation
-    size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, out_rows, mark, mark_at,
-        total;
+    size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, ptile, out_rows, mark,
+        mark_at, total;
     StepLayout() {
         size_t o = 0;
         auto take = [&](size_t n) { size_t r = o; o += (n + 3) / 4 * 4; return r; };
         ids = take(MAX_TOK); tok_slot = take(MAX_TOK); tok_pos = take(MAX_TOK);
         seg_start = take(MAX_TOK); seg_len = take(MAX_TOK); seg_slot = take(MAX_TOK); seg_pos0 = take(MAX_TOK);
-        dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); out_rows = take(MAX_OUT);
+        dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); ptile = take(2 * MAX_TOK); out_rows = take(MAX_OUT);
         mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1);
         total = o;
     }
@@ -110,7 +112,7 @@ int launch_step(qb_model* m, cudaStream_t st) {
             const int ba_tiles = 2 * LV_HEADS / 16;
             // the reference splits this small product 40 ways (split_for); 5 splits of 1024 columns leave its
             // consumers 8x fewer partial sums to add
-            const int kper = m->fused ? 1024 : H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
+            const int kper = m->fused || n > 32 ? 1024 : H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
             // the small 16-bit product first: the big one's weight prefetch then overlaps it
             QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, kper, m->ba, 2 * LV_HEADS)); k++;
             QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
@@ -133,9 +135,16 @@ int launch_step(qb_model* m, cudaStream_t st) {
             const float qscale = 1.4426950408889634f / 16.f;  // scores in base 2, over sqrt(HD)
             QB_TRY(qb_attn_prep(c, s, m->part, 1, n, L.q_norm, L.k_norm, L.inv_freq, qscale, m->q, m->o, L.kc, L.vc,
                                 L.ks, L.vs, m->tok_slot, m->tok_pos, L.cap)); k++;
-            QB_TRY(qb_attn_decode(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->dseg, m->dtok, m->dkeys, m->tok_slot,
-                                  m->tok_pos, L.cap, m->ndseg, m->ndec, m->dmax, m->dec_max_pos + 1, m->ml, m->acc,
-                                  m->o, m->mix)); k += 2;
+            if (m->ndec > 0) {
+                QB_TRY(qb_attn_decode(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->dseg, m->dtok, m->dkeys, m->tok_slot,
+                                      m->tok_pos, L.cap, m->ndseg, m->ndec, m->dmax, m->dec_max_pos + 1, m->ml, m->acc,
+                                      m->o, m->mix)); k += 2;
+            }
+            if (m->ntile > 0) {
+                QB_TRY(qb_attn_prefill(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->ptile, m->tok_slot, m->tok_pos, L.cap,
+                                       m->ntile, m->tile_max_pos + 1, m->ml, m->acc, m->o, m->mix));
+                k += qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) > 1 ? 2 : 1;
+            }
         }
         QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
         QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
@@ -169,7 +178,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     const size_t T = MAX_TOK;
     QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
     QB_TRY(dalloc(&m->part, T * (size_t)DELTA_IN));
-    QB_TRY(dalloc(&m->ba, (size_t)40 * 32 * 2 * LV_HEADS + T * 2 * LV_HEADS));
+    QB_TRY(dalloc(&m->ba, (size_t)40 * 32 * 2 * LV_HEADS + 5 * T * 2 * LV_HEADS));  // 40 splits of 32 rows or 5 of T
     QB_TRY(dalloc(&m->o, T * MIX)); QB_TRY(dalloc(&m->mix, T * MIX)); QB_TRY(dalloc(&m->mid, T * FF));
     QB_TRY(dalloc(&m->cv, T * CVW)); QB_TRY(dalloc(&m->q, T * NH * HD));
     QB_TRY(dalloc(&m->ml, (size_t)PAIRS * NH * 2)); QB_TRY(dalloc(&m->acc, (size_t)PAIRS * NH * HD));
@@ -184,7 +193,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     int* d = m->d_step;
     m->ids = d + L.ids; m->tok_slot = d + L.tok_slot; m->tok_pos = d + L.tok_pos; m->seg_start = d + L.seg_start;
     m->seg_len = d + L.seg_len; m->seg_slot = d + L.seg_slot; m->seg_pos0 = d + L.seg_pos0; m->dtok = d + L.dtok;
-    m->dseg = d + L.dseg; m->dkeys = d + L.dkeys; m->out_rows = d + L.out_rows; m->mark = d + L.mark;
+    m->dseg = d + L.dseg; m->dkeys = d + L.dkeys; m->ptile = d + L.ptile; m->out_rows = d + L.out_rows; m->mark = d + L.mark;
     m->mark_at = d + L.mark_at;
     *out = m;
     return QB_OK;
@@ -269,7 +278,7 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
             segs++;
         }
     }
-    int ndec = 0, ndseg = 0, ntile = 0, dmax = 0, max_seg = 0, dec_max_pos = 0, nmark = 0;
+    int ndec = 0, ndseg = 0, ntile = 0, dmax = 0, max_seg = 0, dec_max_pos = 0, tile_max_pos = 0, nmark = 0;
     for (int s = 0; s < segs; s++) {
         int st = h[L.seg_start + s], len = h[L.seg_len + s];
         max_seg = len > max_seg ? len : max_seg;
@@ -290,17 +299,21 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
                 a = e;
             }
         } else {
-            ntile += (len + 9) / 10;  // prompt tiles of 64 / GROUP tokens: the prompt attention is not built yet
+            for (int o = 0; o < len; o += PTILE) {  // prompt tiles of 64 / GROUP consecutive tokens
+                int cnt = len - o < PTILE ? len - o : PTILE, last = (int)toks[st + o + cnt - 1].pos;
+                h[L.ptile + 2 * ntile] = st + o; h[L.ptile + 2 * ntile + 1] = cnt;
+                tile_max_pos = last > tile_max_pos ? last : tile_max_pos;
+                ntile++;
+            }
         }
         h[L.mark_at + s] = nmark;
         for (int t = st; t < st + len; t++) h[L.mark + nmark++] = (int)toks[t].id;
     }
     h[L.mark_at + segs] = nmark;
     for (int i = 0; i < n_out; i++) h[L.out_rows + i] = out[i];
-    if (ntile > 0) return QB_ERR_UNSUPPORTED;
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
-    m->max_seg = max_seg; m->dec_max_pos = dec_max_pos;
+    m->max_seg = max_seg; m->dec_max_pos = dec_max_pos; m->tile_max_pos = tile_max_pos;
     return QB_OK;
 }
 
@@ -316,7 +329,9 @@ int qb_model_run(qb_model* m, void* stream) {
         return QB_OK;
     }
     GraphKey key = {{m->n, m->n_out, m->segs, m->ndec, m->ntile, m->max_seg,
-                     m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0, m->ndseg, m->dmax}};
+                     (m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0) +
+                         64 * (m->ntile ? qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) : 0),
+                     m->ndseg, m->dmax}};
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         // a first uncaptured run sets the kernels' attributes (not allowed while capturing) and warms the caches

@@ -62,6 +62,59 @@ def test_steps_match_cpu_oracle(small):
         pos += 3  # two of four drafts accepted: the next step restarts inside this one
 
 
+def test_prompt_steps_match_cpu_oracle(ctx):
+    """Prompt chunks (long segments: prompt attention tiles, the tensor-core products, the unfused DeltaNet kernels),
+    alone and mixed with another sequence's decode token, then a verify step that continues the prompt."""
+    m = M.synthetic(ctx, nlayers=2, slots=2, max_ctx=512, vocab=2000, seed=11, pattern=("delta", "attn"))
+    cpu = cpu_step.CpuModel.from_device(m)
+    seq = [(31 + 11 * i) % 2000 for i in range(160)]
+    steps = [
+        ([(seq[i], 0, i) for i in range(75)], [74]),                                  # first chunk, from position 0
+        ([(9, 1, 0)] + [(seq[i], 0, i) for i in range(75, 118)], [0, 43]),            # second chunk + a new sequence
+        ([(seq[i], 0, i) for i in range(118, 123)] + [(10, 1, 1)], list(range(6))),   # verify rows + decode token
+        ([(seq[i], 0, i) for i in range(120, 140)], [19]),                            # restart inside the drafts, 20 rows
+    ]
+    for toks, out in steps:
+        m.step(toks, out)
+        got = m.argmax()
+        logits, want, h, xn = cpu.step(toks, out)
+        assert agree(m.hidden().cpu().numpy(), h)
+        assert agree(m.logits().cpu().numpy(), logits)
+        srt = np.sort(logits[:, :2000], axis=1)
+        for r in range(len(out)):
+            assert got[r] == int(want[r]) or srt[r, -1] - srt[r, -2] < 1e-3
+
+
+def test_full_prompt_chunk(ctx):
+    """The benchmark's prompt chunk, 2048 tokens in one step: against the CPU oracle of the same step (logits of three
+    rows, every row of the residual stream), and against 2048 single-token steps. The two GPU paths round differently
+    (the 16-row product applies a group's scale in f32 after the group's sum, the tensor-core product and the oracle
+    round weight * scale to f16 first, as the reference's kernels do), so they agree within the step tolerance of each
+    other, not bit for bit; the token after the prompt continues from either state."""
+    def fresh():
+        return M.synthetic(ctx, nlayers=2, slots=1, max_ctx=2304, vocab=2000, seed=13, pattern=("delta", "attn"))
+    a, b = fresh(), fresh()
+    cpu = cpu_step.CpuModel.from_device(b)
+    n = 2048
+    seq = [(1000 + 7919 * i) % 2000 for i in range(n + 1)]
+    for i in range(n):
+        a.step([(seq[i], 0, i)], [0])
+    toks, out = [(seq[i], 0, i) for i in range(n)], [n - 1, 100, 1000]
+    b.step(toks, out)
+    logits, want, h, xn = cpu.step(toks, out)
+    assert agree(b.logits().cpu().numpy(), logits) and agree(b.hidden().cpu().numpy(), h)
+    assert b.argmax() == list(want)
+
+    def near(x, y):  # two roundings apart: twice the step tolerance
+        x, y = np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64)
+        return np.linalg.norm(x - y) / np.linalg.norm(y) < 4e-3
+    assert near(b.logits()[0].cpu().numpy(), a.logits()[0].cpu().numpy())
+    a.step([(seq[n], 0, n)], [0])
+    b.step([(seq[n], 0, n)], [0])
+    assert near(b.logits().cpu().numpy(), a.logits().cpu().numpy())
+    assert near(b.hidden().cpu().numpy(), a.hidden().cpu().numpy())
+
+
 def test_rows_are_invariant_to_drafts(ctx):
     """speccheck's property (src/checks.rs:892-937): the logits of a row are bit-identical whether its token runs
     alone or with drafts after it, and greedy decoding with drafts gives exactly the tokens of one token per step."""
