@@ -131,6 +131,33 @@ int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, c
                     int max_keys, float* part_ml, float* part_acc, float* out, void* mix_f16);
 int qb_attn_tile_splits(int ntile, int max_keys);
 
+/* ---- One launch for a layer's weight-streaming tail (decode / verify steps of up to qb_layer_chain_max_rows() = 7
+ * token rows): out_proj, h += . and RMSNorm(post_norm), gate_up with SwiGLU, down, h += . and RMSNorm(next_norm), and
+ * the NEXT layer's in-projection. Replaces, for such steps, four Gemm::marlin launches and two add_rmsnorm launches of
+ * the reference's launch_step (src/cuda/qwen/mod.rs:744-766; Stack::mlp; kernels/marlin.cuh; kernels/dense.cuh:12-26)
+ * with one cooperative persistent kernel whose blocks meet at grid barriers; same inputs, same outputs:
+ *   mix     f16 [m][6144]  the mixer's output (in)          h     f32 [m][5120] residual stream (in / out)
+ *   xn      f16 [m][5120]  RMSNorm(h) * next_norm (out)      part  f32 [m][next_n] the next in-projection (out; unused
+ *                                                                  when next_w is NULL: the last layer)
+ *   h_tmp, part_h (f32 [m][5120]) and mid (f16 [m][17408]) are scratch. All matrices in the Marlin layout. */
+typedef struct qb_chain {
+    int m;
+    const void* mix;
+    const void *out_w, *out_s;
+    const void *gate_up_w, *gate_up_s;
+    const void *down_w, *down_s;
+    const void *next_w, *next_s;
+    int next_n;
+    const float *post_norm, *next_norm;
+    float *h, *h_tmp, *part_h;
+    void* mid;
+    void* xn;
+    float* part;
+    float eps;
+} qb_chain;
+int qb_layer_chain(qb_ctx* ctx, void* stream, const qb_chain* c);
+int qb_layer_chain_max_rows(void);
+
 /* ---- Gated DeltaNet. Slot memory (sst floats per slot), metadata and the rollback plan are the reference's
  * (kernels/qwen_deltanet.cuh:12-82; host side src/cuda/qwen/deltanet.rs:83-104,181-226).
  * qb_delta_conv   delta_conv, kernels/qwen_deltanet.cuh:84-131
@@ -207,6 +234,8 @@ int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
 int qb_model_use_fused(qb_model* m, int on);
+/* on (default): steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers */
+int qb_model_use_chain(qb_model* m, int on);
 /* Engine::argmax (src/cuda/core.rs:1100-1103): greedy token per logit row of the last step; synchronises the stream */
 int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);
 float* qb_model_logits(qb_model* m);   /* device f32 [n_out][vocab_rows] */

@@ -57,6 +57,9 @@ SIGNATURES = {
     "qb_model_logits": [P],
     "qb_model_hidden": [P],
     "qb_model_xn": [P],
+    "qb_layer_chain": [P, P, P],
+    "qb_layer_chain_max_rows": [],
+    "qb_model_use_chain": [P, I],
     "qb_model_launches": [P],
     "qb_model_step_kernels": [P],
     "qb_row_order": [I, I, P],
@@ -76,6 +79,15 @@ class QbLayer(C.Structure):
         ("input_norm", P), ("post_norm", P), ("gate_up_w", P), ("gate_up_s", P), ("down_w", P), ("down_s", P),
         ("conv_w", P), ("a_log", P), ("dt_bias", P), ("norm_w", P), ("mem", P), ("sst", LL), ("meta", P),
         ("q_norm", P), ("k_norm", P), ("inv_freq", P), ("kc", P), ("vc", P), ("ks", P), ("vs", P), ("cap", I),
+    ]
+
+
+class QbChain(C.Structure):
+    """qb_chain of include/qwenny_b200.h."""
+    _fields_ = [
+        ("m", I), ("mix", P), ("out_w", P), ("out_s", P), ("gate_up_w", P), ("gate_up_s", P), ("down_w", P),
+        ("down_s", P), ("next_w", P), ("next_s", P), ("next_n", I), ("post_norm", P), ("next_norm", P),
+        ("h", P), ("h_tmp", P), ("part_h", P), ("mid", P), ("xn", P), ("part", P), ("eps", F),
     ]
 
 

@@ -20,6 +20,8 @@ int qb_create(int device, qb_ctx** out) {
     QB_CUDA(cudaMemset(c->counters, 0, c->ncounters * sizeof(int)));
     QB_CUDA(cudaMalloc(&c->err, 64));
     QB_CUDA(cudaMemset(c->err, 0, 64));
+    QB_CUDA(cudaMalloc(&c->gbar, 64));
+    QB_CUDA(cudaMemset(c->gbar, 0, 64));
     *out = c;
     return QB_OK;
 }
@@ -29,6 +31,7 @@ void qb_destroy(qb_ctx* c) {
     cudaFree(c->scratch);
     cudaFree(c->counters);
     cudaFree(c->err);
+    cudaFree(c->gbar);
     delete c;
 }
 

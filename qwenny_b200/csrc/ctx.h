@@ -14,6 +14,8 @@ struct qb_ctx {
     int* counters = nullptr;
     size_t ncounters = 0;
     int* err = nullptr;  // device word
+    unsigned* gbar = nullptr;  // grid-barrier counters of the persistent layer kernel (zero between launches)
+    bool chain_pdl = true;     // that kernel's launch carries the programmatic-dependent-launch attribute too
     // measurement override of the GEMV plan (0: built-in choice)
     int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
     bool no_cluster = false, no_tc = false;

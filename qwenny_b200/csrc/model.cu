@@ -46,7 +46,7 @@ struct qb_model {
     const float* final_norm = nullptr;
     const void *lm_w = nullptr, *lm_s = nullptr;
     // activations (Bufs)
-    float *h = nullptr, *part = nullptr, *ba = nullptr, *o = nullptr, *cv = nullptr, *q = nullptr, *ml = nullptr,
+    float *h = nullptr, *h2 = nullptr, *part_h = nullptr, *part = nullptr, *ba = nullptr, *o = nullptr, *cv = nullptr, *q = nullptr, *ml = nullptr,
           *acc = nullptr, *logits = nullptr;
     __half *xn = nullptr, *mix = nullptr, *mid = nullptr;
     unsigned long long* keys = nullptr;
@@ -61,9 +61,10 @@ struct qb_model {
     int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0,
         tile_max_pos = 0;
     std::map<GraphKey, cudaGraphExec_t> graphs;
-    bool use_graphs = true, fused = true;
+    bool use_graphs = true, fused = true, chain = true;
     long long launches = 0;  // kernels launched (or replayed) since creation
     int step_kernels = 0;    // kernels of the last step
+    int ba_kper = 1024;      // k range of a split of the DeltaNet 16-bit in-projection in the current step
 };
 
 namespace {
@@ -96,55 +97,93 @@ int dalloc(T** p, size_t n) {
         if (rc_) return rc_; \
     } while (0)
 
-// The kernels of one step over the uploaded tokens, in the reference's order (launch_step)
+// A layer's in-projection(s): the small 16-bit product of a DeltaNet layer, then the int4 one (whose weight prefetch
+// overlaps it). `with_w4`: false when the previous layer's persistent kernel already ran the int4 product.
+int launch_in_proj(qb_model* m, cudaStream_t st, const qb_layer& L, bool with_w4, int& k) {
+    qb_ctx* c = m->ctx;
+    const int n = m->n;
+    void* s = (void*)st;
+    if (L.kind == QB_LAYER_DELTA) {
+        const int ba_tiles = 2 * LV_HEADS / 16;
+        QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS)); k++;
+    }
+    if (with_w4) {
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN,
+                              H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    }
+    return QB_OK;
+}
+
+// A layer's mixer: m->part (+ m->ba) -> m->mix (f16)
+int launch_mixer(qb_model* m, cudaStream_t st, const qb_layer& L, int& k) {
+    qb_ctx* c = m->ctx;
+    const int n = m->n;
+    void* s = (void*)st;
+    if (L.kind == QB_LAYER_DELTA) {
+        const int ba_splits = H / m->ba_kper;
+        if (m->fused && n <= CR - CONV_K + 1) {
+            QB_TRY(qb_delta_mixer(c, s, m->part, 1, n, m->ba, ba_splits, L.conv_w, L.a_log, L.dt_bias, L.norm_w, L.mem,
+                                  L.sst, L.meta, nullptr, m->mix, m->seg_start, m->seg_len, m->seg_slot, m->seg_pos0,
+                                  m->segs)); k++;
+        } else {
+            QB_TRY(qb_delta_conv(c, s, m->part, 1, n, m->ba, ba_splits, L.conv_w, L.a_log, L.dt_bias, L.mem, L.sst,
+                                 m->cv, m->tok_slot, m->tok_pos)); k++;
+            QB_TRY(qb_delta_rule(c, s, m->part, 1, n, m->cv, L.mem, L.sst, L.meta, m->o, m->seg_start, m->seg_len,
+                                 m->seg_slot, m->seg_pos0, m->segs)); k++;
+            QB_TRY(qb_delta_norm(c, s, m->part, 1, n, L.norm_w, m->o, m->mix, L.meta, m->seg_len, m->seg_slot,
+                                 m->seg_pos0, m->segs)); k++;
+        }
+    } else {
+        const float qscale = 1.4426950408889634f / 16.f;  // scores in base 2, over sqrt(HD)
+        QB_TRY(qb_attn_prep(c, s, m->part, 1, n, L.q_norm, L.k_norm, L.inv_freq, qscale, m->q, m->o, L.kc, L.vc, L.ks,
+                            L.vs, m->tok_slot, m->tok_pos, L.cap)); k++;
+        if (m->ndec > 0) {
+            QB_TRY(qb_attn_decode(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->dseg, m->dtok, m->dkeys, m->tok_slot, m->tok_pos,
+                                  L.cap, m->ndseg, m->ndec, m->dmax, m->dec_max_pos + 1, m->ml, m->acc, m->o, m->mix));
+            k += 2;
+        }
+        if (m->ntile > 0) {
+            QB_TRY(qb_attn_prefill(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->ptile, m->tok_slot, m->tok_pos, L.cap, m->ntile,
+                                   m->tile_max_pos + 1, m->ml, m->acc, m->o, m->mix));
+            k += qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) > 1 ? 2 : 1;
+        }
+    }
+    return QB_OK;
+}
+
+// The kernels of one step over the uploaded tokens, in the reference's order (launch_step). Steps of up to
+// qb_layer_chain_max_rows() tokens run everything between two mixers as one persistent launch.
 int launch_step(qb_model* m, cudaStream_t st) {
     qb_ctx* c = m->ctx;
     const int n = m->n;
     int k = 0;
     void* s = (void*)st;
+    const bool chain = m->chain && n <= qb_layer_chain_max_rows();
+    // the reference splits the small 16-bit product 40 ways (split_for); 5 splits of 1024 columns leave its consumers
+    // 8x fewer partial sums to add
+    m->ba_kper = m->fused || n > 32 ? 1024 : H / qb_split_for(2 * LV_HEADS / 16, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
     QB_TRY(qb_mark_seen(c, s, m->seen, m->mark, m->mark_at, m->seg_slot, m->seg_pos0, m->segs, m->vocab_rows)); k++;
     QB_TRY(qb_embed(c, s, m->embed, m->ids, m->h, m->keys, m->n_out, n)); k++;
     QB_TRY(qb_rmsnorm(c, s, m->h, m->layers[0].w.input_norm, m->xn, EPS, n)); k++;
     for (int i = 0; i < m->nlayers; i++) {
         const qb_layer& L = m->layers[i].w;
         const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
-        if (L.kind == QB_LAYER_DELTA) {
-            const int ba_tiles = 2 * LV_HEADS / 16;
-            // the reference splits this small product 40 ways (split_for); 5 splits of 1024 columns leave its
-            // consumers 8x fewer partial sums to add
-            const int kper = m->fused || n > 32 ? 1024 : H / qb_split_for(ba_tiles, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
-            // the small 16-bit product first: the big one's weight prefetch then overlaps it
-            QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, kper, m->ba, 2 * LV_HEADS)); k++;
-            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, DELTA_IN, H, 0, QB_EPI_PLAIN,
-                                  nullptr, nullptr, 0)); k++;
-            if (m->fused && n <= CR - CONV_K + 1) {
-                QB_TRY(qb_delta_mixer(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.norm_w,
-                                      L.mem, L.sst, L.meta, nullptr, m->mix, m->seg_start, m->seg_len, m->seg_slot,
-                                      m->seg_pos0, m->segs)); k++;
-            } else {
-                QB_TRY(qb_delta_conv(c, s, m->part, 1, n, m->ba, H / kper, L.conv_w, L.a_log, L.dt_bias, L.mem, L.sst,
-                                     m->cv, m->tok_slot, m->tok_pos)); k++;
-                QB_TRY(qb_delta_rule(c, s, m->part, 1, n, m->cv, L.mem, L.sst, L.meta, m->o, m->seg_start, m->seg_len,
-                                     m->seg_slot, m->seg_pos0, m->segs)); k++;
-                QB_TRY(qb_delta_norm(c, s, m->part, 1, n, L.norm_w, m->o, m->mix, L.meta, m->seg_len, m->seg_slot,
-                                     m->seg_pos0, m->segs)); k++;
+        QB_TRY(launch_in_proj(m, st, L, !chain || i == 0, k));
+        QB_TRY(launch_mixer(m, st, L, k));
+        if (chain) {
+            qb_chain ch = {};
+            ch.m = n; ch.mix = m->mix;
+            ch.out_w = L.out_w; ch.out_s = L.out_s; ch.gate_up_w = L.gate_up_w; ch.gate_up_s = L.gate_up_s;
+            ch.down_w = L.down_w; ch.down_s = L.down_s;
+            if (i + 1 < m->nlayers) {
+                const qb_layer& N = m->layers[i + 1].w;
+                ch.next_w = N.in_proj_w; ch.next_s = N.in_proj_s; ch.next_n = N.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
             }
-        } else {
-            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, ATTN_IN, H, 0, QB_EPI_PLAIN,
-                                  nullptr, nullptr, 0)); k++;
-            const float qscale = 1.4426950408889634f / 16.f;  // scores in base 2, over sqrt(HD)
-            QB_TRY(qb_attn_prep(c, s, m->part, 1, n, L.q_norm, L.k_norm, L.inv_freq, qscale, m->q, m->o, L.kc, L.vc,
-                                L.ks, L.vs, m->tok_slot, m->tok_pos, L.cap)); k++;
-            if (m->ndec > 0) {
-                QB_TRY(qb_attn_decode(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->dseg, m->dtok, m->dkeys, m->tok_slot,
-                                      m->tok_pos, L.cap, m->ndseg, m->ndec, m->dmax, m->dec_max_pos + 1, m->ml, m->acc,
-                                      m->o, m->mix)); k += 2;
-            }
-            if (m->ntile > 0) {
-                QB_TRY(qb_attn_prefill(c, s, m->q, L.kc, L.vc, L.ks, L.vs, m->ptile, m->tok_slot, m->tok_pos, L.cap,
-                                       m->ntile, m->tile_max_pos + 1, m->ml, m->acc, m->o, m->mix));
-                k += qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) > 1 ? 2 : 1;
-            }
+            ch.post_norm = L.post_norm; ch.next_norm = w_next;
+            ch.h = m->h; ch.h_tmp = m->h2; ch.part_h = m->part_h; ch.mid = m->mid; ch.xn = m->xn; ch.part = m->part;
+            ch.eps = EPS;
+            QB_TRY(qb_layer_chain(c, s, &ch)); k++;
+            continue;
         }
         QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
         QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
@@ -177,6 +216,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     m->layers.resize(nlayers);
     const size_t T = MAX_TOK;
     QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
+    QB_TRY(dalloc(&m->h2, (size_t)8 * H)); QB_TRY(dalloc(&m->part_h, (size_t)8 * H));  // the persistent layer kernel's
     QB_TRY(dalloc(&m->part, T * (size_t)DELTA_IN));
     QB_TRY(dalloc(&m->ba, (size_t)40 * 32 * 2 * LV_HEADS + 5 * T * 2 * LV_HEADS));  // 40 splits of 32 rows or 5 of T
     QB_TRY(dalloc(&m->o, T * MIX)); QB_TRY(dalloc(&m->mix, T * MIX)); QB_TRY(dalloc(&m->mid, T * FF));
@@ -202,7 +242,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
 void qb_model_destroy(qb_model* m) {
     if (!m) return;
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
-    void* bufs[] = {m->h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
+    void* bufs[] = {m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
     cudaFreeHost(m->h_step);
@@ -241,6 +281,16 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
 int qb_model_use_graphs(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     m->use_graphs = on != 0;
+    return QB_OK;
+}
+
+int qb_model_use_chain(qb_model* m, int on) {
+    if (!m) return QB_ERR_ARG;
+    if (m->chain != (on != 0)) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->chain = on != 0;
     return QB_OK;
 }
 

@@ -124,6 +124,25 @@ class Context:
                                     _p(dev["tok_slot"]), _p(dev["tok_pos"]), cap, st["ntile"], st["tile_max_pos"] + 1,
                                     _p(part_ml), _p(part_acc), _p(out), _p(mix)), "qb_attn_prefill")
 
+    def layer_chain(self, m, mix, out, gate_up, down, nxt, post_norm, next_norm, h, h_tmp, part_h, mid, xn, part,
+                    eps=1e-6):
+        """qb_layer_chain: out / gate_up / down / nxt are (words, scales) pairs of Marlin tensors; nxt may be None."""
+        from ._lib import QbChain
+        a = lambda t: t.data_ptr() if t is not None else None
+        c = QbChain()
+        c.m = m
+        c.mix = a(mix)
+        c.out_w, c.out_s = a(out[0]), a(out[1])
+        c.gate_up_w, c.gate_up_s = a(gate_up[0]), a(gate_up[1])
+        c.down_w, c.down_s = a(down[0]), a(down[1])
+        if nxt is not None:
+            c.next_w, c.next_s, c.next_n = a(nxt[0]), a(nxt[1]), nxt[2]
+        c.post_norm, c.next_norm = a(post_norm), a(next_norm)
+        c.h, c.h_tmp, c.part_h, c.mid, c.xn, c.part = a(h), a(h_tmp), a(part_h), a(mid), a(xn), a(part)
+        c.eps = eps
+        import ctypes
+        check(lib().qb_layer_chain(self.h, _stream(), ctypes.byref(c)), "qb_layer_chain")
+
     # ---- DeltaNet
     def delta_conv(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, mem, sst, cv, dev):
         check(lib().qb_delta_conv(self.h, _stream(), _p(part), splits, n, _p(ba), ba_splits, _p(conv_w), _p(a_log),

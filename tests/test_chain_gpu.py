@@ -1,0 +1,95 @@
+"""The persistent layer kernel (qb_layer_chain: out_proj, residual + RMSNorm, gate_up with SwiGLU, down, residual +
+RMSNorm, the next in-projection in one cooperative launch) against the same chain run as the separate, individually
+parity-tested launches, and the whole step with and without it. Tolerance between the two: the products sum their k
+groups in different orders (f32), and a value of xn / mid on an f16 rounding boundary may flip, so outputs agree to the
+step tolerance rather than bit for bit; the residual stream after the first product agrees to f32 rounding."""
+import numpy as np
+import pytest
+import torch
+
+from qwenny_b200 import model as M
+
+pytestmark = pytest.mark.gpu
+H, MIX, FF = 5120, 6144, 17408
+
+
+def rel(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm())
+
+
+def separate(ctx, m, mix, w, h):
+    """The chain as the step runner launches it without the persistent kernel."""
+    out, gu, down, nxt, post, nextn = w
+    h = h.clone()
+    xn = torch.empty(m, H, dtype=torch.float16, device="cuda")
+    part = ctx.marlin_gemm(mix, out.words, out.scales)
+    ctx.add_rmsnorm(h, part, 1, m, post, xn)
+    mid = ctx.marlin_gemm(xn, gu.words, gu.scales, epi="silu")
+    part = ctx.marlin_gemm(mid, down.words, down.scales)
+    ctx.add_rmsnorm(h, part, 1, m, nextn, xn)
+    y = ctx.marlin_gemm(xn, nxt.words, nxt.scales) if nxt is not None else None
+    return h, xn, mid, y
+
+
+@pytest.mark.parametrize("m,next_n", [(5, 16384), (1, 14336), (7, 16384), (3, 0)])
+def test_layer_chain_matches_separate_launches(ctx, m, next_n):
+    g = torch.Generator(device="cuda").manual_seed(300 + m)
+    out, gu, down = M.Marlin.random(H, MIX, g), M.Marlin.random(2 * FF, H, g), M.Marlin.random(H, FF, g)
+    nxt = M.Marlin.random(next_n, H, g) if next_n else None
+    post = (1 + 0.02 * torch.randn(H, generator=g, device="cuda")).float()
+    nextn = (1 + 0.02 * torch.randn(H, generator=g, device="cuda")).float()
+    mix = torch.randn(m, MIX, generator=g, device="cuda").half()
+    h0 = torch.randn(m, H, generator=g, device="cuda")
+    want_h, want_xn, want_mid, want_y = separate(ctx, m, mix, (out, gu, down, nxt, post, nextn), h0)
+
+    h, h_tmp, part_h = h0.clone(), torch.zeros(8, H, device="cuda"), torch.zeros(8, H, device="cuda")
+    mid = torch.zeros(m, FF, dtype=torch.float16, device="cuda")
+    xn = torch.zeros(m, H, dtype=torch.float16, device="cuda")
+    part = torch.zeros(m, max(next_n, 1), device="cuda")
+    for rep in range(2):  # the second launch finds the barriers and tickets as the first left them
+        h.copy_(h0)
+        ctx.layer_chain(m, mix, (out.words, out.scales), (gu.words, gu.scales), (down.words, down.scales),
+                        (nxt.words, nxt.scales, next_n) if nxt is not None else None, post, nextn, h, h_tmp, part_h,
+                        mid, xn, part)
+        torch.cuda.synchronize()
+        assert ctx.device_error() == 0
+        assert rel(mid.float(), want_mid.float()) < 2e-3
+        assert rel(h, want_h) < 1e-4
+        assert rel(xn.float(), want_xn.float()) < 2e-3
+        if nxt is not None:
+            assert rel(part, want_y) < 2e-3
+            ok = (part - want_y).abs() <= 2e-3 + 1e-2 * want_y.abs()
+            assert ok.float().mean() > 0.999
+
+
+def test_layer_chain_rejects(ctx):
+    from qwenny_b200 import QbError
+    g = torch.Generator(device="cuda").manual_seed(310)
+    out = M.Marlin.random(H, MIX, g)
+    z = torch.zeros(8, H, device="cuda")
+    with pytest.raises(QbError):  # more rows than the resident X holds
+        ctx.layer_chain(8, z.half(), (out.words, out.scales), (out.words, out.scales), (out.words, out.scales), None, z[0],
+                        z[0], z, z, z, z.half(), z.half(), z)
+
+
+def test_step_with_and_without_chain(ctx):
+    """Greedy tokens and logits of verify steps with the persistent kernel on (default) and off."""
+    def fresh():
+        return M.synthetic(ctx, nlayers=4, slots=1, max_ctx=256, vocab=2000, seed=21)
+    a, b = fresh(), fresh()
+    b.use_chain(False)
+    seq = [(77 + 131 * i) % 2000 for i in range(40)]
+    pos = 0
+    while pos + 5 <= len(seq):
+        toks = [(seq[pos + i], 0, pos + i) for i in range(5)]
+        a.step(toks, list(range(5)))
+        b.step(toks, list(range(5)))
+        la, lb = a.logits(), b.logits()
+        assert rel(la, lb) < 2e-3
+        ta, tb = a.argmax(), b.argmax()
+        srt = lb.sort(dim=1).values
+        for r in range(5):
+            assert ta[r] == tb[r] or float(srt[r, -1] - srt[r, -2]) < 1e-3
+        pos += 3
+    assert a.step_kernels < b.step_kernels
