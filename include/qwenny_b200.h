@@ -234,7 +234,8 @@ int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
 int qb_model_use_fused(qb_model* m, int on);
-/* on (default): steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers */
+/* on: steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers (default off: measured
+ * slower than the separate launches) */
 int qb_model_use_chain(qb_model* m, int on);
 /* Engine::argmax (src/cuda/core.rs:1100-1103): greedy token per logit row of the last step; synchronises the stream */
 int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);

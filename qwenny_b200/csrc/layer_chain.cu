@@ -60,6 +60,9 @@ struct ChainArgs {
     unsigned* gbar;
     int* err;
     float eps;
+    int probe;          // measurement only: 1 = consumers release every stage unread, 2 = no residual / norm prologue
+    long long* trace;   // measurement only (may be null): per block 17 timestamps (ns): per phase {begin, X ready,
+                        // first stage landed, share written}, then the end
 };
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
@@ -214,9 +217,11 @@ __global__ void __launch_bounds__(CH_THREADS, 1) layer_chain_kernel(const __grid
     bool dead = false;
     int slot = 0, wrap = 0;
 
+    long long* tr = a.trace ? a.trace + (size_t)blockIdx.x * 17 : nullptr;
     for (int p = 0; p < a.nph; p++) {
         const ChainPhase& P = a.ph[p];
-        if (P.xmode == CH_X_NORM) {
+        if (tr && tid == 0) tr[4 * p] = global_ns();
+        if (P.xmode == CH_X_NORM && a.probe != 2) {
             // ---- every block: h_out = h_in + add, resident X = norm_w * h_out / rms(h_out), after the barrier of the
             // phase that produced `add`
             if (p > 0) {
@@ -272,6 +277,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) layer_chain_kernel(const __grid
             }
             named_bar_sync(3, NCT);  // the resident X is complete
         }
+        if (tr && tid == 0) tr[4 * p + 1] = global_ns();
         if (!P.B) continue;
 
         int beg, end, kst;
@@ -287,8 +293,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1) layer_chain_kernel(const __grid
             } else {
                 for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], par); i++) {}
             }
+            if (tr && tid == 0 && x == beg) tr[4 * p + 2] = global_ns();
             const uint8_t* base = stages + (size_t)slot * STAGE_BYTES;
-            {
+            if (a.probe != 1) {
                 const uint4* wp = (const uint4*)(base + (size_t)(kg * 8 * CH_CG + cg) * 512) + lane;
                 // ldmatrix row address of this lane: token row lane % 8 of the stage's X slice or of the resident X, or
                 // the zero row past the m live rows; columns 8 (lane / 8) of each pair of k16 steps
@@ -414,6 +421,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) layer_chain_kernel(const __grid
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[b][i] = 0.f;
         }
+        if (tr && tid == 0) tr[4 * p + 3] = global_ns();
         // ---- the block's share of the product is written: arrive at the phase's barrier
         if (p + 1 < a.nph) {
             __threadfence();
@@ -426,6 +434,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) layer_chain_kernel(const __grid
     }
     // ---- the last block to leave clears the barriers for the next launch
     named_bar_sync(3, NCT);
+    if (tr && tid == 0) tr[16] = global_ns();
     if (tid == 0) {
         __threadfence();
         unsigned old = atomicAdd(a.gbar + CH_BAR_EXIT, 1u);
@@ -472,6 +481,9 @@ int qb_layer_chain(qb_ctx* ctx, void* stream, const qb_chain* c) {
     a.counters = ctx->counters;
     a.gbar = ctx->gbar;
     a.err = ctx->err;
+    a.probe = ctx->probe;
+    a.trace = ctx->trace;
+    if (ctx->trace) ctx->trace += 4 * 1024;  // the next launch's slots
 
     const int grid = ctx->sms;
     // the most blocks that share a column block: a block's range is at least floor(total / grid) stages

@@ -61,7 +61,10 @@ struct qb_model {
     int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0,
         tile_max_pos = 0;
     std::map<GraphKey, cudaGraphExec_t> graphs;
-    bool use_graphs = true, fused = true, chain = true;
+    bool use_graphs = true, fused = true;
+    // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
+    // shared memory with the resident X and every grid barrier waits for the slowest block): off unless asked for
+    bool chain = false;
     long long launches = 0;  // kernels launched (or replayed) since creation
     int step_kernels = 0;    // kernels of the last step
     int ba_kper = 1024;      // k range of a split of the DeltaNet 16-bit in-projection in the current step

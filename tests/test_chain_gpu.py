@@ -74,11 +74,11 @@ def test_layer_chain_rejects(ctx):
 
 
 def test_step_with_and_without_chain(ctx):
-    """Greedy tokens and logits of verify steps with the persistent kernel on (default) and off."""
+    """Greedy tokens and logits of verify steps with the persistent kernel on and off (the default)."""
     def fresh():
         return M.synthetic(ctx, nlayers=4, slots=1, max_ctx=256, vocab=2000, seed=21)
     a, b = fresh(), fresh()
-    b.use_chain(False)
+    a.use_chain(True)
     seq = [(77 + 131 * i) % 2000 for i in range(40)]
     pos = 0
     while pos + 5 <= len(seq):
