@@ -31,7 +31,9 @@ typedef struct qb_ctx qb_ctx;
 enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2 };
 
 /* ---- context: what Gemm::load allocates once (src/cuda/core.rs:437-464: SM count, Marlin's `red` and `locks`).
- * Allocates the split-K scratch and tickets on `device`; everything after creation is allocation-free. */
+ * Allocates the split-K scratch and tickets on `device`; everything after creation is allocation-free. Like the
+ * reference's single `red` / `locks` pair, a context serves one stream at a time: launches that share a context must
+ * not overlap on the device (models that run concurrently take a context each). */
 int qb_create(int device, qb_ctx** out);
 void qb_destroy(qb_ctx* ctx);
 /* Non-zero once a kernel gave up a bounded wait (1 producer, 2 consumer, ...); reads and clears the word (syncs). */

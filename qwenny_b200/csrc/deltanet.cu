@@ -105,51 +105,84 @@ delta_conv_kernel(const float* p, int splits, int n, const float* ba, int ba_spl
 }
 
 // ------------------------------------------------------------------------------------------------ delta_rule
-constexpr int RCOLS = 32;               // value columns per block
-constexpr int LPC = 4;                  // lanes per column
-constexpr int RPT = LKD / LPC;          // key rows per thread: rows 4 (rg + LPC j) + i
-constexpr int RNT = RCOLS * LPC;        // 128 threads
-constexpr int RSLICES = LVD / RCOLS;    // 4
-constexpr int TCH = 8;                  // tokens staged per round
+// Geometry: 128 threads per block, LPC lanes per value column, 128 / LPC columns per block. LPC = 4 (32 key rows per
+// thread, the reference's split) for decode steps; LPC = 8 (16 rows per thread, twice the blocks and warps) for
+// prompt segments, where the per-token dependency chain, not the state traffic, sets the pace. Both add a column's
+// products in the same order, so a state is bit for bit the same whichever ran.
+constexpr int RCOLS = 32;               // value columns per block at most (LPC = 4)
+constexpr int RNT = 128;                // threads
+constexpr int TCH = 8;                  // tokens staged per round (two rounds of shared memory: one computing, one landing)
 
 struct Round {
     float q[TCH][LKD], k[TCH][LKD], v[TCH][RCOLS], e[TCH], b[TCH], kq[TCH];
 };
 
-__device__ __forceinline__ void ld_rows(float* x, const float* src, int rg) {
+// The rows of a thread. LPC = 4, sub = rg: rows 4 (rg + 4 j) + i as x[4 j + i], j < 8, i < 4.
+// LPC = 8, sub = 4 ih + rg: rows 4 (rg + 4 j) + 2 ih + e as x[2 j + e], j < 8, e < 2 (the same rows, split by i / 2).
+template <int LPC>
+__device__ __forceinline__ void ld_rows(float* x, const float* src, int sub) {
+    if (LPC == 4) {
 #pragma unroll
-    for (int j = 0; j < RPT / 4; j++) {
-        float4 v = ld4(src + 4 * (rg + LPC * j));
-        x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
+        for (int j = 0; j < 8; j++) {
+            float4 v = ld4(src + 4 * (sub + 4 * j));
+            x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float2 v = *(const float2*)(src + 4 * ((sub & 3) + 4 * j) + 2 * (sub >> 2));
+            x[2 * j] = v.x; x[2 * j + 1] = v.y;
+        }
     }
 }
-__device__ __forceinline__ void st_rows(float* dst, const float* x, int rg) {
+template <int LPC>
+__device__ __forceinline__ void st_rows(float* dst, const float* x, int sub) {
+    if (LPC == 4) {
 #pragma unroll
-    for (int j = 0; j < RPT / 4; j++)
-        *(float4*)(dst + 4 * (rg + LPC * j)) = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        for (int j = 0; j < 8; j++)
+            *(float4*)(dst + 4 * (sub + 4 * j)) = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            *(float2*)(dst + 4 * ((sub & 3) + 4 * j) + 2 * (sub >> 2)) = make_float2(x[2 * j], x[2 * j + 1]);
+    }
 }
 __device__ __forceinline__ float col_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     return v;
 }
-// S^T x for the thread's rows: four interleaved partial sums, (a + b) + (c + d), then the column's 4 lanes. Replayed
-// and fresh tokens share this function, so a replayed state is bit for bit the state one token per step reaches.
+// S^T x for the thread's rows: the partial sum of the rows with the same i (row % 4) runs over j in order; then
+// (d0 + d1) + (d2 + d3) (inside the thread for LPC = 4, across the ih lanes for LPC = 8), then the column's 4 rg lanes.
+// Replayed and fresh tokens share this function, so a replayed state is bit for bit the state one token per step
+// reaches.
+template <int LPC>
 __device__ __forceinline__ float dot_rows(const float* S, const float* x) {
-    float d4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (LPC == 4) {
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < RPT; j++) d4[j & 3] += S[j] * x[j];
-    return col_sum((d4[0] + d4[1]) + (d4[2] + d4[3]));
+        for (int j = 0; j < 32; j++) d4[j & 3] += S[j] * x[j];
+        return col_sum((d4[0] + d4[1]) + (d4[2] + d4[3]));
+    } else {
+        float d2[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 16; j++) d2[j & 1] += S[j] * x[j];
+        float s = d2[0] + d2[1];
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        return col_sum(s);
+    }
 }
 
+template <int LPC>
 __global__ void __launch_bounds__(RNT)
 delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem, long long sst, const int* meta,
                   float* out, const int* seg_start, const int* seg_len, const int* seg_slot, const int* seg_pos0) {
-    __shared__ __align__(16) Round R;
+    constexpr int COLS = RNT / LPC, RPT = LKD / LPC, SLICES = LVD / COLS;
+    __shared__ __align__(16) Round Rb[2];  // the round being computed and the one in flight (cp.async)
     pdl_launch_dependents();
     const int slice = blockIdx.x, h = blockIdx.y, sg = blockIdx.z, kh = h / (LV_HEADS / LK_HEADS);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = lane % LPC;
-    const int lc = warp * (32 / LPC) + lane / LPC, col = slice * RCOLS + lc;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = lane % LPC;  // rg: the lane's place in its column
+    const int lc = warp * (32 / LPC) + lane / LPC, col = slice * COLS + lc;
     // the segment arrays and the slot metadata were written before this step's first kernel
     const int t0 = seg_start[sg], len = seg_len[sg], slot = seg_slot[sg], p0 = seg_pos0[sg];
     const Plan pl = make_plan(meta, slot, p0, len);
@@ -163,14 +196,14 @@ delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem
 #pragma unroll
         for (int i = 0; i < RPT; i++) S[i] = 0.f;
     } else {
-        ld_rows(S, sbuf(pl.in), rg);
+        ld_rows<LPC>(S, sbuf(pl.in), rg);
     }
     // replay the accepted tokens between the checkpoint and the restart position, from the bank
     for (int i = 0; i < pl.r; i++) {
         const float* e = entry(pl.in, pl.from + i);
         float k[RPT];
-        ld_rows(k, e + kh * LKD, rg);
-        float dk = dot_rows(S, k);
+        ld_rows<LPC>(k, e + kh * LKD, rg);
+        float dk = dot_rows<LPC>(S, k);
         float ex = e[LK_HEADS * LKD + LV_HEADS * LVD + h], be = e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h];
         float delta = (e[LK_HEADS * LKD + h * LVD + col] - ex * dk) * be;
 #pragma unroll
@@ -178,24 +211,32 @@ delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem
     }
     pdl_wait();
 
-    for (int c0 = 0; c0 < len; c0 += TCH) {
+    // stage a round with asynchronous copies: q and k of the key head, the block's v columns, the gates of head h
+    auto stage = [&](Round& R, int c0) {
         const int m = min(TCH, len - c0);
-        // stage the round: q and k of the key head, the block's v columns, the gates of head h
         for (int x = tid; x < m * (LKD / 4); x += RNT) {
             int tk = x / (LKD / 4), d = (x % (LKD / 4)) * 4;
             const float* row = cv + (size_t)(t0 + c0 + tk) * CVW + kh * LKD + d;
-            *(float4*)&R.q[tk][d] = ld4(row);
-            *(float4*)&R.k[tk][d] = ld4(row + LK_HEADS * LKD);
+            cp_async16(&R.q[tk][d], row);
+            cp_async16(&R.k[tk][d], row + LK_HEADS * LKD);
         }
-        for (int x = tid; x < m * (RCOLS / 4); x += RNT) {
-            int tk = x / (RCOLS / 4), d = (x % (RCOLS / 4)) * 4;
-            *(float4*)&R.v[tk][d] = ld4(cv + (size_t)(t0 + c0 + tk) * CVW + 2 * LK_HEADS * LKD + h * LVD + slice * RCOLS + d);
+        for (int x = tid; x < m * (COLS / 4); x += RNT) {
+            int tk = x / (COLS / 4), d = (x % (COLS / 4)) * 4;
+            cp_async16(&R.v[tk][d], cv + (size_t)(t0 + c0 + tk) * CVW + 2 * LK_HEADS * LKD + h * LVD + slice * COLS + d);
         }
         if (tid < 2 * m) {
             int tk = tid >> 1, which = tid & 1;
-            (which ? R.b : R.e)[tk] = cv[(size_t)(t0 + c0 + tk) * CVW + LQKV + which * LV_HEADS + h];
+            cp_async4(&(which ? R.b : R.e)[tk], cv + (size_t)(t0 + c0 + tk) * CVW + LQKV + which * LV_HEADS + h);
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    stage(Rb[0], 0);
+    for (int c0 = 0, rb = 0; c0 < len; c0 += TCH, rb ^= 1) {
+        const int m = min(TCH, len - c0);
+        Round& R = Rb[rb];
+        cp_async_wait_all();
+        __syncthreads();  // the round has landed, and every thread is past the previous round (its buffer is free)
+        if (c0 + TCH < len) stage(Rb[rb ^ 1], c0 + TCH);
         // k . q per token: warp w takes tokens w, w + 4
         for (int tk = warp; tk < m; tk += RNT / 32) {
             float4 a = ld4(&R.q[tk][lane * 4]), b = ld4(&R.k[tk][lane * 4]);
@@ -207,7 +248,7 @@ delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem
             float* e = entry(pl.cbuf, p0 + c0 + tk);
             if (slice == 0 && h % (LV_HEADS / LK_HEADS) == 0 && tid < LKD / 4)
                 *(float4*)(e + kh * LKD + tid * 4) = ld4(&R.k[tk][tid * 4]);
-            if (tid < RCOLS) e[LK_HEADS * LKD + h * LVD + slice * RCOLS + tid] = R.v[tk][tid];
+            if (tid < COLS) e[LK_HEADS * LKD + h * LVD + slice * COLS + tid] = R.v[tk][tid];
             if (slice == 0 && tid == 0) {
                 e[LK_HEADS * LKD + LV_HEADS * LVD + h] = R.e[tk];
                 e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h] = R.b[tk];
@@ -215,22 +256,21 @@ delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem
         }
         __syncthreads();
         for (int tk = 0; tk < m; tk++) {
-            if (pl.wck && p0 + c0 + tk == pl.ck) st_rows(sbuf(pl.cbuf), S, rg);
+            if (pl.wck && p0 + c0 + tk == pl.ck) st_rows<LPC>(sbuf(pl.cbuf), S, rg);
             float k[RPT], q[RPT];
-            ld_rows(k, R.k[tk], rg);
-            ld_rows(q, R.q[tk], rg);
-            float dk = dot_rows(S, k), dq = dot_rows(S, q);
+            ld_rows<LPC>(k, R.k[tk], rg);
+            ld_rows<LPC>(q, R.q[tk], rg);
+            float dk = dot_rows<LPC>(S, k), dq = dot_rows<LPC>(S, q);
             float ex = R.e[tk], delta = (R.v[tk][lc] - ex * dk) * R.b[tk];
             if (rg == 0) out[(size_t)(t0 + c0 + tk) * MIX + h * LVD + col] = ex * dq + delta * R.kq[tk];
 #pragma unroll
             for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
         }
-        __syncthreads();
     }
-    st_rows(sbuf(pl.ebuf), S, rg);
+    st_rows<LPC>(sbuf(pl.ebuf), S, rg);
     // conv ring: the conv inputs of the segment's last CR tokens, this block's share of the channels
-    const int NB = RSLICES * LV_HEADS, CH = (LQKV + NB - 1) / NB;
-    const int cb = (h * RSLICES + slice) * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
+    const int NB = SLICES * LV_HEADS, CH = (LQKV + NB - 1) / NB;
+    const int cb = (h * SLICES + slice) * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
     for (int i = tid; i < mm * ch; i += RNT) {
         int tk = len - mm + i / ch, c = cb + i % ch;
         float v = 0.f;
@@ -238,6 +278,8 @@ delta_rule_kernel(const float* p, int splits, int n, const float* cv, float* mem
         sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
     }
 }
+
+constexpr int LPC = 4, RPT = LKD / LPC;  // the decode geometry, shared with the one-launch mixer below
 
 // ------------------------------------------------------------------------------------------------ delta_norm
 constexpr int NORM_HEADS = 16;
@@ -286,8 +328,12 @@ int qb_delta_rule(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
     if (!ctx || !p || !cv || !mem || !meta || !out || !seg_start || !seg_len || !seg_slot || !seg_pos0 || n <= 0 ||
         segs <= 0 || splits < 1)
         return QB_ERR_ARG;
-    return launch(ctx, delta_rule_kernel, dim3(RSLICES, LV_HEADS, segs), dim3(RNT), 0, (cudaStream_t)stream, p, splits,
-                  n, cv, mem, sst, meta, out, seg_start, seg_len, seg_slot, seg_pos0);
+    // steps with prompt segments take the finer geometry (same bits, more blocks and warps)
+    if (n >= 64)
+        return launch(ctx, delta_rule_kernel<8>, dim3(LVD / (RNT / 8), LV_HEADS, segs), dim3(RNT), 0, (cudaStream_t)stream,
+                      p, splits, n, cv, mem, sst, meta, out, seg_start, seg_len, seg_slot, seg_pos0);
+    return launch(ctx, delta_rule_kernel<4>, dim3(LVD / (RNT / 4), LV_HEADS, segs), dim3(RNT), 0, (cudaStream_t)stream, p,
+                  splits, n, cv, mem, sst, meta, out, seg_start, seg_len, seg_slot, seg_pos0);
 }
 
 int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, const float* nw, const float* out,
@@ -350,15 +396,15 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
 #pragma unroll
         for (int i = 0; i < RPT; i++) S[i] = 0.f;
     } else {
-        ld_rows(S, sbuf(pl.in), rg);
+        ld_rows<4>(S, sbuf(pl.in), rg);
     }
     if (tid < FCH) *(float4*)R.w[tid] = ld4(cw + gchan(tid) * CONV_K);
     const float nwv = nw[tid % LVD], alog = a_log[h], dtb = dt_bias[h];
     for (int i = 0; i < pl.r; i++) {
         const float* e = entry(pl.in, pl.from + i);
         float k[RPT];
-        ld_rows(k, e + kh * LKD, rg);
-        float dk = dot_rows(S, k);
+        ld_rows<4>(k, e + kh * LKD, rg);
+        float dk = dot_rows<4>(S, k);
         float ex = e[LK_HEADS * LKD + LV_HEADS * LVD + h], be = e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h];
         float delta = (e[LK_HEADS * LKD + h * LVD + col] - ex * dk) * be;
 #pragma unroll
@@ -449,11 +495,11 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
         __syncthreads();
         // ---- the recurrence
         for (int tk = 0; tk < m; tk++) {
-            if (pl.wck && p0 + c0 + tk == pl.ck) st_rows(sbuf(pl.cbuf), S, rg);
+            if (pl.wck && p0 + c0 + tk == pl.ck) st_rows<4>(sbuf(pl.cbuf), S, rg);
             float k[RPT], q[RPT];
-            ld_rows(k, &R.c[tk][LKD], rg);
-            ld_rows(q, &R.c[tk][0], rg);
-            float dk = dot_rows(S, k), dq = dot_rows(S, q);
+            ld_rows<4>(k, &R.c[tk][LKD], rg);
+            ld_rows<4>(q, &R.c[tk][0], rg);
+            float dk = dot_rows<4>(S, k), dq = dot_rows<4>(S, q);
             float ex = R.e[tk], delta = (R.c[tk][2 * LKD + col] - ex * dk) * R.b[tk];
             if (rg == 0) R.o[tk][col] = ex * dq + delta * R.kq[tk];
 #pragma unroll
@@ -475,7 +521,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
         }
         __syncthreads();
     }
-    st_rows(sbuf(pl.ebuf), S, rg);
+    st_rows<4>(sbuf(pl.ebuf), S, rg);
     // ---- the last block of the launch records the segments' steps in the slot metadata
     __shared__ int last;
     if (tid == 0) {

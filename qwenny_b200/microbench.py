@@ -127,6 +127,38 @@ def step(args):
           f"{m.step_kernels} kernels, greedy {tok}, device error {ctx.device_error()}")
 
 
+def delta(args):
+    """The DeltaNet kernels of one prompt segment: conv once, then the rule kernel timed alone."""
+    ctx = Context(0)
+    n = args.rows
+    g = torch.Generator(device="cuda").manual_seed(0)
+    LQKV, DELTA_IN, LVH, CVW, MIX = 10240, 16384, 48, 10336, 6144
+    sst = (2 * 48 * 128 * 128 + 2 * 16 * 8288 + 32 * LQKV + 1023) // 1024 * 1024
+    part = torch.randn(1, n, DELTA_IN, generator=g, device="cuda")
+    ba = torch.randn(1, n, 2 * LVH, generator=g, device="cuda")
+    conv_w = torch.randn(LQKV, 4, generator=g, device="cuda") * 0.3
+    a_log, dt_bias = torch.randn(LVH, generator=g, device="cuda") * 0.5, torch.randn(LVH, generator=g, device="cuda") * 0.5
+    mem = torch.zeros(sst, device="cuda")
+    meta = torch.tensor([[-1, 0, 0, 0]], dtype=torch.int32, device="cuda")
+    dev = {k: torch.zeros(n + 8, dtype=torch.int32, device="cuda") for k in ("tok_slot", "seg_start", "seg_slot", "seg_pos0")}
+    dev["tok_pos"] = torch.arange(n + 8, dtype=torch.int32, device="cuda")
+    dev["seg_len"] = torch.full((8,), n, dtype=torch.int32, device="cuda")
+    cv = torch.zeros(n, CVW, device="cuda")
+    o = torch.zeros(n, MIX, device="cuda")
+    ctx.delta_conv(part, 1, n, ba, 1, conv_w, a_log, dt_bias, mem, sst, cv, dev)
+    for _ in range(args.reps):
+        ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.reps
+    print(f"delta_rule rows={n}: {us:.1f} us/launch = {us * 1e3 / n:.0f} ns/token, device error {ctx.device_error()}")
+
+
 def chain(args):
     """The persistent layer kernel alone: out_proj, norm, gate_up, down, norm, next in-projection."""
     from ._lib import lib
@@ -200,6 +232,9 @@ def main():
     c.add_argument("--no-graph", action="store_true"); c.add_argument("--no-pdl", action="store_true")
     c.add_argument("--chain", action="store_true", help="the persistent layer kernel instead of separate launches")
     c.set_defaults(fn=step)
+    e = sub.add_parser("delta")
+    e.add_argument("--rows", type=int, default=2048); e.add_argument("--reps", type=int, default=5)
+    e.set_defaults(fn=delta)
     d = sub.add_parser("chain")
     d.add_argument("--rows", type=int, default=5); d.add_argument("--reps", type=int, default=20)
     d.add_argument("--no-pdl", action="store_true"); d.add_argument("--plain", action="store_true")

@@ -226,3 +226,37 @@ def test_fused_mixer_matches_the_three_kernels(ctx, case):
     assert torch.allclose(y1.float(), y2.float(), rtol=2e-3, atol=1e-6)
     assert torch.allclose(mem1, mem2, rtol=2e-6, atol=2e-6)   # far inside the 1e-4 bound on the f32 state
     assert torch.equal(mem1 != mem, mem2 != mem)              # the same places were written
+
+
+def test_prompt_geometry_gives_the_same_bits(ctx):
+    """Steps with prompt segments run the delta rule with 8 lanes per value column instead of 4 (twice the blocks);
+    both add a column's products in the same order: a 150-token prompt in one step (fine geometry) leaves exactly the
+    raw outputs and the end state of the same prompt in steps of 50 (decode geometry), and a 70-token continuation
+    that restarts inside the previous step's last 16 tokens replays from the bank to the same bits."""
+    g = synth.gen(97)
+    w = [t.cuda() for t in weights(g)]
+    T = 220
+    part = torch.randn(1, T, R.DELTA_IN, generator=g).cuda()
+    ba = torch.randn(1, T, 2 * R.LV_HEADS, generator=g).cuda()
+
+    def sl(t, i, j):
+        return t[:, i:j].contiguous()
+
+    def run(cuts):
+        mem = torch.zeros(SST, device="cuda")
+        meta = torch.tensor([[-1, 0, 0, 0]], dtype=torch.int32, device="cuda")
+        outs = {}
+        for a, b in cuts:
+            _, o = layer_step(ctx, w, mem, meta, sl(part, a, b), sl(ba, a, b), [(0, 0, i) for i in range(a, b)])
+            for i in range(a, b):
+                outs[i] = o[i - a].clone()
+        mt = meta.cpu().numpy()[0]
+        return outs, mem[mt[2] * R.SLOT_STATE:(mt[2] + 1) * R.SLOT_STATE].clone(), mt
+    # 150 in one step, then restart 10 tokens back (a rejected tail) with 80 tokens: both steps in the fine geometry
+    fine, sf, mf = run([(0, 150), (140, 220)])
+    # the same positions in steps of at most 50 tokens (decode geometry), restarting at 140 too
+    coarse, sc, mc = run([(0, 50), (50, 100), (100, 150), (140, 190), (190, 220)])
+    assert mf[0] == mc[0] == T
+    for i in range(T):
+        assert torch.equal(fine[i], coarse[i]), f"position {i}"
+    assert torch.equal(sf, sc)

@@ -99,6 +99,7 @@ def test_full_prompt_chunk(ctx):
     seq = [(1000 + 7919 * i) % 2000 for i in range(n + 1)]
     for i in range(n):
         a.step([(seq[i], 0, i)], [0])
+    torch.cuda.synchronize()  # the two models share one context (scratch, tickets): one stream at a time
     toks, out = [(seq[i], 0, i) for i in range(n)], [n - 1, 100, 1000]
     b.step(toks, out)
     logits, want, h, xn = cpu.step(toks, out)
@@ -110,6 +111,7 @@ def test_full_prompt_chunk(ctx):
         return np.linalg.norm(x - y) / np.linalg.norm(y) < 4e-3
     assert near(b.logits()[0].cpu().numpy(), a.logits()[0].cpu().numpy())
     a.step([(seq[n], 0, n)], [0])
+    torch.cuda.synchronize()
     b.step([(seq[n], 0, n)], [0])
     assert near(b.logits().cpu().numpy(), a.logits().cpu().numpy())
     assert near(b.hidden().cpu().numpy(), a.hidden().cpu().numpy())
