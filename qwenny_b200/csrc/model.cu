@@ -53,6 +53,11 @@ struct qb_model {
     unsigned* seen = nullptr;
     // step arrays (Step), one device allocation and one pinned host mirror: a single copy per step
     int *d_step = nullptr, *h_step = nullptr;
+    // two pinned mirrors in turn, each guarded by an event recorded after its copy: a caller may queue step after step
+    // without waiting, and a mirror is rewritten only once the copy that read it has run
+    int* h_mirror[2] = {nullptr, nullptr};
+    cudaEvent_t h_event[2] = {nullptr, nullptr};
+    int h_cur = 0;
     size_t step_ints = 0;
     int *ids, *tok_slot, *tok_pos, *seg_start, *seg_len, *seg_slot, *seg_pos0, *dtok, *dseg, *dkeys, *ptile, *out_rows,
         *mark, *mark_at;
@@ -230,9 +235,13 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     StepLayout L;
     m->step_ints = L.total;
     QB_TRY(dalloc(&m->d_step, L.total));
-    QB_CUDA(cudaMallocHost((void**)&m->h_step, L.total * sizeof(int)));
+    for (int i = 0; i < 2; i++) {
+        QB_CUDA(cudaMallocHost((void**)&m->h_mirror[i], L.total * sizeof(int)));
+        std::memset(m->h_mirror[i], 0, L.total * sizeof(int));
+        QB_CUDA(cudaEventCreateWithFlags(&m->h_event[i], cudaEventDisableTiming));
+    }
+    m->h_step = m->h_mirror[0];
     QB_CUDA(cudaMallocHost((void**)&m->h_keys, MAX_OUT * sizeof(unsigned long long)));
-    std::memset(m->h_step, 0, L.total * sizeof(int));
     int* d = m->d_step;
     m->ids = d + L.ids; m->tok_slot = d + L.tok_slot; m->tok_pos = d + L.tok_pos; m->seg_start = d + L.seg_start;
     m->seg_len = d + L.seg_len; m->seg_slot = d + L.seg_slot; m->seg_pos0 = d + L.seg_pos0; m->dtok = d + L.dtok;
@@ -248,7 +257,10 @@ void qb_model_destroy(qb_model* m) {
     void* bufs[] = {m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
-    cudaFreeHost(m->h_step);
+    for (int i = 0; i < 2; i++) {
+        cudaFreeHost(m->h_mirror[i]);
+        if (m->h_event[i]) cudaEventDestroy(m->h_event[i]);
+    }
     cudaFreeHost(m->h_keys);
     delete m;
 }
@@ -314,7 +326,9 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
     for (int i = 0; i < n_out; i++)
         if (out[i] < 0 || out[i] >= n) return QB_ERR_ARG;
     StepLayout L;
-    int* h = m->h_step;
+    m->h_cur ^= 1;
+    QB_CUDA(cudaEventSynchronize(m->h_event[m->h_cur]));  // the copy that last read this mirror has run
+    int* h = m->h_step = m->h_mirror[m->h_cur];
     int segs = 0;
     for (int i = 0; i < n; i++) {
         const qb_tok& t = toks[i];
@@ -365,6 +379,7 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
     h[L.mark_at + segs] = nmark;
     for (int i = 0; i < n_out; i++) h[L.out_rows + i] = out[i];
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    QB_CUDA(cudaEventRecord(m->h_event[m->h_cur], (cudaStream_t)stream));
     m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
     m->max_seg = max_seg; m->dec_max_pos = dec_max_pos; m->tile_max_pos = tile_max_pos;
     return QB_OK;

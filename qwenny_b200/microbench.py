@@ -91,8 +91,18 @@ def attn(args):
     out = gate.clone()
     mix = torch.zeros(n, MIX, dtype=torch.float16, device="cuda")
 
+    if n > 8:  # a prompt segment: tiles of 10 tokens
+        tiles = []
+        for o in range(0, n, 10):
+            tiles += [o, min(10, n - o)]
+        dev["ptile"] = i32(tiles)
+        st = dict(ntile=len(tiles) // 2, tile_max_pos=pos0 + n - 1)
+
     def one():
-        ctx.attn_decode(q, kc, vc, ks, vs, dev, st, cap, ml, acc, out, mix)
+        if n > 8:
+            ctx.attn_prefill(q, kc, vc, ks, vs, dev, st, cap, ml, acc, out, mix)
+        else:
+            ctx.attn_decode(q, kc, vc, ks, vs, dev, st, cap, ml, acc, out, mix)
     if args.plain:
         for _ in range(args.reps):
             one()
@@ -101,6 +111,11 @@ def attn(args):
         return
     us = _time_graph(one, torch.cuda.Stream(), args.reps)
     by = NKV * 520 * (pos0 + n)
+    if n > 8:
+        fl = 4.0 * HD * NH * sum(pos0 + i + 1 for i in range(n))  # causal: row i sees pos0 + i + 1 keys
+        print(f"attn context={pos0} rows={n}: {us:.1f} us per prompt attention, {fl / us / 1e6:.1f} TFLOP/s; "
+              f"device error {ctx.device_error()}")
+        return
     print(f"attn context={pos0} rows={n}: {us:.2f} us per decode + combine, {by / us / 1e3:.0f} GB/s of {by / 1e6:.1f} MB; "
           f"device error {ctx.device_error()}")
 

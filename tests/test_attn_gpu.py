@@ -200,3 +200,27 @@ def test_attn_prefill_matches_decode_rows(ctx):
         one = run_decode(ctx, q[t:t + 1].contiguous(), gate[t:t + 1].contiguous(), cache, st1,
                          ref_cuda.upload_step(st1), cap, 1)
         assert close(out[t].cpu().numpy(), one[0].cpu().numpy()).all()
+
+
+def test_attn_prefill_pairs_and_segment_boundaries(ctx, ref):
+    """Steps with many tiles run two tiles per block. Two prompt segments of 25 and 33 tokens (3 + 4 tiles, one split):
+    tiles 0-1 and 4-5 pair up, tiles 2 and 3 belong to different sequences and run one after the other in their
+    block, tile 6 is alone."""
+    g = synth.gen(131)
+    cap = 1024
+    cache = make_cache(2, cap, g, 0)
+    toks = [(0, 0, 300 + i) for i in range(25)] + [(0, 1, 40 + i) for i in range(33)]
+    n = len(toks)
+    q = torch.randn(n, R.NH, R.HD, generator=g) * QSCALE
+    gate = torch.sigmoid(torch.randn(n, R.MIX, generator=g))
+    st = R.build_step(toks, list(range(n)))
+    assert st["ndec"] == 0 and st["ntile"] == 7
+    dv = ref_cuda.upload_step(st)
+    dc = [t.cuda() for t in cache]
+    mine, mix = run_prefill(ctx, q.cuda(), gate.cuda(), dc, st, dv, cap, n, mix=True)
+    theirs = run_prefill(ref, q.cuda(), gate.cuda(), dc, st, dv, cap, n)
+    a, b = mine.cpu().numpy(), theirs.cpu().numpy()
+    assert close(a, b).all()
+    assert np.array_equal(mix.cpu().numpy(), a.astype(np.float16))
+    want = R.attn_decode(q.numpy(), gate.numpy(), *[t.numpy() for t in cache], st["tok_slot"], st["tok_pos"], cap)
+    assert close(a, want).all()

@@ -87,10 +87,9 @@ def test_prompt_steps_match_cpu_oracle(ctx):
 
 def test_full_prompt_chunk(ctx):
     """The benchmark's prompt chunk, 2048 tokens in one step: against the CPU oracle of the same step (logits of three
-    rows, every row of the residual stream), and against 2048 single-token steps. The two GPU paths round differently
-    (the 16-row product applies a group's scale in f32 after the group's sum, the tensor-core product and the oracle
-    round weight * scale to f16 first, as the reference's kernels do), so they agree within the step tolerance of each
-    other, not bit for bit; the token after the prompt continues from either state."""
+    rows, every row of the residual stream), and against 2048 single-token steps (different summation orders in the
+    products and different softmax splits: agreement within the step tolerance, not bit for bit); the token after the
+    prompt continues from either state."""
     def fresh():
         return M.synthetic(ctx, nlayers=2, slots=1, max_ctx=2304, vocab=2000, seed=13, pattern=("delta", "attn"))
     a, b = fresh(), fresh()
@@ -106,17 +105,33 @@ def test_full_prompt_chunk(ctx):
     assert agree(b.logits().cpu().numpy(), logits) and agree(b.hidden().cpu().numpy(), h)
     assert b.argmax() == list(want)
 
-    def near(x, y):
-        # two rounding models 2048 tokens apart (states and int8 KV codes written under each): a relative L2 error of
-        # 1e-3 to 6e-3 per step was measured; the per-element tolerance of one product is 1e-2
+    def near(x, y):  # different products and softmax splits: twice the step tolerance
         x, y = np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64)
-        return np.linalg.norm(x - y) / np.linalg.norm(y) < 1e-2
+        return np.linalg.norm(x - y) / np.linalg.norm(y) < 4e-3
     assert near(b.logits()[0].cpu().numpy(), a.logits()[0].cpu().numpy())
     a.step([(seq[n], 0, n)], [0])
     torch.cuda.synchronize()
     b.step([(seq[n], 0, n)], [0])
     assert near(b.logits().cpu().numpy(), a.logits().cpu().numpy())
     assert near(b.hidden().cpu().numpy(), a.hidden().cpu().numpy())
+
+
+def test_queued_steps_equal_waited_steps(ctx):
+    """A caller may queue steps without waiting for any of them: each step's token arrays travel through a pinned
+    mirror that is not rewritten before its copy has run."""
+    a = M.synthetic(ctx, nlayers=2, slots=1, max_ctx=256, vocab=2000, seed=17, pattern=("delta", "attn"))
+    seq = [(31 + 577 * i) % 2000 for i in range(150)]
+    for i, t in enumerate(seq):
+        a.step([(t, 0, i)], [0])
+        a.logits()  # waits
+    la = a.logits().clone()
+    torch.cuda.synchronize()
+    b = M.synthetic(ctx, nlayers=2, slots=1, max_ctx=256, vocab=2000, seed=17, pattern=("delta", "attn"))
+    for i, t in enumerate(seq):
+        b.step([(t, 0, i)], [0])
+    assert torch.equal(b.logits(), la)
+    for name in ("kc", "vc", "ks", "vs"):
+        assert torch.equal(a.layers[1][name], b.layers[1][name])
 
 
 def test_rows_are_invariant_to_drafts(ctx):
