@@ -2,7 +2,10 @@
 
     python -m qwenny_b200.microbench gemv N K [--rows 5] [--epi plain|silu|argmax] [--reps 24] [--tune cg,kg,stages,ctas]
     python -m qwenny_b200.microbench attn [--context 32000] [--rows 5] [--reps 20]
-    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--no-graph] [--no-pdl]
+    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--chain]
+    python -m qwenny_b200.microbench prefill [--layers 64] [--prompt 32768] [--chunk 2048]
+    python -m qwenny_b200.microbench delta [--rows 2048]
+    python -m qwenny_b200.microbench chain [--rows 5] [--trace] [--probe 1|2]
 
 Each prints CUDA-event timings (launches replayed from a CUDA graph, inputs larger than L2 where the shape allows)
 and is small enough to sit under `ncu` (-k <kernel> -s <warm-up launches> -c <few>). Synthetic inputs, seeded.
@@ -142,6 +145,30 @@ def step(args):
           f"{m.step_kernels} kernels, greedy {tok}, device error {ctx.device_error()}")
 
 
+def prefill(args):
+    """A whole prompt through the full model in chunks (the prefill configuration of the benchmark: 32768 tokens in
+    2048-row chunks, 64 layers); reports the time of every chunk and the prompt's tok/s."""
+    ctx = Context(0)
+    ctx.set_pdl(True)
+    m = M.synthetic(ctx, nlayers=args.layers, max_ctx=args.prompt, vocab=151936)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 151936, (args.prompt,), generator=g).tolist()
+    chunks = [(a, min(args.prompt, a + args.chunk)) for a in range(0, args.prompt, args.chunk)]
+    for rep in range(2):  # the first pass warms up (kernel attributes, caches); the DeltaNet states restart at position 0
+        times = []
+        for a, b in chunks:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(m.stream)
+            m.step([(ids[i], 0, i) for i in range(a, b)], [b - a - 1])
+            e1.record(m.stream)
+            times.append((e0, e1))
+        tok = m.argmax()
+        ms = [x.elapsed_time(y) for x, y in times]
+    tot = sum(ms)
+    print(f"prefill layers={args.layers} prompt={args.prompt} chunk={args.chunk}: {tot:.1f} ms = {args.prompt / tot * 1e3:.0f} tok/s; "
+          f"first chunk {ms[0]:.1f} ms, last chunk {ms[-1]:.1f} ms; greedy {tok}, device error {ctx.device_error()}")
+
+
 def delta(args):
     """The DeltaNet kernels of one prompt segment: conv once, then the rule kernel timed alone."""
     ctx = Context(0)
@@ -247,6 +274,10 @@ def main():
     c.add_argument("--no-graph", action="store_true"); c.add_argument("--no-pdl", action="store_true")
     c.add_argument("--chain", action="store_true", help="the persistent layer kernel instead of separate launches")
     c.set_defaults(fn=step)
+    f = sub.add_parser("prefill")
+    f.add_argument("--layers", type=int, default=64); f.add_argument("--prompt", type=int, default=32768)
+    f.add_argument("--chunk", type=int, default=2048)
+    f.set_defaults(fn=prefill)
     e = sub.add_parser("delta")
     e.add_argument("--rows", type=int, default=2048); e.add_argument("--reps", type=int, default=5)
     e.set_defaults(fn=delta)
