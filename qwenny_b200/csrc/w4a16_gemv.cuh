@@ -10,9 +10,10 @@
 //  * consumer warp (cg, kg) owns 64 outputs x one scale group of the stage. The Marlin word of lane (g, t) holds
 //    outputs {g, g + 8} x columns {2t, 2t+1, 2t+8, 2t+9} of a 16-output block: exactly the A fragment of
 //    mma.m16n8k16 when the WEIGHTS are the A operand and the tokens the n = 8 side, so the nibbles go from one
-//    128-bit shared load through four lop3 and four hsub2 straight into the tensor core, no shuffles, no
-//    re-layout. The group scale is applied in f32 to the group's partial sum (exact, and 8x fewer multiplies
-//    than scaling every weight);
+//    128-bit shared load through one shift and four ands straight into the tensor core as f16 subnormals
+//    (n * 2^-24), no shuffles, no re-layout, no subtraction: the offset of 8 leaves through one extra mma per k16
+//    step. The group scale (times 2^24) is applied in f32 to the group's partial sum (exact, and 8x fewer
+//    multiplies than scaling every weight);
 //  * two ways to deal the work. Matrices whose column blocks x k splits fit one wave of blocks run CLUSTERED: one
 //    thread-block cluster per column block, rank r takes the r-th equal share of its k stages, and the ranks' f32
 //    partials meet in rank 0 through distributed shared memory (no global traffic, no fences), added in rank order.
@@ -276,21 +277,40 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             }
             uint4 sc4 = *(const uint4*)(base + C::W_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
             if (a.probe == 1) goto stage_done;
-            float tmp[NT][4][4];
-            uint32_t bx[NT][2][2];  // [token tile][k16 step of the pair][b0, b1]
+            // The nibbles go to the tensor core as f16 SUBNORMALS, with no subtraction at all: a low nibble n of a
+            // 16-bit half is, as it stands, the half n * 2^-24 (q & 0x000f000f), a high one 16 n * 2^-24
+            // (q & 0x00f000f0), both exact. The columns the high nibbles meet (b1 of the X fragment) are scaled by
+            // 1/16 once per fragment, and the offset of 8 leaves through ONE extra mma per k16 step against a constant
+            // A fragment (-8 * 2^-24 and -128 * 2^-24): corr = -8 * 2^-24 * sum_k x_k, the same for the 64 outputs.
+            // Per Marlin word that is 1 shift + 4 and (+ the mma) instead of 4 lop3 + 1 shift + 4 hsub2; the products
+            // are exact either way, the sums stay in f32, and 2^24 is folded into the group scale.
+            float tmp[NT][4][4], corr[NT][4];
+            uint32_t bx[NT][2][2];  // [token tile][k16 step of the pair][b0, b1 / 16]
+            const uint32_t nbias[4] = {0x80088008u, 0x80088008u, 0x80808080u, 0x80808080u};
+            const uint32_t sixteenth = 0x2c002c00u;  // half2(0.0625, 0.0625)
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
                 uint4 w = wp[ks * CG * 32];
                 if ((ks & 1) == 0) {
 #pragma unroll
-                    for (int j = 0; j < NT; j++)
+                    for (int j = 0; j < NT; j++) {
                         ldsm_x4(bx[j][0][0], bx[j][0][1], bx[j][1][0], bx[j][1][1], xs[j] + ks * 32);
+                        __half2 h0 = __hmul2(*(__half2*)&bx[j][0][1], *(const __half2*)&sixteenth);
+                        __half2 h1 = __hmul2(*(__half2*)&bx[j][1][1], *(const __half2*)&sixteenth);
+                        bx[j][0][1] = *(uint32_t*)&h0;
+                        bx[j][1][1] = *(uint32_t*)&h1;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    if (ks == 0) mma16816_zero(corr[j], nbias, bx[j][0][0], bx[j][0][1]);
+                    else mma16816(corr[j], nbias, bx[j][ks & 1][0], bx[j][ks & 1][1]);
                 }
                 uint32_t wq[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
-                    uint32_t af[4];
-                    dequant_word(wq[b], af);
+                    const uint32_t q = wq[b], q8 = q >> 8;
+                    uint32_t af[4] = {q & 0x000f000fu, q8 & 0x000f000fu, q & 0x00f000f0u, q8 & 0x00f000f0u};
 #pragma unroll
                     for (int j = 0; j < NT; j++) {
                         if (ks == 0) mma16816_zero(tmp[j][b], af, bx[j][0][0], bx[j][0][1]);
@@ -298,15 +318,15 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     }
                 }
             }
-            // the group's scales: half 2 b + h of the lane's 16 bytes is output 16 b + g + 8 h
+            // the group's scales (times 2^24): half 2 b + h of the lane's 16 bytes is output 16 b + g + 8 h
             const __half* sh = (const __half*)&sc4;
 #pragma unroll
             for (int b = 0; b < 4; b++) {
-                float s0 = __half2float(sh[2 * b]), s1 = __half2float(sh[2 * b + 1]);
+                float s0 = __half2float(sh[2 * b]) * 16777216.f, s1 = __half2float(sh[2 * b + 1]) * 16777216.f;
 #pragma unroll
                 for (int j = 0; j < NT; j++) {
-                    acc[j][b][0] += s0 * tmp[j][b][0]; acc[j][b][1] += s0 * tmp[j][b][1];
-                    acc[j][b][2] += s1 * tmp[j][b][2]; acc[j][b][3] += s1 * tmp[j][b][3];
+                    acc[j][b][0] += s0 * (tmp[j][b][0] + corr[j][0]); acc[j][b][1] += s0 * (tmp[j][b][1] + corr[j][1]);
+                    acc[j][b][2] += s1 * (tmp[j][b][2] + corr[j][2]); acc[j][b][3] += s1 * (tmp[j][b][3] + corr[j][3]);
                 }
             }
         }
