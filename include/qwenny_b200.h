@@ -236,6 +236,8 @@ int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
 int qb_model_use_fused(qb_model* m, int on);
+/* on (default): the DeltaNet layers' 16-bit in-projection runs on a second stream beside the int4 one */
+int qb_model_use_fork(qb_model* m, int on);
 /* on: steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers (default off: measured
  * slower than the separate launches) */
 int qb_model_use_chain(qb_model* m, int on);

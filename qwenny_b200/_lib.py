@@ -60,6 +60,7 @@ SIGNATURES = {
     "qb_layer_chain": [P, P, P],
     "qb_layer_chain_max_rows": [],
     "qb_model_use_chain": [P, I],
+    "qb_model_use_fork": [P, I],
     "qb_model_launches": [P],
     "qb_model_step_kernels": [P],
     "qb_row_order": [I, I, P],

@@ -115,6 +115,7 @@ static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const G
 static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int ctas) {
     GemvPlan p;
     if (cg) { p.cg = cg; p.kg = kg; }
+    else if (n >= 65536 && n % 512 == 0) { p.cg = 8; p.kg = 1; }  // the output layer: no k groups to add up per piece
     else if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
     else if (k % 512 == 0 && n % 128 == 0) { p.cg = 2; p.kg = 4; }
     else if (k % 256 == 0) { p.cg = 4; p.kg = 2; }

@@ -70,6 +70,11 @@ struct qb_model {
     // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
     // shared memory with the resident X and every grid barrier waits for the slowest block): off unless asked for
     bool chain = false;
+    // the DeltaNet layers' small 16-bit in-projection runs on a second stream, beside the int4 one (fork / join by
+    // events; inside a captured graph the two become parallel branches)
+    bool fork = true;
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> ev;  // per layer: fork, join
     long long launches = 0;  // kernels launched (or replayed) since creation
     int step_kernels = 0;    // kernels of the last step
     int ba_kper = 1024;      // k range of a split of the DeltaNet 16-bit in-projection in the current step
@@ -107,13 +112,21 @@ int dalloc(T** p, size_t n) {
 
 // A layer's in-projection(s): the small 16-bit product of a DeltaNet layer, then the int4 one (whose weight prefetch
 // overlaps it). `with_w4`: false when the previous layer's persistent kernel already ran the int4 product.
-int launch_in_proj(qb_model* m, cudaStream_t st, const qb_layer& L, bool with_w4, int& k) {
+int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, int& k) {
     qb_ctx* c = m->ctx;
+    const qb_layer& L = m->layers[layer].w;
     const int n = m->n;
     void* s = (void*)st;
     if (L.kind == QB_LAYER_DELTA) {
         const int ba_tiles = 2 * LV_HEADS / 16;
-        QB_TRY(qb_gemm_f16_plain(c, s, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS)); k++;
+        void* sb = s;
+        if (m->fork) {
+            QB_CUDA(cudaEventRecord(m->ev[2 * layer], st));
+            QB_CUDA(cudaStreamWaitEvent(m->side, m->ev[2 * layer], 0));
+            sb = (void*)m->side;
+        }
+        QB_TRY(qb_gemm_f16_plain(c, sb, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS)); k++;
+        if (m->fork) QB_CUDA(cudaEventRecord(m->ev[2 * layer + 1], m->side));
     }
     if (with_w4) {
         QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN,
@@ -123,12 +136,14 @@ int launch_in_proj(qb_model* m, cudaStream_t st, const qb_layer& L, bool with_w4
 }
 
 // A layer's mixer: m->part (+ m->ba) -> m->mix (f16)
-int launch_mixer(qb_model* m, cudaStream_t st, const qb_layer& L, int& k) {
+int launch_mixer(qb_model* m, cudaStream_t st, int layer, int& k) {
     qb_ctx* c = m->ctx;
+    const qb_layer& L = m->layers[layer].w;
     const int n = m->n;
     void* s = (void*)st;
     if (L.kind == QB_LAYER_DELTA) {
         const int ba_splits = H / m->ba_kper;
+        if (m->fork) QB_CUDA(cudaStreamWaitEvent(st, m->ev[2 * layer + 1], 0));  // the 16-bit in-projection joins
         if (m->fused && n <= CR - CONV_K + 1) {
             QB_TRY(qb_delta_mixer(c, s, m->part, 1, n, m->ba, ba_splits, L.conv_w, L.a_log, L.dt_bias, L.norm_w, L.mem,
                                   L.sst, L.meta, nullptr, m->mix, m->seg_start, m->seg_len, m->seg_slot, m->seg_pos0,
@@ -176,8 +191,8 @@ int launch_step(qb_model* m, cudaStream_t st) {
     for (int i = 0; i < m->nlayers; i++) {
         const qb_layer& L = m->layers[i].w;
         const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
-        QB_TRY(launch_in_proj(m, st, L, !chain || i == 0, k));
-        QB_TRY(launch_mixer(m, st, L, k));
+        QB_TRY(launch_in_proj(m, st, i, !chain || i == 0, k));
+        QB_TRY(launch_mixer(m, st, i, k));
         if (chain) {
             qb_chain ch = {};
             ch.m = n; ch.mix = m->mix;
@@ -222,6 +237,9 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     m->ctx = ctx; m->nlayers = nlayers; m->slots = slots; m->max_ctx = max_ctx;
     m->vocab_rows = vocab_rows; m->vocab_valid = vocab_valid;
     m->layers.resize(nlayers);
+    QB_CUDA(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
+    m->ev.resize(2 * nlayers);
+    for (auto& e : m->ev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     const size_t T = MAX_TOK;
     QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
     QB_TRY(dalloc(&m->h2, (size_t)8 * H)); QB_TRY(dalloc(&m->part_h, (size_t)8 * H));  // the persistent layer kernel's
@@ -254,6 +272,8 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
 void qb_model_destroy(qb_model* m) {
     if (!m) return;
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& e : m->ev) cudaEventDestroy(e);
+    if (m->side) cudaStreamDestroy(m->side);
     void* bufs[] = {m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
@@ -296,6 +316,16 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
 int qb_model_use_graphs(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     m->use_graphs = on != 0;
+    return QB_OK;
+}
+
+int qb_model_use_fork(qb_model* m, int on) {
+    if (!m) return QB_ERR_ARG;
+    if (m->fork != (on != 0)) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->fork = on != 0;
     return QB_OK;
 }
 
