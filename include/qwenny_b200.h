@@ -28,7 +28,8 @@ extern "C" {
 typedef struct qb_ctx qb_ctx;
 
 /* Epilogues of a matrix product: src/cuda/core.rs:58-64 (enum Epi). */
-enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2 };
+enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2,
+       QB_EPI_RESID = 3 /* qb_marlin_gemm_fused only: Y is the residual stream, added to in place */ };
 
 /* ---- context: what Gemm::load allocates once (src/cuda/core.rs:437-464: SM count, Marlin's `red` and `locks`).
  * Allocates the split-K scratch and tickets on `device`; everything after creation is allocation-free. Like the
@@ -55,6 +56,20 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
 
 /* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
  * next qb_marlin_gemm calls; zeros restore the built-in choice. */
+/* The residual add and RMSNorm between two products folded into them (steps of up to 16 rows): replaces the pairs
+ * Gemm::marlin + Stack::add_rmsnorm of launch_step (src/cuda/qwen/mod.rs:744-766; kernels/dense.cuh:12-26) without a
+ * launch of their own. RMSNorm is linear up to the row's 1 / rms, so the product after a norm runs on the un-normalised
+ * row and scales its result:
+ *   epi == QB_EPI_RESID  Y is the f32 residual stream [m][n] (in / out): Y += X . W^T; xu_out f16 [m][n] gets
+ *                        f16(norm_w_out[c] * Y[t][c]) (the next product's input, NOT yet divided by the rms), and the
+ *                        context keeps, per 64 outputs, the sums of squares of the new rows;
+ *   x_unnormed != 0      X is such an xu (of the last QB_EPI_RESID product on this context; its n is this k): row t of
+ *                        the result is multiplied by rsqrt(mean(Y[t]^2) + eps) before the epilogue (plain, SwiGLU or
+ *                        argmax). The rounding to f16 happens before the division by the rms instead of after it
+ *                        (same relative precision; |norm_w * h| must stay inside the f16 range). */
+int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
+                         int k, int epi, const int* xrows, unsigned long long* keys, int n_valid,
+                         const float* norm_w_out, void* xu_out, int x_unnormed, float eps);
 int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
 /* qb_marlin_gemm without a context and without any allocation, for callers that cannot call cudaMalloc (an engine
@@ -83,6 +98,9 @@ int qb_marlin_probe(qb_ctx* ctx, int mode);
  * Y f32 [K/kper splits][n][ldy] partial products which the consumer sums (any n: blocks of 32 tokens). */
 int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
                       int n, int kper, float* Y, int ldy);
+/* the same product on the un-normalised rows of a QB_EPI_RESID product (n <= 16): results scaled by 1 / rms */
+int qb_gemm_f16_unnormed(qb_ctx* ctx, void* stream, const void* W, const void* X, int K, int ntiles, int n, int kper,
+                         float* Y, int ldy, float eps);
 
 /* ---- per-token kernels. n = tokens of the step (grid size in the reference's launches).
  * qb_embed        embed, kernels/dense.cuh:6-11 (src/cuda/qwen/mod.rs:612-621): out f32 [n][5120] = E bf16 rows;
@@ -238,6 +256,9 @@ int qb_model_use_graphs(qb_model* m, int on);
 int qb_model_use_fused(qb_model* m, int on);
 /* on (default): the DeltaNet layers' 16-bit in-projection runs on a second stream beside the int4 one */
 int qb_model_use_fork(qb_model* m, int on);
+/* on: steps of up to 16 rows use qb_marlin_gemm_fused / qb_gemm_f16_unnormed: no add_rmsnorm launches (default off:
+ * measured slower than the separate launches) */
+int qb_model_use_fused_norm(qb_model* m, int on);
 /* on: steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers (default off: measured
  * slower than the separate launches) */
 int qb_model_use_chain(qb_model* m, int on);

@@ -22,12 +22,14 @@ SIGNATURES = {
     "qb_version": [],
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
+    "qb_marlin_gemm_fused": [P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, I, F],
     "qb_marlin_tune": [P, I, I, I, I],
     "qb_marlin_trace": [P, P],
     "qb_marlin_probe": [P, I],
     "qb_marlin_gemm_noalloc": [P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_static_scratch_bytes": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
+    "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
     "qb_embed": [P, P, P, P, P, P, I, I],
     "qb_rmsnorm": [P, P, P, P, P, F, I],
     "qb_add_rmsnorm": [P, P, P, P, I, I, P, P, F],
@@ -61,6 +63,7 @@ SIGNATURES = {
     "qb_layer_chain_max_rows": [],
     "qb_model_use_chain": [P, I],
     "qb_model_use_fork": [P, I],
+    "qb_model_use_fused_norm": [P, I],
     "qb_model_launches": [P],
     "qb_model_step_kernels": [P],
     "qb_row_order": [I, I, P],

@@ -20,6 +20,9 @@ int qb_create(int device, qb_ctx** out) {
     QB_CUDA(cudaMemset(c->counters, 0, c->ncounters * sizeof(int)));
     QB_CUDA(cudaMalloc(&c->err, 64));
     QB_CUDA(cudaMemset(c->err, 0, 64));
+    c->sq_groups = 1024;
+    QB_CUDA(cudaMalloc(&c->sq, c->sq_groups * 16 * sizeof(float)));
+    QB_CUDA(cudaMemset(c->sq, 0, c->sq_groups * 16 * sizeof(float)));
     QB_CUDA(cudaMalloc(&c->gbar, 64));
     QB_CUDA(cudaMemset(c->gbar, 0, 64));
     *out = c;
@@ -32,6 +35,7 @@ void qb_destroy(qb_ctx* c) {
     cudaFree(c->counters);
     cudaFree(c->err);
     cudaFree(c->gbar);
+    cudaFree(c->sq);
     delete c;
 }
 

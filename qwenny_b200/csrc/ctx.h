@@ -14,6 +14,8 @@ struct qb_ctx {
     int* counters = nullptr;
     size_t ncounters = 0;
     int* err = nullptr;  // device word
+    float* sq = nullptr;       // sums of squares of the last residual product's rows: [sq_groups][16]
+    size_t sq_groups = 0;
     unsigned* gbar = nullptr;  // grid-barrier counters of the persistent layer kernel (zero between launches)
     bool chain_pdl = true;     // that kernel's launch carries the programmatic-dependent-launch attribute too
     // measurement override of the GEMV plan (0: built-in choice)

@@ -168,7 +168,8 @@ extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas
 }
 
 static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m,
-                     int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid) {
+                     int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid,
+                     const float* nw_out = nullptr, void* xu_out = nullptr, bool unnormed = false, float eps = 0.f) {
     int nt = m <= 8 ? 1 : 2;
     GemvPlan p = pick(ctx, n, k, m, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas);
     if (ctx->tune_nstages) p.nstages = ctx->tune_nstages;
@@ -183,11 +184,13 @@ static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B,
     a.trace = ctx->trace;
     if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
+    a.nw_out = nw_out; a.xu_out = (__half*)xu_out; a.sq = ctx->sq; a.rs = unnormed ? ctx->sq : nullptr; a.eps = eps;
 #define QB_GO(NT)                                                              \
     switch (epi) {                                                             \
         case QB_EPI_PLAIN: return launch_shape<NT, EPI_PLAIN>(ctx, st, a, p);  \
         case QB_EPI_SILU: return launch_shape<NT, EPI_SILU>(ctx, st, a, p);    \
         case QB_EPI_ARGMAX: return launch_shape<NT, EPI_ARGMAX>(ctx, st, a, p);\
+        case QB_EPI_RESID: return launch_shape<NT, EPI_RESID>(ctx, st, a, p);  \
         default: return QB_ERR_ARG;                                            \
     }
     if (nt == 1) { QB_GO(1) } else { QB_GO(2) }
@@ -200,6 +203,7 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
     if (!ctx || !X || !B || !Y || !S || m < 0 || n <= 0 || k <= 0 || n % 256 || k % 128) return QB_ERR_ARG;
     if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
     if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
+    if (epi < 0 || epi > QB_EPI_ARGMAX) return QB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     // more than 16 rows: the tensor-core product (plain and SwiGLU epilogues, contiguous rows)
     if (m > 16 && epi != QB_EPI_ARGMAX && !xrows && !ctx->no_tc)
@@ -219,6 +223,22 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
 
 
 // ------------------------------------------------------------------------------------------------ no-allocation variant
+// Residual + RMSNorm folded into the products on either side of it (steps of up to 16 rows); see the header.
+extern "C" int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S,
+                                    int m, int n, int k, int epi, const int* xrows, unsigned long long* keys,
+                                    int n_valid, const float* norm_w_out, void* xu_out, int x_unnormed, float eps) {
+    if (!ctx || !X || !B || !Y || !S || m < 1 || n <= 0 || k <= 0 || n % 256 || k % 128) return QB_ERR_ARG;
+    if (m > 16) return QB_ERR_UNSUPPORTED;
+    if (epi < 0 || epi > QB_EPI_RESID) return QB_ERR_ARG;
+    if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
+    if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
+    if (epi == QB_EPI_RESID && (!norm_w_out || !xu_out || xrows)) return QB_ERR_ARG;
+    if ((epi == QB_EPI_RESID && (size_t)(n / 64) > ctx->sq_groups) || (x_unnormed && (size_t)(k / 64) > ctx->sq_groups))
+        return QB_ERR_TOO_LARGE;
+    return gemm_rows(ctx, (cudaStream_t)stream, X, B, Y, S, m, n, k, 0, epi, xrows, keys, n_valid, norm_w_out, xu_out,
+                     x_unnormed != 0, eps);
+}
+
 // Some hosts can never call cudaMalloc once they are serving: an engine that has handed all free device memory to its
 // KV-cache page pool (the reference sizes that pool from what is left after loading, src/cuda/qwen/mod.rs:422-428), a
 // plugin loaded into a process whose allocator is owned by someone else, code running inside a stream capture. For
@@ -267,6 +287,7 @@ extern "C" int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B
     c.ncounters = STATIC_TICKETS;
     c.err = (int*)(g_static_ptr[dev] + STATIC_PARTIAL_BYTES + STATIC_TICKETS * sizeof(int));
     c.no_cluster = true;
+    if (epi < 0 || epi > QB_EPI_ARGMAX) return QB_ERR_ARG;
     // sizes beyond the fixed array: refuse before anything is enqueued
     if ((size_t)(n / 64) > STATIC_TICKETS) return QB_ERR_TOO_LARGE;
     {

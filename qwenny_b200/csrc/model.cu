@@ -73,6 +73,11 @@ struct qb_model {
     // the DeltaNet layers' small 16-bit in-projection runs on a second stream, beside the int4 one (fork / join by
     // events; inside a captured graph the two become parallel branches)
     bool fork = true;
+    // decode / verify steps: the residual add and RMSNorm between two products run inside them (no launches of their
+    // own). Measured slower than the separate add_rmsnorm launches (6.70 against 6.00 ms per 64-layer step: the small
+    // kernel between two products costs nothing while the next product's blocks are filling their rings anyway, and the
+    // residual epilogue lengthens every cluster's tail), so it is off unless asked for.
+    bool fuse_norm = false;
     cudaStream_t side = nullptr;
     std::vector<cudaEvent_t> ev;  // per layer: fork, join
     long long launches = 0;  // kernels launched (or replayed) since creation
@@ -112,7 +117,7 @@ int dalloc(T** p, size_t n) {
 
 // A layer's in-projection(s): the small 16-bit product of a DeltaNet layer, then the int4 one (whose weight prefetch
 // overlaps it). `with_w4`: false when the previous layer's persistent kernel already ran the int4 product.
-int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, int& k) {
+int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, bool unnormed, int& k) {
     qb_ctx* c = m->ctx;
     const qb_layer& L = m->layers[layer].w;
     const int n = m->n;
@@ -125,12 +130,24 @@ int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, int& k
             QB_CUDA(cudaStreamWaitEvent(m->side, m->ev[2 * layer], 0));
             sb = (void*)m->side;
         }
-        QB_TRY(qb_gemm_f16_plain(c, sb, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS)); k++;
+        if (unnormed) {
+            QB_TRY(qb_gemm_f16_unnormed(c, sb, L.in_ba, m->xn, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS, EPS));
+        } else {
+            QB_TRY(qb_gemm_f16_plain(c, sb, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS));
+        }
+        k++;
         if (m->fork) QB_CUDA(cudaEventRecord(m->ev[2 * layer + 1], m->side));
     }
     if (with_w4) {
-        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN,
-                              H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+        const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
+        if (unnormed) {
+            QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, QB_EPI_PLAIN, nullptr,
+                                        nullptr, 0, nullptr, nullptr, 1, EPS));
+        } else {
+            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, 0, QB_EPI_PLAIN, nullptr,
+                                  nullptr, 0));
+        }
+        k++;
     }
     return QB_OK;
 }
@@ -182,6 +199,7 @@ int launch_step(qb_model* m, cudaStream_t st) {
     int k = 0;
     void* s = (void*)st;
     const bool chain = m->chain && n <= qb_layer_chain_max_rows();
+    const bool fnorm = m->fuse_norm && !chain && n <= 16;
     // the reference splits the small 16-bit product 40 ways (split_for); 5 splits of 1024 columns leave its consumers
     // 8x fewer partial sums to add
     m->ba_kper = m->fused || n > 32 ? 1024 : H / qb_split_for(2 * LV_HEADS / 16, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
@@ -191,7 +209,7 @@ int launch_step(qb_model* m, cudaStream_t st) {
     for (int i = 0; i < m->nlayers; i++) {
         const qb_layer& L = m->layers[i].w;
         const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
-        QB_TRY(launch_in_proj(m, st, i, !chain || i == 0, k));
+        QB_TRY(launch_in_proj(m, st, i, !chain || i == 0, fnorm && i > 0, k));
         QB_TRY(launch_mixer(m, st, i, k));
         if (chain) {
             qb_chain ch = {};
@@ -208,6 +226,18 @@ int launch_step(qb_model* m, cudaStream_t st) {
             QB_TRY(qb_layer_chain(c, s, &ch)); k++;
             continue;
         }
+        if (fnorm) {
+            // out_proj adds into the residual stream and leaves xn = f16(post_norm * h), not yet divided by the rms;
+            // gate_up runs on it and scales its result; down adds again; the next product (the next layer's
+            // in-projection or the output layer) scales
+            QB_TRY(qb_marlin_gemm_fused(c, s, m->mix, L.out_w, m->h, L.out_s, n, H, MIX, QB_EPI_RESID, nullptr, nullptr, 0,
+                                        L.post_norm, m->xn, 0, EPS)); k++;
+            QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, QB_EPI_SILU, nullptr,
+                                        nullptr, 0, nullptr, nullptr, 1, EPS)); k++;
+            QB_TRY(qb_marlin_gemm_fused(c, s, m->mid, L.down_w, m->h, L.down_s, n, H, FF, QB_EPI_RESID, nullptr, nullptr, 0,
+                                        w_next, m->xn, 0, EPS)); k++;
+            continue;
+        }
         QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
         QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
         QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr,
@@ -215,7 +245,10 @@ int launch_step(qb_model* m, cudaStream_t st) {
         QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
         QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, w_next, m->xn, EPS)); k++;
     }
-    if (m->n_out > 0) {
+    if (m->n_out > 0 && fnorm) {
+        QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, QB_EPI_ARGMAX,
+                                    m->out_rows, m->keys, m->vocab_valid, nullptr, nullptr, 1, EPS)); k++;
+    } else if (m->n_out > 0) {
         QB_TRY(qb_marlin_gemm(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, 0, QB_EPI_ARGMAX,
                               m->out_rows, m->keys, m->vocab_valid)); k++;
     }
@@ -316,6 +349,16 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
 int qb_model_use_graphs(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     m->use_graphs = on != 0;
+    return QB_OK;
+}
+
+int qb_model_use_fused_norm(qb_model* m, int on) {
+    if (!m) return QB_ERR_ARG;
+    if (m->fuse_norm != (on != 0)) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->fuse_norm = on != 0;
     return QB_OK;
 }
 

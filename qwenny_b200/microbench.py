@@ -130,6 +130,7 @@ def step(args):
     m.use_graphs(not args.no_graph)
     m.use_chain(args.chain)
     m.use_fork(not args.no_fork)
+    m.use_fused_norm(args.fused_norm)
     toks = [(1000 + i, 0, args.context + i) for i in range(args.rows)]
     out = list(range(args.rows)) if args.rows <= 16 else [args.rows - 1]  # a prompt chunk wants its last row only
     for _ in range(2):
@@ -274,6 +275,7 @@ def main():
     c.add_argument("--rows", type=int, default=5); c.add_argument("--context", type=int, default=32000)
     c.add_argument("--no-graph", action="store_true"); c.add_argument("--no-pdl", action="store_true")
     c.add_argument("--no-fork", action="store_true", help="the 16-bit in-projection in line instead of on a second stream")
+    c.add_argument("--fused-norm", action="store_true", help="residual + RMSNorm inside the products around them")
     c.add_argument("--chain", action="store_true", help="the persistent layer kernel instead of separate launches")
     c.set_defaults(fn=step)
     f = sub.add_parser("prefill")

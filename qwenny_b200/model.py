@@ -129,6 +129,9 @@ class Model:
     def use_fused(self, on: bool):
         check(lib().qb_model_use_fused(self.h, int(on)), "qb_model_use_fused")
 
+    def use_fused_norm(self, on: bool):
+        check(lib().qb_model_use_fused_norm(self.h, int(on)), "qb_model_use_fused_norm")
+
     def use_fork(self, on: bool):
         check(lib().qb_model_use_fork(self.h, int(on)), "qb_model_use_fork")
 

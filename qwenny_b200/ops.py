@@ -84,6 +84,18 @@ class Context:
     def embed(self, table, ids, out, keys, nkeys, n):
         check(lib().qb_embed(self.h, _stream(), _p(table), _p(ids), _p(out), _p(keys), nkeys, n), "qb_embed")
 
+    def marlin_gemm_fused(self, x, words, scales, y, m, epi="plain", norm_w_out=None, xu_out=None, x_unnormed=False,
+                          xrows=None, keys=None, n_valid=None, eps=1e-6):
+        """qb_marlin_gemm_fused: epi "resid" adds into y (the f32 residual stream), writes xu_out = f16(norm_w_out * y)
+        and records the rows' sums of squares; x_unnormed scales the result rows by 1 / rms of those rows."""
+        n = words.shape[1] // 2
+        k = words.shape[0] * 16
+        code = {"plain": 0, "silu": 1, "argmax": 2, "resid": 3}[epi]
+        check(lib().qb_marlin_gemm_fused(self.h, _stream(), _p(x), _p(words), _p(y), _p(scales), m, n, k, code, _p(xrows),
+                                         _p(keys), n if n_valid is None else n_valid, _p(norm_w_out), _p(xu_out),
+                                         int(x_unnormed), eps), "qb_marlin_gemm_fused")
+        return y
+
     def rmsnorm(self, x, w, y, n, eps=1e-6):
         check(lib().qb_rmsnorm(self.h, _stream(), _p(x), _p(w), _p(y), eps, n), "qb_rmsnorm")
 

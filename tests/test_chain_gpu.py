@@ -93,3 +93,56 @@ def test_step_with_and_without_chain(ctx):
             assert ta[r] == tb[r] or float(srt[r, -1] - srt[r, -2]) < 1e-3
         pos += 3
     assert a.step_kernels < b.step_kernels
+
+
+@pytest.mark.parametrize("m", [1, 5, 12])
+def test_fused_residual_and_norm_products(ctx, m):
+    """qb_marlin_gemm_fused: out_proj adds into the residual stream, leaves the un-normalised f16(w * h) rows and their
+    sums of squares; gate_up runs on those rows and scales its result by 1 / rms; against marlin_gemm + add_rmsnorm +
+    marlin_gemm. The residual stream is the same sum in another order (f32 rounding); the second product rounds its
+    input to f16 before the division by the rms instead of after it (same relative precision)."""
+    g = torch.Generator(device="cuda").manual_seed(400 + m)
+    out, gu = M.Marlin.random(H, MIX, g), M.Marlin.random(2 * FF, H, g)
+    post = (1 + 0.02 * torch.randn(H, generator=g, device="cuda")).float()
+    mix = torch.randn(m, MIX, generator=g, device="cuda").half()
+    h0 = torch.randn(m, H, generator=g, device="cuda")
+    want_h = h0.clone()
+    xn = torch.empty(m, H, dtype=torch.float16, device="cuda")
+    part = ctx.marlin_gemm(mix, out.words, out.scales)
+    ctx.add_rmsnorm(want_h, part, 1, m, post, xn)
+    want_mid = ctx.marlin_gemm(xn, gu.words, gu.scales, epi="silu")
+    h = h0.clone()
+    xu = torch.zeros(m, H, dtype=torch.float16, device="cuda")
+    mid = torch.zeros(m, FF, dtype=torch.float16, device="cuda")
+    ctx.marlin_gemm_fused(mix, out.words, out.scales, h, m, epi="resid", norm_w_out=post, xu_out=xu)
+    ctx.marlin_gemm_fused(xu, gu.words, gu.scales, mid, m, epi="silu", x_unnormed=True)
+    torch.cuda.synchronize()
+    assert ctx.device_error() == 0
+    assert rel(h, want_h) < 1e-6
+    assert torch.equal(xu, (post * h).half())
+    assert rel(mid.float(), want_mid.float()) < 1e-3
+    ok = (mid.float() - want_mid.float()).abs() <= 2e-3 + 1e-2 * want_mid.float().abs()
+    assert ok.float().mean() > 0.9999
+
+
+def test_step_with_and_without_fused_norm(ctx):
+    def fresh():
+        return M.synthetic(ctx, nlayers=4, slots=1, max_ctx=256, vocab=2000, seed=23)
+    a, b = fresh(), fresh()
+    a.use_fused_norm(True)
+    seq = [(91 + 313 * i) % 2000 for i in range(40)]
+    pos = 0
+    while pos + 5 <= len(seq):
+        toks = [(seq[pos + i], 0, pos + i) for i in range(5)]
+        a.step(toks, list(range(5)))
+        la, ta = a.logits(), a.argmax()
+        torch.cuda.synchronize()
+        b.step(toks, list(range(5)))
+        lb, tb = b.logits(), b.argmax()
+        torch.cuda.synchronize()
+        assert rel(la, lb) < 2e-3
+        srt = lb.sort(dim=1).values
+        for r in range(5):
+            assert ta[r] == tb[r] or float(srt[r, -1] - srt[r, -2]) < 1e-3
+        pos += 3
+    assert a.step_kernels < b.step_kernels
