@@ -373,10 +373,16 @@ __global__ void __launch_bounds__(FNT)
 delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_splits, const float* cw,
                    const float* a_log, const float* dt_bias, const float* nw, float* mem, long long sst, int* meta,
                    float* out, __half* y, const int* seg_start, const int* seg_len, const int* seg_slot,
-                   const int* seg_pos0, int segs, int* ticket) {
+                   const int* seg_pos0, int segs, int* ticket, long long* trace) {
     extern __shared__ __align__(16) uint8_t fsm[];
     FusedRound& R = *(FusedRound*)fsm;
     pdl_launch_dependents();
+    // measurement only: thread 0 stamps the phases of the (first) round into trace[block][10]
+    long long* tr = trace && threadIdx.x == 0 ? trace + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 10 : nullptr;
+    auto stamp = [&](int i) {
+        if (tr) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; }
+    };
+    stamp(0);
     const int h = blockIdx.x, sg = blockIdx.y, kh = h / (LV_HEADS / LK_HEADS);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = tid % LPC, col = tid / LPC;
     const int t0 = seg_start[sg], len = seg_len[sg], slot = seg_slot[sg], p0 = seg_pos0[sg];
@@ -411,6 +417,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
         for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
     }
     pdl_wait();
+    stamp(1);
 
     // the block's share of the conv ring: channels cb .. cb + ch of the segment's last CR tokens
     const int CH = (LQKV + LV_HEADS - 1) / LV_HEADS;
@@ -450,6 +457,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             }
         }
         __syncthreads();
+        stamp(2);
         // ---- conv + SiLU
         for (int x = tid; x < m * FCH; x += FNT) {
             int tk = x / FCH, c = x - tk * FCH;
@@ -459,6 +467,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             R.c[tk][c] = silu(acc);
         }
         __syncthreads();
+        stamp(3);
         // ---- L2 norm of q and k (a warp per (token, q | k), 4 channels per lane), q also / sqrt(128)
         for (int task = warp; task < 2 * m; task += FNT / 32) {
             int tk = task >> 1, which = task & 1;
@@ -469,6 +478,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             *v4 = make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc);
         }
         __syncthreads();
+        stamp(4);
         for (int tk = warp; tk < m; tk += FNT / 32) {  // k . q
             float4 a = ld4(&R.c[tk][lane * 4]), b = ld4(&R.c[tk][LKD + lane * 4]);
             float x = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
@@ -493,6 +503,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
         }
         __syncthreads();
+        stamp(5);
         // ---- the recurrence
         for (int tk = 0; tk < m; tk++) {
             if (pl.wck && p0 + c0 + tk == pl.ck) st_rows<4>(sbuf(pl.cbuf), S, rg);
@@ -506,6 +517,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
         }
         __syncthreads();
+        stamp(6);
         // ---- gated RMSNorm over the head's 128 value columns (a warp per token), then y = w o r silu(z)
         for (int tk = warp; tk < m; tk += FNT / 32) {
             float4 v = ld4(&R.o[tk][lane * 4]);
@@ -520,8 +532,10 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             y[(size_t)t * MIX + h * LVD + c] = __float2half_rn(nwv * (o * R.rn[tk]) * silu(R.z[tk][c]));
         }
         __syncthreads();
+        stamp(7);
     }
     st_rows<4>(sbuf(pl.ebuf), S, rg);
+    stamp(8);
     // ---- the last block of the launch records the segments' steps in the slot metadata
     __shared__ int last;
     if (tid == 0) {
@@ -567,5 +581,5 @@ extern "C" int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int spl
     }
     return qb::launch(ctx, qb::delta_fused_kernel, dim3(qb::LV_HEADS, segs), dim3(qb::FNT), sizeof(qb::FusedRound), (cudaStream_t)stream, p,
                       splits, n, ba, ba_splits, cw, a_log, dt_bias, nw, mem, sst, meta, out, (__half*)y, seg_start,
-                      seg_len, seg_slot, seg_pos0, segs, ticket);
+                      seg_len, seg_slot, seg_pos0, segs, ticket, ctx->trace);
 }

@@ -189,6 +189,36 @@ def delta(args):
     dev["seg_len"] = torch.full((8,), n, dtype=torch.int32, device="cuda")
     cv = torch.zeros(n, CVW, device="cuda")
     o = torch.zeros(n, MIX, device="cuda")
+    if n <= 29:
+        # a decode / verify step: the one-launch mixer, continuing a sequence at position 1000
+        from ._lib import lib
+        norm_w = torch.ones(128, device="cuda")
+        dev["tok_pos"] = torch.arange(1000, 1000 + n + 8, dtype=torch.int32, device="cuda")
+        dev["seg_pos0"] = torch.full((8,), 1000, dtype=torch.int32, device="cuda")
+        mems = [torch.randn(sst, device="cuda") * 0.01 for _ in range(20)]  # states in rotation: 3 MB each
+        y = torch.zeros(n, MIX, dtype=torch.float16, device="cuda")
+        i = [0]
+
+        def one():
+            meta.copy_(torch.tensor([[1000, 1000, 0, 0]], dtype=torch.int32))
+            ctx.delta_mixer(part, 1, n, ba, 1, conv_w, a_log, dt_bias, norm_w, mems[i[0] % 20], sst, meta, None, y, dev, 1)
+            i[0] += 1
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+        buf = torch.zeros(4096, dtype=torch.int64, device="cuda")
+        lib().qb_marlin_trace(ctx.h, buf.data_ptr())
+        one()
+        torch.cuda.synchronize()
+        lib().qb_marlin_trace(ctx.h, None)
+        t = buf[:48 * 10].view(48, 10).cpu().numpy().astype(np.float64)
+        t0 = t[:, 0].min()
+        names = ["start", "dependencies done", "loads", "conv", "l2 norm", "kq, bank, ring", "recurrence", "norm + write", "state stored"]
+        for j, nm in enumerate(names):
+            c = t[:, j] - t0
+            print(f"  {nm:18s} min {c.min() / 1e3:6.2f}  median {np.median(c) / 1e3:6.2f}  max {c.max() / 1e3:6.2f} us")
+        print("device error", ctx.device_error())
+        return
     ctx.delta_conv(part, 1, n, ba, 1, conv_w, a_log, dt_bias, mem, sst, cv, dev)
     for _ in range(args.reps):
         ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1)
