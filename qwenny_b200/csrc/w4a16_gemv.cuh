@@ -268,16 +268,19 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 }
             }
         };
-        // the weights of the first ring-full of stages do not depend on the previous kernel: start them, then wait
-        // for it (its activations are this kernel's X)
+        // the weights do not depend on the previous kernel: start them, then wait for it (its activations are this
+        // kernel's X)
         uint32_t pre = mine < (uint32_t)nstages ? mine : (uint32_t)nstages;
         const int cb0 = beg / kst, st0 = beg - cb0 * kst;
         int cb = cb0, st = st0;
         auto next = [&]() { if (++st == kst) { st = 0; cb++; } };
-        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, 0);
+        // (only the first stage's: with the whole ring requested at once by every block, the first stages land behind
+        // the later ones' traffic; the rest follow right after the wait, while the consumers are busy with stage 0)
+        const uint32_t early = min(pre, 1u);
+        for (uint32_t it = 0; it < early; it++, next()) issue(cb, st, (int)it, 0);
         pdl_wait();
         cb = cb0; st = st0;
-        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, 1);
+        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, it < early ? 1 : 2);
         bool ok = true;
         int slot = 0;
         uint32_t par = 0;  // parity of the consumers' release this slot is waiting for
