@@ -179,6 +179,10 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
+// The two halves separately: arrive as soon as this block is done with the others' memory, wait where their answer is
+// needed (work in between overlaps the barrier)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 // The address of this block's shared location `p` in block `rank` of the cluster, and a 128-bit load from there
 __device__ __forceinline__ uint32_t cluster_map(const void* p, uint32_t rank) {
     uint32_t r;

@@ -348,24 +348,30 @@ int qb_delta_norm(qb_ctx* ctx, void* stream, const float* p, int splits, int n, 
 }  // extern "C"
 
 // =================================================================================================== fused mixer
-// delta_conv + delta_rule + delta_norm of a step in ONE launch: block (value head h, segment), 512 threads. The head's
-// whole f32 state (128 x 128) lives in the block's registers (32 per thread: column tid / 4, rows 4 (tid % 4 + 4 j) + i,
-// the same layout and operation order as delta_rule_kernel, so both give the same bits); the block recomputes the conv
-// of the 384 channels it needs (its key head's q and k, its own v) from the in-projection rows or the ring, runs the
-// recurrence, and finishes the gated RMSNorm over its 128 value columns in shared memory. The conv ring is written by
-// the blocks in shares; the slot metadata by the LAST block of the launch to finish (an atomic ticket), because every
-// block reads the old metadata when it starts.
+// delta_conv + delta_rule + delta_norm of a decode / verify step in ONE launch: a cluster of two blocks per (value
+// head h, segment), each with half of the head's 128 value columns (256 threads: column tid / 4, rows
+// 4 (tid % 4 + 4 j) + i, the same layout and operation order as delta_rule_kernel<4>, so both give the same bits). A
+// block's slice of the f32 state lives in its registers; it recomputes the conv of the 320 channels it needs (its key
+// head's q and k, its own v columns) from the in-projection rows or the ring, runs the recurrence, and the two blocks
+// finish the gated RMSNorm over the head's 128 columns together: they exchange their per-lane partial sums of
+// squares through distributed shared memory and add them in the order one warp over the whole row would. Every
+// phase's global loads are issued together (one round trip per phase). The conv ring is written by the blocks in
+// shares; the slot metadata by the LAST block of the launch to finish (an atomic ticket), because every block reads
+// the old metadata when it starts.
 namespace qb {
 
-constexpr int FNT = 512;
-constexpr int FCH = 3 * LKD;  // q, k, v channels of a block
+constexpr int FNT = 256;             // threads of a block
+constexpr int FCOLS = LVD / 2;       // value columns of a block
+constexpr int FCH = 2 * LKD + FCOLS; // q, k, v channels of a block
+constexpr int FLD = 8;               // loads in flight per thread in the staging loops
 
 struct FusedRound {
     float x[TCH + CONV_K - 1][FCH];  // conv inputs of the round's tokens and the 3 positions before them
-    float c[TCH][FCH];               // conv outputs: q [0,128), k [128,256), v [256,384)
-    float z[TCH][LVD];               // the gate input of the norm
-    float o[TCH][LVD];               // raw outputs of the round
+    float c[TCH][FCH];               // conv outputs: q [0,128), k [128,256), v [256,320)
+    float z[TCH][FCOLS];             // the gate input of the norm
+    float o[TCH][FCOLS];             // raw outputs of the round
     float w[FCH][CONV_K];            // conv taps of the block's channels
+    float lp[TCH][32];               // per token: the 32 lane partials of the row's sum of squares (16 per block)
     float e[TCH], b[TCH], kq[TCH], rn[TCH];
 };
 
@@ -383,20 +389,22 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
         if (tr) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; }
     };
     stamp(0);
-    const int h = blockIdx.x, sg = blockIdx.y, kh = h / (LV_HEADS / LK_HEADS);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = tid % LPC, col = tid / LPC;
+    const int h = blockIdx.x >> 1, hf = blockIdx.x & 1, sg = blockIdx.y, kh = h / (LV_HEADS / LK_HEADS);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, rg = tid % LPC, lc = tid / LPC;
+    const int col = hf * FCOLS + lc;  // the thread's value column of the head
     const int t0 = seg_start[sg], len = seg_len[sg], slot = seg_slot[sg], p0 = seg_pos0[sg];
+    // global conv channel of the block's channel ch
+    auto gchan = [&](int ch) {
+        return ch < LKD ? kh * LKD + ch : ch < 2 * LKD ? LK_HEADS * LKD + kh * LKD + (ch - LKD)
+                                                       : 2 * LK_HEADS * LKD + h * LVD + hf * FCOLS + (ch - 2 * LKD);
+    };
+    // ---- everything that does not depend on this step's earlier kernels: the taps, the norm weight, the state
+    for (int c = tid; c < FCH; c += FNT) *(float4*)R.w[c] = ld4(cw + gchan(c) * CONV_K);
+    const float nwv = nw[hf * FCOLS + tid % FCOLS], alog = a_log[h], dtb = dt_bias[h];
     const Plan pl = make_plan(meta, slot, p0, len);
     float* sm0 = mem + slot * sst;
     auto sbuf = [&](int b) { return sm0 + (size_t)b * SLOT_STATE + ((size_t)h * LVD + col) * LKD; };
     auto entry = [&](int b, int pos) { return sm0 + 2 * SLOT_STATE + (size_t)b * SLOT_BANK + (size_t)(pos % KEEP) * REP; };
-    // global conv channel of the block's channel ch
-    auto gchan = [&](int ch) {
-        return ch < LKD ? kh * LKD + ch : ch < 2 * LKD ? LK_HEADS * LKD + kh * LKD + (ch - LKD)
-                                                       : 2 * LK_HEADS * LKD + h * LVD + (ch - 2 * LKD);
-    };
-
-    // ---- everything that does not depend on this step's earlier kernels: the state, the taps, the norm weight
     float S[RPT];
     if (pl.zero) {
 #pragma unroll
@@ -404,8 +412,6 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
     } else {
         ld_rows<4>(S, sbuf(pl.in), rg);
     }
-    if (tid < FCH) *(float4*)R.w[tid] = ld4(cw + gchan(tid) * CONV_K);
-    const float nwv = nw[tid % LVD], alog = a_log[h], dtb = dt_bias[h];
     for (int i = 0; i < pl.r; i++) {
         const float* e = entry(pl.in, pl.from + i);
         float k[RPT];
@@ -420,38 +426,92 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
     stamp(1);
 
     // the block's share of the conv ring: channels cb .. cb + ch of the segment's last CR tokens
-    const int CH = (LQKV + LV_HEADS - 1) / LV_HEADS;
-    const int cb = h * CH, ch = max(0, min(CH, LQKV - cb)), mm = min(len, CR);
+    constexpr int NB = 2 * LV_HEADS, CH = (LQKV + NB - 1) / NB;  // channels per block (the last block has fewer)
+    const int cb = blockIdx.x * CH, mm = min(len, CR);
+    static_assert(TCH * ((LQKV + 2 * LV_HEADS - 1) / (2 * LV_HEADS)) <= 4 * FNT, "a round's ring share fits 4 values per thread");
 
+    bool lp_pending = false;  // a cluster barrier phase this block has arrived at and not yet waited for
     for (int c0 = 0; c0 < len; c0 += TCH) {
         const int m = min(TCH, len - c0);
-        // ---- one round of independent loads: conv inputs (step rows or ring), z, gates
-        for (int x = tid; x < (m + CONV_K - 1) * FCH; x += FNT) {
-            int row = x / FCH, c = x - row * FCH, gc = gchan(c), si = c0 + row - (CONV_K - 1), qp = p0 + si;
-            float v = 0.f;
-            if (qp >= 0) {
+        // ---- ONE round trip of independent loads: conv inputs (step rows or ring), z, gates, the ring share; all of
+        // them into registers first, the shared-memory stores after
+        constexpr int NROW = TCH + CONV_K - 1, NZV = (TCH * FCOLS + FNT - 1) / FNT;
+        // conv inputs: thread tid takes channel tid of every row, and threads below FCH - FNT also channel FNT + tid
+        float xv[NROW][2], zv[NZV], ringv[4], gate = 0.f;
+        const int gc0 = gchan(tid), gc1 = gchan(min(FNT + tid, FCH - 1));
+        const bool two = FNT + tid < FCH;
+#pragma unroll
+        for (int row = 0; row < NROW; row++) {
+            xv[row][0] = xv[row][1] = 0.f;
+            const int si = c0 + row - (CONV_K - 1), qp = p0 + si;
+            if (row < m + CONV_K - 1 && qp >= 0) {
                 if (si >= 0) {
-                    for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + si) * DELTA_IN + gc];
+                    // (one split is the common case: a plain load, so that every row's loads are in flight together;
+                    // a warp issues in order, and a sum inside a loop would wait for each load before the next)
+                    const float* pr = p + (size_t)(t0 + si) * DELTA_IN;
+                    xv[row][0] = __ldcg(pr + gc0);
+                    if (two) xv[row][1] = __ldcg(pr + gc1);
+                    for (int s = 1; s < splits; s++) {
+                        pr += (size_t)n * DELTA_IN;
+                        xv[row][0] += __ldcg(pr + gc0);
+                        if (two) xv[row][1] += __ldcg(pr + gc1);
+                    }
                 } else {
-                    v = sm0[SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV + gc];
+                    const float* rr = sm0 + SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV;
+                    xv[row][0] = __ldcg(rr + gc0);
+                    if (two) xv[row][1] = __ldcg(rr + gc1);
                 }
             }
-            R.x[row][c] = v;
         }
-        for (int x = tid; x < m * LVD; x += FNT) {
-            int tk = x / LVD, c = x - tk * LVD;
-            float v = 0.f;
-            for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + c];
-            R.z[tk][c] = v;
+#pragma unroll
+        for (int u = 0; u < NZV; u++) {
+            const int x = u * FNT + tid;
+            zv[u] = 0.f;
+            if (x < m * FCOLS) {
+                int tk = x / FCOLS, c = x - tk * FCOLS;
+                const float* pz = p + (size_t)(t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + hf * FCOLS + c;
+                zv[u] = __ldcg(pz);
+                for (int s = 1; s < splits; s++) zv[u] += __ldcg(pz + (size_t)s * n * DELTA_IN);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = u * FNT + tid, tk = c0 + i / CH, c = cb + i % CH;
+            ringv[u] = 0.f;
+            if (i < m * CH && c < LQKV && tk >= len - mm) {
+                const float* pq = p + (size_t)(t0 + tk) * DELTA_IN + c;
+                ringv[u] = __ldcg(pq);
+                for (int s = 1; s < splits; s++) ringv[u] += __ldcg(pq + (size_t)s * n * DELTA_IN);
+            }
         }
         if (tid < 2 * m) {  // the gates of head h
             int tk = tid >> 1, which = tid & 1, t = t0 + c0 + tk;
-            float v = 0.f;
-            for (int s = 0; s < ba_splits; s++) v += ba[((size_t)s * n + t) * (2 * LV_HEADS) + (which ? h : LV_HEADS + h)];
+            const float* pb = ba + (size_t)t * (2 * LV_HEADS) + (which ? h : LV_HEADS + h);
+            float gs[8];  // up to 8 splits in flight together, added in split order
+#pragma unroll
+            for (int s = 0; s < 8; s++) gs[s] = s < ba_splits ? __ldcg(pb + (size_t)s * n * (2 * LV_HEADS)) : 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; s++) gate += gs[s];
+            for (int s = 8; s < ba_splits; s++) gate += __ldcg(pb + (size_t)s * n * (2 * LV_HEADS));
+        }
+#pragma unroll
+        for (int row = 0; row < NROW; row++) {
+            if (row < m + CONV_K - 1) {
+                R.x[row][tid] = xv[row][0];
+                if (two) R.x[row][FNT + tid] = xv[row][1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NZV; u++) {
+            const int x = u * FNT + tid;
+            if (x < m * FCOLS) R.z[x / FCOLS][x % FCOLS] = zv[u];
+        }
+        if (tid < 2 * m) {
+            int tk = tid >> 1, which = tid & 1;
             if (which) {
-                R.b[tk] = 1.f / (1.f + expf(-v));
+                R.b[tk] = 1.f / (1.f + expf(-gate));
             } else {
-                float a = v + dtb;
+                float a = gate + dtb;
                 float sp = a > 20.f ? a : log1pf(expf(a));
                 R.e[tk] = expf(-expf(alog) * sp);
             }
@@ -484,23 +544,17 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             float x = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
             if (lane == 0) R.kq[tk] = x;
         }
-        // ---- the delta rule inputs from the new checkpoint on, for a later restart
+        // ---- the delta rule inputs from the new checkpoint on, for a later restart (k by the first block of the key
+        // head's first value head, v by each block for its columns, the gates by the head's first block)
         for (int tk = max(0, pl.ck - (p0 + c0)); tk < m; tk++) {
             float* e = entry(pl.cbuf, p0 + c0 + tk);
-            if (h % (LV_HEADS / LK_HEADS) == 0 && tid < LKD) e[kh * LKD + tid] = R.c[tk][LKD + tid];
-            if (tid >= LKD && tid < LKD + LVD) e[LK_HEADS * LKD + h * LVD + tid - LKD] = R.c[tk][2 * LKD + tid - LKD];
-            if (tid == 2 * LKD) {
+            if (hf == 0 && h % (LV_HEADS / LK_HEADS) == 0 && tid < LKD) e[kh * LKD + tid] = R.c[tk][LKD + tid];
+            if (tid >= LKD && tid < LKD + FCOLS)
+                e[LK_HEADS * LKD + h * LVD + hf * FCOLS + tid - LKD] = R.c[tk][2 * LKD + tid - LKD];
+            if (hf == 0 && tid == LKD + FCOLS) {
                 e[LK_HEADS * LKD + LV_HEADS * LVD + h] = R.e[tk];
                 e[LK_HEADS * LKD + LV_HEADS * LVD + LV_HEADS + h] = R.b[tk];
             }
-        }
-        // ---- this round's rows of the conv ring (the block's channel share), from the in-projection rows
-        for (int i = tid; i < m * ch; i += FNT) {
-            int tk = c0 + i / ch, c = cb + i % ch;
-            if (tk < len - mm) continue;
-            float v = 0.f;
-            for (int s = 0; s < splits; s++) v += p[((size_t)s * n + t0 + tk) * DELTA_IN + c];
-            sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = v;
         }
         __syncthreads();
         stamp(5);
@@ -511,31 +565,60 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             ld_rows<4>(k, &R.c[tk][LKD], rg);
             ld_rows<4>(q, &R.c[tk][0], rg);
             float dk = dot_rows<4>(S, k), dq = dot_rows<4>(S, q);
-            float ex = R.e[tk], delta = (R.c[tk][2 * LKD + col] - ex * dk) * R.b[tk];
-            if (rg == 0) R.o[tk][col] = ex * dq + delta * R.kq[tk];
+            float ex = R.e[tk], delta = (R.c[tk][2 * LKD + lc] - ex * dk) * R.b[tk];
+            if (rg == 0) R.o[tk][lc] = ex * dq + delta * R.kq[tk];
 #pragma unroll
             for (int j = 0; j < RPT; j++) S[j] = ex * S[j] + k[j] * delta;
         }
         __syncthreads();
         stamp(6);
-        // ---- gated RMSNorm over the head's 128 value columns (a warp per token), then y = w o r silu(z)
+        // ---- gated RMSNorm over the head's 128 value columns. One warp over the whole row would give lane L the
+        // columns 4 L .. 4 L + 3 and add the 32 lane partials as a butterfly; this block has the columns of lanes
+        // 16 hf .. 16 hf + 15: it computes those partials, hands them to its partner through distributed shared
+        // memory, and both run the same butterfly over the 32.
+        if (lp_pending) { cluster_wait(); lp_pending = false; }  // the partner is done with the last round's partials
+        for (int x = tid; x < m * 16; x += FNT) {
+            int tk = x >> 4, l16 = x & 15;
+            float4 v = ld4(&R.o[tk][l16 * 4]);
+            float part = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            R.lp[tk][hf * 16 + l16] = part;
+        }
+        cluster_sync();
+        {
+            const uint32_t rem = cluster_map(&R.lp[0][0], hf ^ 1);
+            for (int x = tid; x < m * 16; x += FNT) {
+                int tk = x >> 4, l16 = x & 15, idx = tk * 32 + (hf ^ 1) * 16 + l16;
+                float v;
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(rem + idx * 4));
+                R.lp[tk][(hf ^ 1) * 16 + l16] = v;
+            }
+        }
+        cluster_arrive();  // this block has read its partner's partials (the matching wait: before they are rewritten)
+        __syncthreads();   // this block's copy of them is complete
+        lp_pending = true;
         for (int tk = warp; tk < m; tk += FNT / 32) {
-            float4 v = ld4(&R.o[tk][lane * 4]);
-            float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+            float ss = warp_sum(R.lp[tk][lane]);
             if (lane == 0) R.rn[tk] = rsqrtf(ss / LVD + EPS);
         }
         __syncthreads();
-        for (int x = tid; x < m * LVD; x += FNT) {
-            int tk = x / LVD, c = x - tk * LVD, t = t0 + c0 + tk;
+        for (int x = tid; x < m * FCOLS; x += FNT) {
+            int tk = x / FCOLS, c = x - tk * FCOLS, t = t0 + c0 + tk;
             float o = R.o[tk][c];
-            if (out) out[(size_t)t * MIX + h * LVD + c] = o;
-            y[(size_t)t * MIX + h * LVD + c] = __float2half_rn(nwv * (o * R.rn[tk]) * silu(R.z[tk][c]));
+            if (out) out[(size_t)t * MIX + h * LVD + hf * FCOLS + c] = o;
+            y[(size_t)t * MIX + h * LVD + hf * FCOLS + c] = __float2half_rn(nwv * (o * R.rn[tk]) * silu(R.z[tk][c]));
+        }
+        // ---- this round's rows of the conv ring (the block's channel share), loaded with the round's inputs
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = u * FNT + tid, tk = c0 + i / CH, c = cb + i % CH;
+            if (i < m * CH && c < LQKV && tk >= len - mm) sm0[SLOT_RING + (size_t)((p0 + tk) & (CR - 1)) * LQKV + c] = ringv[u];
         }
         __syncthreads();
         stamp(7);
     }
     st_rows<4>(sbuf(pl.ebuf), S, rg);
     stamp(8);
+    if (lp_pending) cluster_wait();  // the partner may read this block's shared memory until here
     // ---- the last block of the launch records the segments' steps in the slot metadata
     __shared__ int last;
     if (tid == 0) {
@@ -577,9 +660,24 @@ extern "C" int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int spl
     if (!opted) {
         QB_CUDA(cudaFuncSetAttribute(qb::delta_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)sizeof(qb::FusedRound)));
+        QB_CUDA(cudaFuncSetAttribute(qb::delta_fused_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared));
         opted = true;
     }
-    return qb::launch(ctx, qb::delta_fused_kernel, dim3(qb::LV_HEADS, segs), dim3(qb::FNT), sizeof(qb::FusedRound), (cudaStream_t)stream, p,
-                      splits, n, ba, ba_splits, cw, a_log, dt_bias, nw, mem, sst, meta, out, (__half*)y, seg_start,
-                      seg_len, seg_slot, seg_pos0, segs, ticket, ctx->trace);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(2 * qb::LV_HEADS, segs);
+    lc.blockDim = dim3(qb::FNT);
+    lc.dynamicSmemBytes = sizeof(qb::FusedRound);
+    lc.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = ctx->pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, qb::delta_fused_kernel, p, splits, n, ba, ba_splits, cw, a_log, dt_bias, nw, mem,
+                                       sst, meta, out, (__half*)y, seg_start, seg_len, seg_slot, seg_pos0, segs, ticket,
+                                       ctx->trace);
+    return e == cudaSuccess ? QB_OK : (int)e;
 }

@@ -211,7 +211,7 @@ def delta(args):
         one()
         torch.cuda.synchronize()
         lib().qb_marlin_trace(ctx.h, None)
-        t = buf[:48 * 10].view(48, 10).cpu().numpy().astype(np.float64)
+        t = buf[:96 * 10].view(96, 10).cpu().numpy().astype(np.float64)
         t0 = t[:, 0].min()
         names = ["start", "dependencies done", "loads", "conv", "l2 norm", "kq, bank, ring", "recurrence", "norm + write", "state stored"]
         for j, nm in enumerate(names):
