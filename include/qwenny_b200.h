@@ -111,6 +111,15 @@ int qb_gemm_f16_unnormed(qb_ctx* ctx, void* stream, const void* W, const void* X
  * qb_sum_parts    sum_parts, kernels/qwen.cu:141-143
  * qb_mark_seen    mark_seen, kernels/sampling.cuh:14-26 (src/cuda/core.rs:949-960); vocab = bits per slot
  * qb_marlin_gather marlin_gather, kernels/marlin.cuh:605-608 (qb_marlin_gemm's xrows makes it unnecessary) */
+/* mtp_in (kernels/qwen.cu:100-133): fc's input of an MTP step, y f16 [n][10240] = [pre_e * e / rms(e); pre_h * g /
+ * rms(g)], e = emb[t], g = fw * h[rows[t]] / rms(h[rows[t]]).
+ * qb_draft_pick: the greedy row of draft_sample (kernels/sampling.cuh:298 with argmax_draft_row, src/sample.rs:58-62):
+ * the draft of logit row i is the index in keys[i] (the argmax epilogue's), mapped through head_ids when a draft head
+ * made the logits; written to next_ids[i] and chain[i * chain_ld + t]. */
+int qb_mtp_in(qb_ctx* ctx, void* stream, const float* emb, const float* h, const int* rows, const float* fw,
+              const float* pre_e, const float* pre_h, void* y, float eps, int n);
+int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, const int* head_ids, int n_out,
+                  int* next_ids, int* chain, int chain_ld, int t);
 int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
              int nkeys, int n);
 int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n);
@@ -231,6 +240,19 @@ typedef struct qb_layer {
     int cap;
 } qb_layer;
 
+/* The MTP draft layer (Mtp, src/cuda/qwen/mod.rs:648-661) */
+#define QB_MAX_DRAFTS 8
+typedef struct qb_mtp {
+    qb_layer layer;                  /* its decoder layer (own KV cache / state) */
+    const void *fc_w, *fc_s;         /* fc 5120 x 10240, Marlin */
+    const float *pre_e, *pre_h;      /* the norms of fc's two inputs, f32 [5120] (1 + w) */
+    const float* norm;               /* the MTP's final norm, f32 [5120] */
+    const void *head_w, *head_s;     /* draft head: head_rows x 5120 Marlin rows of the output layer, or NULL (the
+                                        whole output layer drafts) (src/cuda/qwen/draft.rs) */
+    int head_rows, head_valid;
+    const int* head_ids;             /* device: the token of each draft-head row */
+} qb_mtp;
+
 /* A token of a step (Tok, src/engine.rs:90-95) */
 typedef struct qb_tok {
     uint32_t id, slot, pos;
@@ -250,6 +272,13 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
  * graph. Steps with segments longer than 8 tokens (prompt attention) return QB_ERR_UNSUPPORTED. */
 int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
+/* The MTP draft step (f-row 1 of the scope: what turns steps/s into accepted tok/s). qb_model_set_mtp: Mtp::load's
+ * pointers. qb_model_draft: Engine::draft with greedy rows = draft_chains (src/cuda/qwen/mod.rs:870-896): k <=
+ * QB_MAX_DRAFTS drafts for each row of h_out, from the hidden states the last qb_model_step left at h_rows; h_drafts
+ * host [n_out][k]. */
+int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp);
+int qb_model_draft(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
+                   int n_out, int k, int* h_drafts);
 int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */

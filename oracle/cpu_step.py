@@ -43,23 +43,40 @@ class CpuModel:
         self.lm = dequant_marlin(lm_words, lm_scales)
 
     @staticmethod
+    def _host_layer(l):
+        d = dict(kind=l["kind"])
+        for name in ("in_proj", "out", "gate_up", "down"):
+            d[name + "_words"] = l[name].words.cpu().numpy().view(np.uint32)
+            d[name + "_scales"] = l[name].scales.cpu().numpy()
+        for k, v in l.items():
+            if isinstance(v, torch.Tensor):
+                d[k] = v.cpu().numpy()
+            elif k in ("sst", "cap"):
+                d[k] = v
+        return d
+
+    @staticmethod
     def from_device(model):
-        """Host copy of a qwenny_b200.model.Model (small models only)."""
-        layers = []
-        for l in model.layers:
-            d = dict(kind=l["kind"])
-            for name in ("in_proj", "out", "gate_up", "down"):
-                d[name + "_words"] = l[name].words.cpu().numpy().view(np.uint32)
-                d[name + "_scales"] = l[name].scales.cpu().numpy()
-            for k, v in l.items():
-                if isinstance(v, torch.Tensor):
-                    d[k] = v.cpu().numpy()
-                elif k in ("sst", "cap"):
-                    d[k] = v
-            layers.append(d)
-        return CpuModel(layers, model.embed.float().cpu().numpy(), model.final_norm.cpu().numpy(),
-                        model.lm_head.words.cpu().numpy().view(np.uint32), model.lm_head.scales.cpu().numpy(),
-                        model.vocab_valid, model.slots)
+        """Host copy of a qwenny_b200.model.Model (small models only), its MTP layer included."""
+        layers = [CpuModel._host_layer(l) for l in model.layers]
+        mtp = getattr(model, "mtp", None)
+        if mtp is not None:
+            layers.append(CpuModel._host_layer(mtp["layer"]))
+        cm = CpuModel(layers, model.embed.float().cpu().numpy(), model.final_norm.cpu().numpy(),
+                      model.lm_head.words.cpu().numpy().view(np.uint32), model.lm_head.scales.cpu().numpy(),
+                      model.vocab_valid, model.slots)
+        cm.mtp = None
+        if mtp is not None:
+            cm.mtp_layer = cm.layers.pop()
+            cm.mtp = dict(fc=dequant_marlin(mtp["fc"].words.cpu().numpy().view(np.uint32), mtp["fc"].scales.cpu().numpy()),
+                          pre_e=mtp["pre_e"].cpu().numpy(), pre_h=mtp["pre_h"].cpu().numpy(),
+                          norm=mtp["norm"].cpu().numpy(), head=None)
+            if mtp.get("head") is not None:
+                cm.mtp["head"] = dequant_marlin(mtp["head"].words.cpu().numpy().view(np.uint32),
+                                                mtp["head"].scales.cpu().numpy())
+                cm.mtp["head_valid"] = mtp["head_valid"]
+                cm.mtp["head_ids"] = mtp["head_ids"].cpu().numpy()
+        return cm
 
     @staticmethod
     def _mm(x_f16: np.ndarray, w: torch.Tensor) -> np.ndarray:
@@ -73,27 +90,61 @@ class CpuModel:
         xn = R.rmsnorm(h, self.layers[0]["input_norm"])
         for i, l in enumerate(self.layers):
             w_next = self.layers[i + 1]["input_norm"] if i + 1 < len(self.layers) else self.final_norm
-            part = self._mm(xn, l["in_proj_f32"])[None]
-            if l["kind"] == "delta":
-                ba = self._mm(xn, l["in_ba_f32"])[None]
-                cv = R.delta_conv(part, ba, l["conv_w"], l["a_log"], l["dt_bias"], l["mem"], l["sst"], st["tok_slot"],
-                                  st["tok_pos"])
-                o = R.delta_rule(part, cv, l["mem"], l["sst"], l["meta"], st["seg_start"], st["seg_len"],
-                                 st["seg_slot"], st["seg_pos0"])
-                mix = R.delta_norm(part, l["norm_w"], o, l["meta"], st["seg_len"], st["seg_slot"], st["seg_pos0"])
-            else:
-                q, gate, k, v = R.attn_prep(part, l["q_norm"], l["k_norm"], l["inv_freq"], QSCALE, st["tok_pos"])
-                R.kv_store(l["kc"], l["vc"], l["ks"], l["vs"], k, v, st["tok_slot"], st["tok_pos"], l["cap"])
-                o = R.attn_decode(q, gate, l["kc"], l["vc"], l["ks"], l["vs"], st["tok_slot"], st["tok_pos"], l["cap"])
-                mix = o.astype(np.float16)
-            h, xn = R.add_rmsnorm(h, self._mm(mix, l["out_f32"])[None], l["post_norm"])
-            gu = self._mm(xn, l["gate_up_f32"])
-            b = gu.reshape(n, -1, 2, 8)
-            mid = (R.silu(b[:, :, 0, :]) * b[:, :, 1, :]).reshape(n, -1).astype(np.float16)
-            h, xn = R.add_rmsnorm(h, self._mm(mid, l["down_f32"])[None], w_next)
+            h, xn = self._layer(l, st, h, xn, w_next)
+        self.h_last = h
         logits = self._mm(xn[st["out_rows"]], self.lm)
         keys = R.argmax_keys(logits, self.vocab_valid)
         return logits, R.key_token(keys), h, xn
+
+    def draft(self, toks, rows, out, k):
+        """Engine::draft with greedy rows (draft_chains, src/cuda/qwen/mod.rs:870-896) on the residual stream the last
+        step() left. Returns (drafts [len(out)][k], logits of every MTP step)."""
+        chains, all_logits = [[] for _ in out], []
+        cur, at, outs, own = list(toks), list(rows), list(out), False
+        for t in range(k):
+            st = R.build_step(cur, outs)
+            e = R.embed(self.embed, st["ids"])
+            fw = self.mtp["norm"] if own else self.final_norm
+            xin = R.mtp_in(e, self.h_last, np.asarray(at), fw, self.mtp["pre_e"], self.mtp["pre_h"])
+            h = self._mm(xin, self.mtp["fc"])
+            xn = R.rmsnorm(h, self.mtp_layer["input_norm"])
+            h, xn = self._layer(self.mtp_layer, st, h, xn, self.mtp["norm"])
+            self.h_last = h
+            if self.mtp["head"] is not None:
+                logits = self._mm(xn[st["out_rows"]], self.mtp["head"])
+                idx = R.key_token(R.argmax_keys(logits, self.mtp["head_valid"]))
+                picked = [int(self.mtp["head_ids"][i]) for i in idx]
+            else:
+                logits = self._mm(xn[st["out_rows"]], self.lm)
+                picked = [int(i) for i in R.key_token(R.argmax_keys(logits, self.vocab_valid))]
+            all_logits.append(logits)
+            for i, p in enumerate(picked):
+                chains[i].append(p)
+            cur = [(picked[i], cur[o][1], cur[o][2] + 1) for i, o in enumerate(outs)]
+            at, outs, own = list(range(len(cur))), list(range(len(cur))), True
+        return chains, all_logits
+
+    def _layer(self, l, st, h, xn, w_next):
+        n = st["n"]
+        part = self._mm(xn, l["in_proj_f32"])[None]
+        if l["kind"] == "delta":
+            ba = self._mm(xn, l["in_ba_f32"])[None]
+            cv = R.delta_conv(part, ba, l["conv_w"], l["a_log"], l["dt_bias"], l["mem"], l["sst"], st["tok_slot"],
+                              st["tok_pos"])
+            o = R.delta_rule(part, cv, l["mem"], l["sst"], l["meta"], st["seg_start"], st["seg_len"],
+                             st["seg_slot"], st["seg_pos0"])
+            mix = R.delta_norm(part, l["norm_w"], o, l["meta"], st["seg_len"], st["seg_slot"], st["seg_pos0"])
+        else:
+            q, gate, k, v = R.attn_prep(part, l["q_norm"], l["k_norm"], l["inv_freq"], QSCALE, st["tok_pos"])
+            R.kv_store(l["kc"], l["vc"], l["ks"], l["vs"], k, v, st["tok_slot"], st["tok_pos"], l["cap"])
+            o = R.attn_decode(q, gate, l["kc"], l["vc"], l["ks"], l["vs"], st["tok_slot"], st["tok_pos"], l["cap"])
+            mix = o.astype(np.float16)
+        h, xn = R.add_rmsnorm(h, self._mm(mix, l["out_f32"])[None], l["post_norm"])
+        gu = self._mm(xn, l["gate_up_f32"])
+        b = gu.reshape(n, -1, 2, 8)
+        mid = (R.silu(b[:, :, 0, :]) * b[:, :, 1, :]).reshape(n, -1).astype(np.float16)
+        h, xn = R.add_rmsnorm(h, self._mm(mid, l["down_f32"])[None], w_next)
+        return h, xn
 
 
 def time_baseline(seconds: float = 15.0, threads: int | None = None, rows: int = 5, vocab: int = 151936):

@@ -218,6 +218,18 @@ def add_rmsnorm(h: np.ndarray, parts: np.ndarray, w_next: np.ndarray, eps: float
     return h, rmsnorm(h, w_next, eps)
 
 
+def mtp_in(emb: np.ndarray, h: np.ndarray, rows: np.ndarray, fw: np.ndarray, pre_e: np.ndarray, pre_h: np.ndarray,
+           eps: float = EPS) -> np.ndarray:
+    """fc's input of an MTP step (mtp_in, kernels/qwen.cu:100-133): y[t] = [pre_e * e / rms(e); pre_h * g / rms(g)] f16,
+    e = emb[t], g = fw * h[rows[t]] / rms(h[rows[t]])."""
+    def unit(x):
+        x = x.astype(np.float32)
+        return x * (1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + eps)).astype(np.float32)
+    e = emb.astype(np.float32)
+    g = (fw * unit(h[rows])).astype(np.float32)
+    return np.concatenate([pre_e * unit(e), pre_h * unit(g)], axis=-1).astype(np.float16)
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # Attention: cache layout, prep, decode
 

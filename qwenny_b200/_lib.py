@@ -30,6 +30,10 @@ SIGNATURES = {
     "qb_static_scratch_bytes": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
     "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
+    "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
+    "qb_draft_pick": [P, P, P, P, I, P, P, I, I],
+    "qb_model_set_mtp": [P, P],
+    "qb_model_draft": [P, P, P, I, P, P, I, I, P],
     "qb_embed": [P, P, P, P, P, P, I, I],
     "qb_rmsnorm": [P, P, P, P, P, F, I],
     "qb_add_rmsnorm": [P, P, P, P, I, I, P, P, F],
@@ -83,6 +87,14 @@ class QbLayer(C.Structure):
         ("input_norm", P), ("post_norm", P), ("gate_up_w", P), ("gate_up_s", P), ("down_w", P), ("down_s", P),
         ("conv_w", P), ("a_log", P), ("dt_bias", P), ("norm_w", P), ("mem", P), ("sst", LL), ("meta", P),
         ("q_norm", P), ("k_norm", P), ("inv_freq", P), ("kc", P), ("vc", P), ("ks", P), ("vs", P), ("cap", I),
+    ]
+
+
+class QbMtp(C.Structure):
+    """qb_mtp of include/qwenny_b200.h."""
+    _fields_ = [
+        ("layer", QbLayer), ("fc_w", P), ("fc_s", P), ("pre_e", P), ("pre_h", P), ("norm", P), ("head_w", P),
+        ("head_s", P), ("head_rows", I), ("head_valid", I), ("head_ids", P),
     ]
 
 

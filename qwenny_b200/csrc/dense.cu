@@ -129,11 +129,74 @@ __global__ void __launch_bounds__(128) gather_rows_kernel(const uint4* x, const 
     for (int c = threadIdx.x; c < k8; c += blockDim.x) out[(size_t)blockIdx.x * k8 + c] = row[c];
 }
 
+// MTP input (the draft layer of speculative decoding), one block per token t:
+// y[t] = [pre_e * e / rms(e); pre_h * g / rms(g)] as f16 [2 H], e = the token's embedding (emb [n][H], from embed),
+// g = fw * h[rows[t]] / rms(h[rows[t]]): h is the residual stream before a final norm fw (the target's and its final
+// norm, or the MTP layer's own of the step before and its norm). Replaces mtp_in, kernels/qwen.cu:100-133.
+__global__ void __launch_bounds__(ROW_THREADS) mtp_in_kernel(const float* emb, const float* h, const int* rows,
+                                                             const float* fw, const float* pre_e, const float* pre_h,
+                                                             __half* y, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    float wf[8], we[8], wh[8];
+    const int c = 8 * threadIdx.x;
+    *(float4*)&wf[0] = *(const float4*)(fw + c); *(float4*)&wf[4] = *(const float4*)(fw + c + 4);
+    *(float4*)&we[0] = *(const float4*)(pre_e + c); *(float4*)&we[4] = *(const float4*)(pre_e + c + 4);
+    *(float4*)&wh[0] = *(const float4*)(pre_h + c); *(float4*)&wh[4] = *(const float4*)(pre_h + c + 4);
+    pdl_wait();
+    const float* er = emb + (size_t)blockIdx.x * H + c;
+    const float* hr = h + (size_t)rows[blockIdx.x] * H + c;
+    float e[8], g[8];
+    *(float4*)&e[0] = *(const float4*)er; *(float4*)&e[4] = *(const float4*)(er + 4);
+    *(float4*)&g[0] = *(const float4*)hr; *(float4*)&g[4] = *(const float4*)(hr + 4);
+    float se = 0.f, sg = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { se += e[i] * e[i]; sg += g[i] * g[i]; }
+    const float re = rsqrtf(block_sum(se, sh) / H + eps), rg = rsqrtf(block_sum(sg, sh) / H + eps);
+    float sg2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { g[i] = wf[i] * (g[i] * rg); sg2 += g[i] * g[i]; }
+    const float rg2 = rsqrtf(block_sum(sg2, sh) / H + eps);
+    __half* yr = y + (size_t)blockIdx.x * 2 * H + c;
+    store_norm8(yr, e, we, re);
+    store_norm8(yr + H, g, wh, rg2);
+}
+
+// The greedy case of the reference's draft sampler (draft_sample with top_k 1, kernels/sampling.cuh:298; the row of
+// argmax_draft_row, src/sample.rs:58-62): draft i of a chain is the argmax of its logit row, which the argmax epilogue
+// of the head product left in keys[i] (largest logit, lowest index among equals); a draft head's columns map to tokens
+// through head_ids. Writes the draft as the next MTP step's token id and at chain[i][t].
+__global__ void __launch_bounds__(64) draft_pick_kernel(const unsigned long long* keys, const int* head_ids, int n_out,
+                                                        int* next_ids, int* chain, int chain_ld, int t) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_out) return;
+    const int idx = (int)(0xffffffffu - (uint32_t)(keys[i] & 0xffffffffu));
+    const int tok = head_ids ? head_ids[idx] : idx;
+    next_ids[i] = tok;
+    chain[(size_t)i * chain_ld + t] = tok;
+}
+
 }  // namespace qb
 
 using namespace qb;
 
 extern "C" {
+
+int qb_mtp_in(qb_ctx* ctx, void* stream, const float* emb, const float* h, const int* rows, const float* fw,
+              const float* pre_e, const float* pre_h, void* y, float eps, int n) {
+    if (!ctx || !emb || !h || !rows || !fw || !pre_e || !pre_h || !y || n <= 0) return QB_ERR_ARG;
+    return launch(ctx, mtp_in_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, emb, h, rows, fw, pre_e, pre_h,
+                  (__half*)y, eps);
+}
+
+int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, const int* head_ids, int n_out,
+                  int* next_ids, int* chain, int chain_ld, int t) {
+    if (!ctx || !keys || !next_ids || !chain || n_out <= 0 || t < 0 || t >= chain_ld) return QB_ERR_ARG;
+    return launch(ctx, draft_pick_kernel, dim3((n_out + 63) / 64), dim3(64), 0, (cudaStream_t)stream, keys, head_ids, n_out,
+                  next_ids, chain, chain_ld, t);
+}
 
 int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
              int nkeys, int n) {

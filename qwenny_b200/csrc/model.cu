@@ -32,7 +32,7 @@ struct Layer {
 };
 
 struct GraphKey {
-    int v[9];
+    int v[10];
     bool operator<(const GraphKey& o) const { return std::memcmp(v, o.v, sizeof v) < 0; }
 };
 
@@ -65,7 +65,13 @@ struct qb_model {
     // host-side shape of the uploaded step
     int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0,
         tile_max_pos = 0;
-    std::map<GraphKey, cudaGraphExec_t> graphs;
+    // MTP draft layer (optional): stored as layers[nlayers]; fc's input, the rows of the residual stream its tokens take
+    // their hidden states from, the drafts of the running chains
+    bool has_mtp = false;
+    qb_mtp mtp = {};
+    __half* xin2 = nullptr;
+    int *mtp_rows = nullptr, *draft_ids = nullptr, *dchain = nullptr, *h_chain = nullptr;
+    std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;  // the graph and its kernel count
     bool use_graphs = true, fused = true;
     // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
     // shared memory with the resident X and every grid barrier waits for the slowest block): off unless asked for
@@ -90,14 +96,14 @@ namespace {
 struct StepLayout {
     // offsets (ints) of the step arrays inside the single step allocation
     size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, ptile, out_rows, mark,
-        mark_at, total;
+        mark_at, mtp_rows, total;
     StepLayout() {
         size_t o = 0;
         auto take = [&](size_t n) { size_t r = o; o += (n + 3) / 4 * 4; return r; };
         ids = take(MAX_TOK); tok_slot = take(MAX_TOK); tok_pos = take(MAX_TOK);
         seg_start = take(MAX_TOK); seg_len = take(MAX_TOK); seg_slot = take(MAX_TOK); seg_pos0 = take(MAX_TOK);
         dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); ptile = take(2 * MAX_TOK); out_rows = take(MAX_OUT);
-        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1);
+        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1); mtp_rows = take(MAX_TOK);
         total = o;
     }
 };
@@ -191,6 +197,50 @@ int launch_mixer(qb_model* m, cudaStream_t st, int layer, int& k) {
     return QB_OK;
 }
 
+// The plain form of a layer after its mixer: out_proj, residual + norm, gate_up (SwiGLU), down, residual + norm
+// (Stack::layer / mlp, src/cuda/qwen/mod.rs:498-575)
+int launch_layer_tail(qb_model* m, cudaStream_t st, const qb_layer& L, const float* w_next, int& k) {
+    qb_ctx* c = m->ctx;
+    const int n = m->n;
+    void* s = (void*)st;
+    QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
+    QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr, nullptr, 0)); k++;
+    QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, w_next, m->xn, EPS)); k++;
+    return QB_OK;
+}
+
+// The kernels of one MTP step over the uploaded tokens (launch_mtp, src/cuda/qwen/mod.rs:799-840): the tokens'
+// embeddings and their hidden states at mtp_rows of the residual stream (the target's with its final norm, or, `own`,
+// the MTP layer's of the step before with the MTP's norm) through mtp_in, fc, the MTP's decoder layer, and the draft
+// head (or the output layer) with the argmax epilogue. fc writes the MTP's residual stream in place of the
+// reference's product + sum_parts (one split).
+int launch_mtp(qb_model* m, cudaStream_t st, bool own) {
+    qb_ctx* c = m->ctx;
+    const int n = m->n;
+    int k = 0;
+    void* s = (void*)st;
+    const qb_mtp& M = m->mtp;
+    const qb_layer& L = m->layers[m->nlayers].w;
+    m->ba_kper = 1024;
+    QB_TRY(qb_embed(c, s, m->embed, m->ids, m->o, m->keys, m->n_out, n)); k++;
+    QB_TRY(qb_mtp_in(c, s, m->o, m->h, m->mtp_rows, own ? M.norm : m->final_norm, M.pre_e, M.pre_h, m->xin2, EPS, n)); k++;
+    QB_TRY(qb_marlin_gemm(c, s, m->xin2, M.fc_w, m->h, M.fc_s, n, H, 2 * H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    QB_TRY(qb_rmsnorm(c, s, m->h, L.input_norm, m->xn, EPS, n)); k++;
+    QB_TRY(launch_in_proj(m, st, m->nlayers, true, false, k));
+    QB_TRY(launch_mixer(m, st, m->nlayers, k));
+    QB_TRY(launch_layer_tail(m, st, L, M.norm, k));
+    if (m->n_out > 0) {
+        const bool head = M.head_w != nullptr;
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, head ? M.head_w : m->lm_w, m->logits, head ? M.head_s : m->lm_s, m->n_out,
+                              head ? M.head_rows : m->vocab_rows, H, 0, QB_EPI_ARGMAX, m->out_rows, m->keys,
+                              head ? M.head_valid : m->vocab_valid)); k++;
+    }
+    m->step_kernels = k;
+    return QB_OK;
+}
+
 // The kernels of one step over the uploaded tokens, in the reference's order (launch_step). Steps of up to
 // qb_layer_chain_max_rows() tokens run everything between two mixers as one persistent launch.
 int launch_step(qb_model* m, cudaStream_t st) {
@@ -238,12 +288,7 @@ int launch_step(qb_model* m, cudaStream_t st) {
                                         w_next, m->xn, 0, EPS)); k++;
             continue;
         }
-        QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
-        QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
-        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr,
-                              nullptr, 0)); k++;
-        QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
-        QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, w_next, m->xn, EPS)); k++;
+        QB_TRY(launch_layer_tail(m, st, L, w_next, k));
     }
     if (m->n_out > 0 && fnorm) {
         QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, QB_EPI_ARGMAX,
@@ -269,9 +314,9 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     qb_model* m = new qb_model();
     m->ctx = ctx; m->nlayers = nlayers; m->slots = slots; m->max_ctx = max_ctx;
     m->vocab_rows = vocab_rows; m->vocab_valid = vocab_valid;
-    m->layers.resize(nlayers);
+    m->layers.resize(nlayers + 1);  // + the MTP layer's place
     QB_CUDA(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
-    m->ev.resize(2 * nlayers);
+    m->ev.resize(2 * (nlayers + 1));
     for (auto& e : m->ev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     const size_t T = MAX_TOK;
     QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
@@ -298,16 +343,18 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     m->seg_len = d + L.seg_len; m->seg_slot = d + L.seg_slot; m->seg_pos0 = d + L.seg_pos0; m->dtok = d + L.dtok;
     m->dseg = d + L.dseg; m->dkeys = d + L.dkeys; m->ptile = d + L.ptile; m->out_rows = d + L.out_rows; m->mark = d + L.mark;
     m->mark_at = d + L.mark_at;
+    m->mtp_rows = d + L.mtp_rows;
     *out = m;
     return QB_OK;
 }
 
 void qb_model_destroy(qb_model* m) {
     if (!m) return;
-    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
     for (auto& e : m->ev) cudaEventDestroy(e);
     if (m->side) cudaStreamDestroy(m->side);
-    void* bufs[] = {m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
+    if (m->h_chain) cudaFreeHost(m->h_chain);
+    void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
     for (int i = 0; i < 2; i++) {
@@ -318,8 +365,15 @@ void qb_model_destroy(qb_model* m) {
     delete m;
 }
 
+static int set_layer_at(qb_model* m, int i, const qb_layer* l);
+
 int qb_model_set_layer(qb_model* m, int i, const qb_layer* l) {
     if (!m || !l || i < 0 || i >= m->nlayers) return QB_ERR_ARG;
+    return set_layer_at(m, i, l);
+}
+
+// i == nlayers: the MTP layer's place
+static int set_layer_at(qb_model* m, int i, const qb_layer* l) {
     if (!l->in_proj_w || !l->in_proj_s || !l->out_w || !l->out_s || !l->gate_up_w || !l->gate_up_s || !l->down_w ||
         !l->down_s || !l->input_norm || !l->post_norm)
         return QB_ERR_ARG;
@@ -355,7 +409,7 @@ int qb_model_use_graphs(qb_model* m, int on) {
 int qb_model_use_fused_norm(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->fuse_norm != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
         m->graphs.clear();
     }
     m->fuse_norm = on != 0;
@@ -365,7 +419,7 @@ int qb_model_use_fused_norm(qb_model* m, int on) {
 int qb_model_use_fork(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->fork != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
         m->graphs.clear();
     }
     m->fork = on != 0;
@@ -375,7 +429,7 @@ int qb_model_use_fork(qb_model* m, int on) {
 int qb_model_use_chain(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->chain != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
         m->graphs.clear();
     }
     m->chain = on != 0;
@@ -385,7 +439,7 @@ int qb_model_use_chain(qb_model* m, int on) {
 int qb_model_use_fused(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->fused != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
         m->graphs.clear();
     }
     m->fused = on != 0;
@@ -394,7 +448,14 @@ int qb_model_use_fused(qb_model* m, int on) {
 
 // Step::upload: the step's tokens (each sequence's contiguous and in order), the rows whose logits are wanted.
 // Every token of a segment is added to its slot's seen set (the reference's `marks: None`).
+static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows);
+
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out) {
+    return upload_step(m, stream, toks, n, out, n_out, nullptr);
+}
+
+// rows (MTP steps): per token the row of the residual stream of the step before that holds its hidden state
+static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows) {
     if (!m || !toks || n < 1 || n > MAX_TOK || n_out < 0 || n_out > MAX_OUT || (n_out && !out)) return QB_ERR_ARG;
     for (int i = 0; i < n_out; i++)
         if (out[i] < 0 || out[i] >= n) return QB_ERR_ARG;
@@ -451,6 +512,8 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
     }
     h[L.mark_at + segs] = nmark;
     for (int i = 0; i < n_out; i++) h[L.out_rows + i] = out[i];
+    if (rows)
+        for (int i = 0; i < n; i++) h[L.mtp_rows + i] = rows[i];
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     QB_CUDA(cudaEventRecord(m->h_event[m->h_cur], (cudaStream_t)stream));
     m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
@@ -459,11 +522,16 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const 
 }
 
 // Graphs::run: replay the step's graph, capturing it the first time its shape is seen; larger steps launch directly.
-int qb_model_run(qb_model* m, void* stream) {
+// kind: 0 the model's step, 1 an MTP step on the target's hidden states, 2 an MTP step on its own
+static int run_kind(qb_model* m, void* stream, int kind) {
     if (!m || m->n <= 0 || !m->embed) return QB_ERR_ARG;
-    for (auto& l : m->layers)
-        if (!l.set) return QB_ERR_ARG;
+    for (int i = 0; i < m->nlayers; i++)
+        if (!m->layers[i].set) return QB_ERR_ARG;
+    if (kind && !m->has_mtp) return QB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    auto launch_step = [kind](qb_model* mm, cudaStream_t s2) {
+        return kind == 0 ? ::launch_step(mm, s2) : launch_mtp(mm, s2, kind == 2);
+    };
     if (!m->use_graphs || m->n > GRAPH_TOK) {
         QB_TRY(launch_step(m, st));
         m->launches += m->step_kernels;
@@ -472,7 +540,7 @@ int qb_model_run(qb_model* m, void* stream) {
     GraphKey key = {{m->n, m->n_out, m->segs, m->ndec, m->ntile, m->max_seg,
                      (m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0) +
                          64 * (m->ntile ? qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) : 0),
-                     m->ndseg, m->dmax}};
+                     m->ndseg, m->dmax, kind}};
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         // a first uncaptured run sets the kernels' attributes (not allowed while capturing) and warms the caches
@@ -489,11 +557,69 @@ int qb_model_run(qb_model* m, void* stream) {
         e = cudaGraphInstantiate(&ex, g, 0);
         cudaGraphDestroy(g);
         if (e != cudaSuccess) return (int)e;
-        it = m->graphs.emplace(key, ex).first;
+        it = m->graphs.emplace(key, std::make_pair(ex, m->step_kernels)).first;
         return QB_OK;  // the uncaptured run above was this step
     }
-    QB_CUDA(cudaGraphLaunch(it->second, st));
+    QB_CUDA(cudaGraphLaunch(it->second.first, st));
+    m->step_kernels = it->second.second;
     m->launches += m->step_kernels;
+    return QB_OK;
+}
+
+int qb_model_run(qb_model* m, void* stream) { return run_kind(m, stream, 0); }
+
+// The MTP draft layer (Mtp, src/cuda/qwen/mod.rs:648-661): its decoder layer, fc [5120][10240], the two input norms
+// and its final norm, and optionally a draft head (rows of the output layer for part of the vocabulary,
+// src/cuda/qwen/draft.rs) with the token of each of its rows.
+int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp) {
+    if (!m || !mtp || !mtp->fc_w || !mtp->fc_s || !mtp->pre_e || !mtp->pre_h || !mtp->norm) return QB_ERR_ARG;
+    if (mtp->head_w && (!mtp->head_s || !mtp->head_ids || mtp->head_rows <= 0 || mtp->head_rows % 256 ||
+                        mtp->head_valid <= 0 || mtp->head_valid > mtp->head_rows || mtp->head_rows > m->vocab_rows))
+        return QB_ERR_ARG;
+    QB_TRY(set_layer_at(m, m->nlayers, &mtp->layer));
+    m->mtp = *mtp;
+    if (!m->xin2) {
+        QB_TRY(dalloc(&m->xin2, (size_t)MAX_TOK * 2 * H));
+        QB_TRY(dalloc(&m->draft_ids, (size_t)MAX_TOK));
+        QB_TRY(dalloc(&m->dchain, (size_t)MAX_OUT * QB_MAX_DRAFTS));
+        QB_CUDA(cudaMallocHost((void**)&m->h_chain, MAX_OUT * QB_MAX_DRAFTS * sizeof(int)));
+    }
+    m->has_mtp = true;
+    return QB_OK;
+}
+
+// Engine::draft with greedy rows (draft_chains, src/cuda/qwen/mod.rs:870-896): k drafts for each of the n_out rows
+// `out` of the MTP step over `toks`, whose hidden states are rows `rows` of the residual stream the last model step
+// left. The first MTP step runs on the target's hidden states; each further one on the MTP's own, one position on,
+// with the draft just made as its token (its id stays on the device). h_drafts: host [n_out][k]. Waits for the chain.
+int qb_model_draft(qb_model* m, void* stream, const qb_tok* toks, int n, const int* rows, const int* out, int n_out,
+                   int k, int* h_drafts) {
+    if (!m || !m->has_mtp || !toks || !rows || n < 1 || n > MAX_TOK || n_out < 0 || n_out > MAX_OUT || k < 0 ||
+        k > QB_MAX_DRAFTS || (n_out && (!out || !h_drafts)))
+        return QB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool none = k == 0 || n_out == 0;
+    QB_TRY(upload_step(m, stream, toks, n, out, none ? 0 : n_out, rows));
+    QB_TRY(run_kind(m, stream, 1));
+    if (none) return QB_OK;
+    const int* head_ids = m->mtp.head_w ? m->mtp.head_ids : nullptr;
+    QB_TRY(qb_draft_pick(m->ctx, stream, m->keys, head_ids, n_out, m->draft_ids, m->dchain, QB_MAX_DRAFTS, 0));
+    std::vector<qb_tok> cur(n_out);
+    std::vector<int> at(out, out + n_out), all(n_out);
+    for (int i = 0; i < n_out; i++) { cur[i] = toks[out[i]]; all[i] = i; }
+    for (int t = 1; t < k; t++) {
+        for (auto& c : cur) { c.id = 0; c.pos += 1; }
+        QB_TRY(upload_step(m, stream, cur.data(), n_out, all.data(), n_out, at.data()));
+        // the step's token ids are the drafts just made (ids_from_drafts, src/cuda/core.rs:1077-1080)
+        QB_CUDA(cudaMemcpyAsync(m->ids, m->draft_ids, n_out * sizeof(int), cudaMemcpyDeviceToDevice, st));
+        QB_TRY(run_kind(m, stream, 2));
+        QB_TRY(qb_draft_pick(m->ctx, stream, m->keys, head_ids, n_out, m->draft_ids, m->dchain, QB_MAX_DRAFTS, t));
+        at = all;
+    }
+    QB_CUDA(cudaMemcpyAsync(m->h_chain, m->dchain, (size_t)n_out * QB_MAX_DRAFTS * sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    for (int i = 0; i < n_out; i++)
+        for (int t = 0; t < k; t++) h_drafts[i * k + t] = m->h_chain[i * QB_MAX_DRAFTS + t];
     return QB_OK;
 }
 

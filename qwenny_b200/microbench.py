@@ -4,7 +4,8 @@
     python -m qwenny_b200.microbench attn [--context 32000] [--rows 5] [--reps 20]
     python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--chain]
     python -m qwenny_b200.microbench prefill [--layers 64] [--prompt 32768] [--chunk 2048]
-    python -m qwenny_b200.microbench delta [--rows 2048]
+    python -m qwenny_b200.microbench delta [--rows 2048 | --rows 5]
+    python -m qwenny_b200.microbench draft [--k 4] [--draft-rows 65536]
     python -m qwenny_b200.microbench chain [--rows 5] [--trace] [--probe 1|2]
 
 Each prints CUDA-event timings (launches replayed from a CUDA graph, inputs larger than L2 where the shape allows)
@@ -171,6 +172,31 @@ def prefill(args):
           f"first chunk {ms[0]:.1f} ms, last chunk {ms[-1]:.1f} ms; greedy {tok}, device error {ctx.device_error()}")
 
 
+def draft(args):
+    """The MTP draft chain: k greedy drafts for one sequence after a verify step (one target layer stands in for the
+    stack: the chain's cost does not depend on it). MTP layer at the 27B widths, context as given, draft head of
+    --draft-rows rows (0: the whole output layer)."""
+    ctx = Context(0)
+    ctx.set_pdl(True)
+    m = M.synthetic(ctx, nlayers=1, position=args.context, max_ctx=32768, pattern=("attn",), mtp=True,
+                    draft_rows=args.draft_rows)
+    toks = [(1000 + i, 0, args.context + i) for i in range(5)]
+    m.step(toks, list(range(5)))
+    got = m.argmax()
+    mt = [(got[i], 0, args.context + i + 1) for i in range(5)]
+    for _ in range(3):
+        d = m.draft(mt, list(range(5)), [4], args.k)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(m.stream)
+    for _ in range(args.reps):
+        d = m.draft(mt, list(range(5)), [4], args.k)
+    e1.record(m.stream)
+    torch.cuda.synchronize()
+    print(f"draft chain k={args.k} context={args.context} draft_rows={args.draft_rows}: "
+          f"{e0.elapsed_time(e1) / args.reps * 1e3:.1f} us per chain (host round trip included), drafts {d}, "
+          f"device error {ctx.device_error()}")
+
+
 def delta(args):
     """The DeltaNet kernels of one prompt segment: conv once, then the rule kernel timed alone."""
     ctx = Context(0)
@@ -312,6 +338,10 @@ def main():
     f.add_argument("--layers", type=int, default=64); f.add_argument("--prompt", type=int, default=32768)
     f.add_argument("--chunk", type=int, default=2048)
     f.set_defaults(fn=prefill)
+    h = sub.add_parser("draft")
+    h.add_argument("--k", type=int, default=4); h.add_argument("--context", type=int, default=32000)
+    h.add_argument("--draft-rows", type=int, default=65536); h.add_argument("--reps", type=int, default=20)
+    h.set_defaults(fn=draft)
     e = sub.add_parser("delta")
     e.add_argument("--rows", type=int, default=2048); e.add_argument("--reps", type=int, default=5)
     e.set_defaults(fn=delta)

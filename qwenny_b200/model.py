@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import QbLayer, QbTok, check, lib
+from ._lib import QbMtp, QbLayer, QbTok, check, lib
 
 H, NH, NKV, HD = 5120, 24, 4, 256
 LK_HEADS, LV_HEADS, LKD, LVD = 16, 48, 128, 128
@@ -73,24 +73,56 @@ class Model:
               "qb_model_create")
         self.h = h
         for i, l in enumerate(layers):
-            q = QbLayer()
-            q.kind = 0 if l["kind"] == "delta" else 1
-            for name in ("in_proj", "out", "gate_up", "down"):
-                setattr(q, name + "_w", l[name].words.data_ptr())
-                setattr(q, name + "_s", l[name].scales.data_ptr())
-            q.input_norm, q.post_norm = l["input_norm"].data_ptr(), l["post_norm"].data_ptr()
-            if l["kind"] == "delta":
-                q.in_ba = l["in_ba"].data_ptr()
-                for name in ("conv_w", "a_log", "dt_bias", "norm_w", "mem", "meta"):
-                    setattr(q, name, l[name].data_ptr())
-                q.sst = l["sst"]
-            else:
-                for name in ("q_norm", "k_norm", "inv_freq", "kc", "vc", "ks", "vs"):
-                    setattr(q, name, l[name].data_ptr())
-                q.cap = l["cap"]
+            q = self._layer_struct(l)
             check(lib().qb_model_set_layer(self.h, i, C.byref(q)), f"qb_model_set_layer({i})")
         check(lib().qb_model_set_head(self.h, _p(embed), _p(final_norm), _p(lm_head.words), _p(lm_head.scales)),
               "qb_model_set_head")
+        self.mtp = None
+
+    @staticmethod
+    def _layer_struct(l):
+        q = QbLayer()
+        q.kind = 0 if l["kind"] == "delta" else 1
+        for name in ("in_proj", "out", "gate_up", "down"):
+            setattr(q, name + "_w", l[name].words.data_ptr())
+            setattr(q, name + "_s", l[name].scales.data_ptr())
+        q.input_norm, q.post_norm = l["input_norm"].data_ptr(), l["post_norm"].data_ptr()
+        if l["kind"] == "delta":
+            q.in_ba = l["in_ba"].data_ptr()
+            for name in ("conv_w", "a_log", "dt_bias", "norm_w", "mem", "meta"):
+                setattr(q, name, l[name].data_ptr())
+            q.sst = l["sst"]
+        else:
+            for name in ("q_norm", "k_norm", "inv_freq", "kc", "vc", "ks", "vs"):
+                setattr(q, name, l[name].data_ptr())
+            q.cap = l["cap"]
+        return q
+
+    def set_mtp(self, mtp: dict):
+        """mtp: dict(layer=<layer dict>, fc=Marlin 5120 x 10240, pre_e, pre_h, norm, head=Marlin or None, head_valid,
+        head_ids=int32 device tensor or None) (Mtp, src/cuda/qwen/mod.rs:648-661)."""
+        q = QbMtp()
+        q.layer = self._layer_struct(mtp["layer"])
+        q.fc_w, q.fc_s = mtp["fc"].words.data_ptr(), mtp["fc"].scales.data_ptr()
+        q.pre_e, q.pre_h, q.norm = mtp["pre_e"].data_ptr(), mtp["pre_h"].data_ptr(), mtp["norm"].data_ptr()
+        if mtp.get("head") is not None:
+            q.head_w, q.head_s = mtp["head"].words.data_ptr(), mtp["head"].scales.data_ptr()
+            q.head_rows, q.head_valid = mtp["head"].n, mtp["head_valid"]
+            q.head_ids = mtp["head_ids"].data_ptr()
+        check(lib().qb_model_set_mtp(self.h, C.byref(q)), "qb_model_set_mtp")
+        self.mtp = mtp
+
+    def draft(self, toks, rows, out, k):
+        """Engine::draft with greedy rows: k drafts per row of `out`; returns [len(out)][k] token ids (waits)."""
+        arr = self._toks(toks)
+        r = (C.c_int * len(rows))(*rows)
+        o = (C.c_int * max(1, len(out)))(*out)
+        res = (C.c_int * max(1, len(out) * k))()
+        s = C.c_void_p(self.stream.cuda_stream)
+        check(lib().qb_model_draft(self.h, s, arr, len(toks), r, o, len(out), k, res), "qb_model_draft")
+        self._n, self._n_out = (len(out) if k > 1 else len(toks)), len(out)
+        self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
+        return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
 
     def close(self):
         if getattr(self, "h", None):
@@ -117,7 +149,7 @@ class Model:
         o = (C.c_int * max(1, len(out)))(*out)
         s = C.c_void_p(self.stream.cuda_stream)
         check(lib().qb_model_step(self.h, s, arr, len(toks), o, len(out)), "qb_model_step")
-        self._n, self._n_out = len(toks), len(out)
+        self._n, self._n_out, self._cols = len(toks), len(out), None
 
     def argmax(self, n_out=None):
         n_out = self._n_out if n_out is None else n_out
@@ -145,7 +177,8 @@ class Model:
         """f32 [n_out][vocab_rows] of the last step (a copy)."""
         self.stream.synchronize()
         ptr = lib().qb_model_logits(self.h)
-        return _device_copy(ptr, (self._n_out, self.lm_head.n), torch.float32)
+        cols = getattr(self, "_cols", None) or self.lm_head.n
+        return _device_copy(ptr, (self._n_out, cols), torch.float32)
 
     def hidden(self) -> torch.Tensor:
         self.stream.synchronize()
@@ -193,7 +226,7 @@ def _device_copy(ptr: int, shape, dtype) -> torch.Tensor:
 
 
 def synthetic(ctx, nlayers=64, slots=1, max_ctx=32768, vocab=151936, seed=0, device="cuda", position=0,
-              pattern=LAYER_PATTERN):
+              pattern=LAYER_PATTERN, mtp=False, draft_rows=0):
     """The random-init 27B-shape hybrid decoder. With position > 0 the caches are filled as if `position` tokens had
     been processed: random int8 keys / values with scales |N(0, 0.05)|, DeltaNet state N(0, 0.01), metadata
     {position, position, 0}."""
@@ -203,8 +236,8 @@ def synthetic(ctx, nlayers=64, slots=1, max_ctx=32768, vocab=151936, seed=0, dev
     sst = (SLOT_FLOATS + 1023) // 1024 * 1024
     norm = lambda n: 1 + torch.randn(n, generator=g, device=device) * 0.02
     layers = []
-    for i in range(nlayers):
-        kind = pattern[i % len(pattern)]
+
+    def make_layer(kind):
         l = dict(kind=kind, input_norm=norm(H), post_norm=norm(H),
                  out=Marlin.random(H, MIX, g, device), gate_up=Marlin.random(2 * FF, H, g, device),
                  down=Marlin.random(H, FF, g, device))
@@ -237,8 +270,24 @@ def synthetic(ctx, nlayers=64, slots=1, max_ctx=32768, vocab=151936, seed=0, dev
                 l["vc"] = torch.zeros(nb * HD, dtype=torch.uint8, device=device)
                 l["ks"], l["vs"] = torch.zeros(nb, device=device), torch.zeros(nb, device=device)
             l["cap"] = cap
-        layers.append(l)
+        return l
+
+    for i in range(nlayers):
+        layers.append(make_layer(pattern[i % len(pattern)]))
     vocab_rows = (vocab + 255) // 256 * 256
     embed = (torch.randn(vocab, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
     lm_head = Marlin.random(vocab_rows, H, g, device)
-    return Model(ctx, layers, embed, norm(H), lm_head, vocab, slots, max_ctx)
+    model = Model(ctx, layers, embed, norm(H), lm_head, vocab, slots, max_ctx)
+    if mtp:
+        # the MTP draft layer: an attention layer of its own, fc over [embedding; hidden], its norms, and (draft_rows > 0)
+        # a draft head of that many rows over a random subset of the vocabulary
+        d = dict(layer=make_layer("attn"), fc=Marlin.random(H, 2 * H, g, device), pre_e=norm(H), pre_h=norm(H),
+                 norm=norm(H), head=None, head_valid=0, head_ids=None)
+        if draft_rows:
+            rows = (draft_rows + 255) // 256 * 256
+            d["head"] = Marlin.random(rows, H, g, device)
+            d["head_valid"] = draft_rows
+            ids = torch.randperm(vocab, generator=g, device=device)[:rows].to(torch.int32)
+            d["head_ids"] = ids
+        model.set_mtp(d)
+    return model

@@ -96,6 +96,14 @@ class Context:
                                          int(x_unnormed), eps), "qb_marlin_gemm_fused")
         return y
 
+    def mtp_in(self, emb, h, rows, fw, pre_e, pre_h, y, n, eps=1e-6):
+        check(lib().qb_mtp_in(self.h, _stream(), _p(emb), _p(h), _p(rows), _p(fw), _p(pre_e), _p(pre_h), _p(y), eps, n),
+              "qb_mtp_in")
+
+    def draft_pick(self, keys, head_ids, n_out, next_ids, chain, chain_ld, t):
+        check(lib().qb_draft_pick(self.h, _stream(), _p(keys), _p(head_ids), n_out, _p(next_ids), _p(chain), chain_ld, t),
+              "qb_draft_pick")
+
     def rmsnorm(self, x, w, y, n, eps=1e-6):
         check(lib().qb_rmsnorm(self.h, _stream(), _p(x), _p(w), _p(y), eps, n), "qb_rmsnorm")
 
