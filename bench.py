@@ -85,9 +85,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload(layers: int) -> str:
+    return (f"full 27B-shape hybrid decoder verify step ({layers} layers, int4 g128 weights, int8 KV): 5 rows (1 token + 4 "
+            f"MTP drafts) at context {POSITION}, one slot per GPU (BASELINE configs[3])")
+
+
 def cpu_baseline(seconds: float):
     from oracle import cpu_step
-    r = cpu_step.time_baseline(seconds=seconds)
+    # every host core this process may use (torchrun sets OMP_NUM_THREADS=1 for its workers; the baseline is the CPU
+    # path with all the threads it can have)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    r = cpu_step.time_baseline(seconds=seconds, threads=cores)
     return {"value": r["rows_per_s"], "unit": "tok/s", "cores": r["cores"], "kind": "port", "sample": r["sample"],
             "ms_per_step": r["step_s"] * 1e3}
 
@@ -109,7 +120,7 @@ def run_reference(args):
     line = {"metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": "full 27B-shape verify step, 5 rows at context 32000 (BASELINE configs[3])",
+            "config": {"workload": workload(args.layers),
                        "rows_per_step": ROWS, "note": "reference CUDA path unavailable on B200 (its Marlin kernels "
                        "fault with an illegal instruction); CPU port of its fp32 check path, one 4-layer block x16"},
             "cpu_baseline": {"value": v, "unit": "tok/s", "cores": vals[-1]["cores"], "kind": "port",
@@ -225,9 +236,7 @@ def run_ours(args):
             "metric": METRIC, "value": replicas.job_throughput(ROWS, ms_dev, world), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_dev, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"full 27B-shape hybrid decoder verify step ({args.layers} layers, int4 g128 weights, "
-                                   f"int8 KV): 5 rows (1 token + 4 MTP drafts) at context {POSITION}, one slot per GPU "
-                                   "(BASELINE configs[3])",
+            "config": {"workload": workload(args.layers),
                        "rows_per_step": ROWS, "steps_per_s_per_gpu": 1e3 / ms_dev, "position": POSITION,
                        "cuda_graph": True, "programmatic_dependent_launch": not args.no_pdl,
                        "l2": "inputs larger than L2: 14.4 GB of weights, KV and state stream per step",
