@@ -56,6 +56,11 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
 
 /* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
  * next qb_marlin_gemm calls; zeros restore the built-in choice. */
+/* The zero-point variants marlin_*_z (kernels/marlin.cuh:126-133,588-594): same arguments; S holds the scales followed
+ * by the table (8 - z) * scale (qb_pack_marlin_z). w = (q - 8) * scale + (8 - z) * scale; the second term needs only
+ * the group's sum of x, which the kernel has anyway. More than 16 rows run as 16-row slabs. */
+int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
+                     int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 /* The residual add and RMSNorm between two products folded into them (steps of up to 16 rows): replaces the pairs
  * Gemm::marlin + Stack::add_rmsnorm of launch_step (src/cuda/qwen/mod.rs:744-766; kernels/dense.cuh:12-26) without a
  * launch of their own. RMSNorm is linear up to the row's 1 / rms, so the product after a norm runs on the un-normalised
@@ -251,6 +256,7 @@ typedef struct qb_mtp {
                                         whole output layer drafts) (src/cuda/qwen/draft.rs) */
     int head_rows, head_valid;
     const int* head_ids;             /* device: the token of each draft-head row */
+    int head_zero_points;            /* non-zero: head_s holds the (8 - z) * scale table too (Mat::marlin_rows with zeros) */
 } qb_mtp;
 
 /* A token of a step (Tok, src/engine.rs:90-95) */
@@ -309,6 +315,10 @@ int qb_model_step_kernels(const qb_model* m);    /* kernels of one step of the l
 int qb_row_order(int rows, int silu, int* h_order);
 int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int cols, int group, const int* h_order,
                    int n, uint32_t* h_words, uint16_t* h_scales_f16);
+/* with zero points (marlin_scale with zeros, src/cuda/core.rs:255-260): h_zeros u8 [rows][cols/group]; h_scales_f16 gets
+ * 2 * cols/128 rows: the scales, then (8 - z) * scale */
+int qb_pack_marlin_z(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int rows, int cols, int group,
+                     const int* h_order, int n, uint32_t* h_words, uint16_t* h_scales_f16);
 int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n, uint16_t* h_out);
 int qb_split_for(int tiles, int cols, int bits, int kd);
 

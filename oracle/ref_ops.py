@@ -63,7 +63,7 @@ def _marlin_lane_maps():
     return r, c
 
 
-def pack_marlin(q: np.ndarray, scales_f16: np.ndarray, order: np.ndarray):
+def pack_marlin(q: np.ndarray, scales_f16: np.ndarray, order: np.ndarray, zeros: np.ndarray | None = None):
     """q: uint8 [rows][k] stored codes (signed value + 8, 0..15); scales_f16: float16 [rows][k/128]; order: packed
     row -> source row. Returns (words uint32 [k/16][2n], scales float16 [k/128][n]) in Marlin's layout:
     marlin_word src/cuda/core.rs:244-253, pack_marlin :262-311 (word of (k16, c64, lane, blk) at
@@ -82,6 +82,11 @@ def pack_marlin(q: np.ndarray, scales_f16: np.ndarray, order: np.ndarray):
     at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8
     sc = np.zeros((k // QG, n), dtype=np.float16)
     sc[:, at] = scales_f16[order].T
+    if zeros is not None:
+        # the second table (8 - z) * scale, exact in f16 (marlin_scale, src/cuda/core.rs:255-260; pack_marlin :269-283)
+        off = np.zeros((k // QG, n), dtype=np.float16)
+        off[:, at] = ((8.0 - zeros[order].astype(np.float32)) * scales_f16[order].astype(np.float32)).astype(np.float16).T
+        sc = np.concatenate([sc, off], axis=0)
     return np.ascontiguousarray(words), sc
 
 
@@ -100,6 +105,14 @@ def unpack_marlin(words: np.ndarray, sc: np.ndarray):
     o = np.arange(n)
     at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8
     return q, np.ascontiguousarray(sc[:, at].T)
+
+
+def dequant_z(q: np.ndarray, scales_f16: np.ndarray, offsets_f16: np.ndarray) -> np.ndarray:
+    """With zero points: w = f16((q - 8) * scale + (8 - z) * scale), the fused multiply-add rounded once (scale_z,
+    kernels/marlin.cuh:126-133); offsets_f16 [rows][k/128] is the second table."""
+    s = np.repeat(scales_f16.astype(np.float64), QG, axis=1)
+    o = np.repeat(offsets_f16.astype(np.float64), QG, axis=1)
+    return ((q.astype(np.float64) - 8.0) * s + o).astype(np.float16)
 
 
 def dequant(q: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:

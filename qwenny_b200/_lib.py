@@ -22,6 +22,7 @@ SIGNATURES = {
     "qb_version": [],
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
+    "qb_marlin_gemm_z": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_gemm_fused": [P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, I, F],
     "qb_marlin_tune": [P, I, I, I, I],
     "qb_marlin_trace": [P, P],
@@ -72,6 +73,7 @@ SIGNATURES = {
     "qb_model_step_kernels": [P],
     "qb_row_order": [I, I, P],
     "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
+    "qb_pack_marlin_z": [P, P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],
     "qb_split_for": [I, I, I, I],
 }
@@ -94,7 +96,7 @@ class QbMtp(C.Structure):
     """qb_mtp of include/qwenny_b200.h."""
     _fields_ = [
         ("layer", QbLayer), ("fc_w", P), ("fc_s", P), ("pre_e", P), ("pre_h", P), ("norm", P), ("head_w", P),
-        ("head_s", P), ("head_rows", I), ("head_valid", I), ("head_ids", P),
+        ("head_s", P), ("head_rows", I), ("head_valid", I), ("head_ids", P), ("head_zero_points", I),
     ]
 
 

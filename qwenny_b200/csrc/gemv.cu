@@ -9,9 +9,9 @@ struct GemvPlan {
     int cluster_s;  // > 0: clustered split K with this many ranks per column block
 };
 
-static int smem_of(int cg, int kg, int m, int nstages) {
+static int smem_of(int cg, int kg, int m, int nstages, int zp = 0) {
     int nw = cg * kg, tk = kg * 128, tn = cg * 64;
-    return 128 + (tk + 8) * 2 + nstages * (nw * 4096 + kg * tn * 2 + m * (tk + 8) * 2);
+    return 128 + (tk + 8) * 2 + nstages * (nw * 4096 + (1 + zp) * kg * tn * 2 + m * (tk + 8) * 2);
 }
 
 // Blocks of the persistent grid and the most of them that can share one column block (the scratch stride).
@@ -25,11 +25,11 @@ static void grid_of(const qb_ctx* ctx, const GemvPlan& p, int n, int k, int* gri
     *maxc = (int)((kst + per - 1) / per) + 1;
 }
 
-template <int CG, int KG, int NT, int EPI>
+template <int CG, int KG, int NT, int EPI, int ZP = 0>
 static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& p) {
     using C = GemvCfg<CG, KG, NT>;
-    auto kern = w4a16_gemv_kernel<CG, KG, NT, EPI>;
-    int smem = C::smem(p.nstages, a.m);
+    auto kern = w4a16_gemv_kernel<CG, KG, NT, EPI, ZP>;
+    int smem = C::smem(p.nstages, a.m, a.zp);
     static int opted = 0;  // per instantiation
     if (opted < smem) {
         QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -101,6 +101,14 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
 
 template <int NT, int EPI>
 static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const GemvPlan& p) {
+    if (a.zp) {  // the zero-point variants: the three shapes the built-in choice uses
+        if (EPI == EPI_RESID) return QB_ERR_UNSUPPORTED;
+        constexpr int E = EPI == EPI_RESID ? EPI_PLAIN : EPI;
+        if (p.cg == 2 && p.kg == 4) return launch_cfg<2, 4, NT, E, 1>(ctx, st, a, p);
+        if (p.cg == 4 && p.kg == 2) return launch_cfg<4, 2, NT, E, 1>(ctx, st, a, p);
+        if (p.cg == 4 && p.kg == 1) return launch_cfg<4, 1, NT, E, 1>(ctx, st, a, p);
+        return QB_ERR_UNSUPPORTED;
+    }
     if (p.cg == 2 && p.kg == 4) return launch_cfg<2, 4, NT, EPI>(ctx, st, a, p);
     if (p.cg == 4 && p.kg == 2) return launch_cfg<4, 2, NT, EPI>(ctx, st, a, p);
     if (p.cg == 8 && p.kg == 1) return launch_cfg<8, 1, NT, EPI>(ctx, st, a, p);
@@ -112,10 +120,10 @@ static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const G
 // The built-in choice: wide matrices take 256 x 256 tiles (fewer, larger copies; a block's range crosses few column
 // blocks), narrow ones 128 x 512 so that a column block is shared by few blocks; the ring as deep as the blocks per
 // SM allow.
-static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int ctas) {
+static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int ctas, int zp = 0) {
     GemvPlan p;
     if (cg) { p.cg = cg; p.kg = kg; }
-    else if (n >= 65536 && n % 512 == 0) { p.cg = 8; p.kg = 1; }  // the output layer: no k groups to add up per piece
+    else if (n >= 65536 && n % 512 == 0 && !zp) { p.cg = 8; p.kg = 1; }  // the output layer: no k groups to add up per piece
     else if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
     else if (k % 512 == 0 && n % 128 == 0) { p.cg = 2; p.kg = 4; }
     else if (k % 256 == 0) { p.cg = 4; p.kg = 2; }
@@ -123,7 +131,7 @@ static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int
     p.ctas = ctas ? ctas : 2;
     const int budget = (228 * 1024) / p.ctas - 1024;
     p.nstages = 2;
-    while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, m, p.nstages + 1) <= budget) p.nstages++;
+    while (p.nstages < GEMV_MAX_STAGES && smem_of(p.cg, p.kg, m, p.nstages + 1, zp) <= budget) p.nstages++;
     // Clustered split K when the column blocks x ranks fit one wave of blocks: the most ranks (at most 8, the
     // portable cluster size) that fit, then as few as give the same longest share. The in-block reduction buffer
     // doubles as the rank's parking space, so the tile must have kg > 1.
@@ -169,13 +177,14 @@ extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas
 
 static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m,
                      int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid,
-                     const float* nw_out = nullptr, void* xu_out = nullptr, bool unnormed = false, float eps = 0.f) {
+                     const float* nw_out = nullptr, void* xu_out = nullptr, bool unnormed = false, float eps = 0.f,
+                     int zp = 0) {
     int nt = m <= 8 ? 1 : 2;
-    GemvPlan p = pick(ctx, n, k, m, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas);
+    GemvPlan p = pick(ctx, n, k, m, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas, zp);
     if (ctx->tune_nstages) p.nstages = ctx->tune_nstages;
     int tn = p.cg * 64, tk = p.kg * 128;
     if (n % tn || k % tk || p.nstages < 2 || p.nstages > GEMV_MAX_STAGES) return QB_ERR_ARG;
-    if (smem_of(p.cg, p.kg, m, p.nstages) > 227 * 1024 || (size_t)(n / 64) > ctx->ncounters) return QB_ERR_ARG;
+    if (smem_of(p.cg, p.kg, m, p.nstages, zp) > 227 * 1024 || (size_t)(n / 64) > ctx->ncounters) return QB_ERR_ARG;
     GemvArgs a;
     a.X = (const __half*)X; a.xrows = xrows; a.B = (const uint32_t*)B; a.S = (const __half*)S; a.Y = Y;
     a.m = m; a.N = n; a.K = k; a.row0 = row0;
@@ -184,6 +193,7 @@ static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B,
     a.trace = ctx->trace;
     if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
+    a.zp = zp;
     a.nw_out = nw_out; a.xu_out = (__half*)xu_out; a.sq = ctx->sq; a.rs = unnormed ? ctx->sq : nullptr; a.eps = eps;
 #define QB_GO(NT)                                                              \
     switch (epi) {                                                             \
@@ -223,6 +233,27 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
 
 
 // ------------------------------------------------------------------------------------------------ no-allocation variant
+// The zero-point variants (marlin_*_z, kernels/marlin.cuh:126-133): S holds the scales [k/128][n] followed by a second
+// table (8 - z) * scale in the same layout (pack_marlin with zeros, src/cuda/core.rs:262-285). Any row count: more than
+// 16 rows run as 16-row slabs through the skinny kernel (the tensor-core product has no zero-point form yet).
+extern "C" int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m,
+                                int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys,
+                                int n_valid) {
+    if (!ctx || !X || !B || !Y || !S || m < 0 || n <= 0 || k <= 0 || n % 256 || k % 128) return QB_ERR_ARG;
+    if (epi < 0 || epi > QB_EPI_ARGMAX) return QB_ERR_ARG;
+    if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
+    if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int r = 0; r < m; r += 16) {
+        int mm = m - r < 16 ? m - r : 16;
+        int rc = gemm_rows(ctx, st, X, B, Y, S, mm, n, k, xrows ? 0 : row0 + r, epi, xrows ? xrows + r : nullptr,
+                           keys ? keys + (xrows ? r : 0) : nullptr, n_valid, nullptr, nullptr, false, 0.f, 1);
+        if (rc) return rc;
+        if (xrows) Y = (char*)Y + (size_t)mm * (epi == QB_EPI_SILU ? n / 2 * 2 : (size_t)n * 4);
+    }
+    return QB_OK;
+}
+
 // Residual + RMSNorm folded into the products on either side of it (steps of up to 16 rows); see the header.
 extern "C" int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S,
                                     int m, int n, int k, int epi, const int* xrows, unsigned long long* keys,

@@ -233,9 +233,10 @@ int launch_mtp(qb_model* m, cudaStream_t st, bool own) {
     QB_TRY(launch_layer_tail(m, st, L, M.norm, k));
     if (m->n_out > 0) {
         const bool head = M.head_w != nullptr;
-        QB_TRY(qb_marlin_gemm(c, s, m->xn, head ? M.head_w : m->lm_w, m->logits, head ? M.head_s : m->lm_s, m->n_out,
-                              head ? M.head_rows : m->vocab_rows, H, 0, QB_EPI_ARGMAX, m->out_rows, m->keys,
-                              head ? M.head_valid : m->vocab_valid)); k++;
+        auto product = head && M.head_zero_points ? qb_marlin_gemm_z : qb_marlin_gemm;
+        QB_TRY(product(c, s, m->xn, head ? M.head_w : m->lm_w, m->logits, head ? M.head_s : m->lm_s, m->n_out,
+                       head ? M.head_rows : m->vocab_rows, H, 0, QB_EPI_ARGMAX, m->out_rows, m->keys,
+                       head ? M.head_valid : m->vocab_valid)); k++;
     }
     m->step_kernels = k;
     return QB_OK;

@@ -48,8 +48,24 @@ int qb_row_order(int rows, int silu, int* h_order) {
 //   h_scales f32 [rows][cols/group], group a multiple of 128
 //   h_order  n packed rows -> source row (n a multiple of 64)
 //   h_words  out: u32 [cols/16][2n]; h_sc out: f16 bits [cols/128][n], output o of a 64-group at 8 (o % 8) + o / 8
+static int pack_marlin(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int rows, int cols, int group,
+                       const int* h_order, int n, uint32_t* h_words, uint16_t* h_sc);
+
 int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int cols, int group, const int* h_order, int n,
                    uint32_t* h_words, uint16_t* h_sc) {
+    return pack_marlin(h_q, h_scales, nullptr, rows, cols, group, h_order, n, h_words, h_sc);
+}
+
+// With zero points (h_zeros u8 [rows][cols/group], the stored value z of w = (q - z) * scale): h_sc gets 2 cols/128
+// rows, the scales followed by (8 - z) * scale in the same layout (exact in f16: |8 - z| has at most 3 significant bits)
+int qb_pack_marlin_z(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int rows, int cols, int group,
+                     const int* h_order, int n, uint32_t* h_words, uint16_t* h_sc) {
+    if (!h_zeros) return QB_ERR_ARG;
+    return pack_marlin(h_q, h_scales, h_zeros, rows, cols, group, h_order, n, h_words, h_sc);
+}
+
+static int pack_marlin(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int rows, int cols, int group,
+                       const int* h_order, int n, uint32_t* h_words, uint16_t* h_sc) {
     if (!h_q || !h_scales || !h_order || !h_words || !h_sc) return QB_ERR_ARG;
     if (n % 64 || cols % 128 || group % 128 || cols % group) return QB_ERR_ARG;
     for (int i = 0; i < n; i++)
@@ -57,8 +73,11 @@ int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int col
     const int words = cols / 8, groups = cols / 128, qgroups = cols / group;
     for (int o = 0; o < n; o++) {
         int c64 = o / 64, c = o % 64, at = c64 * 64 + 8 * (c % 8) + c / 8;
-        for (int gi = 0; gi < groups; gi++)
-            h_sc[(size_t)gi * n + at] = f16_bits(h_scales[(size_t)h_order[o] * qgroups + gi * 128 / group]);
+        for (int gi = 0; gi < groups; gi++) {
+            const size_t gq = (size_t)h_order[o] * qgroups + gi * 128 / group;
+            h_sc[(size_t)gi * n + at] = f16_bits(h_scales[gq]);
+            if (h_zeros) h_sc[(size_t)(groups + gi) * n + at] = f16_bits((8.f - (float)h_zeros[gq]) * h_scales[gq]);
+        }
     }
     parallel_for(cols / 16, [&](int k16) {
         uint32_t* ws = h_words + (size_t)k16 * 2 * n;

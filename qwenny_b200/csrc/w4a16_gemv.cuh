@@ -55,6 +55,7 @@ struct GemvArgs {
     //  xu = f16(nw_out[c] * h_new[c]) [.][N] for the next product, and records per 64 outputs and token row the sum of
     //  squares of the new values in sq [N/64][SQ_ROWS];
     //  rs != null: X is such an xu; the epilogue multiplies row t of the result by rsqrt(sum_g rs[g][t] / K + eps).
+    int zp;               // zero points: S holds a second table [K/128][N] of (8 - z) * scale after the scales
     const float* nw_out;
     __half* xu_out;
     float* sq;
@@ -85,8 +86,9 @@ struct GemvCfg {
     static constexpr int RED_BYTES = (KG > 1 ? KG - 1 : 1) * CG * NT * 2048;  // lives in a consumed stage's weights
     static constexpr int BAR_BYTES = 128;
     // a stage holds the weights, the group scales and the m live rows of X; one zero row serves the other token rows
-    static constexpr int stage_bytes(int m) { return W_BYTES + S_BYTES + m * XROW * 2; }
-    static constexpr int smem(int nstages, int m) { return BAR_BYTES + XROW * 2 + nstages * stage_bytes(m); }
+    // (zp: the zero-point offsets of the stage's groups follow its scales)
+    static constexpr int stage_bytes(int m, int zp = 0) { return W_BYTES + (1 + zp) * S_BYTES + m * XROW * 2; }
+    static constexpr int smem(int nstages, int m, int zp = 0) { return BAR_BYTES + XROW * 2 + nstages * stage_bytes(m, zp); }
     static_assert(RED_BYTES <= W_BYTES, "the reduction buffer fits a stage's weights");
 };
 
@@ -200,7 +202,8 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT
     }
 }
 
-template <int CG, int KG, int NT, int EPI>
+// ZP: the zero-point variant (a.zp set): compiled apart so that the symmetric product carries none of it
+template <int CG, int KG, int NT, int EPI, int ZP = 0>
 __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kernel(const GemvArgs a) {
     using C = GemvCfg<CG, KG, NT>;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -208,8 +211,8 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     uint64_t* empty = full + GEMV_MAX_STAGES;
     uint8_t* zrow = smem + C::BAR_BYTES;              // XROW halves of zeros: the token rows m .. 8 NT - 1
     uint8_t* stages = zrow + C::XROW * 2;
-    const int STAGE_BYTES = C::stage_bytes(a.m);      // weights | scales | m rows of X
-    const int X_OFF = C::W_BYTES + C::S_BYTES;
+    const int STAGE_BYTES = C::stage_bytes(a.m, ZP);  // weights | scales (| offsets) | m rows of X
+    const int X_OFF = C::W_BYTES + (1 + ZP) * C::S_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nstages = a.nstages;
@@ -245,7 +248,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         // ------------------------------------------------------------ producer
         const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
         const uint32_t mine = (uint32_t)(end - beg);
-        const uint32_t tx = C::W_BYTES + C::S_BYTES + a.m * C::TK * 2;
+        const uint32_t tx = C::W_BYTES + (1 + ZP) * C::S_BYTES + a.m * C::TK * 2;
         // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
         auto issue = [&](int cb, int st, int slot, int what) {
             int n0 = cb * C::TN, k0 = st * C::TK;
@@ -259,6 +262,9 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 if (lane < KG)
                     bulk_g2s(base + C::W_BYTES + lane * (C::TN * 2),
                              a.S + (size_t)(k0 / 128 + lane) * a.N + n0, C::TN * 2, &full[slot], pol_w);
+                if (ZP && lane >= 8 && lane < 8 + KG)
+                    bulk_g2s(base + C::W_BYTES + C::S_BYTES + (lane - 8) * (C::TN * 2),
+                             a.S + (size_t)(a.K / 128 + k0 / 128 + lane - 8) * a.N + n0, C::TN * 2, &full[slot], pol_w);
             }
             if (what != 0) {
                 if (lane < a.m) {
@@ -356,6 +362,8 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                         (kg * 128 + 8 * (lane >> 3)) * 2;
             }
             uint4 sc4 = *(const uint4*)(base + C::W_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
+            uint4 zs4 = make_uint4(0, 0, 0, 0);
+            if (ZP) zs4 = *(const uint4*)(base + C::W_BYTES + C::S_BYTES + (kg * C::TN + cg * 64 + 8 * g) * 2);
             if (a.probe == 1) goto stage_done;
             // The nibbles go to the tensor core as f16 SUBNORMALS, with no subtraction at all: a low nibble n of a
             // 16-bit half is, as it stands, the half n * 2^-24 (q & 0x000f000f), a high one 16 n * 2^-24
@@ -407,6 +415,20 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                 for (int j = 0; j < NT; j++) {
                     acc[j][b][0] += s0 * (tmp[j][b][0] + corr[j][0]); acc[j][b][1] += s0 * (tmp[j][b][1] + corr[j][1]);
                     acc[j][b][2] += s1 * (tmp[j][b][2] + corr[j][2]); acc[j][b][3] += s1 * (tmp[j][b][3] + corr[j][3]);
+                }
+            }
+            if (ZP) {
+                // zero points: w = (q - 8) * scale + (8 - z) * scale; the second term times the group's sum of x, which
+                // the offset mma already holds: corr = -2^-21 * sum_k x_k
+                const __half* zh = (const __half*)&zs4;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    float z0 = __half2float(zh[2 * b]) * -2097152.f, z1 = __half2float(zh[2 * b + 1]) * -2097152.f;
+#pragma unroll
+                    for (int j = 0; j < NT; j++) {
+                        acc[j][b][0] += z0 * corr[j][0]; acc[j][b][1] += z0 * corr[j][1];
+                        acc[j][b][2] += z1 * corr[j][2]; acc[j][b][3] += z1 * corr[j][3];
+                    }
                 }
             }
         }

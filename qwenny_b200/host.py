@@ -32,9 +32,10 @@ def quant_words(codes: np.ndarray) -> np.ndarray:
 
 
 def pack_marlin(codes: np.ndarray, scales: np.ndarray, silu: bool = False, order: np.ndarray | None = None,
-                group: int = QG):
+                group: int = QG, zeros: np.ndarray | None = None):
     """codes uint8 [rows][cols] (q + 8), scales f32 [rows][cols/group] -> (words uint32 [cols/16][2n],
-    scales float16 [cols/128][n]) as Mat::marlin does (src/cuda/core.rs:160-164)."""
+    scales float16 [cols/128][n]) as Mat::marlin does (src/cuda/core.rs:160-164). With zeros (uint8
+    [rows][cols/group], w = (q - z) * scale) the scales are followed by the table (8 - z) * scale: [2 cols/128][n]."""
     rows, cols = codes.shape
     if order is None:
         order = row_order(rows, silu)
@@ -43,6 +44,12 @@ def pack_marlin(codes: np.ndarray, scales: np.ndarray, silu: bool = False, order
     q = np.ascontiguousarray(quant_words(codes))
     sc = np.ascontiguousarray(scales, dtype=np.float32)
     words = np.empty((cols // 16, 2 * n), dtype=np.uint32)
+    if zeros is not None:
+        z = np.ascontiguousarray(zeros, dtype=np.uint8)
+        s16 = np.empty((2 * (cols // 128), n), dtype=np.uint16)
+        check(lib().qb_pack_marlin_z(_np(q), _np(sc), _np(z), rows, cols, group, _np(order), n, _np(words), _np(s16)),
+              "qb_pack_marlin_z")
+        return words, s16.view(np.float16)
     s16 = np.empty((cols // 128, n), dtype=np.uint16)
     check(lib().qb_pack_marlin(_np(q), _np(sc), rows, cols, group, _np(order), n, _np(words), _np(s16)),
           "qb_pack_marlin")

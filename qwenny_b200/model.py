@@ -109,6 +109,7 @@ class Model:
             q.head_w, q.head_s = mtp["head"].words.data_ptr(), mtp["head"].scales.data_ptr()
             q.head_rows, q.head_valid = mtp["head"].n, mtp["head_valid"]
             q.head_ids = mtp["head_ids"].data_ptr()
+            q.head_zero_points = int(bool(mtp.get("head_zero_points")))
         check(lib().qb_model_set_mtp(self.h, C.byref(q)), "qb_model_set_mtp")
         self.mtp = mtp
 

@@ -57,7 +57,7 @@ class Context:
 
     # ---- products
     def marlin_gemm(self, x, words, scales, epi="plain", y=None, row0=0, m=None, xrows=None, keys=None,
-                    n_valid=None):
+                    n_valid=None, zp=False):
         """x f16 [rows][k]; words int32 [k/16][2n]; scales f16 [k/128][n]. Returns y (f32 [m][n] or f16 [m][n/2])."""
         k = x.shape[1]
         n = words.shape[1] // 2
@@ -67,8 +67,9 @@ class Context:
             rows = m if xrows is not None else row0 + m
             y = torch.empty((rows, n // 2), dtype=torch.float16, device=x.device) if epi == "silu" else \
                 torch.empty((rows, n), dtype=torch.float32, device=x.device)
-        check(lib().qb_marlin_gemm(self.h, _stream(), _p(x), _p(words), _p(y), _p(scales), m, n, k, row0, EPI[epi],
-                                   _p(xrows), _p(keys), n if n_valid is None else n_valid), "qb_marlin_gemm")
+        fn = lib().qb_marlin_gemm_z if zp else lib().qb_marlin_gemm  # zp: scales followed by the (8 - z) * scale table
+        check(fn(self.h, _stream(), _p(x), _p(words), _p(y), _p(scales), m, n, k, row0, EPI[epi],
+                 _p(xrows), _p(keys), n if n_valid is None else n_valid), "qb_marlin_gemm")
         return y
 
     def gemm_f16_plain(self, w_packed, x, n, K, ntiles, kper, y=None, xrows=None):

@@ -148,3 +148,40 @@ def test_many_rows_fall_back_to_slabs(ctx):
     x, wdq, xd, wd, sd = make(512, 512, False, 21, 40)
     y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
     assert close(y, R.marlin_gemm(x, wdq)).all()
+
+
+@pytest.mark.parametrize("m,epi", [(1, "plain"), (5, "plain"), (13, "plain"), (5, "silu"), (5, "argmax"), (40, "plain")])
+@pytest.mark.parametrize("rows,cols", [(512, 1024), (2560, 512)])
+def test_zero_point_product_vs_oracle(ctx, m, epi, rows, cols):
+    """The marlin_*_z variants (asymmetric int4): w = (q - 8) * scale + (8 - z) * scale with the second table after the
+    scales; against the oracle's dequantisation (the reference's single f16 rounding of the sum) in f64. 40 rows run
+    as 16-row slabs."""
+    g = synth.gen(700 + m)
+    silu = epi == "silu"
+    x = synth.activations(m, cols, g)
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    zeros = torch.randint(0, 16, (rows, cols // 128), generator=g, dtype=torch.uint8).numpy()
+    words, s16 = host.pack_marlin(codes, sc, silu=silu, zeros=zeros)
+    off = ((8.0 - zeros.astype(np.float32)) * sc).astype(np.float16)
+    wdq = R.dequant_z(codes, sc.astype(np.float16), off)[R.row_order(rows, silu)]
+    dev = lambda a: torch.from_numpy(a).cuda()
+    xd, wd, sd = dev(x), dev(words.view(np.int32)), dev(s16.view(np.int16)).view(torch.float16)
+    want = R.marlin_gemm(x, wdq)
+    if epi == "argmax":
+        keys = torch.zeros(m, dtype=torch.int64, device="cuda")
+        y = ctx.marlin_gemm(xd, wd, sd, epi="argmax", keys=keys, n_valid=rows - 3, zp=True).cpu().numpy()
+        tok = [int(0xffffffff - (int(k) & 0xffffffff)) for k in keys.cpu().numpy()]
+        assert close(y, want).all()
+        for r in range(m):
+            best = np.sort(want[r, :rows - 3])
+            assert tok[r] == int(np.argmax(y[r, :rows - 3])) and (tok[r] == int(np.argmax(want[r, :rows - 3])) or
+                                                                    best[-1] - best[-2] < 1e-3)
+        return
+    y = ctx.marlin_gemm(xd, wd, sd, epi=epi, zp=True).float().cpu().numpy()
+    if silu:
+        b = want.reshape(m, -1, 2, 8)
+        want = (R.silu(b[:, :, 0, :]) * b[:, :, 1, :]).reshape(m, -1)
+    assert close(y, want).all()
+    # and it is not the symmetric product: the zero points matter
+    ys = ctx.marlin_gemm(xd, wd, sd[:cols // 128].contiguous(), epi=epi).float().cpu().numpy()
+    assert not close(ys, want).all()

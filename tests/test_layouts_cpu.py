@@ -2,6 +2,7 @@
 layout algebra the kernels rely on."""
 import numpy as np
 import pytest
+import torch
 
 from oracle import ref_ops as R
 from qwenny_b200 import host, synth
@@ -72,3 +73,20 @@ def test_kv_slots_are_permutations():
     pos = np.repeat(np.arange(32), R.HD)
     dd = np.tile(d, 32)
     assert sorted(R.vslot(pos, dd).tolist()) == list(range(32 * R.HD))
+
+
+def test_pack_marlin_with_zero_points_matches_oracle():
+    """The second scale table (8 - z) * scale of asymmetric int4 (pack_marlin with zeros, src/cuda/core.rs:262-285)."""
+    g = synth.gen(9)
+    rows, cols = 128, 512
+    codes, sc = synth.int4_matrix(rows, cols, g)
+    zeros = torch.randint(0, 16, (rows, cols // 128), generator=g, dtype=torch.uint8).numpy()
+    words, s16 = host.pack_marlin(codes, sc, zeros=zeros)
+    ow, os_ = R.pack_marlin(codes, sc.astype(np.float16), R.row_order(rows, False), zeros=zeros)
+    assert np.array_equal(words, ow) and s16.shape == (2 * cols // 128, rows)
+    assert np.array_equal(s16.view(np.uint16), os_.view(np.uint16))
+    # the offsets are exact: |8 - z| <= 8 times a bf16 significand
+    off = (8.0 - zeros.astype(np.float64)) * sc.astype(np.float64)
+    o = np.arange(rows)
+    at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8
+    assert np.array_equal(s16[cols // 128:][:, at].T.astype(np.float64), off)
