@@ -421,17 +421,19 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
 // values of a 32-key stage arrive through the same bulk-copy ring as in the decode kernel; here the block converts
 // them ONCE to f16 in shared memory (keys as [key][dim], values transposed as [dim][key], the 128 offset subtracted
 // exactly), and every warp reads its mma B fragments from there with ldmatrix, so the conversion is shared by the 8 row
-// tiles instead of being repeated per row tile. Two f16 buffers: the block converts stage i + 1 while slower warps
-// still multiply stage i; one block barrier per stage. Two tiles that are not consecutive tokens of one sequence (a
-// segment boundary) run one after the other in the same block.
-constexpr int PF_SK = 32, PF_NSTG = 3, PF_WARPS = 8, PF_ROWS = 128, PF_TROWS = 64;
+// tiles instead of being repeated per row tile. Three f16 buffers and no block barrier in the loop: every warp converts
+// its share of stage i + 1 BEFORE it multiplies stage i, and mbarriers say when a converted stage is complete
+// (cvt, 8 arrivals) and when a buffer's products are done (done, 8 arrivals), so a warp waits only for a warp that is a
+// whole stage behind. Two tiles that are not consecutive tokens of one sequence (a segment boundary) run one after
+// the other in the same block.
+constexpr int PF_SK = 32, PF_NSTG = 2, PF_NF16 = 3, PF_WARPS = 8, PF_ROWS = 128, PF_TROWS = 64;
 constexpr int PF_RAW = PF_SK * HD * 2 + PF_SK * 8;          // key bytes, value bytes, key scales, value scales
 constexpr int PF_KROW = HD + 8;                              // halves per f16 key row (528 B: ldmatrix rows on distinct banks)
 constexpr int PF_VROW = PF_SK + 8;                           // halves per row of V^T (80 B, same reason)
 constexpr int PF_KF16 = PF_SK * PF_KROW * 2, PF_VF16 = HD * PF_VROW * 2;
 constexpr int PF_F16 = PF_KF16 + PF_VF16 + PF_SK * 8;        // + the stage's 32 key scales and 32 value scales
 constexpr int PF_Q_BYTES = PF_ROWS * SROW * 2;
-constexpr int PF_SMEM = 128 + PF_Q_BYTES + PF_NSTG * PF_RAW + 2 * PF_F16;
+constexpr int PF_SMEM = 128 + PF_Q_BYTES + PF_NSTG * PF_RAW + PF_NF16 * PF_F16;
 static_assert(PF_SMEM <= 227 * 1024 && PF_RAW % 128 == 0 && PF_F16 % 128 == 0 && PF_TROWS >= (64 / GROUP) * GROUP, "prefill attention: shared memory");
 
 __device__ __forceinline__ uint32_t kv_exact2(uint32_t w, uint32_t sel) {
@@ -450,12 +452,15 @@ attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + PF_NSTG;
+    uint64_t* cvt = empty + PF_NSTG;   // per f16 buffer: its stage is converted (all warps)
+    uint64_t* done = cvt + PF_NF16;    // per f16 buffer: its stage is multiplied (all warps)
     __half* qsh = (__half*)(smem + 128);
     uint8_t* ring = smem + 128 + PF_Q_BYTES;
     uint8_t* f16b = ring + PF_NSTG * PF_RAW;
     const int g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, t4 = lane & 3;
     if (threadIdx.x == 0) {
         for (int i = 0; i < PF_NSTG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], PF_WARPS); }
+        for (int i = 0; i < PF_NF16; i++) { mbar_init(&cvt[i], PF_WARPS); mbar_init(&done[i], PF_WARPS); }
         mbar_fence_init();
     }
     __syncthreads();
@@ -537,18 +542,18 @@ attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const 
         const uint32_t qa = smem_u32(qsh + (warp * 16 + (lane & 15)) * SROW + (lane >> 4) * 8);
         __syncthreads();  // Q is complete
 
-        for (int i = 0; i < nstg; i++) {
-            const int J = jbase + i, sl = J % PF_NSTG;
-            const uint32_t par = (J / PF_NSTG) & 1;
-            if (warp == 0 && i + 2 < nstg && copy_ok) issue(i + 2);
+        // Wait for stage i's bytes, convert this warp's share into f16 buffer J % 3 (once its previous stage has been
+        // multiplied by every warp), give the raw slot back, and say so.
+        auto convert = [&](int i) {
+            const int J = jbase + i, sl = J % PF_NSTG, fbi = J % PF_NF16;
+            bool ok = true;
             if (!dead) {
-                dead = !mbar_wait(&full[sl], par);
-                if (dead && lane == 0) atomicExch(err, 6);
-            } else {
-                for (int k = 0; k < 1024 && !mbar_try_wait(&full[sl], par); k++) {}
+                ok = mbar_wait(&full[sl], (J / PF_NSTG) & 1);
+                if (ok && J >= PF_NF16) ok = mbar_wait(&done[fbi], ((J / PF_NF16) - 1) & 1);
+                if (!ok) { dead = true; if (lane == 0) atomicExch(err, 6); }
             }
             const uint8_t* raw = ring + sl * PF_RAW;
-            uint8_t* fb = f16b + (J & 1) * PF_F16;
+            uint8_t* fb = f16b + fbi * PF_F16;
             __half* kf = (__half*)fb;
             __half* vf = (__half*)(fb + PF_KF16);
             float* scf = (float*)(fb + PF_KF16 + PF_VF16);
@@ -591,8 +596,25 @@ attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const 
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[sl]);  // the raw stage is consumed
-            __syncthreads();                          // the f16 stage is complete; the other buffer is free again
+            if (lane == 0) {
+                mbar_arrive(&empty[sl]);  // the raw stage is consumed
+                mbar_arrive(&cvt[fbi]);   // this warp's share of the f16 stage is written
+            }
+        };
+        convert(0);
+        for (int i = 0; i < nstg; i++) {
+            const int J = jbase + i, fbi = J % PF_NF16;
+            if (warp == 0 && i + 2 < nstg && copy_ok) issue(i + 2);
+            if (i + 1 < nstg) convert(i + 1);
+            if (!dead) {
+                dead = !mbar_wait(&cvt[fbi], (J / PF_NF16) & 1);
+                if (dead && lane == 0) atomicExch(err, 7);
+            }
+            uint8_t* fb = f16b + fbi * PF_F16;
+            __half* kf = (__half*)fb;
+            __half* vf = (__half*)(fb + PF_KF16);
+            float* scf = (float*)(fb + PF_KF16 + PF_VF16);
+            const int kb0 = i * PF_SK;
 
             if (kb0 < wmax) {
                 // ---- S = Q K^T over the stage's 32 keys (4 n-tiles)
@@ -669,6 +691,8 @@ attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const 
                     }
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&done[fbi]);  // this warp is through with the stage's f16 buffer
         }
         // ---- the rows are finished: out *= O / L (the gate is there), and the f16 copy
 #pragma unroll
