@@ -87,7 +87,7 @@ class ClockSampler:
 
 def workload(layers: int) -> str:
     return (f"full 27B-shape hybrid decoder verify step ({layers} layers, int4 g128 weights, int8 KV): 5 rows (1 token + 4 "
-            f"MTP drafts) at context {POSITION}, one slot per GPU (BASELINE configs[3])")
+            f"MTP drafts) at context {POSITION}, one slot per GPU (the benchmark's full-step configuration)")
 
 
 def cpu_baseline(seconds: float):

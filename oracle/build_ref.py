@@ -17,7 +17,10 @@ OUT = os.path.join(HERE, "_ref", "qwen27b.ptx")
 CUBIN = os.path.join(HERE, "_ref", "qwen27b.cubin")
 
 
-def build(reference: str = "/root/reference", force: bool = False) -> str | None:
+def build(reference: str | None = None, force: bool = False) -> str | None:
+    # the reference checkout: $QWENNY_REFERENCE, else the directory `reference` beside this repository
+    if reference is None:
+        reference = os.environ.get("QWENNY_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     src = os.path.join(reference, "kernels", "qwen.cu")
     if not os.path.exists(src):
         return OUT if os.path.exists(OUT) else None

@@ -10,7 +10,7 @@ from qwenny_b200 import host, synth
 
 pytestmark = pytest.mark.gpu
 
-# BASELINE tolerance for matrix-product outputs: 1e-2 relative / 2e-3 absolute after rounding both sides to bf16
+# The benchmark's tolerance for matrix-product outputs: 1e-2 relative / 2e-3 absolute after rounding both sides to bf16
 RTOL, ATOL = 1e-2, 2e-3
 
 
@@ -126,7 +126,7 @@ def test_argmax_vs_oracle(ctx):
 
 @pytest.mark.parametrize("m", [1, 5, 16])
 def test_config0_vs_oracle(ctx, m):
-    """BASELINE config 0: N=17408 x K=5120, g128, seed 0."""
+    """The benchmark's single-product configuration: N=17408 x K=5120, g128, seed 0."""
     x, wdq, xd, wd, sd = make(17408, 5120, False, 0, m)
     a = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
     want = R.marlin_gemm(x, wdq)
