@@ -54,8 +54,6 @@ const char* qb_version(void);
 int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                    int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 
-/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
- * next qb_marlin_gemm calls; zeros restore the built-in choice. */
 /* The zero-point variants marlin_*_z (kernels/marlin.cuh:126-133,588-594): same arguments; S holds the scales followed
  * by the table (8 - z) * scale (qb_pack_marlin_z). w = (q - 8) * scale + (8 - z) * scale; the second term needs only
  * the group's sum of x, which the kernel has anyway. More than 16 rows run as 16-row slabs. */
@@ -75,6 +73,8 @@ int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, vo
 int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                          int k, int epi, const int* xrows, unsigned long long* keys, int n_valid,
                          const float* norm_w_out, void* xu_out, int x_unnormed, float eps);
+/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
+ * next qb_marlin_gemm calls; zeros restore the built-in choice. */
 int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
 /* qb_marlin_gemm without a context and without any allocation, for callers that cannot call cudaMalloc (an engine
