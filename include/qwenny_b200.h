@@ -125,6 +125,30 @@ int qb_mtp_in(qb_ctx* ctx, void* stream, const float* emb, const float* h, const
               const float* pre_e, const float* pre_h, void* y, float eps, int n);
 int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, const int* head_ids, int n_out,
                   int* next_ids, int* chain, int chain_ld, int t);
+/* ---- the GPU sampler (kernels/sampling.cuh; host definition src/sample.rs:88-211).
+ * QB_QD, QB_QCAP: drafts per chain and kept tokens per stored draft distribution (QD, QCAP, kernels/sampling.cuh:73-74).
+ * qb_sample_rows   sample_rows, kernels/sampling.cuh:188-291 (Step::sample, src/cuda/core.rs:977-1005): one token per
+ *                  logit row [n_out][vocab] in vLLM's order (repetition penalty over seen + the step's tokens of the
+ *                  row's sequence, presence penalty over outs + those tokens, temperature, top-k, top-p), drawn with
+ *                  the host's uniform numbers; params f32 [n_out][8] = temperature, top_k, top_p, repetition penalty,
+ *                  u1, u2, draft (-1: none; d <= -2: the draft -d - 2 drawn by qb_draft_sample), presence penalty.
+ *                  out_tok[row] = token, out_acc[row] = draft accepted, or -1: the row needs more candidates than
+ *                  QB_QCAP (top_k 0 or above it) and is the host's, as in the reference. seen / outs: vocab / 32 words
+ *                  per slot. Tokens are those of the reference kernel, draw for draw.
+ * qb_draft_sample  draft_sample, kernels/sampling.cuh:298-352 (Step::draft_sample, src/cuda/core.rs:1036-1073): a
+ *                  draft per row of a draft step from its `width` logits (rows ld apart; column i is token
+ *                  head_ids[i], or i when head_ids is null) under the row's sampling, u = params[4], t = params[5] the
+ *                  draft's index in its chain; drafts[row] = token, and q (qtok, qn, qid ascending, qp) is stored for
+ *                  (slot, t). */
+#define QB_QD 16
+#define QB_QCAP 1024
+int qb_sample_rows(qb_ctx* ctx, void* stream, const float* logits, int vocab, int n_out, const int* out_rows,
+                   const int* tok_slot, const int* ids, const int* row_first, const unsigned* seen,
+                   const unsigned* outs, const float* params, const int* qtok, const int* qn, const int* qid,
+                   const float* qp, int* out_tok, int* out_acc);
+int qb_draft_sample(qb_ctx* ctx, void* stream, const float* logits, int width, int ld, const int* head_ids, int vocab,
+                    int n_out, const int* out_rows, const int* tok_slot, const unsigned* seen, const unsigned* outs,
+                    const float* params, int* drafts, int* qtok, int* qn, int* qid, float* qp);
 int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
              int nkeys, int n);
 int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n);

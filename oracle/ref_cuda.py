@@ -154,6 +154,22 @@ class RefModule:
     def mark_seen(self, seen, mark, mark_at, seg_slot, seg_pos0, segs):
         self.launch("mark_seen", (segs,), 256, 0, [_ptr(seen), _ptr(mark), _ptr(mark_at), _ptr(seg_slot), _ptr(seg_pos0)])
 
+    # ------------------------------------------------------------------------------------------ sampler
+    def sample_rows(self, logits, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn, qid, qp, out_tok,
+                    out_acc, n_out):
+        """Step::sample's launch (src/cuda/core.rs:982-999): one block of 1024 threads per logit row; the vocabulary is
+        the module's compile-time VOCAB."""
+        self.launch("sample_rows", (n_out,), 1024, 0,
+                    [_ptr(logits), _ptr(out_rows), _ptr(tok_slot), _ptr(ids), _ptr(row_first), _ptr(seen), _ptr(outs),
+                     _ptr(params), _ptr(qtok), _ptr(qn), _ptr(qid), _ptr(qp), _ptr(out_tok), _ptr(out_acc)])
+
+    def draft_sample(self, logits, width, ld, head_ids, out_rows, tok_slot, seen, outs, params, drafts, qtok, qn, qid,
+                     qp, n_out):
+        """Step::draft_sample's launch (src/cuda/core.rs:1052-1071)."""
+        self.launch("draft_sample", (n_out,), 1024, 0,
+                    [_ptr(logits), C.c_int(width), C.c_int(ld), _ptr(head_ids), _ptr(out_rows), _ptr(tok_slot),
+                     _ptr(seen), _ptr(outs), _ptr(params), _ptr(drafts), _ptr(qtok), _ptr(qn), _ptr(qid), _ptr(qp)])
+
     # ------------------------------------------------------------------------------------------ attention
     def attn_prep(self, part, splits, n, q_norm, k_norm, inv_freq, qscale, q, out, kc, vc, ks, vs, tok_slot, tok_pos,
                   cap):

@@ -33,6 +33,8 @@ SIGNATURES = {
     "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
     "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
     "qb_draft_pick": [P, P, P, P, I, P, P, I, I],
+    "qb_sample_rows": [P, P, P, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "qb_draft_sample": [P, P, P, I, I, P, I, I, P, P, P, P, P, P, P, P, P, P],
     "qb_model_set_mtp": [P, P],
     "qb_model_draft": [P, P, P, I, P, P, I, I, P],
     "qb_embed": [P, P, P, P, P, P, I, I],

@@ -7,6 +7,7 @@
     python -m qwenny_b200.microbench delta [--rows 2048 | --rows 5]
     python -m qwenny_b200.microbench draft [--k 4] [--draft-rows 65536]
     python -m qwenny_b200.microbench chain [--rows 5] [--trace] [--probe 1|2]
+    python -m qwenny_b200.microbench sampler [--rows 5] [--top-k 50] [--top-p 0.95] [--penalty 1.1] [--draft-rows 0]
 
 Each prints CUDA-event timings (launches replayed from a CUDA graph, inputs larger than L2 where the shape allows)
 and is small enough to sit under `ncu` (-k <kernel> -s <warm-up launches> -c <few>). Synthetic inputs, seeded.
@@ -197,6 +198,53 @@ def draft(args):
           f"device error {ctx.device_error()}")
 
 
+def sampler(args):
+    """qb_sample_rows over --rows logit rows of the 27B vocabulary (or qb_draft_sample over a draft head of
+    --draft-rows columns): seeded logits with a few likely tokens, 200 tokens seen per slot."""
+    ctx = Context(0)
+    ctx.set_pdl(True)
+    V, n, QD, QCAP = 248320, args.rows, 16, 1024
+    g = torch.Generator(device="cuda").manual_seed(3)
+    W = args.draft_rows or V
+    logits = torch.randn(n, W, generator=g, device="cuda") * 2
+    logits[:, ::9973] += 6
+    out_rows = torch.arange(n, dtype=torch.int32, device="cuda")
+    tok_slot = torch.zeros(n, dtype=torch.int32, device="cuda")
+    ids = torch.randint(0, V, (n,), generator=g, device="cuda", dtype=torch.int32)
+    row_first = torch.zeros(n, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(V // 32, dtype=torch.int32, device="cuda")
+    seen[torch.randint(0, V // 32, (200,), generator=g, device="cuda")] = 1 << 7
+    outs = seen.clone()
+    qtok = torch.full((QD,), -1, dtype=torch.int32, device="cuda")
+    qn = torch.zeros(QD, dtype=torch.int32, device="cuda")
+    qid = torch.zeros(QD * QCAP, dtype=torch.int32, device="cuda")
+    qp = torch.zeros(QD * QCAP, dtype=torch.float32, device="cuda")
+    params = torch.tensor([[args.temperature, args.top_k, args.top_p, args.penalty, 0.37 + 0.1 * j, 0.5, -1, 0.0]
+                           for j in range(n)], dtype=torch.float32, device="cuda")
+    tok = torch.zeros(n, dtype=torch.int32, device="cuda")
+    acc = torch.zeros(n, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    if args.draft_rows:
+        hid = torch.arange(W, dtype=torch.int32, device="cuda") * 3
+        params[:, 5] = 0
+        one = torch.zeros(1, dtype=torch.int32, device="cuda")  # rows of one launch may not share a (slot, t)
+        fn = lambda: ctx.draft_sample(logits, W, W, hid, V, 1, one, tok_slot, seen, outs, params, tok, qtok, qn, qid,
+                                      qp)
+    else:
+        fn = lambda: ctx.sample_rows(logits, V, n, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn,
+                                     qid, qp, tok, acc)
+    if args.plain:
+        with torch.cuda.stream(stream):
+            for _ in range(args.reps):
+                fn()
+        torch.cuda.synchronize()
+        us = float("nan")
+    else:
+        us = _time_graph(fn, stream, args.reps)
+    print(f"sampler rows={1 if args.draft_rows else n} width={W} top_k={args.top_k} top_p={args.top_p} "
+          f"penalty={args.penalty}: {us:.1f} us per launch, tokens {tok.tolist()}, device error {ctx.device_error()}")
+
+
 def delta(args):
     """The DeltaNet kernels of one prompt segment: conv once, then the rule kernel timed alone."""
     ctx = Context(0)
@@ -350,6 +398,12 @@ def main():
     d.add_argument("--no-pdl", action="store_true"); d.add_argument("--plain", action="store_true")
     d.add_argument("--probe", type=int, default=0); d.add_argument("--trace", action="store_true")
     d.set_defaults(fn=chain)
+    sp = sub.add_parser("sampler")
+    sp.add_argument("--rows", type=int, default=5); sp.add_argument("--top-k", type=int, default=50)
+    sp.add_argument("--top-p", type=float, default=0.95); sp.add_argument("--penalty", type=float, default=1.1)
+    sp.add_argument("--temperature", type=float, default=0.8); sp.add_argument("--draft-rows", type=int, default=0)
+    sp.add_argument("--reps", type=int, default=20); sp.add_argument("--plain", action="store_true")
+    sp.set_defaults(fn=sampler)
     args = ap.parse_args()
     args.fn(args)
 

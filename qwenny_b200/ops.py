@@ -105,6 +105,20 @@ class Context:
         check(lib().qb_draft_pick(self.h, _stream(), _p(keys), _p(head_ids), n_out, _p(next_ids), _p(chain), chain_ld, t),
               "qb_draft_pick")
 
+    def sample_rows(self, logits, vocab, n_out, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn, qid,
+                    qp, out_tok, out_acc):
+        """Step::sample (src/cuda/core.rs:977-1005) without the host rows: out_acc -1 marks those."""
+        check(lib().qb_sample_rows(self.h, _stream(), _p(logits), vocab, n_out, _p(out_rows), _p(tok_slot), _p(ids),
+                                   _p(row_first), _p(seen), _p(outs), _p(params), _p(qtok), _p(qn), _p(qid), _p(qp),
+                                   _p(out_tok), _p(out_acc)), "qb_sample_rows")
+
+    def draft_sample(self, logits, width, ld, head_ids, vocab, n_out, out_rows, tok_slot, seen, outs, params, drafts,
+                     qtok, qn, qid, qp):
+        """Step::draft_sample (src/cuda/core.rs:1036-1073)."""
+        check(lib().qb_draft_sample(self.h, _stream(), _p(logits), width, ld, _p(head_ids), vocab, n_out, _p(out_rows),
+                                    _p(tok_slot), _p(seen), _p(outs), _p(params), _p(drafts), _p(qtok), _p(qn),
+                                    _p(qid), _p(qp)), "qb_draft_sample")
+
     def rmsnorm(self, x, w, y, n, eps=1e-6):
         check(lib().qb_rmsnorm(self.h, _stream(), _p(x), _p(w), _p(y), eps, n), "qb_rmsnorm")
 
