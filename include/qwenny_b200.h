@@ -128,7 +128,8 @@ int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, con
 /* ---- the GPU sampler (kernels/sampling.cuh; host definition src/sample.rs:88-211).
  * QB_QD, QB_QCAP: drafts per chain and kept tokens per stored draft distribution (QD, QCAP, kernels/sampling.cuh:73-74).
  * qb_sample_rows   sample_rows, kernels/sampling.cuh:188-291 (Step::sample, src/cuda/core.rs:977-1005): one token per
- *                  logit row [n_out][vocab] in vLLM's order (repetition penalty over seen + the step's tokens of the
+ *                  logit row (`width` logits, rows ld floats apart; the reference's VOCAB is all three of width, ld
+ *                  and vocab) in vLLM's order (repetition penalty over seen + the step's tokens of the
  *                  row's sequence, presence penalty over outs + those tokens, temperature, top-k, top-p), drawn with
  *                  the host's uniform numbers; params f32 [n_out][8] = temperature, top_k, top_p, repetition penalty,
  *                  u1, u2, draft (-1: none; d <= -2: the draft -d - 2 drawn by qb_draft_sample), presence penalty.
@@ -139,13 +140,20 @@ int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, con
  *                  draft per row of a draft step from its `width` logits (rows ld apart; column i is token
  *                  head_ids[i], or i when head_ids is null) under the row's sampling, u = params[4], t = params[5] the
  *                  draft's index in its chain; drafts[row] = token, and q (qtok, qn, qid ascending, qp) is stored for
- *                  (slot, t). */
+ *                  (slot, t).
+ * qb_host_sample_row  sample::sample_row / sample_row_q (src/sample.rs:141-200) as Step::sample_on_host calls them
+ *                  (src/cuda/core.rs:1007-1032) for the rows qb_sample_rows marks -1. HOST pointers: the row's n
+ *                  logits, the slot's two sets (n / 32 words or more; null: empty), the step's tokens of the row's
+ *                  sequence after its first up to the row's own, the row's eight parameters, and, for a row whose draft
+ *                  is marked sampled, the stored q (ascending ids; nq 0: none, the draft counts as an argmax's). */
 #define QB_QD 16
 #define QB_QCAP 1024
-int qb_sample_rows(qb_ctx* ctx, void* stream, const float* logits, int vocab, int n_out, const int* out_rows,
-                   const int* tok_slot, const int* ids, const int* row_first, const unsigned* seen,
-                   const unsigned* outs, const float* params, const int* qtok, const int* qn, const int* qid,
-                   const float* qp, int* out_tok, int* out_acc);
+int qb_sample_rows(qb_ctx* ctx, void* stream, const float* logits, int width, int ld, int vocab, int n_out,
+                   const int* out_rows, const int* tok_slot, const int* ids, const int* row_first,
+                   const unsigned* seen, const unsigned* outs, const float* params, const int* qtok, const int* qn,
+                   const int* qid, const float* qp, int* out_tok, int* out_acc);
+int qb_host_sample_row(const float* logits, int n, const unsigned* seen, const unsigned* outs, const int* step,
+                       int nstep, const float* row, const int* q_ids, const float* q_p, int nq, int* tok, int* acc);
 int qb_draft_sample(qb_ctx* ctx, void* stream, const float* logits, int width, int ld, const int* head_ids, int vocab,
                     int n_out, const int* out_rows, const int* tok_slot, const unsigned* seen, const unsigned* outs,
                     const float* params, int* drafts, int* qtok, int* qn, int* qid, float* qp);
@@ -309,6 +317,24 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, cons
 int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp);
 int qb_model_draft(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
                    int n_out, int k, int* h_drafts);
+/* The sampler on the step's logits (f-row 2 of the scope).
+ * qb_model_set_outputs   Step::set_outputs: the tokens a slot's request generated so far, h_words = vocab_rows / 32
+ *                        host words (the presence penalty's set; the seen set is kept by the steps themselves).
+ * qb_model_sample        Step::sample (src/cuda/core.rs:977-1005): a token per logit row of the last step under
+ *                        h_params [n_out][8] (see qb_sample_rows), on the device; rows with top_k 0 or above QB_QCAP
+ *                        on the host from the same state (Step::sample_on_host, :1007-1032 = qb_host_sample_row).
+ *                        h_tok / h_acc host [n_out]; waits for the step.
+ * qb_model_draft_sampled Engine::draft with sampled rows (draft_chains + launch_drafts, src/cuda/qwen/mod.rs:866-918):
+ *                        qb_model_draft whose drafts are drawn on the device by qb_draft_sample under h_sampling
+ *                        [n_out][8] (Params::draft_row; temperature <= 0: the argmax row) with the draws h_u
+ *                        [n_out][k]; each draft's distribution is kept for (slot, t).
+ * qb_model_draft_q       Step::draft_q (src/cuda/core.rs:1088-1098): that distribution (ids ascending, host [QB_QCAP]
+ *                        each) and the token drawn from it. */
+int qb_model_set_outputs(qb_model* m, void* stream, int slot, const unsigned* h_words);
+int qb_model_sample(qb_model* m, void* stream, const float* h_params, int n_out, int* h_tok, int* h_acc);
+int qb_model_draft_sampled(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
+                           int n_out, int k, const float* h_sampling, const float* h_u, int* h_drafts);
+int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* n, int* h_ids, float* h_p);
 int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */

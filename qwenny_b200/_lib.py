@@ -33,10 +33,15 @@ SIGNATURES = {
     "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
     "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
     "qb_draft_pick": [P, P, P, P, I, P, P, I, I],
-    "qb_sample_rows": [P, P, P, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "qb_sample_rows": [P, P, P, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "qb_host_sample_row": [P, I, P, P, P, I, P, P, P, I, P, P],
     "qb_draft_sample": [P, P, P, I, I, P, I, I, P, P, P, P, P, P, P, P, P, P],
     "qb_model_set_mtp": [P, P],
     "qb_model_draft": [P, P, P, I, P, P, I, I, P],
+    "qb_model_set_outputs": [P, P, I, P],
+    "qb_model_sample": [P, P, P, I, P, P],
+    "qb_model_draft_sampled": [P, P, P, I, P, P, I, I, P, P, P],
+    "qb_model_draft_q": [P, P, I, I, P, P, P, P],
     "qb_embed": [P, P, P, P, P, P, I, I],
     "qb_rmsnorm": [P, P, P, P, P, F, I],
     "qb_add_rmsnorm": [P, P, P, P, I, I, P, P, F],

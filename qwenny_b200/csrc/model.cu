@@ -60,7 +60,7 @@ struct qb_model {
     int h_cur = 0;
     size_t step_ints = 0;
     int *ids, *tok_slot, *tok_pos, *seg_start, *seg_len, *seg_slot, *seg_pos0, *dtok, *dseg, *dkeys, *ptile, *out_rows,
-        *mark, *mark_at;
+        *mark, *mark_at, *row_first;
     unsigned long long* h_keys = nullptr;  // pinned
     // host-side shape of the uploaded step
     int n = 0, n_out = 0, segs = 0, ndec = 0, ntile = 0, ndseg = 0, dmax = 0, max_seg = 0, dec_max_pos = 0,
@@ -71,6 +71,13 @@ struct qb_model {
     qb_mtp mtp = {};
     __half* xin2 = nullptr;
     int *mtp_rows = nullptr, *draft_ids = nullptr, *dchain = nullptr, *h_chain = nullptr;
+    // the sampler's state (Step, src/cuda/core.rs:743-756), allocated with the first call that needs it: the slots'
+    // generated-token sets, the rows' parameters and results, the stored draft distributions
+    unsigned* outs = nullptr;
+    float *sparams = nullptr, *qp = nullptr;
+    int *sampled = nullptr, *qtok = nullptr, *qn = nullptr, *qid = nullptr;
+    float* h_sparams = nullptr;  // pinned [MAX_OUT][8]
+    int* h_sampled = nullptr;    // pinned: tokens [MAX_OUT], accepted [MAX_OUT], then the chains [slots][QB_QD]
     std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;  // the graph and its kernel count
     bool use_graphs = true, fused = true;
     // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
@@ -96,14 +103,14 @@ namespace {
 struct StepLayout {
     // offsets (ints) of the step arrays inside the single step allocation
     size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, ptile, out_rows, mark,
-        mark_at, mtp_rows, total;
+        mark_at, mtp_rows, row_first, total;
     StepLayout() {
         size_t o = 0;
         auto take = [&](size_t n) { size_t r = o; o += (n + 3) / 4 * 4; return r; };
         ids = take(MAX_TOK); tok_slot = take(MAX_TOK); tok_pos = take(MAX_TOK);
         seg_start = take(MAX_TOK); seg_len = take(MAX_TOK); seg_slot = take(MAX_TOK); seg_pos0 = take(MAX_TOK);
         dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); ptile = take(2 * MAX_TOK); out_rows = take(MAX_OUT);
-        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1); mtp_rows = take(MAX_TOK);
+        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1); mtp_rows = take(MAX_TOK); row_first = take(MAX_OUT);
         total = o;
     }
 };
@@ -345,6 +352,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     m->dseg = d + L.dseg; m->dkeys = d + L.dkeys; m->ptile = d + L.ptile; m->out_rows = d + L.out_rows; m->mark = d + L.mark;
     m->mark_at = d + L.mark_at;
     m->mtp_rows = d + L.mtp_rows;
+    m->row_first = d + L.row_first;
     *out = m;
     return QB_OK;
 }
@@ -355,6 +363,10 @@ void qb_model_destroy(qb_model* m) {
     for (auto& e : m->ev) cudaEventDestroy(e);
     if (m->side) cudaStreamDestroy(m->side);
     if (m->h_chain) cudaFreeHost(m->h_chain);
+    if (m->h_sparams) cudaFreeHost(m->h_sparams);
+    if (m->h_sampled) cudaFreeHost(m->h_sampled);
+    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp};
+    for (void* b : sb) cudaFree(b);
     void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
@@ -512,7 +524,13 @@ static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, con
         for (int t = st; t < st + len; t++) h[L.mark + nmark++] = (int)toks[t].id;
     }
     h[L.mark_at + segs] = nmark;
-    for (int i = 0; i < n_out; i++) h[L.out_rows + i] = out[i];
+    for (int i = 0; i < n_out; i++) {
+        h[L.out_rows + i] = out[i];
+        int first = 0;  // the first token of the row's segment (Step::upload, src/cuda/core.rs:893-894)
+        for (int sg = 0; sg < segs; sg++)
+            if (h[L.seg_start + sg] <= out[i]) first = h[L.seg_start + sg];
+        h[L.row_first + i] = first;
+    }
     if (rows)
         for (int i = 0; i < n; i++) h[L.mtp_rows + i] = rows[i];
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
@@ -636,6 +654,164 @@ int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out) {
     QB_CUDA(cudaMemcpyAsync(m->h_keys, m->keys, n_out * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
     QB_CUDA(cudaStreamSynchronize(st));
     for (int i = 0; i < n_out; i++) h_tokens[i] = (int)(0xffffffffu - (uint32_t)(m->h_keys[i] & 0xffffffffu));
+    return QB_OK;
+}
+
+// ---- the sampler on the step's logits (Step::sample, set_outputs, draft_sample, draft_q: src/cuda/core.rs:977-1100)
+
+static int ensure_sampler(qb_model* m) {
+    if (m->outs) return QB_OK;
+    const size_t q = (size_t)m->slots * QB_QD;
+    QB_TRY(dalloc(&m->outs, (size_t)m->slots * m->vocab_rows / 32));
+    QB_TRY(dalloc(&m->sparams, (size_t)MAX_OUT * 8));
+    QB_TRY(dalloc(&m->sampled, (size_t)2 * MAX_OUT));
+    QB_TRY(dalloc(&m->qtok, q)); QB_TRY(dalloc(&m->qn, q));
+    QB_TRY(dalloc(&m->qid, q * QB_QCAP)); QB_TRY(dalloc(&m->qp, q * QB_QCAP));
+    QB_CUDA(cudaMemset(m->qtok, 0xff, q * sizeof(int)));  // -1: no draft stored
+    QB_CUDA(cudaMallocHost((void**)&m->h_sparams, (size_t)QB_MAX_DRAFTS * MAX_OUT * 8 * sizeof(float)));
+    QB_CUDA(cudaMallocHost((void**)&m->h_sampled, (2 * MAX_OUT + q) * sizeof(int)));
+    QB_CUDA(cudaDeviceSynchronize());
+    return QB_OK;
+}
+
+// The tokens a slot's request generated so far, as a set of vocab_rows bits (the presence penalty's; host words)
+int qb_model_set_outputs(qb_model* m, void* stream, int slot, const unsigned* words) {
+    if (!m || !words || slot < 0 || slot >= m->slots) return QB_ERR_ARG;
+    QB_TRY(ensure_sampler(m));
+    const size_t w = (size_t)m->vocab_rows / 32;
+    QB_CUDA(cudaMemcpyAsync(m->outs + slot * w, words, w * sizeof(unsigned), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    QB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));  // `words` is the caller's
+    return QB_OK;
+}
+
+// Step::sample_on_host: row j of the last step on the host, from the logits and the sets on the device
+static int sample_on_host(qb_model* m, cudaStream_t st, int j, const float* row, int* tok, int* acc) {
+    StepLayout L;
+    const int* h = m->h_step;
+    const int rt = h[L.out_rows + j], first = h[L.row_first + j], slot = h[L.tok_slot + rt];
+    const size_t w = (size_t)m->vocab_rows / 32;
+    std::vector<float> logits(m->vocab_valid);
+    std::vector<unsigned> seen(w), outs(w);
+    std::vector<int> step(rt - first), qi;
+    std::vector<float> qv;
+    QB_CUDA(cudaMemcpyAsync(logits.data(), m->logits + (size_t)j * m->vocab_rows, logits.size() * sizeof(float),
+                            cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaMemcpyAsync(seen.data(), m->seen + slot * w, w * sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaMemcpyAsync(outs.data(), m->outs + slot * w, w * sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+    if (!step.empty())
+        QB_CUDA(cudaMemcpyAsync(step.data(), m->ids + first + 1, step.size() * sizeof(int), cudaMemcpyDeviceToHost, st));
+    int nq = 0;
+    if (row[6] <= -2.f && rt - first < QB_QD) {
+        const int q = slot * QB_QD + (rt - first);
+        int head[2] = {0, 0};
+        QB_CUDA(cudaMemcpyAsync(&head[0], m->qtok + q, sizeof(int), cudaMemcpyDeviceToHost, st));
+        QB_CUDA(cudaMemcpyAsync(&head[1], m->qn + q, sizeof(int), cudaMemcpyDeviceToHost, st));
+        QB_CUDA(cudaStreamSynchronize(st));
+        if (head[0] == (int)(-row[6] - 2.f) && head[1] > 0) {
+            nq = head[1];
+            qi.resize(nq); qv.resize(nq);
+            QB_CUDA(cudaMemcpyAsync(qi.data(), m->qid + (size_t)q * QB_QCAP, nq * sizeof(int), cudaMemcpyDeviceToHost, st));
+            QB_CUDA(cudaMemcpyAsync(qv.data(), m->qp + (size_t)q * QB_QCAP, nq * sizeof(float), cudaMemcpyDeviceToHost, st));
+        }
+    }
+    QB_CUDA(cudaStreamSynchronize(st));
+    return qb_host_sample_row(logits.data(), m->vocab_valid, seen.data(), outs.data(), step.data(), (int)step.size(), row,
+                              qi.data(), qv.data(), nq, tok, acc);
+}
+
+// Step::sample: the next token of each logit row of the last step under the rows' parameters (host [n_out][8], see
+// qb_sample_rows), on the device; rows with more candidates than the kernel sorts on the host, from the same state.
+// h_tok / h_acc: host [n_out]. Waits for the step.
+int qb_model_sample(qb_model* m, void* stream, const float* params, int n_out, int* h_tok, int* h_acc) {
+    if (!m || !params || !h_tok || !h_acc || n_out != m->n_out || n_out <= 0) return QB_ERR_ARG;
+    QB_TRY(ensure_sampler(m));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::memcpy(m->h_sparams, params, (size_t)n_out * 8 * sizeof(float));
+    QB_CUDA(cudaMemcpyAsync(m->sparams, m->h_sparams, (size_t)n_out * 8 * sizeof(float), cudaMemcpyHostToDevice, st));
+    QB_TRY(qb_sample_rows(m->ctx, stream, m->logits, m->vocab_valid, m->vocab_rows, m->vocab_rows, n_out, m->out_rows,
+                          m->tok_slot, m->ids, m->row_first, m->seen, m->outs, m->sparams, m->qtok, m->qn, m->qid, m->qp,
+                          m->sampled, m->sampled + MAX_OUT));
+    m->launches++;
+    QB_CUDA(cudaMemcpyAsync(m->h_sampled, m->sampled, 2 * MAX_OUT * sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    for (int j = 0; j < n_out; j++) {
+        h_tok[j] = m->h_sampled[j];
+        h_acc[j] = m->h_sampled[MAX_OUT + j];
+        if (h_acc[j] < 0) QB_TRY(sample_on_host(m, st, j, params + 8 * j, &h_tok[j], &h_acc[j]));
+    }
+    return QB_OK;
+}
+
+// Engine::draft with sampled rows (draft_chains + launch_drafts, src/cuda/qwen/mod.rs:866-918): as qb_model_draft,
+// but every step's drafts are drawn on the device by qb_draft_sample under the rows' draft parameters (`sampling`:
+// host [n_out][8] as Params::draft_row gives them; a row with temperature <= 0 takes the argmax, argmax_draft_row)
+// with the draws u (host [n_out][k]); the distribution of each draft is kept for (slot, t) for the target's
+// qb_model_sample rows that mark it sampled. h_drafts: host [n_out][k].
+int qb_model_draft_sampled(qb_model* m, void* stream, const qb_tok* toks, int n, const int* rows, const int* out,
+                           int n_out, int k, const float* sampling, const float* u, int* h_drafts) {
+    if (!m || !m->has_mtp || !toks || !rows || !sampling || !u || n < 1 || n > MAX_TOK || n_out < 1 || n_out > MAX_OUT ||
+        k < 1 || k > QB_MAX_DRAFTS || !out || !h_drafts)
+        return QB_ERR_ARG;
+    QB_TRY(ensure_sampler(m));
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool head = m->mtp.head_w != nullptr;
+    const int width = head ? m->mtp.head_valid : m->vocab_valid, ld = head ? m->mtp.head_rows : m->vocab_rows;
+    auto draw = [&](int t) -> int {
+        float* hp = m->h_sparams + (size_t)t * MAX_OUT * 8;  // a region per step: the copies run later
+        for (int i = 0; i < n_out; i++) {
+            float* r = hp + 8 * i;
+            if (sampling[8 * i] > 0.f) {
+                std::memcpy(r, sampling + 8 * i, 8 * sizeof(float));
+                r[4] = u[i * k + t];
+            } else {
+                const float g[8] = {1.f, 1.f, 1.f, 1.f, 0.5f, 0.f, -1.f, 0.f};
+                std::memcpy(r, g, sizeof g);
+            }
+            r[5] = (float)t;
+        }
+        QB_CUDA(cudaMemcpyAsync(m->sparams, hp, (size_t)n_out * 8 * sizeof(float), cudaMemcpyHostToDevice, st));
+        QB_TRY(qb_draft_sample(m->ctx, stream, m->logits, width, ld, head ? m->mtp.head_ids : nullptr, m->vocab_rows, n_out,
+                               m->out_rows, m->tok_slot, m->seen, m->outs, m->sparams, m->draft_ids, m->qtok, m->qn, m->qid,
+                               m->qp));
+        m->launches++;
+        return QB_OK;
+    };
+    QB_TRY(upload_step(m, stream, toks, n, out, n_out, rows));
+    QB_TRY(run_kind(m, stream, 1));
+    QB_TRY(draw(0));
+    std::vector<qb_tok> cur(n_out);
+    std::vector<int> at(out, out + n_out), all(n_out);
+    for (int i = 0; i < n_out; i++) { cur[i] = toks[out[i]]; all[i] = i; }
+    for (int t = 1; t < k; t++) {
+        for (auto& c : cur) { c.id = 0; c.pos += 1; }
+        QB_TRY(upload_step(m, stream, cur.data(), n_out, all.data(), n_out, at.data()));
+        QB_CUDA(cudaMemcpyAsync(m->ids, m->draft_ids, n_out * sizeof(int), cudaMemcpyDeviceToDevice, st));
+        QB_TRY(run_kind(m, stream, 2));
+        QB_TRY(draw(t));
+        at = all;
+    }
+    int* chains = m->h_sampled + 2 * MAX_OUT;
+    QB_CUDA(cudaMemcpyAsync(chains, m->qtok, (size_t)m->slots * QB_QD * sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    for (int i = 0; i < n_out; i++)
+        for (int t = 0; t < k; t++) h_drafts[i * k + t] = chains[(int)toks[out[i]].slot * QB_QD + t];
+    return QB_OK;
+}
+
+// Step::draft_q: the distribution kept for slot `slot`'s draft at index t and the token drawn from it; ids / p: host
+// [QB_QCAP]. Waits for the stream.
+int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* n, int* ids, float* p) {
+    if (!m || slot < 0 || slot >= m->slots || t < 0 || t >= QB_QD || !tok || !n || !ids || !p) return QB_ERR_ARG;
+    QB_TRY(ensure_sampler(m));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int q = slot * QB_QD + t;
+    QB_CUDA(cudaMemcpyAsync(tok, m->qtok + q, sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaMemcpyAsync(n, m->qn + q, sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    if (*n < 0 || *n > QB_QCAP) return QB_ERR_DEVICE;
+    QB_CUDA(cudaMemcpyAsync(ids, m->qid + (size_t)q * QB_QCAP, *n * sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaMemcpyAsync(p, m->qp + (size_t)q * QB_QCAP, *n * sizeof(float), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
     return QB_OK;
 }
 

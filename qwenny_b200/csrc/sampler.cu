@@ -499,13 +499,14 @@ int launch_sampler(qb_ctx* ctx, void* stream, SamplerArgs a, int n_out) {
 }  // namespace
 }  // namespace qb
 
-extern "C" int qb_sample_rows(qb_ctx* ctx, void* stream, const float* logits, int vocab, int n_out, const int* out_rows,
-                              const int* tok_slot, const int* ids, const int* row_first, const unsigned* seen,
-                              const unsigned* outs, const float* params, const int* qtok, const int* qn, const int* qid,
-                              const float* qp, int* out_tok, int* out_acc) {
-    if (!ids || !row_first || !qtok || !qn || !qid || !qp || !out_acc || vocab % 32) return QB_ERR_ARG;
+extern "C" int qb_sample_rows(qb_ctx* ctx, void* stream, const float* logits, int width, int ld, int vocab, int n_out,
+                              const int* out_rows, const int* tok_slot, const int* ids, const int* row_first,
+                              const unsigned* seen, const unsigned* outs, const float* params, const int* qtok,
+                              const int* qn, const int* qid, const float* qp, int* out_tok, int* out_acc) {
+    if (!ids || !row_first || !qtok || !qn || !qid || !qp || !out_acc || vocab % 32 || width > vocab || ld < width)
+        return QB_ERR_ARG;
     qb::SamplerArgs a = {};
-    a.logits = logits; a.W = vocab; a.ld = vocab; a.head_ids = nullptr;
+    a.logits = logits; a.W = width; a.ld = ld; a.head_ids = nullptr;
     a.out_rows = out_rows; a.tok_slot = tok_slot; a.ids = ids; a.row_first = row_first;
     a.seen = seen; a.outs = outs; a.set_words = vocab / 32; a.params = params;
     a.qtok = const_cast<int*>(qtok); a.qn = const_cast<int*>(qn); a.qid = const_cast<int*>(qid);

@@ -69,3 +69,23 @@ def pack_f16(w: np.ndarray, order: np.ndarray | None = None) -> np.ndarray:
 
 def split_for(tiles: int, cols: int, bits: int, kd: int) -> int:
     return lib().qb_split_for(tiles, cols, bits, kd)
+
+
+def sample_row(logits: np.ndarray, seen_words, outs_words, step, row, q=None) -> tuple[int, bool]:
+    """sample::sample_row / sample_row_q (src/sample.rs:141-200) as Step::sample_on_host calls them: the sampler rows
+    the GPU kernel leaves to the host. seen_words / outs_words: the slot's bitsets (uint32 words) or None; step: the
+    step's tokens of the row's sequence after its first; q: (ids ascending, probabilities) of a sampled draft."""
+    lg = np.ascontiguousarray(logits, dtype=np.float32)
+    sw = None if seen_words is None else np.ascontiguousarray(seen_words, dtype=np.uint32)
+    ow = None if outs_words is None else np.ascontiguousarray(outs_words, dtype=np.uint32)
+    st = np.ascontiguousarray(step if step is not None else [], dtype=np.int32)
+    r = np.ascontiguousarray(row, dtype=np.float32)
+    qi = qp = None
+    if q is not None:
+        qi, qp = np.ascontiguousarray(q[0], dtype=np.int32), np.ascontiguousarray(q[1], dtype=np.float32)
+    tok, acc = C.c_int(0), C.c_int(0)
+    check(lib().qb_host_sample_row(_np(lg), len(lg), _np(sw) if sw is not None else None,
+                                   _np(ow) if ow is not None else None, _np(st) if len(st) else None, len(st), _np(r),
+                                   _np(qi) if qi is not None else None, _np(qp) if qp is not None else None,
+                                   0 if qi is None else len(qi), C.byref(tok), C.byref(acc)), "qb_host_sample_row")
+    return tok.value, bool(acc.value)

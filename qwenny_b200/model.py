@@ -125,6 +125,48 @@ class Model:
         self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
         return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
 
+    def set_outputs(self, slot, words):
+        """Step::set_outputs: the set of tokens the slot's request generated (uint32 words over the padded vocabulary)."""
+        w = np.ascontiguousarray(words, dtype=np.uint32)
+        check(lib().qb_model_set_outputs(self.h, C.c_void_p(self.stream.cuda_stream), slot,
+                                         w.ctypes.data_as(C.c_void_p)), "qb_model_set_outputs")
+
+    def sample(self, params):
+        """Step::sample: [(token, draft accepted)] per logit row of the last step; params [n_out][8]."""
+        p = np.ascontiguousarray(params, dtype=np.float32)
+        n = len(p)
+        tok, acc = (C.c_int * n)(), (C.c_int * n)()
+        check(lib().qb_model_sample(self.h, C.c_void_p(self.stream.cuda_stream), p.ctypes.data_as(C.c_void_p), n, tok,
+                                    acc), "qb_model_sample")
+        return [(tok[i], bool(acc[i])) for i in range(n)]
+
+    def draft_sampled(self, toks, rows, out, k, sampling, u):
+        """Engine::draft with sampled rows: sampling [len(out)][8] (Params::draft_row; temperature <= 0: the argmax),
+        u [len(out)][k] draws; returns [len(out)][k] drafts (waits)."""
+        arr = self._toks(toks)
+        r = (C.c_int * len(rows))(*rows)
+        o = (C.c_int * len(out))(*out)
+        res = (C.c_int * (len(out) * k))()
+        sp = np.ascontiguousarray(sampling, dtype=np.float32)
+        uu = np.ascontiguousarray(u, dtype=np.float32)
+        assert sp.shape == (len(out), 8) and uu.shape == (len(out), k)
+        check(lib().qb_model_draft_sampled(self.h, C.c_void_p(self.stream.cuda_stream), arr, len(toks), r, o, len(out),
+                                           k, sp.ctypes.data_as(C.c_void_p), uu.ctypes.data_as(C.c_void_p), res),
+              "qb_model_draft_sampled")
+        self._n, self._n_out = (len(out) if k > 1 else len(toks)), len(out)
+        self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
+        return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
+
+    def draft_q(self, slot, t):
+        """Step::draft_q: (ids ascending, probabilities, token drawn) kept for the slot's draft at index t."""
+        tok, n = C.c_int(0), C.c_int(0)
+        ids = np.zeros(1024, dtype=np.int32)
+        p = np.zeros(1024, dtype=np.float32)
+        check(lib().qb_model_draft_q(self.h, C.c_void_p(self.stream.cuda_stream), slot, t, C.byref(tok), C.byref(n),
+                                     ids.ctypes.data_as(C.c_void_p), p.ctypes.data_as(C.c_void_p)),
+              "qb_model_draft_q")
+        return ids[:n.value].copy(), p[:n.value].copy(), tok.value
+
     def close(self):
         if getattr(self, "h", None):
             lib().qb_model_destroy(self.h)

@@ -106,9 +106,10 @@ class Context:
               "qb_draft_pick")
 
     def sample_rows(self, logits, vocab, n_out, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn, qid,
-                    qp, out_tok, out_acc):
+                    qp, out_tok, out_acc, width=None, ld=None):
         """Step::sample (src/cuda/core.rs:977-1005) without the host rows: out_acc -1 marks those."""
-        check(lib().qb_sample_rows(self.h, _stream(), _p(logits), vocab, n_out, _p(out_rows), _p(tok_slot), _p(ids),
+        check(lib().qb_sample_rows(self.h, _stream(), _p(logits), width or vocab, ld or vocab, vocab, n_out,
+                                   _p(out_rows), _p(tok_slot), _p(ids),
                                    _p(row_first), _p(seen), _p(outs), _p(params), _p(qtok), _p(qn), _p(qid), _p(qp),
                                    _p(out_tok), _p(out_acc)), "qb_sample_rows")
 

@@ -111,3 +111,54 @@ def test_draft_draw_matches_kept_dist():
     # the same distribution from kept_dist over the columns
     p, idx = S.kept_dist(logits, seen[head_ids], None, r)
     assert sorted(head_ids[idx].tolist()) == qi.tolist()
+
+
+def _words(tokens, vocab):
+    w = np.zeros((vocab + 31) // 32, dtype=np.uint32)
+    for t in tokens:
+        w[t >> 5] |= np.uint32(1 << (t & 31))
+    return w
+
+
+def test_host_rows_of_the_library_match_the_oracle():
+    """qb_host_sample_row (the rows the GPU kernel leaves to the host: top_k 0 or above 1024) against the oracle, token
+    for token: both are float32 in the host definition's order, so no boundary allowance."""
+    from qwenny_b200 import host
+    g = np.random.default_rng(17)
+    rng = S.Rng(3)
+    vocab = 6000
+    for trial in range(40):
+        logits = (g.standard_normal(vocab) * 2.5).astype(F)
+        logits[g.integers(0, vocab, 8)] += g.uniform(3, 8, 8).astype(F)
+        seen_t, outs_t = g.integers(0, vocab, 80), g.integers(0, vocab, 30)
+        step = list(g.integers(0, vocab, trial % 4))
+        temp, k, p, rep, pres = [(1.0, 0, 0.95, 1.1, 0.0), (1.5, 0, 1.0, 1.0, 0.0), (0.7, 2000, 0.8, 1.2, 1.5),
+                                 (0.9, 5, 0.5, 1.3, 0.0), (0.0, 0, 1.0, 1.3, 2.0)][trial % 5]
+        top = int(np.argsort(-logits)[trial % 3])
+        draft = None if trial % 3 == 0 else top
+        r = S.params_row(temp, k, p, rep, pres, rng, draft=draft)
+        seen = np.zeros(vocab, dtype=bool)
+        gen = np.zeros(vocab, dtype=bool)
+        seen[seen_t] = True
+        gen[outs_t] = True
+        seen[step] = True
+        gen[step] = True
+        want = S.sample_row(logits, seen, gen, r)
+        got = host.sample_row(logits, _words(seen_t, vocab), _words(outs_t, vocab), step, r)
+        assert got == want, (trial, got, want)
+        if draft is not None and temp > 0:
+            # the same row with its draft marked sampled from a stored q
+            qp, qidx = S.kept_dist(np.roll(logits, 1), None, None, np.array([1.1, 40, 1, 1, 0, 0, -1, 0], dtype=F))
+            qidx = np.concatenate([qidx, [draft]]) if draft not in qidx else qidx
+            qp = np.concatenate([qp, [F(0.05)]]) if len(qp) < len(qidx) else qp
+            o = np.argsort(qidx)
+            r2 = r.copy()
+            S.mark_sampled(r2)
+            r3 = r.copy()
+            want = S.sample_row_q(logits, seen, gen, r3, qidx[o], qp[o])
+            got = host.sample_row(logits, _words(seen_t, vocab), _words(outs_t, vocab), step, r2, (qidx[o], qp[o]))
+            assert got == want, (trial, got, want)
+    # the reference's flat row (src/sample.rs:217-229)
+    flat = np.zeros(5000, dtype=F)
+    assert host.sample_row(flat, None, None, None, [1, 0, 1, 1, 0.9999, 0, -1, 0])[0] == 4999
+    assert host.sample_row(flat, None, None, None, [1, 1024, 1, 1, 0.9999, 0, -1, 0])[0] == 1023

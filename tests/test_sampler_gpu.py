@@ -341,3 +341,95 @@ def test_speed_against_the_reference_kernel(ctx, ref, capsys):
     with capsys.disabled():
         print(f"\nsample_rows, 2 rows x {V}: {us[0]:.1f} us here, {us[1]:.1f} us the reference kernel")
     assert us[0] < us[1]
+
+
+@pytest.mark.parametrize("draft_rows", [0, 1000])
+def test_model_sampling_and_sampled_draft_chain(ctx, draft_rows):
+    """Through the host API, the design of the reference's samplecheck (src/checks.rs:685-818): a sequence's history
+    in one step, its last row sampled under several parameter sets (device rows and host rows); then drafts drawn on
+    the device from the MTP layer's distribution, fed to the target, and accepted or resampled against the stored q:
+    every token is the host definition's for the logits the model produced."""
+    from qwenny_b200 import model as M
+    vocab = 2000
+    m = M.synthetic(ctx, nlayers=2, slots=2, max_ctx=256, vocab=vocab, seed=77, pattern=("delta", "attn"), mtp=True,
+                    draft_rows=draft_rows)
+    vr = m.lm_head.n  # padded rows
+    hist = [100 + (i * 7) % 23 for i in range(40)]
+    n = len(hist)
+    gen = set(hist[-12:])
+    m.set_outputs(0, bitset(gen, vr))
+    rng = S.Rng(13)
+    m.step([(t, 0, i) for i, t in enumerate(hist)], [n - 1])
+    lg = m.logits().cpu().numpy()[0, :vocab]
+    seen = np.zeros(vocab, dtype=bool)
+    seen[hist] = True
+    genb = np.zeros(vocab, dtype=bool)
+    genb[list(gen)] = True
+    genb[hist[1:]] = True  # the step's tokens after its first count as drafts fed so far
+    near = 0
+    for (temp, k, p, rep, pres) in SETS + [(1.0, 0, 0.95, 1.1, 0.0), (1.5, 0, 1.0, 1.0, 0.7), (0.8, 1500, 0.9, 1.2, 0.0)]:
+        for it in range(3):
+            r = S.params_row(temp, k, p, rep, pres, rng)
+            got = m.sample([r])[0]
+            t, a, margin = S.sample_row(lg, seen, genb, r, want_margin=True)
+            if k == 0 or k > QCAP:
+                assert got == (t, a)  # a host row: the host definition's arithmetic, no allowance
+            else:
+                near += check_host(got[0], got[1], (t, a), margin, f"{(temp, k, p, rep, pres)}")
+    assert near <= 1
+    # sampled drafts
+    head_ids = m.mtp["head_ids"].cpu().numpy()[:draft_rows] if draft_rows else None
+    for (temp, k, p, rep, pres) in [(1.0, 20, 0.95, 1.0, 1.5), (0.7, 0, 0.8, 1.1, 0.0), (1.3, 50, 1.0, 1.0, 0.0)]:
+        for it in range(3):
+            nxt = 300 + it
+            m.step([(t, 0, i) for i, t in enumerate(hist)], [n - 1])
+            ds = S.draft_row(temp, k, p, rep, pres)
+            u = np.array([[rng.next_f32() for _ in range(3)]], dtype=F)
+            d = m.draft_sampled([(nxt, 0, n - 1)], [n - 1], [0], 3, [ds], u)[0]
+            assert len(d) == 3
+            # the last draft step's logits: the host's statement of its draw
+            dl = m.logits().cpu().numpy()[0]
+            width = draft_rows or vocab
+            seen_d, gen_d = seen.copy(), np.zeros(vocab, dtype=bool)
+            gen_d[list(gen)] = True
+            seen_d[d[:2]] = True
+            gen_d[d[:2]] = True
+            r = ds.copy()
+            r[4], r[5] = u[0, 2], 2
+            tok, qi, qv, margin = S.draft_draw(dl[:width], seen_d, gen_d, r, head_ids, want_margin=True)
+            ids2, p2, t2 = m.draft_q(0, 2)
+            assert t2 == d[2] and np.array_equal(ids2, qi)
+            np.testing.assert_allclose(p2, qv, rtol=2e-5, atol=1e-9)
+            assert tok == d[2] or margin < 1e-5
+            for t in range(3):
+                ids_t, p_t, tok_t = m.draft_q(0, t)
+                assert tok_t == d[t] and tok_t in ids_t and abs(p_t.sum() - 1) < 1e-4 and np.all(np.diff(ids_t) > 0)
+            # the target's step over the next token and the drafts; rows 0..2 carry a sampled draft
+            step = [(nxt, 0, n)] + [(d[j], 0, n + 1 + j) for j in range(3)]
+            m.step(step, [0, 1, 2, 3])
+            lgs = m.logits().cpu().numpy()[:, :vocab]
+            rows = []
+            for j in range(4):
+                r = S.params_row(temp, k if k else 40, p, rep, pres, rng, draft=d[j] if j < 3 else None)
+                if j < 3:
+                    S.mark_sampled(r)
+                rows.append(r)
+            got = m.sample(rows)
+            seen_t = seen.copy()
+            seen_t[[nxt] + d] = True  # the steps mark all their tokens, the drafts included
+            for j in range(4):
+                g2 = np.zeros(vocab, dtype=bool)
+                g2[list(gen)] = True
+                g2[d[:j]] = True
+                if j < 3:
+                    ids_j, p_j, _ = m.draft_q(0, j)
+                    r = rows[j].copy()
+                    r[6] = d[j]
+                    t, a, margin = S.sample_row_q(lgs[j], seen_t, g2, r, ids_j, p_j, want_margin=True)
+                else:
+                    t, a, margin = S.sample_row(lgs[j], seen_t, g2, rows[j], want_margin=True)
+                near += check_host(got[j][0], got[j][1], (t, a), margin, f"sampled draft row {j}")
+                if not got[j][1]:
+                    break
+    assert near <= 1
+    m.close()
