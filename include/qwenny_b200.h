@@ -14,6 +14,7 @@
  */
 #ifndef QWENNY_B200_H
 #define QWENNY_B200_H
+#include <stddef.h>
 #include <stdint.h>
 #ifdef __cplusplus
 extern "C" {
@@ -335,6 +336,20 @@ int qb_model_sample(qb_model* m, void* stream, const float* h_params, int n_out,
 int qb_model_draft_sampled(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
                            int n_out, int k, const float* h_sampling, const float* h_u, int* h_drafts);
 int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* n, int* h_ids, float* h_p);
+/* A slot's saved images (f-row 3 of the scope), byte for byte the reference's:
+ * qb_model_kv_bytes / save_kv / load_kv      Model::save_kv / load_kv (src/cuda/qwen/mod.rs:1031-1061): per attention
+ *     layer (the MTP's last) and kv head the keys of positions [from, to), the values in blocks of 16 positions, the
+ *     two scale rows (Attn::layout, src/cuda/qwen/attn.rs:182-196); from a multiple of 16.
+ * qb_model_state_bytes / save_state / load_state  Model::save_state / load_state (:993-1029): per DeltaNet layer the end
+ *     state and the conv ring's last three positions (DeltaNet::save / load, src/cuda/qwen/deltanet.rs:181-226), then
+ *     the slot's seen set; *pos = the position the state is at; a loaded slot continues at `pos`.
+ * One gather (scatter) kernel over all layers and one copy per call; h_* are host buffers; the calls wait. */
+size_t qb_model_kv_bytes(const qb_model* m, int from, int to);
+int qb_model_save_kv(qb_model* m, void* stream, int slot, int from, int to, void* h_out, size_t bytes);
+int qb_model_load_kv(qb_model* m, void* stream, int slot, int from, int to, const void* h_data, size_t bytes);
+size_t qb_model_state_bytes(const qb_model* m);
+int qb_model_save_state(qb_model* m, void* stream, int slot, void* h_out, size_t bytes, int* pos);
+int qb_model_load_state(qb_model* m, void* stream, int slot, const void* h_data, size_t bytes, int pos);
 int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
@@ -352,6 +367,7 @@ int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);
 float* qb_model_logits(qb_model* m);   /* device f32 [n_out][vocab_rows] */
 float* qb_model_hidden(qb_model* m);   /* device f32 [n][5120], the residual stream after the last layer */
 void* qb_model_xn(qb_model* m);        /* device f16 [n][5120], the final norm's output */
+unsigned* qb_model_seen(qb_model* m);  /* device [slots][vocab_rows / 32]: the slots' seen sets (Step::seen) */
 long long qb_model_launches(const qb_model* m);  /* kernels launched or replayed so far */
 int qb_model_step_kernels(const qb_model* m);    /* kernels of one step of the last shape */
 

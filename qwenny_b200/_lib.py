@@ -38,6 +38,12 @@ SIGNATURES = {
     "qb_draft_sample": [P, P, P, I, I, P, I, I, P, P, P, P, P, P, P, P, P, P],
     "qb_model_set_mtp": [P, P],
     "qb_model_draft": [P, P, P, I, P, P, I, I, P],
+    "qb_model_kv_bytes": [P, I, I],
+    "qb_model_save_kv": [P, P, I, I, I, P, C.c_size_t],
+    "qb_model_load_kv": [P, P, I, I, I, P, C.c_size_t],
+    "qb_model_state_bytes": [P],
+    "qb_model_save_state": [P, P, I, P, C.c_size_t, P],
+    "qb_model_load_state": [P, P, I, P, C.c_size_t, I],
     "qb_model_set_outputs": [P, P, I, P],
     "qb_model_sample": [P, P, P, I, P, P],
     "qb_model_draft_sampled": [P, P, P, I, P, P, I, I, P, P, P],
@@ -71,6 +77,7 @@ SIGNATURES = {
     "qb_model_logits": [P],
     "qb_model_hidden": [P],
     "qb_model_xn": [P],
+    "qb_model_seen": [P],
     "qb_layer_chain": [P, P, P],
     "qb_layer_chain_max_rows": [],
     "qb_model_use_chain": [P, I],
@@ -85,7 +92,8 @@ SIGNATURES = {
     "qb_split_for": [I, I, I, I],
 }
 _RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
-            "qb_model_hidden": P, "qb_model_xn": P, "qb_model_launches": LL}
+            "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,
+            "qb_model_state_bytes": C.c_size_t}
 
 
 class QbLayer(C.Structure):

@@ -14,6 +14,7 @@
 #include <vector>
 #include "common.cuh"
 #include "ctx.h"
+#include "session.h"
 
 using namespace qb;
 
@@ -78,6 +79,11 @@ struct qb_model {
     int *sampled = nullptr, *qtok = nullptr, *qn = nullptr, *qid = nullptr;
     float* h_sparams = nullptr;  // pinned [MAX_OUT][8]
     int* h_sampled = nullptr;    // pinned: tokens [MAX_OUT], accepted [MAX_OUT], then the chains [slots][QB_QD]
+    // saved images (session.cu): the span table (pinned + device), the staging buffer (grows on demand)
+    qb::Span *h_spans = nullptr, *d_spans = nullptr;
+    unsigned char* staging = nullptr;
+    size_t staging_bytes = 0;
+    int *d_positions = nullptr, *h_positions = nullptr;
     std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;  // the graph and its kernel count
     bool use_graphs = true, fused = true;
     // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
@@ -365,7 +371,9 @@ void qb_model_destroy(qb_model* m) {
     if (m->h_chain) cudaFreeHost(m->h_chain);
     if (m->h_sparams) cudaFreeHost(m->h_sparams);
     if (m->h_sampled) cudaFreeHost(m->h_sampled);
-    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp};
+    if (m->h_spans) cudaFreeHost(m->h_spans);
+    if (m->h_positions) cudaFreeHost(m->h_positions);
+    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions};
     for (void* b : sb) cudaFree(b);
     void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
@@ -815,11 +823,194 @@ int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* 
     return QB_OK;
 }
 
+// ---- a slot's saved images (Model::save_kv / load_kv / save_state / load_state, src/cuda/qwen/mod.rs:993-1061)
+
+static int all_layers(const qb_model* m) { return m->nlayers + (m->has_mtp ? 1 : 0); }
+static size_t kv_layer_bytes(int from, int to) {  // Attn::saved_bytes, src/cuda/qwen/attn.rs:198-200
+    const size_t n = to - from, vl = (size_t)(to + 15) / 16 * 16 - from;
+    return NKV * (n * HD + vl * HD + n * 4 + n * 4);
+}
+static constexpr size_t DELTA_BYTES = ((size_t)SLOT_STATE + (CONV_K - 1) * LQKV) * 4;  // DeltaNet::saved_bytes
+
+static int ensure_session(qb_model* m, size_t image) {
+    const size_t cap = (size_t)(m->nlayers + 1) * 16 + 2;
+    if (!m->h_spans) {
+        QB_CUDA(cudaMallocHost((void**)&m->h_spans, cap * sizeof(qb::Span)));
+        QB_CUDA(cudaMalloc((void**)&m->d_spans, cap * sizeof(qb::Span)));
+        QB_CUDA(cudaMalloc((void**)&m->d_positions, (m->nlayers + 1) * sizeof(int)));
+        QB_CUDA(cudaMallocHost((void**)&m->h_positions, (m->nlayers + 1) * sizeof(int)));
+    }
+    if (image > m->staging_bytes) {
+        if (m->staging) QB_CUDA(cudaFree(m->staging));
+        m->staging = nullptr; m->staging_bytes = 0;
+        QB_CUDA(cudaMalloc((void**)&m->staging, image));
+        m->staging_bytes = image;
+    }
+    return QB_OK;
+}
+
+static int run_spans(qb_model* m, cudaStream_t st, bool save, std::vector<qb::Span>& spans) {
+    const unsigned chunks = qb::assign_chunks(spans);
+    std::memcpy(m->h_spans, spans.data(), spans.size() * sizeof(qb::Span));
+    QB_CUDA(cudaMemcpyAsync(m->d_spans, m->h_spans, spans.size() * sizeof(qb::Span), cudaMemcpyHostToDevice, st));
+    QB_TRY(qb::launch_session_copy(m->ctx, st, save, m->d_spans, (int)spans.size(), chunks, m->staging, m->d_positions));
+    m->launches++;
+    return QB_OK;
+}
+
+// the attention layers' regions of positions [from, to) of a slot, in wire order (Attn::layout)
+static void kv_spans(const qb_model* m, int slot, int from, int to, std::vector<qb::Span>& spans) {
+    const size_t n = to - from, vl = (size_t)(to + 15) / 16 * 16 - from;
+    unsigned long long off = 0;
+    auto put = [&](void* base, size_t at, size_t bytes) {
+        qb::Span s = {};
+        s.dev = (unsigned char*)base + at; s.off = off; s.bytes = bytes; s.kind = qb::SPAN_PLAIN;
+        spans.push_back(s);
+        off += bytes;
+    };
+    for (int i = 0; i < all_layers(m); i++) {
+        const qb_layer& L = m->layers[i].w;
+        if (L.kind != QB_LAYER_ATTN) continue;
+        for (int g = 0; g < NKV; g++) {
+            const size_t p = ((size_t)slot * NKV + g) * L.cap + from;
+            put(L.kc, p * HD, n * HD); put(L.vc, p * HD, vl * HD); put(L.ks, p * 4, n * 4); put(L.vs, p * 4, n * 4);
+        }
+    }
+}
+
+static int kv_check(const qb_model* m, int slot, int from, int to, size_t bytes, size_t* image) {
+    if (!m || slot < 0 || slot >= m->slots || from < 0 || from % 16 || from > to) return QB_ERR_ARG;
+    size_t total = 0;
+    for (int i = 0; i < all_layers(m); i++) {
+        const qb_layer& L = m->layers[i].w;
+        if (L.kind != QB_LAYER_ATTN) continue;
+        if (to > L.cap) return QB_ERR_ARG;
+        total += kv_layer_bytes(from, to);
+    }
+    *image = total;
+    return bytes == total ? QB_OK : QB_ERR_ARG;
+}
+
+size_t qb_model_kv_bytes(const qb_model* m, int from, int to) {
+    if (!m || from < 0 || from > to) return 0;
+    size_t total = 0;
+    for (int i = 0; i < all_layers(m); i++)
+        if (m->layers[i].w.kind == QB_LAYER_ATTN) total += kv_layer_bytes(from, to);
+    return total;
+}
+
+size_t qb_model_state_bytes(const qb_model* m) {
+    if (!m) return 0;
+    size_t total = (size_t)m->vocab_rows / 8;  // the seen set
+    for (int i = 0; i < all_layers(m); i++)
+        if (m->layers[i].w.kind == QB_LAYER_DELTA) total += DELTA_BYTES;
+    return total;
+}
+
+// Model::save_kv: every attention layer's cache of slot `slot` for positions [from, to) (from a multiple of 16) into
+// h_out (qb_model_kv_bytes(from, to) bytes). Waits for the stream.
+int qb_model_save_kv(qb_model* m, void* stream, int slot, int from, int to, void* h_out, size_t bytes) {
+    size_t image = 0;
+    QB_TRY(kv_check(m, slot, from, to, bytes, &image));
+    if (!h_out && image) return QB_ERR_ARG;
+    if (!image) return QB_OK;
+    QB_TRY(ensure_session(m, image));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<qb::Span> spans;
+    kv_spans(m, slot, from, to, spans);
+    QB_TRY(run_spans(m, st, true, spans));
+    QB_CUDA(cudaMemcpyAsync(h_out, m->staging, image, cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    return QB_OK;
+}
+
+// Model::load_kv: an image from qb_model_save_kv for positions [from, to) into slot `slot`
+int qb_model_load_kv(qb_model* m, void* stream, int slot, int from, int to, const void* h_data, size_t bytes) {
+    size_t image = 0;
+    QB_TRY(kv_check(m, slot, from, to, bytes, &image));
+    if (!h_data && image) return QB_ERR_ARG;
+    if (!image) return QB_OK;
+    QB_TRY(ensure_session(m, image));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<qb::Span> spans;
+    kv_spans(m, slot, from, to, spans);
+    QB_CUDA(cudaMemcpyAsync(m->staging, h_data, image, cudaMemcpyHostToDevice, st));
+    QB_TRY(run_spans(m, st, false, spans));
+    QB_CUDA(cudaStreamSynchronize(st));  // h_data is the caller's
+    return QB_OK;
+}
+
+static void state_spans(const qb_model* m, int slot, bool save, int pos, std::vector<qb::Span>& spans, int* ndelta) {
+    unsigned long long off = 0;
+    int nd = 0;
+    for (int i = 0; i < all_layers(m); i++) {
+        const qb_layer& L = m->layers[i].w;
+        if (L.kind != QB_LAYER_DELTA) continue;
+        qb::Span s = {};
+        s.dev = (unsigned char*)(L.mem + (size_t)slot * L.sst);
+        s.meta = L.meta + slot * META;
+        s.pos = pos;
+        s.kind = qb::SPAN_STATE; s.off = off; s.bytes = (size_t)SLOT_STATE * 4;
+        spans.push_back(s);
+        off += s.bytes;
+        for (int j = 0; j < CONV_K - 1; j++) {
+            s.kind = qb::SPAN_RING; s.j = j; s.off = off; s.bytes = (size_t)LQKV * 4;
+            spans.push_back(s);
+            off += s.bytes;
+        }
+        s.kind = qb::SPAN_META; s.j = nd; s.off = off; s.bytes = 0;
+        if (!save) s.dev = (unsigned char*)(L.meta + slot * META);
+        spans.push_back(s);
+        nd++;
+    }
+    qb::Span s = {};
+    s.dev = (unsigned char*)(m->seen + (size_t)slot * (m->vocab_rows / 32));
+    s.kind = qb::SPAN_PLAIN; s.off = off; s.bytes = (size_t)m->vocab_rows / 8;
+    spans.push_back(s);
+    *ndelta = nd;
+}
+
+// Model::save_state: every DeltaNet layer's end state and the conv ring's last three positions, then the slot's seen
+// set, into h_out (qb_model_state_bytes bytes); *pos = the position the state is at (every layer's must agree: else
+// QB_ERR_DEVICE). Waits for the stream.
+int qb_model_save_state(qb_model* m, void* stream, int slot, void* h_out, size_t bytes, int* pos) {
+    if (!m || slot < 0 || slot >= m->slots || !h_out || !pos || bytes != qb_model_state_bytes(m)) return QB_ERR_ARG;
+    QB_TRY(ensure_session(m, bytes));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<qb::Span> spans;
+    int nd = 0;
+    state_spans(m, slot, true, 0, spans, &nd);
+    QB_TRY(run_spans(m, st, true, spans));
+    QB_CUDA(cudaMemcpyAsync(h_out, m->staging, bytes, cudaMemcpyDeviceToHost, st));
+    if (nd) QB_CUDA(cudaMemcpyAsync(m->h_positions, m->d_positions, nd * sizeof(int), cudaMemcpyDeviceToHost, st));
+    QB_CUDA(cudaStreamSynchronize(st));
+    *pos = nd ? m->h_positions[0] : 0;
+    for (int i = 1; i < nd; i++)
+        if (m->h_positions[i] != *pos) return QB_ERR_DEVICE;
+    return QB_OK;
+}
+
+// Model::load_state: an image from qb_model_save_state taken at position `pos` into slot `slot`: the next step of the
+// slot continues there (state in buffer 0, metadata {pos, pos, 0, 0})
+int qb_model_load_state(qb_model* m, void* stream, int slot, const void* h_data, size_t bytes, int pos) {
+    if (!m || slot < 0 || slot >= m->slots || !h_data || pos < 0 || bytes != qb_model_state_bytes(m)) return QB_ERR_ARG;
+    QB_TRY(ensure_session(m, bytes));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<qb::Span> spans;
+    int nd = 0;
+    state_spans(m, slot, false, pos, spans, &nd);
+    QB_CUDA(cudaMemcpyAsync(m->staging, h_data, bytes, cudaMemcpyHostToDevice, st));
+    QB_TRY(run_spans(m, st, false, spans));
+    QB_CUDA(cudaStreamSynchronize(st));
+    return QB_OK;
+}
+
 // Device pointers of the step's results and activations (tests, samplers): logits f32 [n_out][vocab_rows], the
 // residual stream h f32 [n][5120], the last matrix-product input xn f16 [n][5120]
 float* qb_model_logits(qb_model* m) { return m ? m->logits : nullptr; }
 float* qb_model_hidden(qb_model* m) { return m ? m->h : nullptr; }
 void* qb_model_xn(qb_model* m) { return m ? (void*)m->xn : nullptr; }
+unsigned* qb_model_seen(qb_model* m) { return m ? m->seen : nullptr; }
 long long qb_model_launches(const qb_model* m) { return m ? m->launches : 0; }
 int qb_model_step_kernels(const qb_model* m) { return m ? m->step_kernels : 0; }
 

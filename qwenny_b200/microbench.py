@@ -7,6 +7,7 @@
     python -m qwenny_b200.microbench delta [--rows 2048 | --rows 5]
     python -m qwenny_b200.microbench draft [--k 4] [--draft-rows 65536]
     python -m qwenny_b200.microbench chain [--rows 5] [--trace] [--probe 1|2]
+    python -m qwenny_b200.microbench session [--layers 64] [--context 32768]
     python -m qwenny_b200.microbench sampler [--rows 5] [--top-k 50] [--top-p 0.95] [--penalty 1.1] [--draft-rows 0]
 
 Each prints CUDA-event timings (launches replayed from a CUDA graph, inputs larger than L2 where the shape allows)
@@ -245,6 +246,39 @@ def sampler(args):
           f"penalty={args.penalty}: {us:.1f} us per launch, tokens {tok.tolist()}, device error {ctx.device_error()}")
 
 
+def session(args):
+    """A slot's saved images at the 27B shapes: save_kv / load_kv of positions [0, context) and save_state /
+    load_state, host side in pinned memory; wall-clock per call (each call waits for its copy)."""
+    import time
+    ctx = Context(0)
+    ctx.set_pdl(True)
+    m = M.synthetic(ctx, nlayers=args.layers, position=args.context - 8, max_ctx=args.context)
+    from ._lib import lib
+    n = lib().qb_model_kv_bytes(m.h, 0, args.context)
+    pinned = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    buf = pinned.numpy()
+    res = {}
+    for name, fn in (("save_kv", lambda: m.save_kv(0, 0, args.context, out=buf)),
+                     ("load_kv", lambda: m.load_kv(0, 0, args.context, buf)),
+                     ("save_state", lambda: m.save_state(0)),):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.reps):
+            r = fn()
+        torch.cuda.synchronize()
+        res[name] = (time.perf_counter() - t0) / args.reps
+    st, pos = r
+    t0 = time.perf_counter()
+    for _ in range(args.reps):
+        m.load_state(0, st, pos)
+    res["load_state"] = (time.perf_counter() - t0) / args.reps
+    print(f"session layers={args.layers} context={args.context}: kv image {n / 1e6:.1f} MB (host side pinned), state "
+          f"image {len(st) / 1e6:.1f} MB (host side pageable); " +
+          ", ".join(f"{k} {v * 1e3:.2f} ms ({(n if 'kv' in k else len(st)) / v / 1e9:.1f} GB/s)" for k, v in res.items()) +
+          f"; device error {ctx.device_error()}")
+
+
 def delta(args):
     """The DeltaNet kernels of one prompt segment: conv once, then the rule kernel timed alone."""
     ctx = Context(0)
@@ -398,6 +432,10 @@ def main():
     d.add_argument("--no-pdl", action="store_true"); d.add_argument("--plain", action="store_true")
     d.add_argument("--probe", type=int, default=0); d.add_argument("--trace", action="store_true")
     d.set_defaults(fn=chain)
+    ss = sub.add_parser("session")
+    ss.add_argument("--layers", type=int, default=64); ss.add_argument("--context", type=int, default=32768)
+    ss.add_argument("--reps", type=int, default=3)
+    ss.set_defaults(fn=session)
     sp = sub.add_parser("sampler")
     sp.add_argument("--rows", type=int, default=5); sp.add_argument("--top-k", type=int, default=50)
     sp.add_argument("--top-p", type=float, default=0.95); sp.add_argument("--penalty", type=float, default=1.1)

@@ -125,6 +125,35 @@ class Model:
         self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
         return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
 
+    def save_kv(self, slot, start, end, out=None) -> np.ndarray:
+        """Model::save_kv: the attention layers' caches of positions [start, end) as the reference's byte image
+        (into `out`, a uint8 array of that size, e.g. over pinned memory, when given)."""
+        n = lib().qb_model_kv_bytes(self.h, start, end)
+        out = np.zeros(n, dtype=np.uint8) if out is None else out
+        assert out.dtype == np.uint8 and out.size == n and out.flags.c_contiguous
+        check(lib().qb_model_save_kv(self.h, C.c_void_p(self.stream.cuda_stream), slot, start, end,
+                                     out.ctypes.data_as(C.c_void_p), n), "qb_model_save_kv")
+        return out
+
+    def load_kv(self, slot, start, end, data: np.ndarray):
+        d = np.ascontiguousarray(data, dtype=np.uint8)
+        check(lib().qb_model_load_kv(self.h, C.c_void_p(self.stream.cuda_stream), slot, start, end,
+                                     d.ctypes.data_as(C.c_void_p), len(d)), "qb_model_load_kv")
+
+    def save_state(self, slot):
+        """Model::save_state: (byte image, the position the DeltaNet states are at)."""
+        n = lib().qb_model_state_bytes(self.h)
+        out = np.zeros(n, dtype=np.uint8)
+        pos = C.c_int(0)
+        check(lib().qb_model_save_state(self.h, C.c_void_p(self.stream.cuda_stream), slot,
+                                        out.ctypes.data_as(C.c_void_p), n, C.byref(pos)), "qb_model_save_state")
+        return out, pos.value
+
+    def load_state(self, slot, data: np.ndarray, pos: int):
+        d = np.ascontiguousarray(data, dtype=np.uint8)
+        check(lib().qb_model_load_state(self.h, C.c_void_p(self.stream.cuda_stream), slot,
+                                        d.ctypes.data_as(C.c_void_p), len(d), pos), "qb_model_load_state")
+
     def set_outputs(self, slot, words):
         """Step::set_outputs: the set of tokens the slot's request generated (uint32 words over the padded vocabulary)."""
         w = np.ascontiguousarray(words, dtype=np.uint32)
