@@ -126,6 +126,20 @@ int qb_mtp_in(qb_ctx* ctx, void* stream, const float* emb, const float* h, const
               const float* pre_e, const float* pre_h, void* y, float eps, int n);
 int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, const int* head_ids, int n_out,
                   int* next_ids, int* chain, int chain_ld, int t);
+/* ---- a LoRA adapter applied unmerged (f-row 4 of the scope; kernels/lora.cuh, src/cuda/qwen/lora.rs:160-207).
+ * xa f32 [split][n][M]: the partial sums of the stacked A's product with the step's input (qb_gemm_f16_plain on A
+ * packed by qb_pack_f16; M = adapted modules * rank padded to 16, at most 256). B f16 [rows][rank] in the product's row
+ * order; tab int[8]: the ends of the stacked modules' rows (3, ascending, unused INT_MAX), one unused, then each
+ * module's first column of xa (-1: not adapted). slot_scale f32 [slots]: alpha / r for slots that use the adapter, else
+ * 0 (their tokens get exactly the base model's values). rank 8, 16, 32 or 64.
+ * qb_lora_add   lora_add_r*: y (a plain product's first partial sums, f32 [n][ldy]) += s * B . xa
+ * qb_lora_silu  lora_silu_r*: mid f16 [n][rows / 2] = SwiGLU of the plain [gate; up] product y (the SwiGLU epilogue's
+ *               row order) with the delta added first, as the epilogue rounds it */
+int qb_lora_add(qb_ctx* ctx, void* stream, const float* xa, int split, int M, const void* B, int rows, const int* tab,
+                const int* tok_slot, const float* slot_scale, int n, float* y, int ldy, int rank);
+int qb_lora_silu(qb_ctx* ctx, void* stream, const float* xa, int split, int M, const void* B, int rows, const int* tab,
+                 const int* tok_slot, const float* slot_scale, int n, const float* y, int ldy, void* mid, int rank);
+
 /* ---- the GPU sampler (kernels/sampling.cuh; host definition src/sample.rs:88-211).
  * QB_QD, QB_QCAP: drafts per chain and kept tokens per stored draft distribution (QD, QCAP, kernels/sampling.cuh:73-74).
  * qb_sample_rows   sample_rows, kernels/sampling.cuh:188-291 (Step::sample, src/cuda/core.rs:977-1005): one token per
@@ -292,6 +306,21 @@ typedef struct qb_mtp {
     int head_zero_points;            /* non-zero: head_s holds the (8 - z) * scale table too (Mat::marlin_rows with zeros) */
 } qb_mtp;
 
+/* A layer's LoRA (LayerLora, src/cuda/qwen/lora.rs:199-205): per stacked product its A (shared by the products that
+ * read the same input) and B. a == NULL: the product is not adapted. */
+typedef struct qb_lora_prod {
+    const void* a;       /* stacked A, qb_pack_f16 of f16 [a_tiles * 16][cols] (modules * rank rows, padded to 16) */
+    int a_tiles;
+    const void* b;       /* B f16 [rows][rank] in the product's row order (SwiGLU: row_order), or NULL */
+    const int* tab;      /* device int[8], see qb_lora_add */
+    const void* b2;      /* DeltaNet in-projection only: B of [in_proj_b; in_proj_a] (96 rows) on the same xa, or NULL */
+    const int* tab2;
+} qb_lora_prod;
+typedef struct qb_lora_layer {
+    int rank;            /* 8, 16, 32 or 64 */
+    qb_lora_prod inp, out, gate_up, down;
+} qb_lora_layer;
+
 /* A token of a step (Tok, src/engine.rs:90-95) */
 typedef struct qb_tok {
     uint32_t id, slot, pos;
@@ -350,6 +379,13 @@ int qb_model_load_kv(qb_model* m, void* stream, int slot, int from, int to, cons
 size_t qb_model_state_bytes(const qb_model* m);
 int qb_model_save_state(qb_model* m, void* stream, int slot, void* h_out, size_t bytes, int* pos);
 int qb_model_load_state(qb_model* m, void* stream, int slot, const void* h_data, size_t bytes, int pos);
+/* A LoRA adapter served unmerged (Model::set_adapter, Step::lora; src/cuda/qwen/lora.rs, mod.rs:505-575):
+ * qb_model_set_adapter   layer i's LoRA (NULL: none; the MTP layer is not adapted).
+ * qb_model_set_slot_scale  alpha / r for a slot whose request uses the adapter, 0 for one that does not. Steps without
+ *                        tokens of adapter slots run exactly the base model's kernels; in the others every adapted
+ *                        product is followed by xa = A x and qb_lora_add ([gate; up]: a plain product and qb_lora_silu). */
+int qb_model_set_adapter(qb_model* m, int layer, const qb_lora_layer* lora);
+int qb_model_set_slot_scale(qb_model* m, void* stream, int slot, float scale);
 int qb_model_run(qb_model* m, void* stream);
 int qb_model_use_graphs(qb_model* m, int on);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */

@@ -53,6 +53,9 @@ class CpuModel:
                 d[k] = v.cpu().numpy()
             elif k in ("sst", "cap"):
                 d[k] = v
+            elif k == "lora":  # the adapter's host copies (qwenny_b200.model.synthetic_adapter)
+                d[k] = {name: {f: p[f] for f in ("A", "B", "tab_h", "B2", "tab2_h") if f in p}
+                        for name, p in v.items() if isinstance(p, dict)}
         return d
 
     @staticmethod
@@ -86,6 +89,8 @@ class CpuModel:
         """Returns (logits f32 [n_out][vocab_rows], greedy tokens). Updates the caches and states in place."""
         st = R.build_step(toks, out_rows)
         n = st["n"]
+        if getattr(self, "slot_scale", None) is not None:
+            st["lora_scale"] = np.asarray(self.slot_scale, dtype=np.float32)[st["tok_slot"]]
         h = R.embed(self.embed, st["ids"])
         xn = R.rmsnorm(h, self.layers[0]["input_norm"])
         for i, l in enumerate(self.layers):
@@ -124,11 +129,22 @@ class CpuModel:
             at, outs, own = list(range(len(cur))), list(range(len(cur))), True
         return chains, all_logits
 
+    def _lora(self, l, st, prod, x, which="B", silu=False):
+        """The delta of an adapted product (src/cuda/qwen/lora.rs:1-8): s * B (A x) for the tokens of adapter slots, A
+        and B as the device holds them (f16 values), 0 when the step has no such token or the product no adapter."""
+        lo = l.get("lora")
+        sc = st.get("lora_scale")
+        if lo is None or sc is None or not np.any(sc != 0) or lo.get(prod) is None or lo[prod].get(which) is None:
+            return 0.0
+        p = lo[prod]
+        xa = (x.astype(np.float32) @ p["A"].T)[None]
+        return R.lora_delta(xa, p[which], p["tab_h" if which == "B" else "tab2_h"], sc, silu)
+
     def _layer(self, l, st, h, xn, w_next):
         n = st["n"]
-        part = self._mm(xn, l["in_proj_f32"])[None]
+        part = (self._mm(xn, l["in_proj_f32"]) + self._lora(l, st, "inp", xn))[None]
         if l["kind"] == "delta":
-            ba = self._mm(xn, l["in_ba_f32"])[None]
+            ba = (self._mm(xn, l["in_ba_f32"]) + self._lora(l, st, "inp", xn, "B2"))[None]
             cv = R.delta_conv(part, ba, l["conv_w"], l["a_log"], l["dt_bias"], l["mem"], l["sst"], st["tok_slot"],
                               st["tok_pos"])
             o = R.delta_rule(part, cv, l["mem"], l["sst"], l["meta"], st["seg_start"], st["seg_len"],
@@ -139,11 +155,11 @@ class CpuModel:
             R.kv_store(l["kc"], l["vc"], l["ks"], l["vs"], k, v, st["tok_slot"], st["tok_pos"], l["cap"])
             o = R.attn_decode(q, gate, l["kc"], l["vc"], l["ks"], l["vs"], st["tok_slot"], st["tok_pos"], l["cap"])
             mix = o.astype(np.float16)
-        h, xn = R.add_rmsnorm(h, self._mm(mix, l["out_f32"])[None], l["post_norm"])
-        gu = self._mm(xn, l["gate_up_f32"])
+        h, xn = R.add_rmsnorm(h, (self._mm(mix, l["out_f32"]) + self._lora(l, st, "out", mix))[None], l["post_norm"])
+        gu = self._mm(xn, l["gate_up_f32"]) + self._lora(l, st, "gate_up", xn, silu=True)
         b = gu.reshape(n, -1, 2, 8)
         mid = (R.silu(b[:, :, 0, :]) * b[:, :, 1, :]).reshape(n, -1).astype(np.float16)
-        h, xn = R.add_rmsnorm(h, self._mm(mid, l["down_f32"])[None], w_next)
+        h, xn = R.add_rmsnorm(h, (self._mm(mid, l["down_f32"]) + self._lora(l, st, "down", mid))[None], w_next)
         return h, xn
 
 

@@ -154,6 +154,19 @@ class RefModule:
     def mark_seen(self, seen, mark, mark_at, seg_slot, seg_pos0, segs):
         self.launch("mark_seen", (segs,), 256, 0, [_ptr(seen), _ptr(mark), _ptr(mark_at), _ptr(seg_slot), _ptr(seg_pos0)])
 
+    # ------------------------------------------------------------------------------------------ LoRA
+    def lora_add(self, rank, xa, split, M, B, rows, tab, tok_slot, slot_scale, n, y, ldy):
+        """LoraA::launch without mid (src/cuda/qwen/lora.rs:163-196): a block per 256 rows and 8 tokens."""
+        self.launch(f"lora_add_r{rank}", (-(-rows // 256), -(-n // 8)), 256, 0,
+                    [_ptr(xa), C.c_int(split), C.c_int(M), _ptr(B), C.c_int(rows), _ptr(tab), _ptr(tok_slot),
+                     _ptr(slot_scale), C.c_int(n), _ptr(y), C.c_int(ldy)])
+
+    def lora_silu(self, rank, xa, split, M, B, rows, tab, tok_slot, slot_scale, n, y, ldy, mid):
+        """LoraA::launch with mid: a block per 512 rows of y (256 of mid)."""
+        self.launch(f"lora_silu_r{rank}", (-(-rows // 512), -(-n // 8)), 256, 0,
+                    [_ptr(xa), C.c_int(split), C.c_int(M), _ptr(B), C.c_int(rows), _ptr(tab), _ptr(tok_slot),
+                     _ptr(slot_scale), C.c_int(n), _ptr(y), C.c_int(ldy), _ptr(mid)])
+
     # ------------------------------------------------------------------------------------------ sampler
     def sample_rows(self, logits, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn, qid, qp, out_tok,
                     out_acc, n_out):

@@ -559,3 +559,37 @@ def build_step(toks, out_rows, short=8, max_dec=64, ptile=10, cut=16 * DSPLITS):
         seg_start=i32(seg[0]), seg_len=i32(seg[1]), seg_slot=i32(seg[2]), seg_pos0=i32(seg[3]),
         dtok=i32(dtok), dseg=i32(dseg), dkeys=i32(dkeys), ptile=i32(ptl), out_rows=i32(out_rows),
     )
+
+
+# ------------------------------------------------------------------------------------------------- LoRA (unmerged)
+def lora_delta(xa_parts, B, tab, scale, silu=False):
+    """The delta kernels/lora.cuh adds: xa_parts f32 [split][n][M] summed over the splits in order, B f32 [rows][r]
+    (the product's row order), tab as LoraB::tab (src/cuda/qwen/lora.rs:128-141), scale f32 [n] per token (0: none).
+    Returns f32 [n][rows]: s_t * B[o] . xa[t][off(o) : off(o) + r], accumulated as one fused multiply-add chain per
+    row (here in float64, rounded once: the kernels' f32 chain differs by rounding only)."""
+    xa = np.zeros(xa_parts.shape[1:], dtype=np.float32)
+    for s in range(xa_parts.shape[0]):
+        xa = xa + xa_parts[s]
+    rows, r = B.shape
+    n = xa.shape[0]
+    out = np.zeros((n, rows), dtype=np.float64)
+    if silu:  # 16-row tile p: gate rows 8p .. 8p + 7 (module 0), then their up rows (module 1)
+        mod = (np.arange(rows) % 16) // 8
+    else:
+        mod = sum((np.arange(rows) >= tab[i]).astype(np.int64) for i in range(3))
+    for m in range(4):
+        off = tab[4 + m]
+        sel = np.nonzero(mod == m)[0]
+        if off < 0 or len(sel) == 0:
+            continue
+        out[:, sel] = xa[:, off:off + r].astype(np.float64) @ B[sel].astype(np.float64).T
+    return (out * np.asarray(scale, dtype=np.float64)[:, None]).astype(np.float32)
+
+
+def lora_silu(y, delta):
+    """lora_silu (kernels/lora.cuh:82-107): mid[t][8p + g] = f16(silu(gate) * up) of y + delta in the SwiGLU row order."""
+    v = (y + delta).astype(np.float32)
+    n, rows = v.shape
+    v = v.reshape(n, rows // 16, 2, 8)
+    g, u = v[:, :, 0, :], v[:, :, 1, :]
+    return ((g / (1.0 + np.exp(-g.astype(np.float64)))) * u).reshape(n, rows // 2).astype(np.float16)

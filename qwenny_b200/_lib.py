@@ -33,6 +33,8 @@ SIGNATURES = {
     "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
     "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
     "qb_draft_pick": [P, P, P, P, I, P, P, I, I],
+    "qb_lora_add": [P, P, P, I, I, P, I, P, P, P, I, P, I, I],
+    "qb_lora_silu": [P, P, P, I, I, P, I, P, P, P, I, P, I, P, I],
     "qb_sample_rows": [P, P, P, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "qb_host_sample_row": [P, I, P, P, P, I, P, P, P, I, P, P],
     "qb_draft_sample": [P, P, P, I, I, P, I, I, P, P, P, P, P, P, P, P, P, P],
@@ -44,6 +46,8 @@ SIGNATURES = {
     "qb_model_state_bytes": [P],
     "qb_model_save_state": [P, P, I, P, C.c_size_t, P],
     "qb_model_load_state": [P, P, I, P, C.c_size_t, I],
+    "qb_model_set_adapter": [P, I, P],
+    "qb_model_set_slot_scale": [P, P, I, F],
     "qb_model_set_outputs": [P, P, I, P],
     "qb_model_sample": [P, P, P, I, P, P],
     "qb_model_draft_sampled": [P, P, P, I, P, P, I, I, P, P, P],
@@ -113,6 +117,16 @@ class QbMtp(C.Structure):
         ("layer", QbLayer), ("fc_w", P), ("fc_s", P), ("pre_e", P), ("pre_h", P), ("norm", P), ("head_w", P),
         ("head_s", P), ("head_rows", I), ("head_valid", I), ("head_ids", P), ("head_zero_points", I),
     ]
+
+
+class QbLoraProd(C.Structure):
+    """qb_lora_prod of include/qwenny_b200.h."""
+    _fields_ = [("a", P), ("a_tiles", I), ("b", P), ("tab", P), ("b2", P), ("tab2", P)]
+
+
+class QbLoraLayer(C.Structure):
+    """qb_lora_layer of include/qwenny_b200.h."""
+    _fields_ = [("rank", I), ("inp", QbLoraProd), ("out", QbLoraProd), ("gate_up", QbLoraProd), ("down", QbLoraProd)]
 
 
 class QbChain(C.Structure):

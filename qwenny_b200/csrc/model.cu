@@ -30,6 +30,8 @@ constexpr int PAIRS = 64 * 128;                 // (decode token, split) pairs o
 struct Layer {
     qb_layer w;
     bool set = false;
+    bool has_lora = false;
+    qb_lora_layer lora = {};
 };
 
 struct GraphKey {
@@ -79,6 +81,12 @@ struct qb_model {
     int *sampled = nullptr, *qtok = nullptr, *qn = nullptr, *qid = nullptr;
     float* h_sparams = nullptr;  // pinned [MAX_OUT][8]
     int* h_sampled = nullptr;    // pinned: tokens [MAX_OUT], accepted [MAX_OUT], then the chains [slots][QB_QD]
+    // LoRA served unmerged: the slots' scales (device + host mirror), the partial sums of A x, the plain [gate; up]
+    // product of adapted layers; lora_step: the uploaded step has tokens of adapter slots
+    float* slot_scale = nullptr;
+    std::vector<float> h_scale;
+    float *lpart = nullptr, *lgu = nullptr;
+    bool any_lora = false, lora_step = false;
     // saved images (session.cu): the span table (pinned + device), the staging buffer (grows on demand)
     qb::Span *h_spans = nullptr, *d_spans = nullptr;
     unsigned char* staging = nullptr;
@@ -224,6 +232,65 @@ int launch_layer_tail(qb_model* m, cudaStream_t st, const qb_layer& L, const flo
     return QB_OK;
 }
 
+// xa = A x of a stacked product's adapter into m->lpart (split-K partial sums [split][n][M]); the split count
+int lora_xa(qb_model* m, void* s, const qb_lora_prod& p, const void* x, int cols, int* split, int& k) {
+    *split = (cols + 1023) / 1024;
+    QB_TRY(qb_gemm_f16_plain(m->ctx, s, p.a, x, nullptr, cols, p.a_tiles, m->n, 1024, m->lpart, p.a_tiles * 16)); k++;
+    return QB_OK;
+}
+
+// A layer with a LoRA in a step with adapter tokens (Stack::mix / mlp with `lo`, src/cuda/qwen/mod.rs:521-575): every
+// adapted product is followed by xa = A x and the delta's kernel; [gate; up] runs plain and lora_silu applies SwiGLU.
+int launch_layer_lora(qb_model* m, cudaStream_t st, int layer, const float* w_next, int& k) {
+    qb_ctx* c = m->ctx;
+    const qb_layer& L = m->layers[layer].w;
+    const qb_lora_layer& A = m->layers[layer].lora;
+    const int n = m->n, R = A.rank;
+    void* s = (void*)st;
+    int split = 0;
+    const bool fork = m->fork;
+    m->fork = false;  // the 16-bit in-projection in line: its delta follows it on this stream
+    int rc = launch_in_proj(m, st, layer, true, false, k);
+    if (!rc && A.inp.a) {
+        const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
+        rc = lora_xa(m, s, A.inp, m->xn, H, &split, k);
+        if (!rc && A.inp.b) {
+            rc = qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b, rows, A.inp.tab, m->tok_slot, m->slot_scale,
+                             n, m->part, rows, R); k++;
+        }
+        if (!rc && A.inp.b2 && L.kind == QB_LAYER_DELTA) {
+            rc = qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b2, 2 * LV_HEADS, A.inp.tab2, m->tok_slot,
+                             m->slot_scale, n, m->ba, 2 * LV_HEADS, R); k++;
+        }
+    }
+    if (!rc) rc = launch_mixer(m, st, layer, k);
+    m->fork = fork;
+    QB_TRY(rc);
+    QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    if (A.out.a) {
+        QB_TRY(lora_xa(m, s, A.out, m->mix, MIX, &split, k));
+        QB_TRY(qb_lora_add(c, s, m->lpart, split, A.out.a_tiles * 16, A.out.b, H, A.out.tab, m->tok_slot, m->slot_scale, n,
+                           m->part, H, R)); k++;
+    }
+    QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
+    if (A.gate_up.a) {
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->lgu, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+        QB_TRY(lora_xa(m, s, A.gate_up, m->xn, H, &split, k));
+        QB_TRY(qb_lora_silu(c, s, m->lpart, split, A.gate_up.a_tiles * 16, A.gate_up.b, 2 * FF, A.gate_up.tab, m->tok_slot,
+                            m->slot_scale, n, m->lgu, 2 * FF, m->mid, R)); k++;
+    } else {
+        QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr, nullptr, 0)); k++;
+    }
+    QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
+    if (A.down.a) {
+        QB_TRY(lora_xa(m, s, A.down, m->mid, FF, &split, k));
+        QB_TRY(qb_lora_add(c, s, m->lpart, split, A.down.a_tiles * 16, A.down.b, H, A.down.tab, m->tok_slot, m->slot_scale,
+                           n, m->part, H, R)); k++;
+    }
+    QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, w_next, m->xn, EPS)); k++;
+    return QB_OK;
+}
+
 // The kernels of one MTP step over the uploaded tokens (launch_mtp, src/cuda/qwen/mod.rs:799-840): the tokens'
 // embeddings and their hidden states at mtp_rows of the residual stream (the target's with its final norm, or, `own`,
 // the MTP layer's of the step before with the MTP's norm) through mtp_in, fc, the MTP's decoder layer, and the draft
@@ -262,8 +329,8 @@ int launch_step(qb_model* m, cudaStream_t st) {
     const int n = m->n;
     int k = 0;
     void* s = (void*)st;
-    const bool chain = m->chain && n <= qb_layer_chain_max_rows();
-    const bool fnorm = m->fuse_norm && !chain && n <= 16;
+    const bool chain = m->chain && n <= qb_layer_chain_max_rows() && !m->lora_step;
+    const bool fnorm = m->fuse_norm && !chain && n <= 16 && !m->lora_step;
     // the reference splits the small 16-bit product 40 ways (split_for); 5 splits of 1024 columns leave its consumers
     // 8x fewer partial sums to add
     m->ba_kper = m->fused || n > 32 ? 1024 : H / qb_split_for(2 * LV_HEADS / 16, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
@@ -273,6 +340,10 @@ int launch_step(qb_model* m, cudaStream_t st) {
     for (int i = 0; i < m->nlayers; i++) {
         const qb_layer& L = m->layers[i].w;
         const float* w_next = i + 1 < m->nlayers ? m->layers[i + 1].w.input_norm : m->final_norm;
+        if (m->lora_step && m->layers[i].has_lora) {
+            QB_TRY(launch_layer_lora(m, st, i, w_next, k));
+            continue;
+        }
         QB_TRY(launch_in_proj(m, st, i, !chain || i == 0, fnorm && i > 0, k));
         QB_TRY(launch_mixer(m, st, i, k));
         if (chain) {
@@ -373,7 +444,7 @@ void qb_model_destroy(qb_model* m) {
     if (m->h_sampled) cudaFreeHost(m->h_sampled);
     if (m->h_spans) cudaFreeHost(m->h_spans);
     if (m->h_positions) cudaFreeHost(m->h_positions);
-    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions};
+    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions, m->slot_scale, m->lpart, m->lgu};
     for (void* b : sb) cudaFree(b);
     void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
@@ -543,6 +614,9 @@ static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, con
         for (int i = 0; i < n; i++) h[L.mtp_rows + i] = rows[i];
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     QB_CUDA(cudaEventRecord(m->h_event[m->h_cur], (cudaStream_t)stream));
+    m->lora_step = false;
+    if (m->any_lora && !rows)  // the MTP layer is not adapted (mtp_launch, src/cuda/qwen/mod.rs:933-934)
+        for (int i = 0; i < n && !m->lora_step; i++) m->lora_step = m->h_scale[toks[i].slot] != 0.f;
     m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
     m->max_seg = max_seg; m->dec_max_pos = dec_max_pos; m->tile_max_pos = tile_max_pos;
     return QB_OK;
@@ -567,7 +641,7 @@ static int run_kind(qb_model* m, void* stream, int kind) {
     GraphKey key = {{m->n, m->n_out, m->segs, m->ndec, m->ntile, m->max_seg,
                      (m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0) +
                          64 * (m->ntile ? qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) : 0),
-                     m->ndseg, m->dmax, kind}};
+                     m->ndseg, m->dmax, kind + (m->lora_step ? 4 : 0)}};
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         // a first uncaptured run sets the kernels' attributes (not allowed while capturing) and warms the caches
@@ -820,6 +894,48 @@ int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* 
     QB_CUDA(cudaMemcpyAsync(ids, m->qid + (size_t)q * QB_QCAP, *n * sizeof(int), cudaMemcpyDeviceToHost, st));
     QB_CUDA(cudaMemcpyAsync(p, m->qp + (size_t)q * QB_QCAP, *n * sizeof(float), cudaMemcpyDeviceToHost, st));
     QB_CUDA(cudaStreamSynchronize(st));
+    return QB_OK;
+}
+
+// ---- a LoRA adapter served unmerged
+
+static bool lora_prod_ok(const qb_lora_prod& p, bool needs_b) {
+    if (!p.a) return true;
+    return p.a_tiles > 0 && p.a_tiles * 16 <= 256 && (!needs_b || (p.b && p.tab)) && (!p.b || p.tab) && (!p.b2 || p.tab2);
+}
+
+int qb_model_set_adapter(qb_model* m, int layer, const qb_lora_layer* lora) {
+    if (!m || layer < 0 || layer >= m->nlayers) return QB_ERR_ARG;
+    Layer& L = m->layers[layer];
+    if (!lora) {
+        L.has_lora = false;
+    } else {
+        if ((lora->rank != 8 && lora->rank != 16 && lora->rank != 32 && lora->rank != 64) || !lora_prod_ok(lora->inp, false) ||
+            !lora_prod_ok(lora->out, true) || !lora_prod_ok(lora->gate_up, true) || !lora_prod_ok(lora->down, true))
+            return QB_ERR_ARG;
+        if (!m->lpart) {
+            // A x of the widest input (17 splits of 1024 columns) and the plain [gate; up] product of a whole step
+            QB_TRY(dalloc(&m->lpart, (size_t)17 * MAX_TOK * 256));
+            QB_TRY(dalloc(&m->lgu, (size_t)MAX_TOK * 2 * FF));
+        }
+        L.lora = *lora;
+        L.has_lora = true;
+    }
+    m->any_lora = false;
+    for (int i = 0; i < m->nlayers; i++) m->any_lora |= m->layers[i].has_lora;
+    return QB_OK;
+}
+
+int qb_model_set_slot_scale(qb_model* m, void* stream, int slot, float scale) {
+    if (!m || slot < 0 || slot >= m->slots) return QB_ERR_ARG;
+    if (!m->slot_scale) {
+        QB_TRY(dalloc(&m->slot_scale, (size_t)m->slots));
+        m->h_scale.assign(m->slots, 0.f);
+        QB_CUDA(cudaDeviceSynchronize());
+    }
+    m->h_scale[slot] = scale;
+    QB_CUDA(cudaMemcpyAsync(m->slot_scale + slot, &m->h_scale[slot], sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    QB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return QB_OK;
 }
 

@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import QbMtp, QbLayer, QbTok, check, lib
+from ._lib import QbLoraLayer, QbMtp, QbLayer, QbTok, check, lib
 
 H, NH, NKV, HD = 5120, 24, 4, 256
 LK_HEADS, LV_HEADS, LKD, LVD = 16, 48, 128, 128
@@ -124,6 +124,34 @@ class Model:
         self._n, self._n_out = (len(out) if k > 1 else len(toks)), len(out)
         self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
         return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
+
+    def set_adapter(self, i, lora):
+        """Layer i's LoRA (LayerLora, src/cuda/qwen/lora.rs:199-205): lora = dict(rank=r, inp=.., out=.., gate_up=..,
+        down=..), each product None or dict(a=packed f16 device tensor, a_tiles=.., b=f16 [rows][r] device tensor in the
+        product's row order, tab=int32[8] device tensor[, b2=.., tab2=..]); None removes it."""
+        if lora is None:
+            check(lib().qb_model_set_adapter(self.h, i, None), "qb_model_set_adapter")
+            self.layers[i].pop("lora_dev", None)
+            return
+        q = QbLoraLayer()
+        q.rank = lora["rank"]
+        for name in ("inp", "out", "gate_up", "down"):
+            p = lora.get(name)
+            if p is None:
+                continue
+            f = getattr(q, name)
+            f.a, f.a_tiles = p["a"].data_ptr(), p["a_tiles"]
+            if p.get("b") is not None:
+                f.b, f.tab = p["b"].data_ptr(), p["tab"].data_ptr()
+            if p.get("b2") is not None:
+                f.b2, f.tab2 = p["b2"].data_ptr(), p["tab2"].data_ptr()
+        check(lib().qb_model_set_adapter(self.h, i, C.byref(q)), "qb_model_set_adapter")
+        self.layers[i]["lora_dev"] = lora  # keeps the tensors alive
+
+    def set_slot_scale(self, slot, scale):
+        """Model::set_adapter for a slot: alpha / r when its request uses the adapter, else 0."""
+        check(lib().qb_model_set_slot_scale(self.h, C.c_void_p(self.stream.cuda_stream), slot, float(scale)),
+              "qb_model_set_slot_scale")
 
     def save_kv(self, slot, start, end, out=None) -> np.ndarray:
         """Model::save_kv: the attention layers' caches of positions [start, end) as the reference's byte image
@@ -363,3 +391,85 @@ def synthetic(ctx, nlayers=64, slots=1, max_ctx=32768, vocab=151936, seed=0, dev
             d["head_ids"] = ids
         model.set_mtp(d)
     return model
+
+
+IMAX = 2 ** 31 - 1
+
+
+def synthetic_adapter(model, rank=16, seed=5, std=0.05, device="cuda"):
+    """A random LoRA over every layer of `model`, laid out as the reference's loader does (lora::load,
+    src/cuda/qwen/lora.rs:58-141): the products that read one input share one stacked A (adapted modules in order,
+    rows padded to 16), B per stacked product in the product's row order with its table. Adapted here: DeltaNet
+    in_proj_qkv and in_proj_a (not in_proj_z, in_proj_b), attention q_proj and v_proj (not k_proj), out_proj,
+    gate_proj / up_proj (even layers both, odd layers up_proj only), down_proj. Sets the adapter on the model and keeps
+    host copies under layer["lora"] for the CPU oracle."""
+    from . import host
+    g = np.random.default_rng(seed)
+    f16 = lambda a: a.astype(np.float16).astype(np.float32)
+
+    def stack(cols, stacks):
+        """stacks: list of (module rows, adapted flags, silu). Returns the shared A and each stack's B / tab."""
+        a_rows, offs = [], []
+        for rows, flags, _ in stacks:
+            o = []
+            for f in flags:
+                if f:
+                    o.append(len(a_rows) * rank)
+                    a_rows.append(f16(g.standard_normal((rank, cols)) * std))
+                else:
+                    o.append(-1)
+            offs.append(o)
+        A = np.concatenate(a_rows, 0)
+        M = (A.shape[0] + 15) // 16 * 16
+        A = np.concatenate([A, np.zeros((M - A.shape[0], cols), dtype=np.float32)], 0)
+        out = []
+        for (rows, flags, silu), o in zip(stacks, offs):
+            if all(x < 0 for x in o):
+                out.append(None)
+                continue
+            total = sum(rows)
+            B = np.zeros((total, rank), dtype=np.float32)
+            at = 0
+            for r_, f in zip(rows, flags):
+                if f:
+                    B[at:at + r_] = f16(g.standard_normal((r_, rank)) * std)
+                at += r_
+            B = B[host.row_order(total, silu)]
+            tab = [IMAX] * 8
+            end = 0
+            for i, r_ in enumerate(rows):
+                end += r_
+                if not silu and i < 3:
+                    tab[i] = end
+            for i in range(4):
+                tab[4 + i] = o[i] if i < len(o) else -1
+            out.append((B, tab))
+        return A, M, out
+
+    def dev(A, M, b, b2=None):
+        d = dict(a=torch.from_numpy(host.pack_f16(A)).to(device), a_tiles=M // 16, A=A)
+        if b is not None:
+            d.update(b=torch.from_numpy(b[0].astype(np.float16)).to(device),
+                     tab=torch.tensor(b[1], dtype=torch.int32, device=device), B=b[0], tab_h=b[1])
+        if b2 is not None:
+            d.update(b2=torch.from_numpy(b2[0].astype(np.float16)).to(device),
+                     tab2=torch.tensor(b2[1], dtype=torch.int32, device=device), B2=b2[0], tab2_h=b2[1])
+        return d
+
+    for i, l in enumerate(model.layers):
+        lo = dict(rank=rank)
+        if l["kind"] == "delta":
+            A, M, (bi, bb) = stack(H, [([LQKV, DELTA_IN - LQKV], [True, False], False),
+                                       ([LV_HEADS, LV_HEADS], [False, True], False)])
+            lo["inp"] = dev(A, M, bi, bb)
+        else:
+            A, M, (bi,) = stack(H, [([NH * HD * 2, NKV * HD, NKV * HD], [True, False, True], False)])
+            lo["inp"] = dev(A, M, bi)
+        A, M, (bo,) = stack(MIX, [([H], [True], False)])
+        lo["out"] = dev(A, M, bo)
+        A, M, (bg,) = stack(H, [([FF, FF], [i % 2 == 0, True], True)])
+        lo["gate_up"] = dev(A, M, bg)
+        A, M, (bd,) = stack(FF, [([H], [True], False)])
+        lo["down"] = dev(A, M, bd)
+        model.set_adapter(i, lo)
+        l["lora"] = lo

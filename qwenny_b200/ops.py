@@ -105,6 +105,14 @@ class Context:
         check(lib().qb_draft_pick(self.h, _stream(), _p(keys), _p(head_ids), n_out, _p(next_ids), _p(chain), chain_ld, t),
               "qb_draft_pick")
 
+    def lora_add(self, xa, split, M, B, rows, tab, tok_slot, slot_scale, n, y, ldy, rank):
+        check(lib().qb_lora_add(self.h, _stream(), _p(xa), split, M, _p(B), rows, _p(tab), _p(tok_slot), _p(slot_scale),
+                                n, _p(y), ldy, rank), "qb_lora_add")
+
+    def lora_silu(self, xa, split, M, B, rows, tab, tok_slot, slot_scale, n, y, ldy, mid, rank):
+        check(lib().qb_lora_silu(self.h, _stream(), _p(xa), split, M, _p(B), rows, _p(tab), _p(tok_slot),
+                                 _p(slot_scale), n, _p(y), ldy, _p(mid), rank), "qb_lora_silu")
+
     def sample_rows(self, logits, vocab, n_out, out_rows, tok_slot, ids, row_first, seen, outs, params, qtok, qn, qid,
                     qp, out_tok, out_acc, width=None, ld=None):
         """Step::sample (src/cuda/core.rs:977-1005) without the host rows: out_acc -1 marks those."""
