@@ -20,7 +20,8 @@ namespace qb {
 
 constexpr float KV_OFF = 1152.f;
 constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
-constexpr int DSPLITS = 32;    // most key splits of a decode token: 4 kv heads x 32 splits fill the SMs once
+constexpr int DSPLITS = 37;    // most key splits of a decode token: 4 kv heads x 37 splits = one block per SM (148)
+constexpr int TSPLITS = 32;    // most key splits of a prompt tile (a power of two)
 
 __host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
 __host__ __device__ inline size_t scale_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap; }
@@ -36,10 +37,13 @@ __device__ __forceinline__ size_t vslot(int pos, int d) {
     return ((size_t)(pos >> 4) * HD + d) * 16 + t4 * 4 + e;
 }
 
-// Keys per split of a token with `keys` keys: a multiple of 64, at most DSPLITS splits; changes only where keys
-// crosses a multiple of 64 * DSPLITS = 2048 (where the host cuts short segments, so the tokens of a segment always
-// agree).
-__host__ __device__ inline int dec_chunk(int keys) { return max(64, ((keys + DSPLITS - 1) / DSPLITS + 63) / 64 * 64); }
+// Keys per split of a token with `keys` keys: a multiple of 64, at most DSPLITS splits, and the same for every key
+// count between two multiples of 2048 (where the host cuts short segments: a token's splits must not depend on how
+// many drafts follow it in the step), so it is sized for the end of that range.
+__host__ __device__ inline int dec_chunk(int keys) {
+    const int range_end = ((keys - 1) / 2048 + 1) * 2048;
+    return max(64, ((range_end + DSPLITS - 1) / DSPLITS + 63) / 64 * 64);
+}
 __host__ __device__ inline int dec_splits(int keys) { int c = dec_chunk(keys); return (keys + c - 1) / c; }
 
 // ------------------------------------------------------------------------------------------------ attn_prep
@@ -125,7 +129,7 @@ __device__ __forceinline__ uint32_t kv_half2(uint32_t w, uint32_t sel) { return 
 __host__ __device__ __forceinline__ int tile_chunk(int keys, int z) { return max(64, ((keys + z - 1) / z + 63) / 64 * 64); }
 __host__ inline int tile_splits(int ntile, int max_keys) {
     int z = 1;  // fill about two blocks per SM, no split shorter than 256 keys
-    while (z < DSPLITS && ntile * NKV * z * 2 <= 2 * 148 && max_keys / (z * 2) >= 256) z *= 2;
+    while (z < TSPLITS && ntile * NKV * z * 2 <= 2 * 148 && max_keys / (z * 2) >= 256) z *= 2;
     return z;
 }
 
@@ -722,22 +726,26 @@ attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const 
 // so that the accumulator loads of all splits are independent and in flight together.
 __device__ __forceinline__ void combine_row(const float* part_ml, const float* part_acc, size_t base, int ns, float* op,
                                             __half* mp) {
-    __shared__ float se[DSPLITS];
+    static_assert(DSPLITS <= 64 && TSPLITS <= 64, "two splits per lane");
+    __shared__ float se[64];
     __shared__ float sL;
     const int d = threadIdx.x;
     float res;
     if (ns == 1) {
         res = *op;  // the attention kernel finished it
     } else {
-        if (d < 32) {  // DSPLITS <= 32: one split per lane
-            float ms = d < ns ? part_ml[(base + d) * 2] : -INFINITY;
-            float ls = d < ns ? part_ml[(base + d) * 2 + 1] : 0.f;
-            float M = warp_max(ms);
-            float e = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            se[d] = e;
+        if (d < 32) {  // lane d: splits d and d + 32
+            const float ms0 = d < ns ? part_ml[(base + d) * 2] : -INFINITY;
+            const float ls0 = d < ns ? part_ml[(base + d) * 2 + 1] : 0.f;
+            const float ms1 = d + 32 < ns ? part_ml[(base + d + 32) * 2] : -INFINITY;
+            const float ls1 = d + 32 < ns ? part_ml[(base + d + 32) * 2 + 1] : 0.f;
+            const float M = warp_max(fmaxf(ms0, ms1));
+            const float e0 = ms0 == -INFINITY ? 0.f : exp2f(ms0 - M), e1 = ms1 == -INFINITY ? 0.f : exp2f(ms1 - M);
+            se[d] = e0;
+            se[d + 32] = e1;
             // the sum over splits in split order (not a tree: the same order whatever the lane count)
             float L = 0.f;
-            for (int s = 0; s < ns; s++) L += __shfl_sync(0xffffffffu, e * ls, s);
+            for (int s = 0; s < ns; s++) L += __shfl_sync(0xffffffffu, s < 32 ? e0 * ls0 : e1 * ls1, s & 31);
             if (d == 0) sL = L;
         }
         __syncthreads();

@@ -53,6 +53,8 @@ def gemv(args):
         lib().qb_marlin_probe(ctx.h, args.probe)
     n, k, m = args.n, args.k, args.rows
     nbuf = max(2, min(8, int(300e6 / (n * k * 0.516)) + 1))  # weight buffers in rotation: more than L2 in total
+    if args.hot:
+        nbuf = 1  # the same weights every launch: L2-resident when they fit
     g = torch.Generator(device="cuda").manual_seed(0)
     bufs = [M.Marlin.random(n, k, g) for _ in range(nbuf)]
     x = torch.randn(m, k, generator=g, device="cuda").half()
@@ -403,6 +405,7 @@ def main():
     a.add_argument("--reps", type=int, default=24); a.add_argument("--tune", default="")
     a.add_argument("--no-pdl", action="store_true"); a.add_argument("--plain", action="store_true")
     a.add_argument("--probe", type=int, default=0, help="1: time the copy pipeline alone (no arithmetic)")
+    a.add_argument("--hot", action="store_true", help="one weight buffer: L2-resident weights")
     a.set_defaults(fn=gemv)
     b = sub.add_parser("attn")
     b.add_argument("--context", type=int, default=32000); b.add_argument("--rows", type=int, default=5)

@@ -29,7 +29,11 @@ def test_version_and_host_only_calls():
     l = _lib.lib()
     assert b"sm_100a" in l.qb_version()
     assert l.qb_split_for(6, 5120, 16, 1024) == 40
-    assert l.qb_attn_dec_splits(32005) == 32 and l.qb_attn_dec_splits(1) == 1 and l.qb_attn_dec_splits(4097) == 22
+    assert l.qb_attn_dec_splits(32005) == 36 and l.qb_attn_dec_splits(1) == 1 and l.qb_attn_dec_splits(4097) == 22
+    # the same split size for every key count between two multiples of 2048 (a token's sums do not depend on the drafts
+    # that follow it), never more than 37 splits (4 kv heads x 37 = one block per SM)
+    for lo in range(0, 65536, 2048):
+        assert all(l.qb_attn_dec_splits(k) <= 37 for k in (lo + 1, lo + 777, lo + 2048))
 
 
 def test_argument_errors_need_no_device():
