@@ -1,5 +1,7 @@
 // Host side of the W4A16 skinny product: picks a tile shape and split for the shape, launches the persistent grid.
 #include "ctx.h"
+#include <array>
+#include <map>
 #include "w4a16_gemv.cuh"
 
 namespace qb {
@@ -40,11 +42,13 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
     cudaLaunchAttribute at[2];
     int nat = 0;
     // Clusters are placed inside one GPC each, so not every rank count packs the GPU in one wave: ask the driver how
-    // many clusters of a size can be resident (cached per kernel and size) and take the most ranks whose column
-    // blocks all fit, then as few as give the same longest share of k stages.
+    // many clusters of a size can be resident (cached per kernel, size and shared-memory footprint, so that the answer,
+    // and with it the way k is split and summed, depends on the product's shape alone and not on the calls before it)
+    // and take the most ranks whose column blocks all fit, then as few as give the same longest share of k stages.
     int cluster_s = 0;
     if (p.cluster_s > 0) {
-        static int fits[9] = {0};  // per instantiation: resident clusters of size s (0: not asked yet)
+        static std::map<int, std::array<int, 9>> asked;  // per instantiation: smem -> resident clusters of size s
+        std::array<int, 9>& fits = asked.try_emplace(smem, std::array<int, 9>{}).first->second;
         const int ncb = a.N / C::TN, kst = a.K / C::TK;
         int s = p.cluster_s;
         for (; s > 1; s--) {
