@@ -321,6 +321,32 @@ typedef struct qb_lora_layer {
     qb_lora_prod inp, out, gate_up, down;
 } qb_lora_layer;
 
+/* ---- device memory mapped on demand (src/cuda/vmm.rs): Pool (:16-128) and Region (:171-289). A region reserves device
+ * addresses once (kernels and graphs see fixed pointers) and maps 2 MiB pages from the pool where data lives; the pool
+ * makes pages within a budget and reuses unmapped ones. Errors of the driver come back as 2000 + CUresult.
+ * qb_region_map: *ok = 0 when the pool has too few pages (nothing more is mapped); new pages are zeroed on `stream`.
+ * qb_region_unmap: the pages wholly inside [from, to), after the stream's work. qb_region_read / write refuse ranges that
+ * are not mapped (QB_ERR_ARG). Kernels must only be given mapped ranges: an access to an unmapped page is a GPU fault. */
+typedef struct qb_pool qb_pool;
+typedef struct qb_region qb_region;
+int qb_pool_create(int device, qb_pool** out);
+void qb_pool_destroy(qb_pool* p);
+size_t qb_pool_page(const qb_pool* p);
+int qb_pool_set_budget(qb_pool* p, size_t pages);
+int qb_pool_fill(qb_pool* p);
+int qb_pool_release(qb_pool* p, size_t n, size_t* given);
+int qb_pool_usage(qb_pool* p, size_t* used, size_t* budget);
+size_t qb_pool_available(qb_pool* p);
+int qb_region_reserve(qb_pool* p, size_t size, qb_region** out);
+void* qb_region_ptr(const qb_region* r);
+size_t qb_region_size(const qb_region* r);
+int qb_region_is_mapped(const qb_region* r, size_t from, size_t to);
+int qb_region_map(qb_region* r, void* stream, size_t from, size_t to, int* ok);
+int qb_region_unmap(qb_region* r, void* stream, size_t from, size_t to);
+int qb_region_read(qb_region* r, void* stream, size_t from, void* out, size_t n);
+int qb_region_write(qb_region* r, void* stream, size_t from, const void* data, size_t n);
+int qb_region_free(qb_region* r, void* stream);
+
 /* A token of a step (Tok, src/engine.rs:90-95) */
 typedef struct qb_tok {
     uint32_t id, slot, pos;

@@ -89,6 +89,23 @@ SIGNATURES = {
     "qb_model_use_fused_norm": [P, I],
     "qb_model_launches": [P],
     "qb_model_step_kernels": [P],
+    "qb_pool_create": [I, C.POINTER(P)],
+    "qb_pool_destroy": [P],
+    "qb_pool_page": [P],
+    "qb_pool_set_budget": [P, C.c_size_t],
+    "qb_pool_fill": [P],
+    "qb_pool_release": [P, C.c_size_t, P],
+    "qb_pool_usage": [P, P, P],
+    "qb_pool_available": [P],
+    "qb_region_reserve": [P, C.c_size_t, C.POINTER(P)],
+    "qb_region_ptr": [P],
+    "qb_region_size": [P],
+    "qb_region_is_mapped": [P, C.c_size_t, C.c_size_t],
+    "qb_region_map": [P, P, C.c_size_t, C.c_size_t, P],
+    "qb_region_unmap": [P, P, C.c_size_t, C.c_size_t],
+    "qb_region_read": [P, P, C.c_size_t, P, C.c_size_t],
+    "qb_region_write": [P, P, C.c_size_t, P, C.c_size_t],
+    "qb_region_free": [P, P],
     "qb_row_order": [I, I, P],
     "qb_pack_marlin": [P, P, I, I, I, P, I, P, P],
     "qb_pack_marlin_z": [P, P, P, I, I, I, P, I, P, P],
@@ -97,7 +114,8 @@ SIGNATURES = {
 }
 _RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
             "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,
-            "qb_model_state_bytes": C.c_size_t}
+            "qb_model_state_bytes": C.c_size_t, "qb_pool_destroy": None, "qb_pool_page": C.c_size_t,
+            "qb_pool_available": C.c_size_t, "qb_region_ptr": P, "qb_region_size": C.c_size_t}
 
 
 class QbLayer(C.Structure):

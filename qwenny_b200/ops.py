@@ -13,7 +13,10 @@ EPI = {"plain": 0, "silu": 1, "argmax": 2}
 
 
 def _p(t):
-    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+    """A device tensor's address, a raw device address (int), or null."""
+    if t is None:
+        return C.c_void_p(0)
+    return C.c_void_p(t) if isinstance(t, int) else C.c_void_p(t.data_ptr())
 
 
 def _stream():
