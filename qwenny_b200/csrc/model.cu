@@ -107,6 +107,7 @@ struct qb_model {
     bool fuse_norm = false;
     cudaStream_t side = nullptr;
     std::vector<cudaEvent_t> ev;  // per layer: fork, join
+    std::vector<cudaEvent_t> lev;  // per layer and adapted product: fork, join of xa = A x (created with the first adapter)
     long long launches = 0;  // kernels launched (or replayed) since creation
     int step_kernels = 0;    // kernels of the last step
     int ba_kper = 1024;      // k range of a split of the DeltaNet 16-bit in-projection in the current step
@@ -248,42 +249,62 @@ int launch_layer_lora(qb_model* m, cudaStream_t st, int layer, const float* w_ne
     const int n = m->n, R = A.rank;
     void* s = (void*)st;
     int split = 0;
-    const bool fork = m->fork;
-    m->fork = false;  // the 16-bit in-projection in line: its delta follows it on this stream
-    int rc = launch_in_proj(m, st, layer, true, false, k);
-    if (!rc && A.inp.a) {
-        const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
-        rc = lora_xa(m, s, A.inp, m->xn, H, &split, k);
-        if (!rc && A.inp.b) {
-            rc = qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b, rows, A.inp.tab, m->tok_slot, m->slot_scale,
-                             n, m->part, rows, R); k++;
+    // xa = A x reads the same input as the base product it accompanies: with the second stream it runs beside that
+    // product (a parallel branch of the step's graph) and only the delta's kernel stays on the critical path.
+    // `e`: the product's index in the layer (its pair of events); `forked`: the second stream already waits for the
+    // input (the DeltaNet 16-bit in-projection's fork)
+    auto xa_beside = [&](int e, const qb_lora_prod& P, const void* x, int cols, bool forked) -> int {
+        if (!m->fork) return lora_xa(m, s, P, x, cols, &split, k);
+        cudaEvent_t* ev = &m->lev[8 * layer + 2 * e];
+        if (!forked) {
+            QB_CUDA(cudaEventRecord(ev[0], st));
+            QB_CUDA(cudaStreamWaitEvent(m->side, ev[0], 0));
         }
-        if (!rc && A.inp.b2 && L.kind == QB_LAYER_DELTA) {
-            rc = qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b2, 2 * LV_HEADS, A.inp.tab2, m->tok_slot,
-                             m->slot_scale, n, m->ba, 2 * LV_HEADS, R); k++;
+        QB_TRY(lora_xa(m, (void*)m->side, P, x, cols, &split, k));
+        QB_CUDA(cudaEventRecord(ev[1], m->side));
+        return QB_OK;
+    };
+    auto join = [&](int e) -> int {
+        if (m->fork) QB_CUDA(cudaStreamWaitEvent(st, m->lev[8 * layer + 2 * e + 1], 0));
+        return QB_OK;
+    };
+    if (A.inp.a && L.kind != QB_LAYER_DELTA) QB_TRY(xa_beside(0, A.inp, m->xn, H, false));
+    QB_TRY(launch_in_proj(m, st, layer, true, false, k));
+    if (A.inp.a) {
+        const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
+        if (L.kind == QB_LAYER_DELTA) QB_TRY(xa_beside(0, A.inp, m->xn, H, true));  // behind the 16-bit product there
+        QB_TRY(join(0));
+        if (A.inp.b) {
+            QB_TRY(qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b, rows, A.inp.tab, m->tok_slot,
+                               m->slot_scale, n, m->part, rows, R)); k++;
+        }
+        if (A.inp.b2 && L.kind == QB_LAYER_DELTA) {
+            QB_TRY(qb_lora_add(c, s, m->lpart, split, A.inp.a_tiles * 16, A.inp.b2, 2 * LV_HEADS, A.inp.tab2, m->tok_slot,
+                               m->slot_scale, n, m->ba, 2 * LV_HEADS, R)); k++;
         }
     }
-    if (!rc) rc = launch_mixer(m, st, layer, k);
-    m->fork = fork;
-    QB_TRY(rc);
+    QB_TRY(launch_mixer(m, st, layer, k));
+    if (A.out.a) QB_TRY(xa_beside(1, A.out, m->mix, MIX, false));
     QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     if (A.out.a) {
-        QB_TRY(lora_xa(m, s, A.out, m->mix, MIX, &split, k));
+        QB_TRY(join(1));
         QB_TRY(qb_lora_add(c, s, m->lpart, split, A.out.a_tiles * 16, A.out.b, H, A.out.tab, m->tok_slot, m->slot_scale, n,
                            m->part, H, R)); k++;
     }
     QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
     if (A.gate_up.a) {
+        QB_TRY(xa_beside(2, A.gate_up, m->xn, H, false));
         QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->lgu, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
-        QB_TRY(lora_xa(m, s, A.gate_up, m->xn, H, &split, k));
+        QB_TRY(join(2));
         QB_TRY(qb_lora_silu(c, s, m->lpart, split, A.gate_up.a_tiles * 16, A.gate_up.b, 2 * FF, A.gate_up.tab, m->tok_slot,
                             m->slot_scale, n, m->lgu, 2 * FF, m->mid, R)); k++;
     } else {
         QB_TRY(qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr, nullptr, 0)); k++;
     }
+    if (A.down.a) QB_TRY(xa_beside(3, A.down, m->mid, FF, false));
     QB_TRY(qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     if (A.down.a) {
-        QB_TRY(lora_xa(m, s, A.down, m->mid, FF, &split, k));
+        QB_TRY(join(3));
         QB_TRY(qb_lora_add(c, s, m->lpart, split, A.down.a_tiles * 16, A.down.b, H, A.down.tab, m->tok_slot, m->slot_scale,
                            n, m->part, H, R)); k++;
     }
@@ -438,6 +459,7 @@ void qb_model_destroy(qb_model* m) {
     if (!m) return;
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
     for (auto& e : m->ev) cudaEventDestroy(e);
+    for (auto& e : m->lev) cudaEventDestroy(e);
     if (m->side) cudaStreamDestroy(m->side);
     if (m->h_chain) cudaFreeHost(m->h_chain);
     if (m->h_sparams) cudaFreeHost(m->h_sparams);
@@ -917,6 +939,8 @@ int qb_model_set_adapter(qb_model* m, int layer, const qb_lora_layer* lora) {
             // A x of the widest input (17 splits of 1024 columns) and the plain [gate; up] product of a whole step
             QB_TRY(dalloc(&m->lpart, (size_t)17 * MAX_TOK * 256));
             QB_TRY(dalloc(&m->lgu, (size_t)MAX_TOK * 2 * FF));
+            m->lev.resize((size_t)8 * m->nlayers);
+            for (auto& e : m->lev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         }
         L.lora = *lora;
         L.has_lora = true;

@@ -2,7 +2,7 @@
 
     python -m qwenny_b200.microbench gemv N K [--rows 5] [--epi plain|silu|argmax] [--reps 24] [--tune cg,kg,stages,ctas]
     python -m qwenny_b200.microbench attn [--context 32000] [--rows 5] [--reps 20]
-    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--chain]
+    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--chain] [--lora 16]
     python -m qwenny_b200.microbench prefill [--layers 64] [--prompt 32768] [--chunk 2048]
     python -m qwenny_b200.microbench delta [--rows 2048 | --rows 5]
     python -m qwenny_b200.microbench draft [--k 4] [--draft-rows 65536]
@@ -136,6 +136,9 @@ def step(args):
     m.use_chain(args.chain)
     m.use_fork(not args.no_fork)
     m.use_fused_norm(args.fused_norm)
+    if args.lora:  # a LoRA of that rank on every product of every layer; the step's slot uses it
+        M.synthetic_adapter(m, rank=args.lora)
+        m.set_slot_scale(0, 2.0)
     toks = [(1000 + i, 0, args.context + i) for i in range(args.rows)]
     out = list(range(args.rows)) if args.rows <= 16 else [args.rows - 1]  # a prompt chunk wants its last row only
     for _ in range(2):
@@ -148,7 +151,7 @@ def step(args):
     e1.record(m.stream)
     tok = m.argmax()
     ms = e0.elapsed_time(e1) / args.steps
-    print(f"step layers={args.layers} rows={args.rows} context={args.context}: {ms * 1e3:.1f} us/step, "
+    print(f"step layers={args.layers} rows={args.rows} context={args.context} lora={args.lora}: {ms * 1e3:.1f} us/step, "
           f"{m.step_kernels} kernels, greedy {tok}, device error {ctx.device_error()}")
 
 
@@ -418,6 +421,7 @@ def main():
     c.add_argument("--no-fork", action="store_true", help="the 16-bit in-projection in line instead of on a second stream")
     c.add_argument("--fused-norm", action="store_true", help="residual + RMSNorm inside the products around them")
     c.add_argument("--chain", action="store_true", help="the persistent layer kernel instead of separate launches")
+    c.add_argument("--lora", type=int, default=0, help="rank of an unmerged LoRA on every layer (0: none)")
     c.set_defaults(fn=step)
     f = sub.add_parser("prefill")
     f.add_argument("--layers", type=int, default=64); f.add_argument("--prompt", type=int, default=32768)
