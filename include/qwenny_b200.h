@@ -108,6 +108,16 @@ int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, c
 int qb_gemm_f16_unnormed(qb_ctx* ctx, void* stream, const void* W, const void* X, int K, int ntiles, int n, int kper,
                          float* Y, int ldy, float eps);
 
+/* The dense products of checkpoints that are not int4 (gemm_{f16,i8}_t*_{plain,silu,argmax}, kernels/gemm.cuh:118-304;
+ * Gemm::run_split, src/cuda/core.rs:532-560): W in the reference's tile form, wbits 16 (qb_pack_f16, S NULL) or 8
+ * (qb_pack_i8: codes q + 128 and f32 scales [tile][K / 128][16 rows]); epi as qb_marlin_gemm. Plain: Y f32
+ * [K / kper splits][n][ldy] partial sums; SwiGLU: Y f16 [n][ldy] (ldy >= ntiles * 8); argmax: Y f32 [n][ldy] + keys;
+ * the last two need kper == K. qb_pack_i8: Mat::new with int8 (pack, src/cuda/core.rs:337-372): host f32
+ * [rows][cols] -> codes [n / 16 tiles][16 * cols] and scales, rows taken in h_order (NULL: as they are). */
+int qb_gemm_dec(qb_ctx* ctx, void* stream, const void* W, const float* S, int wbits, const void* X, const int* xrows,
+                int K, int ntiles, int n, int kper, int epi, void* Y, int ldy, unsigned long long* keys);
+int qb_pack_i8(const float* h_w, int rows, int cols, const int* h_order, int n, uint8_t* h_out, float* h_scales);
+
 /* ---- per-token kernels. n = tokens of the step (grid size in the reference's launches).
  * qb_embed        embed, kernels/dense.cuh:6-11 (src/cuda/qwen/mod.rs:612-621): out f32 [n][5120] = E bf16 rows;
  *                 clears keys[0..nkeys)

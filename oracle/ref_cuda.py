@@ -137,6 +137,14 @@ class RefModule:
             C.c_int(K // split), _ptr(y), C.c_int(tiles * 16), _ptr(None)])
         return split
 
+    def gemm_dec(self, wt, epi, w_packed, scales, x, y, n, K, tiles, kper, ldy, keys=None, xrows=None):
+        """Gemm::run_split at a decode-sized step (src/cuda/core.rs:532-560) for a 16-bit ("f16") or int8 ("i8") matrix:
+        4 tiles per block, K / kper splits; epi "plain" | "silu" | "argmax"."""
+        tt = next(t for t in (8, 16, 32) if n <= t)
+        self.launch(f"gemm_{wt}_t{tt}_{epi}", (-(-tiles // 4), K // kper, 1), 128, 0, [
+            _ptr(w_packed), _ptr(scales), _ptr(x), _ptr(xrows), C.c_int(K), C.c_int(tiles), C.c_int(n), C.c_int(kper),
+            _ptr(y), C.c_int(ldy), _ptr(keys)])
+
     # ------------------------------------------------------------------------------------------ dense kernels
     def embed(self, table, ids, out, keys, nkeys, n):
         self.launch("embed", (n,), 256, 0, [_ptr(table), _ptr(ids), _ptr(out), _ptr(keys), C.c_int(nkeys)])

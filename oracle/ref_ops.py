@@ -593,3 +593,39 @@ def lora_silu(y, delta):
     v = v.reshape(n, rows // 16, 2, 8)
     g, u = v[:, :, 0, :], v[:, :, 1, :]
     return ((g / (1.0 + np.exp(-g.astype(np.float64)))) * u).reshape(n, rows // 2).astype(np.float16)
+
+
+# ------------------------------------------------------------------------------------------------- int8 dense weights
+def quant_i8(w: np.ndarray):
+    """The int8 form of a 16-bit matrix (pack with int8, src/cuda/core.rs:349-363): per row and group of 128 columns
+    scale = max |w| / 127 (1 for an all-zero group), codes round-half-away(w / scale) clamped to +-127.
+    Returns (q int32 [rows][cols], scale f32 [rows][cols / 128])."""
+    rows, cols = w.shape
+    g = w.astype(np.float32).reshape(rows, cols // 128, 128)
+    mx = np.abs(g).max(-1)
+    scale = np.where(mx > 0, (mx / np.float32(127.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    v = (g / scale[..., None]).astype(np.float32)
+    q = np.clip(np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), -127, 127).astype(np.int32)
+    return q.reshape(rows, cols), scale
+
+
+def pack_i8(w: np.ndarray, order: np.ndarray | None = None):
+    """Codes q + 128 in tiles of 16 rows, mma A-fragment order, two k16 steps per 16-byte load of a lane (frags_int8,
+    src/cuda/core.rs:233-244): uint8 [tiles][cols/32][32 lanes][2][8]; scales f32 [tiles][cols/128][16 rows]."""
+    if order is not None:
+        w = w[order]
+    rows, cols = w.shape
+    q, scale = quant_i8(w)
+    a = (q + 128).astype(np.uint8).reshape(rows // 16, 16, cols // 32, 2, 16).transpose(0, 2, 3, 1, 4)  # [tile][k32][ks][r][c]
+    r, c = frag_map()
+    codes = a[:, :, :, r, c]  # [tile][k32][ks][lane][8]
+    codes = np.ascontiguousarray(codes.transpose(0, 1, 3, 2, 4))  # [tile][k32][lane][ks][8]
+    sc = np.ascontiguousarray(scale.reshape(rows // 16, 16, cols // 128).transpose(0, 2, 1))
+    return codes.reshape(rows // 16, 16 * cols), sc
+
+
+def dequant_i8(w: np.ndarray) -> np.ndarray:
+    """The values the int8 product multiplies with: q * scale in float32."""
+    q, scale = quant_i8(w)
+    rows, cols = w.shape
+    return (q.reshape(rows, cols // 128, 128).astype(np.float32) * scale[..., None]).reshape(rows, cols)

@@ -31,6 +31,8 @@ SIGNATURES = {
     "qb_static_scratch_bytes": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
     "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
+    "qb_gemm_dec": [P, P, P, P, I, P, P, I, I, I, I, I, P, I, P],
+    "qb_pack_i8": [P, I, I, P, I, P, P],
     "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
     "qb_draft_pick": [P, P, P, P, I, P, P, I, I],
     "qb_lora_add": [P, P, P, I, I, P, I, P, P, P, I, P, I, I],

@@ -2,6 +2,7 @@
 // reads. Load-time code, multi-threaded over the k16 steps / tiles as the reference's is.
 #include <cuda_fp16.h>
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -117,6 +118,45 @@ int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n,
                     *o++ = f16_bits(h_w[(size_t)row * cols + rc[e][1]]);
                 }
             }
+    });
+    (void)rows;
+    return QB_OK;
+}
+
+// int8 weights of a 16-bit matrix in the reference's device form (pack with int8, src/cuda/core.rs:337-372,
+// frags_int8 :233-244): per row and group of 128 columns scale = max |w| / 127 (1 for an all-zero group), codes
+// round(w / scale) clamped to +-127 and stored + 128; tiles of 16 rows in mma A-fragment order, two k16 steps per
+// 16-byte load of a lane; scales f32 [tile][group][16 rows].
+int qb_pack_i8(const float* h_w, int rows, int cols, const int* h_order, int n, uint8_t* h_out, float* h_scales) {
+    if (!h_w || !h_out || !h_scales || n % 16 || cols % 128) return QB_ERR_ARG;
+    const int groups = cols / 128;
+    parallel_for(n / 16, [&](int tile) {
+        std::vector<uint8_t> q((size_t)16 * cols);
+        float* st = h_scales + (size_t)tile * groups * 16;
+        for (int r = 0; r < 16; r++) {
+            const int pr = tile * 16 + r;
+            const float* row = h_w + (size_t)(h_order ? h_order[pr] : pr) * cols;
+            for (int gi = 0; gi < groups; gi++) {
+                float mx = 0.f;
+                for (int c = 0; c < 128; c++) mx = std::max(mx, std::fabs(row[gi * 128 + c]));
+                const float scale = mx > 0.f ? mx / 127.f : 1.f;
+                st[gi * 16 + r] = scale;
+                for (int c = 0; c < 128; c++) {
+                    float v = std::round(row[gi * 128 + c] / scale);
+                    v = std::min(127.f, std::max(-127.f, v));
+                    q[(size_t)r * cols + gi * 128 + c] = (uint8_t)((int)v + 128);
+                }
+            }
+        }
+        uint8_t* o = h_out + (size_t)tile * 16 * cols;
+        for (int k32 = 0; k32 < cols / 32; k32++)
+            for (int lane = 0; lane < 32; lane++)
+                for (int ks = 0; ks < 2; ks++) {
+                    const int g = lane / 4, t = lane % 4, c = k32 * 32 + ks * 16 + 2 * t;
+                    const int rc[8][2] = {{g, c}, {g, c + 1}, {g + 8, c}, {g + 8, c + 1},
+                                          {g, c + 8}, {g, c + 9}, {g + 8, c + 8}, {g + 8, c + 9}};
+                    for (int e = 0; e < 8; e++) *o++ = q[(size_t)rc[e][0] * cols + rc[e][1]];
+                }
     });
     (void)rows;
     return QB_OK;

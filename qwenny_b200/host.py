@@ -67,6 +67,19 @@ def pack_f16(w: np.ndarray, order: np.ndarray | None = None) -> np.ndarray:
     return out.view(np.float16)
 
 
+def pack_i8(w: np.ndarray, order: np.ndarray | None = None) -> tuple[np.ndarray, np.ndarray]:
+    """f32 [rows][cols] -> (uint8 [rows/16][16 * cols] codes in fragment order, f32 [rows/16][cols/128][16] scales)."""
+    rows, cols = w.shape
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n = rows if order is None else len(order)
+    out = np.empty((n // 16, 16 * cols), dtype=np.uint8)
+    sc = np.empty((n // 16, cols // 128, 16), dtype=np.float32)
+    o = None if order is None else np.ascontiguousarray(order, dtype=np.int32)
+    check(lib().qb_pack_i8(_np(w), rows, cols, C.c_void_p(0) if o is None else _np(o), n, _np(out), _np(sc)),
+          "qb_pack_i8")
+    return out, sc
+
+
 def split_for(tiles: int, cols: int, bits: int, kd: int) -> int:
     return lib().qb_split_for(tiles, cols, bits, kd)
 

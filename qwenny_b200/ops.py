@@ -108,6 +108,11 @@ class Context:
         check(lib().qb_draft_pick(self.h, _stream(), _p(keys), _p(head_ids), n_out, _p(next_ids), _p(chain), chain_ld, t),
               "qb_draft_pick")
 
+    def gemm_dec(self, w, scales, wbits, x, K, ntiles, n, kper, epi, y, ldy, keys=None, xrows=None):
+        """The dense 16-bit / int8 products (Gemm::run_split); epi: 0 plain, 1 SwiGLU, 2 argmax."""
+        check(lib().qb_gemm_dec(self.h, _stream(), _p(w), _p(scales), wbits, _p(x), _p(xrows), K, ntiles, n, kper, epi,
+                                _p(y), ldy, _p(keys)), "qb_gemm_dec")
+
     def lora_add(self, xa, split, M, B, rows, tab, tok_slot, slot_scale, n, y, ldy, rank):
         check(lib().qb_lora_add(self.h, _stream(), _p(xa), split, M, _p(B), rows, _p(tab), _p(tok_slot), _p(slot_scale),
                                 n, _p(y), ldy, rank), "qb_lora_add")

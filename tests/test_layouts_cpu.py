@@ -90,3 +90,20 @@ def test_pack_marlin_with_zero_points_matches_oracle():
     o = np.arange(rows)
     at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8
     assert np.array_equal(s16[cols // 128:][:, at].T.astype(np.float64), off)
+
+
+def test_pack_i8_matches_oracle():
+    """The library's int8 packer against the oracle's restatement of the reference's (quantisation per row and 128
+    columns, fragment order with two k16 steps per load, scales per tile and group), with a row order and an
+    all-zero group."""
+    g = np.random.default_rng(11)
+    w = (g.standard_normal((64, 384)) * 0.05).astype(np.float32)
+    w[5, 128:256] = 0
+    w[7, 3] = 1.0  # an outlier sets its group's scale
+    order = host.row_order(64, True)
+    codes, sc = host.pack_i8(w, order)
+    oc, os_ = R.pack_i8(w, order)
+    assert np.array_equal(codes, oc) and np.array_equal(sc, os_)
+    q, scale = R.quant_i8(w)
+    assert np.abs(q).max() == 127 and scale[5, 1] == 1.0 and np.all(q[5, 128:256] == 0)
+    assert np.abs(R.dequant_i8(w) - w).max() <= scale.max() * 0.5 + 1e-7
