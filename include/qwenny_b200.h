@@ -159,7 +159,10 @@ int qb_lora_silu(qb_ctx* ctx, void* stream, const float* xa, int split, int M, c
  *                  the host's uniform numbers; params f32 [n_out][8] = temperature, top_k, top_p, repetition penalty,
  *                  u1, u2, draft (-1: none; d <= -2: the draft -d - 2 drawn by qb_draft_sample), presence penalty.
  *                  out_tok[row] = token, out_acc[row] = draft accepted, or -1: the row needs more candidates than
- *                  QB_QCAP (top_k 0 or above it) and is the host's, as in the reference. seen / outs: vocab / 32 words
+ *                  QB_QCAP and is the host's, as in the reference (top_k above QB_QCAP; top_k 0 without a top-p cut).
+ *                  A top_k 0 row WITH a top-p cut is made here when the cut falls among the QB_QCAP most likely tokens
+ *                  (the mass of the whole vocabulary is summed on the device), and comes back -1 only otherwise: the
+ *                  reference sends every such row to the host, a full sort of the vocabulary per row. seen / outs: vocab / 32 words
  *                  per slot. Tokens are those of the reference kernel, draw for draw.
  * qb_draft_sample  draft_sample, kernels/sampling.cuh:298-352 (Step::draft_sample, src/cuda/core.rs:1036-1073): a
  *                  draft per row of a draft step from its `width` logits (rows ld apart; column i is token

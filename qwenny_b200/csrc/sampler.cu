@@ -11,6 +11,10 @@
 // that block sorts them and draws. The arithmetic of the draw (exp of (v - vmax) / temperature, the shape of the
 // prefix sums, every comparison) is the reference kernel's, so the tokens are identical draw for draw.
 //
+// Rows over the whole vocabulary (top_k 0) with a top-p cut, the common serving setting, are the host's in the reference
+// (a full sort of 248,320 values per row and step). Here the blocks also sum the mass of all tokens, the cut is made
+// among the 1024 most likely ones against that mass, and only a row whose cut lies beyond them goes to the host.
+//
 // Equal logits rank by index, exactly: when more values tie at the k-th place than the candidate list holds, the
 // blocks take the first of them in index order (the reference's list keeps whichever its atomics reach first).
 #include "common.cuh"
@@ -140,7 +144,7 @@ __global__ void __launch_bounds__(STH, 1) sampler_kernel(const SamplerArgs a) {
     const int top_k = (int)pr[1];
     const int row_tok = a.out_rows[j], slot = a.tok_slot[row_tok];
     int draft = -1, qrow = -1, first = 0, t = 0, k;
-    bool greedy = false;
+    bool greedy = false, wide = false;
     if (DRAFT) {
         t = (int)pr[5];
         k = min(top_k > 0 ? min(top_k, a.W) : QCAP, QCAP);
@@ -153,11 +157,14 @@ __global__ void __launch_bounds__(STH, 1) sampler_kernel(const SamplerArgs a) {
             if (tt < QD && a.qtok[q] == draft && a.qn[q] > 0) qrow = q;
         }
         greedy = temp <= 0.f || top_k == 1;
-        if (!greedy && (top_k == 0 || top_k > QCAP)) {  // more candidates than a block sorts: the host's row
+        // top_k 0 (the whole vocabulary) with a top-p cut: the cut is made among the QCAP most likely tokens against
+        // the mass of ALL tokens, when it falls there (it does unless the distribution is nearly flat)
+        wide = !greedy && top_k == 0 && top_p < 1.f;
+        if (!greedy && !wide && (top_k == 0 || top_k > QCAP)) {  // more candidates than a block sorts: the host's row
             if (rank == 0 && tid == 0) a.out_acc[j] = -1;
             return;
         }
-        k = greedy ? 1 : min(top_k, a.W);
+        k = greedy ? 1 : wide ? min(QCAP, a.W) : min(top_k, a.W);
     }
 
     // ---- this block's slice: penalised logits as order-preserving keys, read once
@@ -216,6 +223,40 @@ __global__ void __launch_bounds__(STH, 1) sampler_kernel(const SamplerArgs a) {
     }
     if (tid == 0) { S.sv[3] = 0; S.eq = 0; }
     __syncthreads();
+
+    // ---- whole-vocabulary rows: the largest value, then the mass of all tokens at the temperature (the blocks' sums
+    // added in rank order)
+    float zall = 0.f;
+    if (!DRAFT && wide) {
+        unsigned mx = 0;
+        for (int i = tid; i < n_loc; i += STH) mx = max(mx, vals[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) S.wcnt[warp] = mx;
+        __syncthreads();
+        if (warp == 0) {
+            mx = S.wcnt[lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) S.sv[10] = mx;
+        }
+        cluster_sync();
+        if (warp == 0) {
+            mx = lane < SCL ? cluster_ld_u32(cluster_map(&S.sv[10], lane)) : 0u;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) S.sv[11] = mx;
+        }
+        __syncthreads();
+        const float vm = unordered(S.sv[11]);
+        float z = 0.f;
+        for (int i = tid; i < n_loc; i += STH) z += __expf((unordered(vals[i]) - vm) / temp);
+        z = block_sum(z, S.sh);
+        if (tid == 0) S.sh[36] = z;
+        cluster_sync();
+        if (rank == 0)
+            for (int r = 0; r < SCL; r++) zall += __uint_as_float(cluster_ld_u32(cluster_map(&S.sh[36], r)));
+    }
 
     // ---- greedy rows: the argmax of the penalised logits, ties to the lower index
     if (!DRAFT && greedy) {
@@ -372,7 +413,11 @@ __global__ void __launch_bounds__(STH, 1) sampler_kernel(const SamplerArgs a) {
     if (tid == k - 1) S.sh[32] = cum;
     if (tid == 0) S.sv[4] = k;
     __syncthreads();
-    const float total = S.sh[32];
+    const float total = wide ? zall : S.sh[32];
+    if (wide && !(S.sh[32] / total >= top_p)) {  // the cut lies beyond the candidates: the host's row
+        if (tid == 0) a.out_acc[j] = -1;
+        return;
+    }
     if (top_p < 1.f && tid < k && cum / total >= top_p) atomicMin(&S.sv[4], (unsigned)tid + 1);
     __syncthreads();
     const int keep = S.sv[4];

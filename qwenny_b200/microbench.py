@@ -212,8 +212,8 @@ def sampler(args):
     V, n, QD, QCAP = 248320, args.rows, 16, 1024
     g = torch.Generator(device="cuda").manual_seed(3)
     W = args.draft_rows or V
-    logits = torch.randn(n, W, generator=g, device="cuda") * 2
-    logits[:, ::9973] += 6
+    logits = torch.randn(n, W, generator=g, device="cuda") * (1 if args.top_k == 0 else 2)
+    logits[:, ::9973] += 14 if args.top_k == 0 else 6  # top_k 0: as peaked as a language model's, the cut among the candidates
     out_rows = torch.arange(n, dtype=torch.int32, device="cuda")
     tok_slot = torch.zeros(n, dtype=torch.int32, device="cuda")
     ids = torch.randint(0, V, (n,), generator=g, device="cuda", dtype=torch.int32)

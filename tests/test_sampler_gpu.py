@@ -254,6 +254,9 @@ def test_equal_logits_rank_by_index(ctx):
         assert tok == [host, host] and acc == [0, 0] and abs(host - want) <= 1
     tok, acc = rows.mine(ctx, np.array([[1, 0, 1, 1, 0.3, 0, -1, 0], [1, 2000, 1, 1, 0.3, 0, -1, 0]], dtype=F))
     assert acc == [-1, -1]
+    # top_k 0 with a top-p cut over a flat row: the cut lies far beyond the 1024 candidates, the host's row too
+    tok, acc = rows.mine(ctx, np.array([[1, 0, 0.9, 1, 0.3, 0, -1, 0]] * 2, dtype=F))
+    assert acc == [-1, -1]
     # ties below distinct values: three large logits, then the flat rest
     lg = np.zeros((2, V), dtype=F)
     lg[:, [70000, 5, 200000]] = [3.0, 2.0, 1.0]
@@ -372,7 +375,7 @@ def test_model_sampling_and_sampled_draft_chain(ctx, draft_rows):
             r = S.params_row(temp, k, p, rep, pres, rng)
             got = m.sample([r])[0]
             t, a, margin = S.sample_row(lg, seen, genb, r, want_margin=True)
-            if k == 0 or k > QCAP:
+            if (k == 0 and p >= 1.0) or k > QCAP:
                 assert got == (t, a)  # a host row: the host definition's arithmetic, no allowance
             else:
                 near += check_host(got[0], got[1], (t, a), margin, f"{(temp, k, p, rep, pres)}")
@@ -433,3 +436,37 @@ def test_model_sampling_and_sampled_draft_chain(ctx, draft_rows):
                     break
     assert near <= 1
     m.close()
+
+
+def test_whole_vocabulary_rows_with_a_top_p_cut(ctx):
+    """top_k 0 with top_p < 1 (the reference sends these rows to the host): made on the device when the cut falls among
+    the 1024 most likely tokens, against the mass of the whole vocabulary; the tokens are the host definition's."""
+    rows = Rows(80, whole=True)
+    # logits as peaked as a language model's: a few dozen likely tokens carry the mass, 248,000 unlikely ones the rest
+    g = np.random.default_rng(81)
+    lg = g.standard_normal((2, V)).astype(F)
+    for j in range(2):
+        hot = list(g.integers(0, V, 40)) + rows.hist[j][:6]
+        lg[j, hot] += g.uniform(9, 16, len(hot)).astype(F)
+    rows.logits_h = lg
+    rows.logits.copy_(torch.from_numpy(lg))
+    rng = S.Rng(21)
+    near = device = 0
+    for (temp, p, rep, pres) in [(1.0, 0.95, 1.1, 0.0), (0.7, 0.8, 1.0, 0.0), (1.0, 0.5, 1.3, 1.5), (1.3, 0.9, 1.0, 0.0)]:
+        for it in range(5):
+            d = None
+            if it >= 3:  # with an argmax draft
+                seen, gen = rows.sets(0)
+                d = int(S.ranked(rows.logits_h[0], seen, gen, np.array([temp, 0, p, rep, 0, 0, -1, pres], dtype=F), 2)[1][it - 3])
+            params = np.stack([S.params_row(temp, 0, p, rep, pres, rng, draft=d) for _ in range(2)])
+            tok, acc = rows.mine(ctx, params)
+            for j in range(2):
+                seen, gen = rows.sets(j)
+                t, a, margin = S.sample_row(rows.logits_h[j], seen, gen, params[j], want_margin=True)
+                if acc[j] < 0:
+                    # the host's row: its kept set must indeed be larger than the candidates
+                    assert len(S.kept_dist(rows.logits_h[j], seen, gen, params[j])[1]) > QCAP - 8
+                    continue
+                device += 1
+                near += check_host(tok[j], acc[j], (t, a), margin, f"top_k 0, top_p {p}, row {j}")
+    assert device >= 30 and near <= 1
