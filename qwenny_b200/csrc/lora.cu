@@ -32,95 +32,81 @@ struct LoraArgs {
     __half* mid;
 };
 
-// the block's tokens: their scales, and the sum of xa's partial sums for those that use the adapter
-__device__ __forceinline__ void stage_xa(const LoraArgs& a, int t0, float (*xs)[LMAXM], float* sc) {
-    if (threadIdx.x < LTT) {
-        const int t = t0 + threadIdx.x;
-        sc[threadIdx.x] = t < a.n ? a.slot_scale[a.tok_slot[t]] : 0.f;
-    }
+// One kernel for both forms. A thread owns one output of the block's tile: row o of y (the delta is added in place), or
+// SwiGLU output j of mid, whose gate row og = 16 (j / 8) + j % 8 and up row og + 8 sit in the same 16-row tile of y.
+// Grid (outputs / 256, n / 8).
+template <int R, bool SWIGLU>
+__global__ void __launch_bounds__(256) lora_kernel(const LoraArgs a) {
+    __shared__ float xs[LTT][LMAXM];  // xa of the block's tokens, summed over the splits in split order
+    __shared__ float sc[LTT];         // their slots' scales (0: the token does not use the adapter)
+    pdl_wait();
+    const int t0 = blockIdx.y * LTT, tid = threadIdx.x;
+    if (tid < LTT) sc[tid] = t0 + tid < a.n ? a.slot_scale[a.tok_slot[t0 + tid]] : 0.f;
     __syncthreads();
-    for (int i = threadIdx.x; i < LTT * a.M; i += blockDim.x) {
-        const int tl = i / a.M, c = i - tl * a.M, t = t0 + tl;
+    for (int i = tid; i < LTT * a.M; i += 256) {
+        const int tl = i / a.M, c = i - tl * a.M;
         float v = 0.f;
         if (sc[tl] != 0.f)
-            for (int s = 0; s < a.split; s++) v += a.xa[((size_t)s * a.n + t) * a.M + c];
+            for (int s = 0; s < a.split; s++) v += a.xa[((size_t)s * a.n + t0 + tl) * a.M + c];
         xs[tl][c] = v;
     }
     __syncthreads();
-}
 
-template <int R>
-__device__ __forceinline__ void load_row(const __half* B, int o, float (&b)[R]) {
-    const uint4* p = reinterpret_cast<const uint4*>(B + (size_t)o * R);
+    // a row of B as R floats (128-bit loads), and its product with a token's xa as ONE chain of fused multiply-adds in
+    // rank order: the order the reference's kernels sum in
+    auto row_of = [&](int o, float (&b)[R]) {
+        const uint4* p = reinterpret_cast<const uint4*>(a.B + (size_t)o * R);
 #pragma unroll
-    for (int i = 0; i < R / 8; i++) {
-        const uint4 u = p[i];
-        const __half2* h = reinterpret_cast<const __half2*>(&u);
+        for (int i = 0; i < R / 8; i++) {
+            const uint4 u = p[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 f = __half22float2(h[j]);
-            b[8 * i + 2 * j] = f.x;
-            b[8 * i + 2 * j + 1] = f.y;
+            for (int q = 0; q < 4; q++) {
+                const float2 f = __half22float2(h[q]);
+                b[8 * i + 2 * q] = f.x;
+                b[8 * i + 2 * q + 1] = f.y;
+            }
         }
+    };
+    auto delta = [&](const float (&b)[R], int tl, int off) {
+        const float* x = &xs[tl][off];
+        float d = 0.f;
+#pragma unroll
+        for (int q = 0; q < R; q++) d = fmaf(b[q], x[q], d);
+        return d;
+    };
+
+    const int out = blockIdx.x * 256 + tid;
+    if (!SWIGLU) {
+        bool any = false;
+#pragma unroll
+        for (int tl = 0; tl < LTT; tl++) any |= sc[tl] != 0.f;
+        if (!any || out >= a.rows) return;
+        // the stacked module of this row and its columns of xa
+        const int off = a.tab[4 + (out >= a.tab[0]) + (out >= a.tab[1]) + (out >= a.tab[2])];
+        if (off < 0) return;
+        float b[R];
+        row_of(out, b);
+#pragma unroll
+        for (int tl = 0; tl < LTT; tl++)
+            if (sc[tl] != 0.f) a.y[(size_t)(t0 + tl) * a.ldy + out] += sc[tl] * delta(b, tl, off);
+        return;
     }
-}
-
-template <int R>
-__device__ __forceinline__ float dot(const float (&b)[R], const float* x) {
-    float d = 0.f;
-#pragma unroll
-    for (int j = 0; j < R; j++) d = fmaf(b[j], x[j], d);
-    return d;
-}
-
-// y[t][o] += s_t * B[o] . xa[t][off(o) ..]; grid (rows / 256, n / 8)
-template <int R>
-__global__ void __launch_bounds__(256) lora_add_kernel(const LoraArgs a) {
-    __shared__ float xs[LTT][LMAXM];
-    __shared__ float sc[LTT];
-    pdl_wait();
-    const int t0 = blockIdx.y * LTT;
-    stage_xa(a, t0, xs, sc);
-    bool any = false;
-#pragma unroll
-    for (int i = 0; i < LTT; i++) any |= sc[i] != 0.f;
-    const int o = blockIdx.x * blockDim.x + threadIdx.x;
-    if (!any || o >= a.rows) return;
-    const int mod = (o >= a.tab[0]) + (o >= a.tab[1]) + (o >= a.tab[2]);
-    const int off = a.tab[4 + mod];
-    if (off < 0) return;
-    float b[R];
-    load_row<R>(a.B, o, b);
-#pragma unroll
-    for (int tl = 0; tl < LTT; tl++)
-        if (sc[tl] != 0.f) a.y[(size_t)(t0 + tl) * a.ldy + o] += sc[tl] * dot<R>(b, &xs[tl][off]);
-}
-
-// mid[t][8p + g] = silu(gate + dg) * (up + du) of the plain [gate; up] product y in the SwiGLU row order (16-row tile p:
-// gate rows 8p .. 8p + 7, then their up rows); every token, with or without the adapter. Grid (rows / 2 / 256, n / 8)
-template <int R>
-__global__ void __launch_bounds__(256) lora_silu_kernel(const LoraArgs a) {
-    __shared__ float xs[LTT][LMAXM];
-    __shared__ float sc[LTT];
-    pdl_wait();
-    const int t0 = blockIdx.y * LTT;
-    stage_xa(a, t0, xs, sc);
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= a.rows / 2) return;
-    const int og = 16 * (j / 8) + j % 8, ou = og + 8, offg = a.tab[4], offu = a.tab[5];
+    if (out >= a.rows / 2) return;
+    const int og = 16 * (out / 8) + out % 8, ou = og + 8, offg = a.tab[4], offu = a.tab[5];
     float bg[R], bu[R];
-    if (offg >= 0) load_row<R>(a.B, og, bg);
-    if (offu >= 0) load_row<R>(a.B, ou, bu);
+    if (offg >= 0) row_of(og, bg);
+    if (offu >= 0) row_of(ou, bu);
 #pragma unroll
     for (int tl = 0; tl < LTT; tl++) {
         const int t = t0 + tl;
         if (t >= a.n) break;
         float g = a.y[(size_t)t * a.ldy + og], u = a.y[(size_t)t * a.ldy + ou];
         if (sc[tl] != 0.f) {
-            if (offg >= 0) g += sc[tl] * dot<R>(bg, &xs[tl][offg]);
-            if (offu >= 0) u += sc[tl] * dot<R>(bu, &xs[tl][offu]);
+            if (offg >= 0) g += sc[tl] * delta(bg, tl, offg);
+            if (offu >= 0) u += sc[tl] * delta(bu, tl, offu);
         }
-        a.mid[(size_t)t * (a.rows / 2) + j] = __float2half_rn(silu(g) * u);
+        a.mid[(size_t)t * (a.rows / 2) + out] = __float2half_rn(silu(g) * u);  // every token, as the epilogue rounds it
     }
 }
 
@@ -128,8 +114,8 @@ template <int R>
 int run(qb_ctx* ctx, cudaStream_t st, const LoraArgs& a, bool with_silu) {
     const int per = with_silu ? 512 : 256;
     const dim3 grid((a.rows + per - 1) / per, (a.n + LTT - 1) / LTT);
-    return with_silu ? launch(ctx, lora_silu_kernel<R>, grid, dim3(256), 0, st, a)
-                     : launch(ctx, lora_add_kernel<R>, grid, dim3(256), 0, st, a);
+    return with_silu ? launch(ctx, lora_kernel<R, true>, grid, dim3(256), 0, st, a)
+                     : launch(ctx, lora_kernel<R, false>, grid, dim3(256), 0, st, a);
 }
 
 int dispatch(qb_ctx* ctx, void* stream, LoraArgs a, int rank, bool with_silu) {
