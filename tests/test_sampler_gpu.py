@@ -470,3 +470,34 @@ def test_whole_vocabulary_rows_with_a_top_p_cut(ctx):
                 device += 1
                 near += check_host(tok[j], acc[j], (t, a), margin, f"top_k 0, top_p {p}, row {j}")
     assert device >= 30 and near <= 1
+
+
+def test_many_rows_in_one_launch(ctx, ref):
+    """Twenty logit rows of one sequence (a long verify step: each row's penalties see the step's tokens before it): more
+    clusters than fit the SMs at once, every row the reference kernel's token."""
+    n = 20
+    g = np.random.default_rng(90)
+    lg = (g.standard_normal((n, V)) * 2).astype(F)
+    for j in range(n):
+        lg[j, g.integers(0, V, 10)] += g.uniform(4, 9, 10).astype(F)
+    logits = torch.from_numpy(lg).cuda()
+    ids = torch.from_numpy(g.integers(0, V, n).astype(np.int32)).cuda()
+    out_rows = torch.arange(n, dtype=torch.int32, device="cuda")
+    zeros = torch.zeros(n, dtype=torch.int32, device="cuda")
+    base = Rows(91, whole=False)
+    rng = S.Rng(17)
+    params = np.stack([S.params_row(*SETS[j % len(SETS)][:4], SETS[j % len(SETS)][4], rng) for j in range(n)])
+    p = torch.from_numpy(params).cuda()
+    res = []
+    for fn in ("mine", "theirs"):
+        tok = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        acc = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+        if fn == "mine":
+            ctx.sample_rows(logits, V, n, out_rows, zeros, ids, zeros, base.seen, base.outs, p, base.qtok, base.qn,
+                            base.qid, base.qp, tok, acc)
+        else:
+            ref.sample_rows(logits, out_rows, zeros, ids, zeros, base.seen, base.outs, p, base.qtok, base.qn, base.qid,
+                            base.qp, tok, acc, n)
+        torch.cuda.synchronize()
+        res.append((tok.tolist(), acc.tolist()))
+    assert res[0] == res[1] and -7 not in res[0][0]
