@@ -136,7 +136,7 @@ int qb_mtp_in(qb_ctx* ctx, void* stream, const float* emb, const float* h, const
               const float* pre_e, const float* pre_h, void* y, float eps, int n);
 int qb_draft_pick(qb_ctx* ctx, void* stream, const unsigned long long* keys, const int* head_ids, int n_out,
                   int* next_ids, int* chain, int chain_ld, int t);
-/* ---- a LoRA adapter applied unmerged (f-row 4 of the scope; kernels/lora.cuh, src/cuda/qwen/lora.rs:160-207).
+/* ---- a LoRA adapter applied unmerged (kernels/lora.cuh, src/cuda/qwen/lora.rs:160-207).
  * xa f32 [split][n][M]: the partial sums of the stacked A's product with the step's input (qb_gemm_f16_plain on A
  * packed by qb_pack_f16; M = adapted modules * rank padded to 16, at most 256). B f16 [rows][rank] in the product's row
  * order; tab int[8]: the ends of the stacked modules' rows (3, ascending, unused INT_MAX), one unused, then each
@@ -379,14 +379,14 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
  * graph. Steps with segments longer than 8 tokens (prompt attention) return QB_ERR_UNSUPPORTED. */
 int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
-/* The MTP draft step (f-row 1 of the scope: what turns steps/s into accepted tok/s). qb_model_set_mtp: Mtp::load's
+/* The MTP draft step (what turns steps/s into accepted tok/s). qb_model_set_mtp: Mtp::load's
  * pointers. qb_model_draft: Engine::draft with greedy rows = draft_chains (src/cuda/qwen/mod.rs:870-896): k <=
  * QB_MAX_DRAFTS drafts for each row of h_out, from the hidden states the last qb_model_step left at h_rows; h_drafts
  * host [n_out][k]. */
 int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp);
 int qb_model_draft(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
                    int n_out, int k, int* h_drafts);
-/* The sampler on the step's logits (f-row 2 of the scope).
+/* The sampler on the step's logits.
  * qb_model_set_outputs   Step::set_outputs: the tokens a slot's request generated so far, h_words = vocab_rows / 32
  *                        host words (the presence penalty's set; the seen set is kept by the steps themselves).
  * qb_model_sample        Step::sample (src/cuda/core.rs:977-1005): a token per logit row of the last step under
@@ -404,7 +404,7 @@ int qb_model_sample(qb_model* m, void* stream, const float* h_params, int n_out,
 int qb_model_draft_sampled(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
                            int n_out, int k, const float* h_sampling, const float* h_u, int* h_drafts);
 int qb_model_draft_q(qb_model* m, void* stream, int slot, int t, int* tok, int* n, int* h_ids, float* h_p);
-/* A slot's saved images (f-row 3 of the scope), byte for byte the reference's:
+/* A slot's saved images, byte for byte the reference's:
  * qb_model_kv_bytes / save_kv / load_kv      Model::save_kv / load_kv (src/cuda/qwen/mod.rs:1031-1061): per attention
  *     layer (the MTP's last) and kv head the keys of positions [from, to), the values in blocks of 16 positions, the
  *     two scale rows (Attn::layout, src/cuda/qwen/attn.rs:182-196); from a multiple of 16.

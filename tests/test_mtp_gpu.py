@@ -1,4 +1,4 @@
-"""The MTP draft step (the scope's first "next" row): mtp_in against the reference's kernel and the CPU oracle; the
+"""The MTP draft step: mtp_in against the reference's kernel and the CPU oracle; the
 greedy draft chain through the library's host API (qb_model_draft = Engine::draft with argmax rows) against the CPU
 oracle of the same chain, with the whole output layer and with a draft head."""
 import numpy as np
