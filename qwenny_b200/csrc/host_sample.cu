@@ -61,6 +61,27 @@ void ranked(const float* logits, int n, const Sets& s, const float* row, int k, 
         }
     }
     k = k > 0 ? std::min(k, n) : n;
+    if (k == n && n > 4096) {
+        // the whole vocabulary in order: a stable radix sort of the inverted keys (ascending ~key = descending value;
+        // stable = equal values keep their index order), three passes of 11 bits
+        std::vector<uint32_t> key(n), key2(n);
+        std::vector<int> id(n), id2(n);
+        for (int i = 0; i < n; i++) { key[i] = ~okey(vals[i]); id[i] = i; }
+        for (int shift = 0; shift < 33; shift += 11) {
+            size_t count[2049] = {0};
+            for (int i = 0; i < n; i++) count[((key[i] >> shift) & 2047) + 1]++;
+            for (int b = 0; b < 2048; b++) count[b + 1] += count[b];
+            for (int i = 0; i < n; i++) {
+                const size_t at = count[(key[i] >> shift) & 2047]++;
+                key2[at] = key[i];
+                id2[at] = id[i];
+            }
+            key.swap(key2);
+            id.swap(id2);
+        }
+        idx.swap(id);
+        return;
+    }
     std::vector<uint64_t> keys(n);
     for (int i = 0; i < n; i++) keys[i] = ((uint64_t)okey(vals[i]) << 32) | (0xffffffffu - (uint32_t)i);
     if (k < n) std::nth_element(keys.begin(), keys.begin() + (k - 1), keys.end(), std::greater<uint64_t>());
