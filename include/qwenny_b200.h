@@ -29,8 +29,7 @@ extern "C" {
 typedef struct qb_ctx qb_ctx;
 
 /* Epilogues of a matrix product: src/cuda/core.rs:58-64 (enum Epi). */
-enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2,
-       QB_EPI_RESID = 3 /* qb_marlin_gemm_fused only: Y is the residual stream, added to in place */ };
+enum { QB_EPI_PLAIN = 0, QB_EPI_SILU = 1, QB_EPI_ARGMAX = 2 };
 
 /* ---- context: what Gemm::load allocates once (src/cuda/core.rs:437-464: SM count, Marlin's `red` and `locks`).
  * Allocates the split-K scratch and tickets on `device`; everything after creation is allocation-free. Like the
@@ -60,23 +59,6 @@ int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void
  * the group's sum of x, which the kernel has anyway. More than 16 rows run as 16-row slabs. */
 int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                      int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
-/* The residual add and RMSNorm between two products folded into them (steps of up to 16 rows): replaces the pairs
- * Gemm::marlin + Stack::add_rmsnorm of launch_step (src/cuda/qwen/mod.rs:744-766; kernels/dense.cuh:12-26) without a
- * launch of their own. RMSNorm is linear up to the row's 1 / rms, so the product after a norm runs on the un-normalised
- * row and scales its result:
- *   epi == QB_EPI_RESID  Y is the f32 residual stream [m][n] (in / out): Y += X . W^T; xu_out f16 [m][n] gets
- *                        f16(norm_w_out[c] * Y[t][c]) (the next product's input, NOT yet divided by the rms), and the
- *                        context keeps, per 64 outputs, the sums of squares of the new rows;
- *   x_unnormed != 0      X is such an xu (of the last QB_EPI_RESID product on this context; its n is this k): row t of
- *                        the result is multiplied by rsqrt(mean(Y[t]^2) + eps) before the epilogue (plain, SwiGLU or
- *                        argmax). The rounding to f16 happens before the division by the rms instead of after it
- *                        (same relative precision; |norm_w * h| must stay inside the f16 range). */
-int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
-                         int k, int epi, const int* xrows, unsigned long long* keys, int n_valid,
-                         const float* norm_w_out, void* xu_out, int x_unnormed, float eps);
-/* Tuning knob for measurements: fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the
- * next qb_marlin_gemm calls; zeros restore the built-in choice. */
-int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
 
 /* qb_marlin_gemm without a context and without any allocation, for callers that cannot call cudaMalloc (an engine
  * that gave all free device memory to its cache pool, a plugin in a process whose allocator it does not own). It has
@@ -91,23 +73,12 @@ int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B, void* Y, 
                            int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 int qb_static_scratch_bytes(void);
 
-/* Measurement only: the following qb_marlin_gemm calls write per-block timestamps (ns of the global timer: start,
- * first stage landed, last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`. */
-int qb_marlin_trace(qb_ctx* ctx, long long* buf);
-/* Measurement only: mode 1 makes the products' consumers release every stage unread, so a launch times the copy
- * pipeline alone (its results are meaningless); 0 restores the product. */
-int qb_marlin_probe(qb_ctx* ctx, int mode);
-
 /* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
  * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it
  * (src/cuda/core.rs:532-560): W in mma A-fragment order (qb_pack_f16), X f16 [.][K] (rows xrows[t] if given),
  * Y f32 [K/kper splits][n][ldy] partial products which the consumer sums (any n: blocks of 32 tokens). */
 int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
                       int n, int kper, float* Y, int ldy);
-/* the same product on the un-normalised rows of a QB_EPI_RESID product (n <= 16): results scaled by 1 / rms */
-int qb_gemm_f16_unnormed(qb_ctx* ctx, void* stream, const void* W, const void* X, int K, int ntiles, int n, int kper,
-                         float* Y, int ldy, float eps);
-
 /* The dense products of checkpoints that are not int4 (gemm_{f16,i8}_t*_{plain,silu,argmax}, kernels/gemm.cuh:118-304;
  * Gemm::run_split, src/cuda/core.rs:532-560): W in the reference's tile form, wbits 16 (qb_pack_f16, S NULL) or 8
  * (qb_pack_i8: codes q + 128 and f32 scales [tile][K / 128][16 rows]); epi as qb_marlin_gemm. Plain: Y f32
@@ -224,33 +195,6 @@ int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, c
                     const float* vs, const int* ptile, const int* tok_slot, const int* tok_pos, int cap, int ntile,
                     int max_keys, float* part_ml, float* part_acc, float* out, void* mix_f16);
 int qb_attn_tile_splits(int ntile, int max_keys);
-
-/* ---- One launch for a layer's weight-streaming tail (decode / verify steps of up to qb_layer_chain_max_rows() = 7
- * token rows): out_proj, h += . and RMSNorm(post_norm), gate_up with SwiGLU, down, h += . and RMSNorm(next_norm), and
- * the NEXT layer's in-projection. Replaces, for such steps, four Gemm::marlin launches and two add_rmsnorm launches of
- * the reference's launch_step (src/cuda/qwen/mod.rs:744-766; Stack::mlp; kernels/marlin.cuh; kernels/dense.cuh:12-26)
- * with one cooperative persistent kernel whose blocks meet at grid barriers; same inputs, same outputs:
- *   mix     f16 [m][6144]  the mixer's output (in)          h     f32 [m][5120] residual stream (in / out)
- *   xn      f16 [m][5120]  RMSNorm(h) * next_norm (out)      part  f32 [m][next_n] the next in-projection (out; unused
- *                                                                  when next_w is NULL: the last layer)
- *   h_tmp, part_h (f32 [m][5120]) and mid (f16 [m][17408]) are scratch. All matrices in the Marlin layout. */
-typedef struct qb_chain {
-    int m;
-    const void* mix;
-    const void *out_w, *out_s;
-    const void *gate_up_w, *gate_up_s;
-    const void *down_w, *down_s;
-    const void *next_w, *next_s;
-    int next_n;
-    const float *post_norm, *next_norm;
-    float *h, *h_tmp, *part_h;
-    void* mid;
-    void* xn;
-    float* part;
-    float eps;
-} qb_chain;
-int qb_layer_chain(qb_ctx* ctx, void* stream, const qb_chain* c);
-int qb_layer_chain_max_rows(void);
 
 /* ---- Gated DeltaNet. Slot memory (sst floats per slot), metadata and the rollback plan are the reference's
  * (kernels/qwen_deltanet.cuh:12-82; host side src/cuda/qwen/deltanet.rs:83-104,181-226).
@@ -431,12 +375,6 @@ int qb_model_use_graphs(qb_model* m, int on);
 int qb_model_use_fused(qb_model* m, int on);
 /* on (default): the DeltaNet layers' 16-bit in-projection runs on a second stream beside the int4 one */
 int qb_model_use_fork(qb_model* m, int on);
-/* on: steps of up to 16 rows use qb_marlin_gemm_fused / qb_gemm_f16_unnormed: no add_rmsnorm launches (default off:
- * measured slower than the separate launches) */
-int qb_model_use_fused_norm(qb_model* m, int on);
-/* on: steps of up to qb_layer_chain_max_rows() tokens run qb_layer_chain between the mixers (default off: measured
- * slower than the separate launches) */
-int qb_model_use_chain(qb_model* m, int on);
 /* Engine::argmax (src/cuda/core.rs:1100-1103): greedy token per logit row of the last step; synchronises the stream */
 int qb_model_argmax(qb_model* m, void* stream, int* h_tokens, int n_out);
 float* qb_model_logits(qb_model* m);   /* device f32 [n_out][vocab_rows] */

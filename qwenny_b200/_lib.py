@@ -23,14 +23,9 @@ SIGNATURES = {
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_gemm_z": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
-    "qb_marlin_gemm_fused": [P, P, P, P, P, P, I, I, I, I, P, P, I, P, P, I, F],
-    "qb_marlin_tune": [P, I, I, I, I],
-    "qb_marlin_trace": [P, P],
-    "qb_marlin_probe": [P, I],
     "qb_marlin_gemm_noalloc": [P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_static_scratch_bytes": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
-    "qb_gemm_f16_unnormed": [P, P, P, P, I, I, I, I, P, I, F],
     "qb_gemm_dec": [P, P, P, P, I, P, P, I, I, I, I, I, P, I, P],
     "qb_pack_i8": [P, I, I, P, I, P, P],
     "qb_mtp_in": [P, P, P, P, P, P, P, P, P, F, I],
@@ -84,11 +79,7 @@ SIGNATURES = {
     "qb_model_hidden": [P],
     "qb_model_xn": [P],
     "qb_model_seen": [P],
-    "qb_layer_chain": [P, P, P],
-    "qb_layer_chain_max_rows": [],
-    "qb_model_use_chain": [P, I],
     "qb_model_use_fork": [P, I],
-    "qb_model_use_fused_norm": [P, I],
     "qb_model_launches": [P],
     "qb_model_step_kernels": [P],
     "qb_pool_create": [I, C.POINTER(P)],
@@ -113,6 +104,13 @@ SIGNATURES = {
     "qb_pack_marlin_z": [P, P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],
     "qb_split_for": [I, I, I, I],
+}
+# measurement-only entry points (declared in csrc/measure.h, not part of the public header)
+MEASURE_SIGNATURES = {
+    "qb_marlin_tune": [P, I, I, I, I],
+    "qb_marlin_trace": [P, P],
+    "qb_marlin_probe": [P, I],
+    "qb_attr_cache_selftest": [],
 }
 _RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
             "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,
@@ -149,15 +147,6 @@ class QbLoraLayer(C.Structure):
     _fields_ = [("rank", I), ("inp", QbLoraProd), ("out", QbLoraProd), ("gate_up", QbLoraProd), ("down", QbLoraProd)]
 
 
-class QbChain(C.Structure):
-    """qb_chain of include/qwenny_b200.h."""
-    _fields_ = [
-        ("m", I), ("mix", P), ("out_w", P), ("out_s", P), ("gate_up_w", P), ("gate_up_s", P), ("down_w", P),
-        ("down_s", P), ("next_w", P), ("next_s", P), ("next_n", I), ("post_norm", P), ("next_norm", P),
-        ("h", P), ("h_tmp", P), ("part_h", P), ("mid", P), ("xn", P), ("part", P), ("eps", F),
-    ]
-
-
 class QbTok(C.Structure):
     _fields_ = [("id", C.c_uint32), ("slot", C.c_uint32), ("pos", C.c_uint32)]
 
@@ -171,7 +160,7 @@ def lib() -> C.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python -m qwenny_b200.build` (there is no CPU fallback)")
         _lib = C.CDLL(LIB_PATH)
-        for name, args in SIGNATURES.items():
+        for name, args in list(SIGNATURES.items()) + list(MEASURE_SIGNATURES.items()):
             fn = getattr(_lib, name)
             fn.argtypes = args
             fn.restype = _RESTYPE.get(name, I)

@@ -820,12 +820,6 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
 #define QB_DEC(RT)                                                                                              \
     {                                                                                                           \
         using C = DecCfg<RT, 4, 4>;                                                                             \
-        static bool opted = false;                                                                              \
-        if (!opted) {                                                                                           \
-            QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<RT, 4, 4, false>,                                   \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));                \
-            opted = true;                                                                                       \
-        }                                                                                                       \
         rc = launch(ctx, attn_decode_kernel<RT, 4, 4, false>, grid, dim3(C::THREADS), C::SMEM, st, q,          \
                     (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, part_ml, \
                     part_acc, out, (__half*)nullptr, ctx->err);                                                 \
@@ -853,22 +847,12 @@ int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, c
     const int z = tile_splits(ntile, max_keys);
     if (z > 1 && (!part_ml || !part_acc)) return QB_ERR_ARG;
     if (z == 1) {  // many tiles: pairs of tiles per block, the stage converted once per block
-        static bool opted_pf = false;
-        if (!opted_pf) {
-            QB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
-            opted_pf = true;
-        }
         return launch(ctx, attn_prefill_kernel, dim3((ntile + 1) / 2, NKV), dim3(PF_WARPS * 32), PF_SMEM,
                       (cudaStream_t)stream, q, (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, ptile, ntile, tok_slot,
                       tok_pos, cap, out, (__half*)mix_f16, ctx->err);
     }
     using C = DecCfg<4, 2, 5>;  // 10 tokens x 6 heads = 60 rows: 4 row tiles; 2 warps each; 5 stages of 32 keys
     static_assert(PTILE * GROUP <= 64, "a prompt tile fills at most 4 row tiles");
-    static bool opted = false;
-    if (!opted) {
-        QB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<4, 2, 5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        opted = true;
-    }
     cudaStream_t st = (cudaStream_t)stream;
     int rc = launch(ctx, attn_decode_kernel<4, 2, 5, true>, dim3(ntile, NKV, z), dim3(C::THREADS), C::SMEM, st, q,
                     (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, ptile, (const int*)nullptr, tok_slot, tok_pos, cap, z,

@@ -1,7 +1,72 @@
 // Context creation and the error word.
 #include "ctx.h"
+#include <array>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace qb {
+
+namespace {
+std::mutex g_attr_mutex;
+std::map<std::pair<int, const void*>, int> g_attr_smem;
+std::map<std::tuple<int, const void*, int>, std::array<int, 9>> g_attr_clusters;
+}  // namespace
+
+bool AttrCache::need(int device, const void* kern, int smem) {
+    std::lock_guard<std::mutex> lock(g_attr_mutex);
+    auto it = g_attr_smem.find({device, kern});
+    if (it == g_attr_smem.end()) {
+        g_attr_smem[{device, kern}] = smem;
+        return true;
+    }
+    if (it->second >= smem) return false;
+    it->second = smem;
+    return true;
+}
+
+int* AttrCache::clusters(int device, const void* kern, int smem) {
+    std::lock_guard<std::mutex> lock(g_attr_mutex);
+    return g_attr_clusters.try_emplace(std::make_tuple(device, kern, smem), std::array<int, 9>{}).first->second.data();
+}
+
+AttrCache& attr_cache() {
+    static AttrCache c;
+    return c;
+}
+
+int prepare_kernel(int device, const void* kern, int smem) {
+    if (!attr_cache().need(device, kern, smem)) return QB_OK;
+    // Every kernel asks for the same L1 / shared-memory split (all shared): the big streaming kernels need it, and an
+    // SM whose split has to change between two kernels drains first, which would undo the overlap of neighbours.
+    QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    if (smem > 48 * 1024) QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    return QB_OK;
+}
+
+}  // namespace qb
 
 extern "C" {
+
+// Host-only check of the per-device attribute bookkeeping (no CUDA call): 0 when two devices each get their own
+// opt-in for the same kernel, a larger request on one device asks again there only, and repeats ask for nothing.
+int qb_attr_cache_selftest(void) {
+    static int k1, k2;  // stand-ins for two kernels
+    qb::AttrCache& c = qb::attr_cache();
+    const int d0 = 1000, d1 = 1001;  // device numbers no real GPU has
+    if (!c.need(d0, &k1, 100000)) return 1;
+    if (c.need(d0, &k1, 100000)) return 2;
+    if (c.need(d0, &k1, 50000)) return 3;
+    if (!c.need(d1, &k1, 100000)) return 4;   // the second device has not been opted in by the first one's call
+    if (!c.need(d0, &k2, 0)) return 5;
+    if (c.need(d0, &k2, 0)) return 6;
+    if (!c.need(d0, &k1, 200000)) return 7;
+    if (c.need(d1, &k1, 100000)) return 8;
+    int* a = c.clusters(d0, &k1, 4096);
+    a[3] = 17;
+    if (c.clusters(d1, &k1, 4096)[3] != 0 || c.clusters(d0, &k1, 4096)[3] != 17) return 9;
+    return 0;
+}
 
 const char* qb_version(void) { return "qwenny_b200 0.1 (sm_100a)"; }
 
@@ -20,11 +85,6 @@ int qb_create(int device, qb_ctx** out) {
     QB_CUDA(cudaMemset(c->counters, 0, c->ncounters * sizeof(int)));
     QB_CUDA(cudaMalloc(&c->err, 64));
     QB_CUDA(cudaMemset(c->err, 0, 64));
-    c->sq_groups = 1024;
-    QB_CUDA(cudaMalloc(&c->sq, c->sq_groups * 16 * sizeof(float)));
-    QB_CUDA(cudaMemset(c->sq, 0, c->sq_groups * 16 * sizeof(float)));
-    QB_CUDA(cudaMalloc(&c->gbar, 64));
-    QB_CUDA(cudaMemset(c->gbar, 0, 64));
     *out = c;
     return QB_OK;
 }
@@ -34,8 +94,6 @@ void qb_destroy(qb_ctx* c) {
     cudaFree(c->scratch);
     cudaFree(c->counters);
     cudaFree(c->err);
-    cudaFree(c->gbar);
-    cudaFree(c->sq);
     delete c;
 }
 

@@ -14,10 +14,6 @@ struct qb_ctx {
     int* counters = nullptr;
     size_t ncounters = 0;
     int* err = nullptr;  // device word
-    float* sq = nullptr;       // sums of squares of the last residual product's rows: [sq_groups][16]
-    size_t sq_groups = 0;
-    unsigned* gbar = nullptr;  // grid-barrier counters of the persistent layer kernel (zero between launches)
-    bool chain_pdl = true;     // that kernel's launch carries the programmatic-dependent-launch attribute too
     // measurement override of the GEMV plan (0: built-in choice)
     int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
     bool no_cluster = false, no_tc = false;
@@ -32,6 +28,26 @@ struct qb_ctx {
         cudaError_t e_ = (x);              \
         if (e_ != cudaSuccess) return (int)e_; \
     } while (0)
+
+namespace qb {
+
+// Kernel attributes (the opt-in to more than 48 KB of dynamic shared memory, the shared-memory carve-out) belong to the
+// device that is current when cudaFuncSetAttribute runs, so what has been set is remembered per (device, kernel), not
+// per process: a process that drives several GPUs opts every kernel in on each of them. AttrCache is the bookkeeping
+// alone (no CUDA call), shared by all host threads behind one mutex.
+class AttrCache {
+  public:
+    // true when `kern` on `device` has not yet been given at least `smem` bytes (or, smem == 0, has not been seen at
+    // all); the new value is recorded, so the caller must then set the attribute
+    bool need(int device, const void* kern, int smem);
+    // the resident-cluster counts the driver reported for (device, kernel, shared memory), filled by the caller
+    int* clusters(int device, const void* kern, int smem);
+};
+AttrCache& attr_cache();
+// sets what `kern` needs on `device` (which must be current) before a launch with `smem` bytes of dynamic shared memory
+int prepare_kernel(int device, const void* kern, int smem);
+
+}  // namespace qb
 
 // the prompt-sized W4A16 product on tcgen05 (w4a16_gemm_tc.cu); reached through qb_marlin_gemm for more than 16 rows
 int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m, int n,

@@ -656,14 +656,7 @@ extern "C" int qb_delta_mixer(qb_ctx* ctx, void* stream, const float* p, int spl
     if (n > qb::CR - qb::CONV_K + 1) return QB_ERR_UNSUPPORTED;
     // the launch's ticket: the last int of the context's ticket array (the products use the first n / 64)
     int* ticket = ctx->counters + ctx->ncounters - 1;
-    static bool opted = false;
-    if (!opted) {
-        QB_CUDA(cudaFuncSetAttribute(qb::delta_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)sizeof(qb::FusedRound)));
-        QB_CUDA(cudaFuncSetAttribute(qb::delta_fused_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     cudaSharedmemCarveoutMaxShared));
-        opted = true;
-    }
+    if (int rc = qb::prepare_kernel(ctx->device, (const void*)qb::delta_fused_kernel, (int)sizeof(qb::FusedRound))) return rc;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(2 * qb::LV_HEADS, segs);
     lc.blockDim = dim3(qb::FNT);

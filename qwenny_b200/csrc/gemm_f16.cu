@@ -11,8 +11,7 @@ namespace qb {
 template <int NTT>
 __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __restrict__ W, const __half* __restrict__ X,
                                                              const int* __restrict__ xrows, int K, int ntiles, int n,
-                                                             int kper, float* __restrict__ Y, int ldy,
-                                                             const float* __restrict__ rs, float eps) {
+                                                             int kper, float* __restrict__ Y, int ldy) {
     __shared__ float4 red[3][NTT][32];
     pdl_launch_dependents();
     const int tile = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -60,26 +59,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
         for (int j = 0; j < NTT; j++) red[warp - 1][j][lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
     }
     __syncthreads();
-    // rs != null: the X rows are un-normalised (f16(w * h)); row t of the result is scaled by 1 / rms(h[t]) from the
-    // sums of squares the residual product left: the partials dealt to the 4 warps in runs, lane = (partial mod 2, row),
-    // the warps' sums added in warp order
-    __shared__ float rsum[4][16];
-    if (rs) {
-        const int r0 = lane & 15, groups = K / 64, per = (groups + 3) / 4;
-        float ss = 0.f;
-        if (tok0 + r0 < n) {
-            const int row = xrows ? xrows[tok0 + r0] : tok0 + r0;
-            const int g0 = warp * per, g1 = min(groups, g0 + per);
-#pragma unroll 8
-            for (int cgp = g0 + (lane >> 4); cgp < g1; cgp += 2) ss += __ldcg(rs + (size_t)cgp * 16 + row);
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-        if (lane < 16) rsum[warp][lane] = ss;
-    }
-    __syncthreads();
     if (warp == 0) {
-        float rall = 1.f;
-        if (rs) rall = rsqrtf((((rsum[0][lane & 15] + rsum[1][lane & 15]) + rsum[2][lane & 15]) + rsum[3][lane & 15]) / K + eps);
         float* y = Y + (size_t)split * n * ldy;
 #pragma unroll
         for (int j = 0; j < NTT; j++) {
@@ -91,8 +71,7 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 int tok = tok0 + 8 * j + 2 * t + (i & 1), r = tile * 16 + g + (i >> 1) * 8;
-                float sc = rs ? __shfl_sync(0xffffffffu, rall, (8 * j + 2 * t + (i & 1)) & 15) : 1.f;
-                if (tok < n) y[(size_t)tok * ldy + r] = acc[j][i] * sc;
+                if (tok < n) y[(size_t)tok * ldy + r] = acc[j][i];
             }
         }
     }
@@ -102,31 +81,17 @@ __global__ void __launch_bounds__(128) gemm_f16_plain_kernel(const uint4* __rest
 
 using namespace qb;
 
-static int gemm_f16_go(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
-                       int n, int kper, float* Y, int ldy, bool unnormed, float eps);
-
 extern "C" int qb_gemm_f16_plain(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K,
                                  int ntiles, int n, int kper, float* Y, int ldy) {
-    return gemm_f16_go(ctx, stream, W, X, xrows, K, ntiles, n, kper, Y, ldy, false, 0.f);
-}
-
-// The same product on un-normalised rows X = f16(w * h) as a QB_EPI_RESID product leaves them: every split's rows are
-// scaled by 1 / rms(h) (see qb_marlin_gemm_fused); n <= 16.
-extern "C" int qb_gemm_f16_unnormed(qb_ctx* ctx, void* stream, const void* W, const void* X, int K, int ntiles, int n,
-                                    int kper, float* Y, int ldy, float eps) {
-    if (!ctx || n > 16 || (size_t)(K / 64) > ctx->sq_groups) return QB_ERR_ARG;
-    return gemm_f16_go(ctx, stream, W, X, nullptr, K, ntiles, n, kper, Y, ldy, true, eps);
-}
-
-static int gemm_f16_go(qb_ctx* ctx, void* stream, const void* W, const void* X, const int* xrows, int K, int ntiles,
-                       int n, int kper, float* Y, int ldy, bool unnormed, float eps) {
     if (!ctx || !W || !X || !Y || K <= 0 || K % 16 || ntiles <= 0 || n <= 0 || n > 65535 * 32 || kper <= 0 || kper % 16 ||
         ldy < ntiles * 16)
         return QB_ERR_ARG;
     int split = (K + kper - 1) / kper;
     dim3 grid(ntiles, split, n <= 32 ? 1 : (n + 31) / 32);
     cudaStream_t st = (cudaStream_t)stream;
-    if (n <= 8) return launch(ctx, gemm_f16_plain_kernel<1>, grid, dim3(128), 0, st, (const uint4*)W, (const __half*)X, xrows, K, ntiles, n, kper, Y, ldy, unnormed ? (const float*)ctx->sq : (const float*)nullptr, eps);
-    if (n <= 16) return launch(ctx, gemm_f16_plain_kernel<2>, grid, dim3(128), 0, st, (const uint4*)W, (const __half*)X, xrows, K, ntiles, n, kper, Y, ldy, unnormed ? (const float*)ctx->sq : (const float*)nullptr, eps);
-    return launch(ctx, gemm_f16_plain_kernel<4>, grid, dim3(128), 0, st, (const uint4*)W, (const __half*)X, xrows, K, ntiles, n, kper, Y, ldy, unnormed ? (const float*)ctx->sq : (const float*)nullptr, eps);
+    const uint4* w = (const uint4*)W;
+    const __half* x = (const __half*)X;
+    if (n <= 8) return launch(ctx, gemm_f16_plain_kernel<1>, grid, dim3(128), 0, st, w, x, xrows, K, ntiles, n, kper, Y, ldy);
+    if (n <= 16) return launch(ctx, gemm_f16_plain_kernel<2>, grid, dim3(128), 0, st, w, x, xrows, K, ntiles, n, kper, Y, ldy);
+    return launch(ctx, gemm_f16_plain_kernel<4>, grid, dim3(128), 0, st, w, x, xrows, K, ntiles, n, kper, Y, ldy);
 }

@@ -2,6 +2,7 @@
 #include "ctx.h"
 #include <array>
 #include <map>
+#include "measure.h"
 #include "w4a16_gemv.cuh"
 
 namespace qb {
@@ -32,23 +33,17 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
     using C = GemvCfg<CG, KG, NT>;
     auto kern = w4a16_gemv_kernel<CG, KG, NT, EPI, ZP>;
     int smem = C::smem(p.nstages, a.m, a.zp);
-    static int opted = 0;  // per instantiation
-    if (opted < smem) {
-        QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        QB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        opted = smem;
-    }
+    if (int rc = prepare_kernel(ctx->device, (const void*)kern, smem)) return rc;
     cudaLaunchConfig_t lc = {};
     cudaLaunchAttribute at[2];
     int nat = 0;
     // Clusters are placed inside one GPC each, so not every rank count packs the GPU in one wave: ask the driver how
-    // many clusters of a size can be resident (cached per kernel, size and shared-memory footprint, so that the answer,
+    // many clusters of a size can be resident (cached per device, kernel, size and shared-memory footprint, so that the answer,
     // and with it the way k is split and summed, depends on the product's shape alone and not on the calls before it)
     // and take the most ranks whose column blocks all fit, then as few as give the same longest share of k stages.
     int cluster_s = 0;
     if (p.cluster_s > 0) {
-        static std::map<int, std::array<int, 9>> asked;  // per instantiation: smem -> resident clusters of size s
-        std::array<int, 9>& fits = asked.try_emplace(smem, std::array<int, 9>{}).first->second;
+        int* fits = attr_cache().clusters(ctx->device, (const void*)kern, smem);  // resident clusters of size s
         const int ncb = a.N / C::TN, kst = a.K / C::TK;
         int s = p.cluster_s;
         for (; s > 1; s--) {
@@ -106,11 +101,9 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
 template <int NT, int EPI>
 static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const GemvPlan& p) {
     if (a.zp) {  // the zero-point variants: the three shapes the built-in choice uses
-        if (EPI == EPI_RESID) return QB_ERR_UNSUPPORTED;
-        constexpr int E = EPI == EPI_RESID ? EPI_PLAIN : EPI;
-        if (p.cg == 2 && p.kg == 4) return launch_cfg<2, 4, NT, E, 1>(ctx, st, a, p);
-        if (p.cg == 4 && p.kg == 2) return launch_cfg<4, 2, NT, E, 1>(ctx, st, a, p);
-        if (p.cg == 4 && p.kg == 1) return launch_cfg<4, 1, NT, E, 1>(ctx, st, a, p);
+        if (p.cg == 2 && p.kg == 4) return launch_cfg<2, 4, NT, EPI, 1>(ctx, st, a, p);
+        if (p.cg == 4 && p.kg == 2) return launch_cfg<4, 2, NT, EPI, 1>(ctx, st, a, p);
+        if (p.cg == 4 && p.kg == 1) return launch_cfg<4, 1, NT, EPI, 1>(ctx, st, a, p);
         return QB_ERR_UNSUPPORTED;
     }
     if (p.cg == 2 && p.kg == 4) return launch_cfg<2, 4, NT, EPI>(ctx, st, a, p);
@@ -181,7 +174,6 @@ extern "C" int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas
 
 static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m,
                      int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid,
-                     const float* nw_out = nullptr, void* xu_out = nullptr, bool unnormed = false, float eps = 0.f,
                      int zp = 0) {
     int nt = m <= 8 ? 1 : 2;
     GemvPlan p = pick(ctx, n, k, m, ctx->tune_cg, ctx->tune_kg, ctx->tune_ctas, zp);
@@ -198,13 +190,11 @@ static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B,
     if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;
     a.zp = zp;
-    a.nw_out = nw_out; a.xu_out = (__half*)xu_out; a.sq = ctx->sq; a.rs = unnormed ? ctx->sq : nullptr; a.eps = eps;
 #define QB_GO(NT)                                                              \
     switch (epi) {                                                             \
         case QB_EPI_PLAIN: return launch_shape<NT, EPI_PLAIN>(ctx, st, a, p);  \
         case QB_EPI_SILU: return launch_shape<NT, EPI_SILU>(ctx, st, a, p);    \
         case QB_EPI_ARGMAX: return launch_shape<NT, EPI_ARGMAX>(ctx, st, a, p);\
-        case QB_EPI_RESID: return launch_shape<NT, EPI_RESID>(ctx, st, a, p);  \
         default: return QB_ERR_ARG;                                            \
     }
     if (nt == 1) { QB_GO(1) } else { QB_GO(2) }
@@ -251,27 +241,11 @@ extern "C" int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const 
     for (int r = 0; r < m; r += 16) {
         int mm = m - r < 16 ? m - r : 16;
         int rc = gemm_rows(ctx, st, X, B, Y, S, mm, n, k, xrows ? 0 : row0 + r, epi, xrows ? xrows + r : nullptr,
-                           keys ? keys + (xrows ? r : 0) : nullptr, n_valid, nullptr, nullptr, false, 0.f, 1);
+                           keys ? keys + (xrows ? r : 0) : nullptr, n_valid, 1);
         if (rc) return rc;
         if (xrows) Y = (char*)Y + (size_t)mm * (epi == QB_EPI_SILU ? n / 2 * 2 : (size_t)n * 4);
     }
     return QB_OK;
-}
-
-// Residual + RMSNorm folded into the products on either side of it (steps of up to 16 rows); see the header.
-extern "C" int qb_marlin_gemm_fused(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S,
-                                    int m, int n, int k, int epi, const int* xrows, unsigned long long* keys,
-                                    int n_valid, const float* norm_w_out, void* xu_out, int x_unnormed, float eps) {
-    if (!ctx || !X || !B || !Y || !S || m < 1 || n <= 0 || k <= 0 || n % 256 || k % 128) return QB_ERR_ARG;
-    if (m > 16) return QB_ERR_UNSUPPORTED;
-    if (epi < 0 || epi > QB_EPI_RESID) return QB_ERR_ARG;
-    if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
-    if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
-    if (epi == QB_EPI_RESID && (!norm_w_out || !xu_out || xrows)) return QB_ERR_ARG;
-    if ((epi == QB_EPI_RESID && (size_t)(n / 64) > ctx->sq_groups) || (x_unnormed && (size_t)(k / 64) > ctx->sq_groups))
-        return QB_ERR_TOO_LARGE;
-    return gemm_rows(ctx, (cudaStream_t)stream, X, B, Y, S, m, n, k, 0, epi, xrows, keys, n_valid, norm_w_out, xu_out,
-                     x_unnormed != 0, eps);
 }
 
 // Some hosts can never call cudaMalloc once they are serving: an engine that has handed all free device memory to its

@@ -2,7 +2,6 @@
 // context asks for it. Every kernel of the library calls pdl_wait() before it touches anything an earlier kernel of
 // the stream wrote, so the chain of dependencies stays transitive whichever launches carry the attribute.
 #pragma once
-#include <set>
 #include "ctx.h"
 
 namespace qb {
@@ -10,13 +9,7 @@ namespace qb {
 template <typename... KArgs, typename... Args>
 static inline int launch(const qb_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                          cudaStream_t st, Args... args) {
-    // Every kernel asks for the same L1 / shared-memory split (all shared): the big streaming kernels need it, and an
-    // SM whose split has to change between two kernels drains first, which would undo the overlap of neighbours.
-    static std::set<const void*> prepared;
-    if (!prepared.count((const void*)kern)) {
-        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        prepared.insert((const void*)kern);
-    }
+    if (int rc = prepare_kernel(ctx->device, (const void*)kern, (int)smem)) return rc;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = grid;
     lc.blockDim = block;

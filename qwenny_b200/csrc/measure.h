@@ -1,0 +1,22 @@
+/* Measurement-only entry points of libqwenny_b200.so: exported for the timing and profiling drivers, not part of the
+ * public ABI (include/qwenny_b200.h) and not for a serving host. */
+#pragma once
+#include "ctx.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+/* Fixes the tile shape (cg x kg consumer warps), ring depth and blocks per SM of the next qb_marlin_gemm calls on the
+ * context; zeros restore the built-in choice. ctas < 0: as -ctas, and stream-K only; nstages < 0: as -nstages, and no
+ * tensor-core path for more than 16 rows. */
+int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
+/* The following qb_marlin_gemm calls write per-block timestamps (ns of the global timer: start, first stage landed,
+ * last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`; NULL switches it off. */
+int qb_marlin_trace(qb_ctx* ctx, long long* buf);
+/* mode 1 makes the products' consumers release every stage unread, so a launch times the copy pipeline alone (its
+ * results are meaningless); 0 restores the product. */
+int qb_marlin_probe(qb_ctx* ctx, int mode);
+/* Host-only check of the per-device kernel-attribute bookkeeping; 0 when it holds. */
+int qb_attr_cache_selftest(void);
+#ifdef __cplusplus
+}
+#endif

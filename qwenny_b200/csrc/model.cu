@@ -49,7 +49,7 @@ struct qb_model {
     const float* final_norm = nullptr;
     const void *lm_w = nullptr, *lm_s = nullptr;
     // activations (Bufs)
-    float *h = nullptr, *h2 = nullptr, *part_h = nullptr, *part = nullptr, *ba = nullptr, *o = nullptr, *cv = nullptr, *q = nullptr, *ml = nullptr,
+    float *h = nullptr, *part = nullptr, *ba = nullptr, *o = nullptr, *cv = nullptr, *q = nullptr, *ml = nullptr,
           *acc = nullptr, *logits = nullptr;
     __half *xn = nullptr, *mix = nullptr, *mid = nullptr;
     unsigned long long* keys = nullptr;
@@ -94,17 +94,9 @@ struct qb_model {
     int *d_positions = nullptr, *h_positions = nullptr;
     std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;  // the graph and its kernel count
     bool use_graphs = true, fused = true;
-    // the persistent layer kernel is correct but, as measured, slower than the separate launches (its ring shares the
-    // shared memory with the resident X and every grid barrier waits for the slowest block): off unless asked for
-    bool chain = false;
     // the DeltaNet layers' small 16-bit in-projection runs on a second stream, beside the int4 one (fork / join by
     // events; inside a captured graph the two become parallel branches)
     bool fork = true;
-    // decode / verify steps: the residual add and RMSNorm between two products run inside them (no launches of their
-    // own). Measured slower than the separate add_rmsnorm launches (6.70 against 6.00 ms per 64-layer step: the small
-    // kernel between two products costs nothing while the next product's blocks are filling their rings anyway, and the
-    // residual epilogue lengthens every cluster's tail), so it is off unless asked for.
-    bool fuse_norm = false;
     cudaStream_t side = nullptr;
     std::vector<cudaEvent_t> ev;  // per layer: fork, join
     std::vector<cudaEvent_t> lev;  // per layer and adapted product: fork, join of xa = A x (created with the first adapter)
@@ -144,8 +136,8 @@ int dalloc(T** p, size_t n) {
     } while (0)
 
 // A layer's in-projection(s): the small 16-bit product of a DeltaNet layer, then the int4 one (whose weight prefetch
-// overlaps it). `with_w4`: false when the previous layer's persistent kernel already ran the int4 product.
-int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, bool unnormed, int& k) {
+// overlaps it).
+int launch_in_proj(qb_model* m, cudaStream_t st, int layer, int& k) {
     qb_ctx* c = m->ctx;
     const qb_layer& L = m->layers[layer].w;
     const int n = m->n;
@@ -158,25 +150,11 @@ int launch_in_proj(qb_model* m, cudaStream_t st, int layer, bool with_w4, bool u
             QB_CUDA(cudaStreamWaitEvent(m->side, m->ev[2 * layer], 0));
             sb = (void*)m->side;
         }
-        if (unnormed) {
-            QB_TRY(qb_gemm_f16_unnormed(c, sb, L.in_ba, m->xn, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS, EPS));
-        } else {
-            QB_TRY(qb_gemm_f16_plain(c, sb, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS));
-        }
-        k++;
+        QB_TRY(qb_gemm_f16_plain(c, sb, L.in_ba, m->xn, nullptr, H, ba_tiles, n, m->ba_kper, m->ba, 2 * LV_HEADS)); k++;
         if (m->fork) QB_CUDA(cudaEventRecord(m->ev[2 * layer + 1], m->side));
     }
-    if (with_w4) {
-        const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
-        if (unnormed) {
-            QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, QB_EPI_PLAIN, nullptr,
-                                        nullptr, 0, nullptr, nullptr, 1, EPS));
-        } else {
-            QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, 0, QB_EPI_PLAIN, nullptr,
-                                  nullptr, 0));
-        }
-        k++;
-    }
+    const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
+    QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     return QB_OK;
 }
 
@@ -269,7 +247,7 @@ int launch_layer_lora(qb_model* m, cudaStream_t st, int layer, const float* w_ne
         return QB_OK;
     };
     if (A.inp.a && L.kind != QB_LAYER_DELTA) QB_TRY(xa_beside(0, A.inp, m->xn, H, false));
-    QB_TRY(launch_in_proj(m, st, layer, true, false, k));
+    QB_TRY(launch_in_proj(m, st, layer, k));
     if (A.inp.a) {
         const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
         if (L.kind == QB_LAYER_DELTA) QB_TRY(xa_beside(0, A.inp, m->xn, H, true));  // behind the 16-bit product there
@@ -329,7 +307,7 @@ int launch_mtp(qb_model* m, cudaStream_t st, bool own) {
     QB_TRY(qb_mtp_in(c, s, m->o, m->h, m->mtp_rows, own ? M.norm : m->final_norm, M.pre_e, M.pre_h, m->xin2, EPS, n)); k++;
     QB_TRY(qb_marlin_gemm(c, s, m->xin2, M.fc_w, m->h, M.fc_s, n, H, 2 * H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     QB_TRY(qb_rmsnorm(c, s, m->h, L.input_norm, m->xn, EPS, n)); k++;
-    QB_TRY(launch_in_proj(m, st, m->nlayers, true, false, k));
+    QB_TRY(launch_in_proj(m, st, m->nlayers, k));
     QB_TRY(launch_mixer(m, st, m->nlayers, k));
     QB_TRY(launch_layer_tail(m, st, L, M.norm, k));
     if (m->n_out > 0) {
@@ -343,15 +321,12 @@ int launch_mtp(qb_model* m, cudaStream_t st, bool own) {
     return QB_OK;
 }
 
-// The kernels of one step over the uploaded tokens, in the reference's order (launch_step). Steps of up to
-// qb_layer_chain_max_rows() tokens run everything between two mixers as one persistent launch.
+// The kernels of one step over the uploaded tokens, in the reference's order (launch_step).
 int launch_step(qb_model* m, cudaStream_t st) {
     qb_ctx* c = m->ctx;
     const int n = m->n;
     int k = 0;
     void* s = (void*)st;
-    const bool chain = m->chain && n <= qb_layer_chain_max_rows() && !m->lora_step;
-    const bool fnorm = m->fuse_norm && !chain && n <= 16 && !m->lora_step;
     // the reference splits the small 16-bit product 40 ways (split_for); 5 splits of 1024 columns leave its consumers
     // 8x fewer partial sums to add
     m->ba_kper = m->fused || n > 32 ? 1024 : H / qb_split_for(2 * LV_HEADS / 16, H, 16, 1024 * 8 / (n <= 8 ? 8 : n <= 16 ? 16 : 32));
@@ -365,41 +340,11 @@ int launch_step(qb_model* m, cudaStream_t st) {
             QB_TRY(launch_layer_lora(m, st, i, w_next, k));
             continue;
         }
-        QB_TRY(launch_in_proj(m, st, i, !chain || i == 0, fnorm && i > 0, k));
+        QB_TRY(launch_in_proj(m, st, i, k));
         QB_TRY(launch_mixer(m, st, i, k));
-        if (chain) {
-            qb_chain ch = {};
-            ch.m = n; ch.mix = m->mix;
-            ch.out_w = L.out_w; ch.out_s = L.out_s; ch.gate_up_w = L.gate_up_w; ch.gate_up_s = L.gate_up_s;
-            ch.down_w = L.down_w; ch.down_s = L.down_s;
-            if (i + 1 < m->nlayers) {
-                const qb_layer& N = m->layers[i + 1].w;
-                ch.next_w = N.in_proj_w; ch.next_s = N.in_proj_s; ch.next_n = N.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
-            }
-            ch.post_norm = L.post_norm; ch.next_norm = w_next;
-            ch.h = m->h; ch.h_tmp = m->h2; ch.part_h = m->part_h; ch.mid = m->mid; ch.xn = m->xn; ch.part = m->part;
-            ch.eps = EPS;
-            QB_TRY(qb_layer_chain(c, s, &ch)); k++;
-            continue;
-        }
-        if (fnorm) {
-            // out_proj adds into the residual stream and leaves xn = f16(post_norm * h), not yet divided by the rms;
-            // gate_up runs on it and scales its result; down adds again; the next product (the next layer's
-            // in-projection or the output layer) scales
-            QB_TRY(qb_marlin_gemm_fused(c, s, m->mix, L.out_w, m->h, L.out_s, n, H, MIX, QB_EPI_RESID, nullptr, nullptr, 0,
-                                        L.post_norm, m->xn, 0, EPS)); k++;
-            QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, QB_EPI_SILU, nullptr,
-                                        nullptr, 0, nullptr, nullptr, 1, EPS)); k++;
-            QB_TRY(qb_marlin_gemm_fused(c, s, m->mid, L.down_w, m->h, L.down_s, n, H, FF, QB_EPI_RESID, nullptr, nullptr, 0,
-                                        w_next, m->xn, 0, EPS)); k++;
-            continue;
-        }
         QB_TRY(launch_layer_tail(m, st, L, w_next, k));
     }
-    if (m->n_out > 0 && fnorm) {
-        QB_TRY(qb_marlin_gemm_fused(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, QB_EPI_ARGMAX,
-                                    m->out_rows, m->keys, m->vocab_valid, nullptr, nullptr, 1, EPS)); k++;
-    } else if (m->n_out > 0) {
+    if (m->n_out > 0) {
         QB_TRY(qb_marlin_gemm(c, s, m->xn, m->lm_w, m->logits, m->lm_s, m->n_out, m->vocab_rows, H, 0, QB_EPI_ARGMAX,
                               m->out_rows, m->keys, m->vocab_valid)); k++;
     }
@@ -426,7 +371,6 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     for (auto& e : m->ev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     const size_t T = MAX_TOK;
     QB_TRY(dalloc(&m->h, T * H)); QB_TRY(dalloc(&m->xn, T * H));
-    QB_TRY(dalloc(&m->h2, (size_t)8 * H)); QB_TRY(dalloc(&m->part_h, (size_t)8 * H));  // the persistent layer kernel's
     QB_TRY(dalloc(&m->part, T * (size_t)DELTA_IN));
     QB_TRY(dalloc(&m->ba, (size_t)40 * 32 * 2 * LV_HEADS + 5 * T * 2 * LV_HEADS));  // 40 splits of 32 rows or 5 of T
     QB_TRY(dalloc(&m->o, T * MIX)); QB_TRY(dalloc(&m->mix, T * MIX)); QB_TRY(dalloc(&m->mid, T * FF));
@@ -468,7 +412,7 @@ void qb_model_destroy(qb_model* m) {
     if (m->h_positions) cudaFreeHost(m->h_positions);
     void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions, m->slot_scale, m->lpart, m->lgu};
     for (void* b : sb) cudaFree(b);
-    void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->h2, m->part_h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
+    void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
     for (void* b : bufs) cudaFree(b);
     for (int i = 0; i < 2; i++) {
@@ -520,15 +464,6 @@ int qb_model_use_graphs(qb_model* m, int on) {
     return QB_OK;
 }
 
-int qb_model_use_fused_norm(qb_model* m, int on) {
-    if (!m) return QB_ERR_ARG;
-    if (m->fuse_norm != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
-        m->graphs.clear();
-    }
-    m->fuse_norm = on != 0;
-    return QB_OK;
-}
 
 int qb_model_use_fork(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
@@ -540,15 +475,6 @@ int qb_model_use_fork(qb_model* m, int on) {
     return QB_OK;
 }
 
-int qb_model_use_chain(qb_model* m, int on) {
-    if (!m) return QB_ERR_ARG;
-    if (m->chain != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
-        m->graphs.clear();
-    }
-    m->chain = on != 0;
-    return QB_OK;
-}
 
 int qb_model_use_fused(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;

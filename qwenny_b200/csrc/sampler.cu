@@ -518,13 +518,7 @@ int launch_sampler(qb_ctx* ctx, void* stream, SamplerArgs a, int n_out) {
     a.slice = ((a.W + SCL - 1) / SCL + 31) / 32 * 32;
     const size_t smem = sizeof(SamplerSmem) + (size_t)a.slice / 32 * 4 + (size_t)a.slice * 4;
     if (smem > 227 * 1024) return QB_ERR_TOO_LARGE;
-    static bool opted = false;
-    if (!opted) {
-        QB_CUDA(cudaFuncSetAttribute(sampler_kernel<DRAFT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        QB_CUDA(cudaFuncSetAttribute(sampler_kernel<DRAFT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     cudaSharedmemCarveoutMaxShared));
-        opted = true;
-    }
+    if (int rc = qb::prepare_kernel(ctx->device, (const void*)sampler_kernel<DRAFT>, 227 * 1024)) return rc;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(SCL, n_out);
     lc.blockDim = dim3(STH);

@@ -314,19 +314,7 @@ int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B
     tc::Args a;
     a.B = (const uint32_t*)B; a.S = (const __half*)S; a.Y = Y; a.m = m; a.N = n; a.K = k; a.row0 = row0; a.err = ctx->err;
     dim3 grid(n / tc::BO, (m + tc::BT - 1) / tc::BT);
-    static bool opted[2] = {false, false};
-    if (epi == QB_EPI_SILU) {
-        if (!opted[1]) {
-            QB_CUDA(cudaFuncSetAttribute(tc::w4a16_gemm_tc_kernel<tc::EPI_SILU_TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         tc::SMEM_BYTES));
-            opted[1] = true;
-        }
+    if (epi == QB_EPI_SILU)
         return launch(ctx, tc::w4a16_gemm_tc_kernel<tc::EPI_SILU_TC>, grid, dim3(tc::THREADS), tc::SMEM_BYTES, st, map, a);
-    }
-    if (!opted[0]) {
-        QB_CUDA(cudaFuncSetAttribute(tc::w4a16_gemm_tc_kernel<tc::EPI_PLAIN_TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     tc::SMEM_BYTES));
-        opted[0] = true;
-    }
     return launch(ctx, tc::w4a16_gemm_tc_kernel<tc::EPI_PLAIN_TC>, grid, dim3(tc::THREADS), tc::SMEM_BYTES, st, map, a);
 }

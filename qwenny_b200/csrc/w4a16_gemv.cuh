@@ -32,8 +32,7 @@
 
 namespace qb {
 
-enum { EPI_PLAIN = 0, EPI_SILU = 1, EPI_ARGMAX = 2, EPI_RESID = 3 };
-constexpr int SQ_ROWS = 16;  // token rows of the sum-of-squares partials (steps of up to 16 rows)
+enum { EPI_PLAIN = 0, EPI_SILU = 1, EPI_ARGMAX = 2 };
 
 struct GemvArgs {
     const __half* X;      // [rows][K] f16
@@ -49,18 +48,7 @@ struct GemvArgs {
     int* counters;        // [N/64] tickets, zero between launches
     unsigned long long* keys;
     int n_valid;
-    // Residual + RMSNorm folded into the products on either side of it (steps of up to 16 rows). RMSNorm is linear up to
-    // the row's 1 / rms, so the product that follows a norm can run on the UN-normalised row and scale its result:
-    //  EPI_RESID: Y is the f32 residual stream [.][N]; the epilogue adds the product to it in place, writes
-    //  xu = f16(nw_out[c] * h_new[c]) [.][N] for the next product, and records per 64 outputs and token row the sum of
-    //  squares of the new values in sq [N/64][SQ_ROWS];
-    //  rs != null: X is such an xu; the epilogue multiplies row t of the result by rsqrt(sum_g rs[g][t] / K + eps).
     int zp;               // zero points: S holds a second table [K/128][N] of (8 - z) * scale after the scales
-    const float* nw_out;
-    __half* xu_out;
-    float* sq;
-    const float* rs;
-    float eps;
     int* err;             // set non-zero when a bounded wait ran out
     int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone)
     long long* trace;     // measurement only (may be null): per block {start, first stage landed, last stage
@@ -112,19 +100,8 @@ __device__ __forceinline__ void dequant_word(uint32_t q, uint32_t* a) {
 // The epilogue of 64 finished outputs x 8 NT tokens held in the accumulator layout of the mma (acc[j][b][2h+e]:
 // output col + 16 b + g + 8 h, token 8 j + 2 t + e).
 template <int NT, int EPI>
-__device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT][4][4], const int col, const int lane,
-                                              const float rinv_lane) {
+__device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT][4][4], const int col, const int lane) {
     const int g = lane >> 2, t = lane & 3;
-    if (a.rs) {  // the input rows were un-normalised: lanes r and r + 16 hold 1 / rms of token row r
-#pragma unroll
-        for (int j = 0; j < NT; j++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const float r = __shfl_sync(0xffffffffu, rinv_lane, 8 * j + 2 * t + e);
-#pragma unroll
-                for (int b = 0; b < 4; b++) { acc[j][b][e] *= r; acc[j][b][2 + e] *= r; }
-            }
-    }
 #pragma unroll
     for (int j = 0; j < NT; j++)
 #pragma unroll
@@ -135,19 +112,6 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT
                 __half* y = (__half*)a.Y + (size_t)(a.row0 + tok) * (a.N / 2) + col / 2 + g;
 #pragma unroll
                 for (int b = 0; b < 4; b++) y[8 * b] = __float2half_rn(silu(acc[j][b][e]) * acc[j][b][2 + e]);
-            } else if (EPI == EPI_RESID) {
-                float* y = (float*)a.Y + (size_t)(a.row0 + tok) * a.N + col + g;
-                __half* xu = a.xu_out + (size_t)(a.row0 + tok) * a.N + col + g;
-                const float* w = a.nw_out + col + g;
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    acc[j][b][e] += y[16 * b];
-                    acc[j][b][2 + e] += y[16 * b + 8];
-                    y[16 * b] = acc[j][b][e];
-                    y[16 * b + 8] = acc[j][b][2 + e];
-                    xu[16 * b] = __float2half_rn(w[16 * b] * acc[j][b][e]);
-                    xu[16 * b + 8] = __float2half_rn(w[16 * b + 8] * acc[j][b][2 + e]);
-                }
             } else {
                 float* y = (float*)a.Y + (size_t)(a.row0 + tok) * a.N + col + g;
 #pragma unroll
@@ -157,24 +121,6 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT
                 }
             }
         }
-    if (EPI == EPI_RESID) {
-        // the sum of squares of the 64 new values of each token row: the lane's 8, then the 8 lanes g in a fixed order
-#pragma unroll
-        for (int j = 0; j < NT; j++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                int tok = 8 * j + 2 * t + e;
-                float ss = 0.f;
-                if (tok < a.m) {
-#pragma unroll
-                    for (int b = 0; b < 4; b++) ss += acc[j][b][e] * acc[j][b][e] + acc[j][b][2 + e] * acc[j][b][2 + e];
-                }
-                ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-                ss += __shfl_xor_sync(0xffffffffu, ss, 8);
-                ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-                if (g == 0 && tok < a.m) a.sq[(size_t)(col / 64) * SQ_ROWS + a.row0 + tok] = ss;
-            }
-    }
     if (EPI == EPI_ARGMAX) {
 #pragma unroll
         for (int j = 0; j < NT; j++)
@@ -304,29 +250,6 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     // ---------------------------------------------------------------- consumers
     pdl_wait();
     const int cg = warp % CG, kg = warp / CG, g = lane >> 2, t = lane & 3;
-    // 1 / rms of the token rows whose un-normalised form is this product's X (while the first stage is still on its
-    // way). The K / 64 partial sums of squares of a row are dealt to the consumer warps in runs, lane = (partial mod 2,
-    // row), so that every lane has a handful of independent loads; the warps' sums meet in shared memory and are added
-    // in warp order. Lanes r and r + 16 end up with row r's value.
-    float rinv_lane = 1.f;
-    if (a.rs) {
-        __shared__ float rsum[16][SQ_ROWS];
-        const int r0 = lane & 15, groups = a.K / 64, per = (groups + C::NW - 1) / C::NW;
-        float ss = 0.f;
-        if (r0 < a.m) {
-            const int row = a.xrows ? a.xrows[r0] : a.row0 + r0;
-            const int g0 = warp * per, g1 = min(groups, g0 + per);
-#pragma unroll 8
-            for (int cgp = g0 + (lane >> 4); cgp < g1; cgp += 2) ss += __ldcg(a.rs + (size_t)cgp * SQ_ROWS + row);
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-        if (lane < 16) rsum[warp][lane] = ss;
-        named_bar_sync(3, C::NW * 32);
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < C::NW; w++) tot += rsum[w][r0];
-        rinv_lane = rsqrtf(tot / a.K + a.eps);
-    }
     float acc[NT][4][4];
 #pragma unroll
     for (int j = 0; j < NT; j++)
@@ -503,7 +426,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                             acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
                         }
                 }
-                gemv_epilogue<NT, EPI>(a, acc, (pcb * CG + cg) * 64, lane, rinv_lane);
+                gemv_epilogue<NT, EPI>(a, acc, (pcb * CG + cg) * 64, lane);
             }
             cluster_sync();
             return;
@@ -550,7 +473,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                     if (lane == 0) a.counters[colgrp] = 0;  // left zero for the next product
                 }
             }
-            if (finish) gemv_epilogue<NT, EPI>(a, acc, colgrp * 64, lane, rinv_lane);
+            if (finish) gemv_epilogue<NT, EPI>(a, acc, colgrp * 64, lane);
         }
 #pragma unroll
         for (int j = 0; j < NT; j++)

@@ -2,11 +2,10 @@
 
     python -m qwenny_b200.microbench gemv N K [--rows 5] [--epi plain|silu|argmax] [--reps 24] [--tune cg,kg,stages,ctas]
     python -m qwenny_b200.microbench attn [--context 32000] [--rows 5] [--reps 20]
-    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--chain] [--lora 16]
+    python -m qwenny_b200.microbench step [--layers 8] [--steps 3] [--rows 5] [--no-graph] [--no-pdl] [--lora 16]
     python -m qwenny_b200.microbench prefill [--layers 64] [--prompt 32768] [--chunk 2048]
     python -m qwenny_b200.microbench delta [--rows 2048 | --rows 5]
     python -m qwenny_b200.microbench draft [--k 4] [--draft-rows 65536]
-    python -m qwenny_b200.microbench chain [--rows 5] [--trace] [--probe 1|2]
     python -m qwenny_b200.microbench session [--layers 64] [--context 32768]
     python -m qwenny_b200.microbench sampler [--rows 5] [--top-k 50] [--top-p 0.95] [--penalty 1.1] [--draft-rows 0]
 
@@ -133,9 +132,7 @@ def step(args):
     ctx.set_pdl(not args.no_pdl)
     m = M.synthetic(ctx, nlayers=args.layers, position=args.context, max_ctx=32768)
     m.use_graphs(not args.no_graph)
-    m.use_chain(args.chain)
     m.use_fork(not args.no_fork)
-    m.use_fused_norm(args.fused_norm)
     if args.lora:  # a LoRA of that rank on every product of every layer; the step's slot uses it
         M.synthetic_adapter(m, rank=args.lora)
         m.set_slot_scale(0, 2.0)
@@ -346,59 +343,6 @@ def delta(args):
     print(f"delta_rule rows={n}: {us:.1f} us/launch = {us * 1e3 / n:.0f} ns/token, device error {ctx.device_error()}")
 
 
-def chain(args):
-    """The persistent layer kernel alone: out_proj, norm, gate_up, down, norm, next in-projection."""
-    from ._lib import lib
-    ctx = Context(0)
-    ctx.set_pdl(not args.no_pdl)
-    if args.probe:
-        lib().qb_marlin_probe(ctx.h, args.probe)
-    m, Hh, MIX, FF, NN = args.rows, 5120, 6144, 17408, 16384
-    g = torch.Generator(device="cuda").manual_seed(0)
-    sets = [[M.Marlin.random(Hh, MIX, g), M.Marlin.random(2 * FF, Hh, g), M.Marlin.random(Hh, FF, g),
-             M.Marlin.random(NN, Hh, g)] for _ in range(2)]
-    w = (1 + 0.02 * torch.randn(Hh, generator=g, device="cuda")).float()
-    mix = torch.randn(m, MIX, generator=g, device="cuda").half()
-    h = torch.randn(m, Hh, generator=g, device="cuda")
-    h_tmp, part_h = torch.zeros(8, Hh, device="cuda"), torch.zeros(8, Hh, device="cuda")
-    mid = torch.zeros(m, FF, dtype=torch.float16, device="cuda")
-    xn = torch.zeros(m, Hh, dtype=torch.float16, device="cuda")
-    part = torch.zeros(m, NN, device="cuda")
-    i = [0]
-
-    def one():
-        o, gu, d, nx = sets[i[0] % 2]
-        i[0] += 1
-        ctx.layer_chain(m, mix, (o.words, o.scales), (gu.words, gu.scales), (d.words, d.scales),
-                        (nx.words, nx.scales, NN), w, w, h, h_tmp, part_h, mid, xn, part)
-
-    stream = torch.cuda.Stream()
-    if args.plain:
-        with torch.cuda.stream(stream):
-            for _ in range(args.reps):
-                one()
-        torch.cuda.synchronize()
-        print("plain launches done, device error", ctx.device_error())
-        return
-    us = _time_graph(one, stream, args.reps)
-    nbytes = sum(t.bytes() for t in sets[0])
-    print(f"layer_chain rows={m}: {us:.1f} us/launch, {nbytes / us / 1e6:.2f} TB/s of weights, device error {ctx.device_error()}")
-    if args.trace:
-        buf = torch.zeros(4 * 1024 * 4, dtype=torch.int64, device="cuda")
-        lib().qb_marlin_trace(ctx.h, buf.data_ptr())
-        with torch.cuda.stream(stream):
-            for _ in range(3):
-                one()
-        torch.cuda.synchronize()
-        lib().qb_marlin_trace(ctx.h, None)
-        t = buf.view(-1, 4 * 1024)[2][:148 * 17].view(148, 17).cpu().numpy().astype(np.float64)
-        t0 = t[:, 0].min()
-        names = [f"p{p}.{k}" for p in range(4) for k in ("begin", "xready", "landed", "written")] + ["end"]
-        for j, nm in enumerate(names):
-            c = t[:, j] - t0
-            print(f"  {nm:12s} min {c.min() / 1e3:7.2f}  median {np.median(c) / 1e3:7.2f}  max {c.max() / 1e3:7.2f} us")
-
-
 def main():
     ap = argparse.ArgumentParser(prog="python -m qwenny_b200.microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -419,8 +363,6 @@ def main():
     c.add_argument("--rows", type=int, default=5); c.add_argument("--context", type=int, default=32000)
     c.add_argument("--no-graph", action="store_true"); c.add_argument("--no-pdl", action="store_true")
     c.add_argument("--no-fork", action="store_true", help="the 16-bit in-projection in line instead of on a second stream")
-    c.add_argument("--fused-norm", action="store_true", help="residual + RMSNorm inside the products around them")
-    c.add_argument("--chain", action="store_true", help="the persistent layer kernel instead of separate launches")
     c.add_argument("--lora", type=int, default=0, help="rank of an unmerged LoRA on every layer (0: none)")
     c.set_defaults(fn=step)
     f = sub.add_parser("prefill")
@@ -434,11 +376,6 @@ def main():
     e = sub.add_parser("delta")
     e.add_argument("--rows", type=int, default=2048); e.add_argument("--reps", type=int, default=5)
     e.set_defaults(fn=delta)
-    d = sub.add_parser("chain")
-    d.add_argument("--rows", type=int, default=5); d.add_argument("--reps", type=int, default=20)
-    d.add_argument("--no-pdl", action="store_true"); d.add_argument("--plain", action="store_true")
-    d.add_argument("--probe", type=int, default=0); d.add_argument("--trace", action="store_true")
-    d.set_defaults(fn=chain)
     ss = sub.add_parser("session")
     ss.add_argument("--layers", type=int, default=64); ss.add_argument("--context", type=int, default=32768)
     ss.add_argument("--reps", type=int, default=3)

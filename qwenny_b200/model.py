@@ -261,14 +261,8 @@ class Model:
     def use_fused(self, on: bool):
         check(lib().qb_model_use_fused(self.h, int(on)), "qb_model_use_fused")
 
-    def use_fused_norm(self, on: bool):
-        check(lib().qb_model_use_fused_norm(self.h, int(on)), "qb_model_use_fused_norm")
-
     def use_fork(self, on: bool):
         check(lib().qb_model_use_fork(self.h, int(on)), "qb_model_use_fork")
-
-    def use_chain(self, on: bool):
-        check(lib().qb_model_use_chain(self.h, int(on)), "qb_model_use_chain")
 
     def use_graphs(self, on: bool):
         check(lib().qb_model_use_graphs(self.h, int(on)), "qb_model_use_graphs")

@@ -88,18 +88,6 @@ class Context:
     def embed(self, table, ids, out, keys, nkeys, n):
         check(lib().qb_embed(self.h, _stream(), _p(table), _p(ids), _p(out), _p(keys), nkeys, n), "qb_embed")
 
-    def marlin_gemm_fused(self, x, words, scales, y, m, epi="plain", norm_w_out=None, xu_out=None, x_unnormed=False,
-                          xrows=None, keys=None, n_valid=None, eps=1e-6):
-        """qb_marlin_gemm_fused: epi "resid" adds into y (the f32 residual stream), writes xu_out = f16(norm_w_out * y)
-        and records the rows' sums of squares; x_unnormed scales the result rows by 1 / rms of those rows."""
-        n = words.shape[1] // 2
-        k = words.shape[0] * 16
-        code = {"plain": 0, "silu": 1, "argmax": 2, "resid": 3}[epi]
-        check(lib().qb_marlin_gemm_fused(self.h, _stream(), _p(x), _p(words), _p(y), _p(scales), m, n, k, code, _p(xrows),
-                                         _p(keys), n if n_valid is None else n_valid, _p(norm_w_out), _p(xu_out),
-                                         int(x_unnormed), eps), "qb_marlin_gemm_fused")
-        return y
-
     def mtp_in(self, emb, h, rows, fw, pre_e, pre_h, y, n, eps=1e-6):
         check(lib().qb_mtp_in(self.h, _stream(), _p(emb), _p(h), _p(rows), _p(fw), _p(pre_e), _p(pre_h), _p(y), eps, n),
               "qb_mtp_in")
@@ -175,25 +163,6 @@ class Context:
         check(lib().qb_attn_prefill(self.h, _stream(), _p(q), _p(kc), _p(vc), _p(ks), _p(vs), _p(dev["ptile"]),
                                     _p(dev["tok_slot"]), _p(dev["tok_pos"]), cap, st["ntile"], st["tile_max_pos"] + 1,
                                     _p(part_ml), _p(part_acc), _p(out), _p(mix)), "qb_attn_prefill")
-
-    def layer_chain(self, m, mix, out, gate_up, down, nxt, post_norm, next_norm, h, h_tmp, part_h, mid, xn, part,
-                    eps=1e-6):
-        """qb_layer_chain: out / gate_up / down / nxt are (words, scales) pairs of Marlin tensors; nxt may be None."""
-        from ._lib import QbChain
-        a = lambda t: t.data_ptr() if t is not None else None
-        c = QbChain()
-        c.m = m
-        c.mix = a(mix)
-        c.out_w, c.out_s = a(out[0]), a(out[1])
-        c.gate_up_w, c.gate_up_s = a(gate_up[0]), a(gate_up[1])
-        c.down_w, c.down_s = a(down[0]), a(down[1])
-        if nxt is not None:
-            c.next_w, c.next_s, c.next_n = a(nxt[0]), a(nxt[1]), nxt[2]
-        c.post_norm, c.next_norm = a(post_norm), a(next_norm)
-        c.h, c.h_tmp, c.part_h, c.mid, c.xn, c.part = a(h), a(h_tmp), a(part_h), a(mid), a(xn), a(part)
-        c.eps = eps
-        import ctypes
-        check(lib().qb_layer_chain(self.h, _stream(), ctypes.byref(c)), "qb_layer_chain")
 
     # ---- DeltaNet
     def delta_conv(self, part, splits, n, ba, ba_splits, conv_w, a_log, dt_bias, mem, sst, cv, dev):
