@@ -63,15 +63,22 @@ int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, vo
 /* qb_marlin_gemm without a context and without any allocation, for callers that cannot call cudaMalloc (an engine
  * that gave all free device memory to its cache pool, a plugin in a process whose allocator it does not own). It has
  * no counterpart in the reference. Same arguments and results as qb_marlin_gemm for m <= 16 rows, always through the
- * stream-K path, whose scratch (split-K partials, tickets) lives in a fixed array inside the library image: each GPU
- * that loads the library holds qb_static_scratch_bytes() (about 4 MiB) until exit. Limits: n <= 262144 and
- * n/64 x sharers x 2 KiB (4 KiB above 8 rows) <= 4 MiB, i.e. every shape of the 27B model; larger sizes return
- * QB_ERR_TOO_LARGE before anything is enqueued. The first call on a device resolves the array's device address and
- * the SM count for that device (make it before any stream capture, with the device current); calls on one device
- * share the array, so two of them must not overlap on the GPU (same stream, or ordered by events). */
+ * stream-K path, whose scratch (split-K partials, tickets, error word) lives in a fixed array inside the library image:
+ * each GPU that loads the library holds qb_static_scratch_bytes() (about 16 MiB) until exit. Limits: n <= 262144 and
+ * n/64 x sharers x 2 KiB (4 KiB above 8 rows) <= 16 MiB, where sharers is the most blocks of the persistent grid that
+ * meet in one column block. On a 148-SM part that admits every layer product of the 27B model at 1..16 rows
+ * (16384 / 14336 x 5120, 5120 x 6144, 34816 x 5120, 5120 x 17408, 5120 x 10240) and output layers of up to 262144 rows
+ * at 1..8 rows; an output layer of more than 131072 rows at 9..16 rows does not fit. Larger sizes return
+ * QB_ERR_TOO_LARGE before anything is enqueued. The first call on a device resolves the array's device address and the
+ * SM count for that device, and the first call of each tile shape, row-count class (1..8, 9..16) and epilogue sets
+ * that kernel's attributes: make one call of every shape you will use before any stream capture, with the device
+ * current. Calls on one device share the array, so two of them must not overlap on the GPU (same stream, or ordered
+ * by events). A bounded wait that ran out inside such a product is reported by qb_static_device_error (current
+ * device; reads and clears; waits). */
 int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n, int k,
                            int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 int qb_static_scratch_bytes(void);
+int qb_static_device_error(void);
 
 /* ---- dense f16 skinny product (the 16-bit matrices of a pre-quantized checkpoint: in_proj_b / in_proj_a).
  * Replaces gemm_f16_t{8,16,32}_plain (kernels/gemm.cuh:306-326) as Gemm::run_split launches it
@@ -158,6 +165,10 @@ int qb_draft_sample(qb_ctx* ctx, void* stream, const float* logits, int width, i
                     const float* params, int* drafts, int* qtok, int* qn, int* qid, float* qp);
 int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* out, unsigned long long* keys,
              int nkeys, int n);
+/* embed_q8, kernels/qwen.cu:85-98: the same lookup from an int8 table as stored (codes + 128, a f32 scale per 128
+ * columns, S [rows][5120 / 128]); the table may be mapped host memory. */
+int qb_embed_q8(qb_ctx* ctx, void* stream, const void* E, const float* S, const int* ids, float* out,
+                unsigned long long* keys, int nkeys, int n);
 int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n);
 int qb_add_rmsnorm(qb_ctx* ctx, void* stream, float* h, const float* x, int splits, int n, const float* w_next,
                    void* y, float eps);
@@ -330,6 +341,8 @@ int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, cons
 int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp);
 int qb_model_draft(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_rows, const int* h_out,
                    int n_out, int k, int* h_drafts);
+int qb_model_learn_block(qb_model* m, void* stream, int block, const uint32_t* h_words, const uint16_t* h_sc,
+                         const int* h_ids16, int* grew);
 /* The sampler on the step's logits.
  * qb_model_set_outputs   Step::set_outputs: the tokens a slot's request generated so far, h_words = vocab_rows / 32
  *                        host words (the presence penalty's set; the seen set is kept by the steps themselves).
@@ -370,7 +383,14 @@ int qb_model_load_state(qb_model* m, void* stream, int slot, const void* h_data,
 int qb_model_set_adapter(qb_model* m, int layer, const qb_lora_layer* lora);
 int qb_model_set_slot_scale(qb_model* m, void* stream, int slot, float scale);
 int qb_model_run(qb_model* m, void* stream);
+/* The captured steps are a bounded cache (Graphs, src/cuda/core.rs:1105-1252): once less than 128 MiB of device memory
+ * is free at a capture the cache keeps what it holds and drops the least recently used; a capture that finds no memory
+ * lowers the cap to three quarters and its step runs without a graph. qb_model_set_pool names the cache pool whose free
+ * pages go back to the driver when memory is shorter still (NULL: none). Setting a layer, the head, the MTP layer or an
+ * adapter drops every captured step (they hold the old pointers). */
 int qb_model_use_graphs(qb_model* m, int on);
+int qb_model_set_pool(qb_model* m, qb_pool* pool);
+int qb_model_graph_stats(const qb_model* m, long long* held, long long* cap, long long* graphless);
 /* 1 (default): fused launches where the library has them (qb_delta_mixer); 0: one launch per reference kernel */
 int qb_model_use_fused(qb_model* m, int on);
 /* on (default): the DeltaNet layers' 16-bit in-projection runs on a second stream beside the int4 one */
@@ -399,6 +419,19 @@ int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int col
 int qb_pack_marlin_z(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int rows, int cols, int group,
                      const int* h_order, int n, uint32_t* h_words, uint16_t* h_scales_f16);
 int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n, uint16_t* h_out);
+/* A draft head learning rows (DraftHead::learn, src/cuda/qwen/draft.rs:56-72; Gemm::put_block, src/cuda/core.rs:614-671).
+ * qb_marlin_block      the host half: the 16 stored rows h_rows16 of a quantized matrix (h_q, h_scales, h_zeros as for
+ *                      qb_pack_marlin_z; zero_points 0: a symmetric matrix, every stored z must be 8) -> the block's words
+ *                      u32 [cols/16][32] and scales f16 [tables * cols/128][16] (tables 2 with zero points)
+ * qb_marlin_put_block  marlin_put_block, kernels/marlin.cuh:614-622, its arguments plus the number of k16 steps (the
+ *                      reference's grid size): writes the block as rows 16 blk .. of the 64-row group c64 of the Marlin
+ *                      matrix (B, S) of n rows; words / sc are DEVICE staging buffers
+ * qb_model_learn_block both for the model's draft head (set with qb_model_set_mtp), through staging buffers allocated
+ *                      once, plus the block's 16 tokens into head_ids; the head's valid rows grow to cover the block */
+int qb_marlin_block(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int zero_points, int rows,
+                    int cols, int group, const int* h_rows16, uint32_t* h_words, uint16_t* h_sc);
+int qb_marlin_put_block(qb_ctx* ctx, void* stream, void* B, void* S, const void* words, const void* sc, int n, int c64,
+                        int blk, int groups, int tables, int k16s);
 int qb_split_for(int tiles, int cols, int bits, int kd);
 
 /* Programmatic dependent launch for the kernels that support it (their weight prefetch then overlaps the tail of

@@ -20,9 +20,23 @@ QSCALE = math.log2(math.e) / 16.0
 
 
 def dequant_marlin(words: np.ndarray, scales: np.ndarray) -> torch.Tensor:
-    """Marlin words + scales -> f32 [n][k] in packed row order (what the kernels multiply by)."""
-    q, s = R.unpack_marlin(words, scales)
-    return torch.from_numpy(R.dequant(q, s).astype(np.float32))
+    """Marlin words + scales -> f32 [n][k] in packed row order (what the kernels multiply by): ref_ops.unpack_marlin
+    followed by ref_ops.dequant (w = f16((q - 8) * f16 scale)), the same index arithmetic run through torch's threaded
+    CPU kernels so that full-width layers unpack in seconds (tests/test_oracle_cpu.py holds the two forms equal)."""
+    k16, n2 = words.shape
+    n, k = n2 // 2, k16 * 16
+    w = torch.from_numpy(np.ascontiguousarray(words).view(np.int32)).reshape(k16, n // 64, 32, 4)
+    r, c = R._marlin_lane_maps()
+    inv = np.zeros(256, dtype=np.int64)
+    inv[(r * 16 + c).reshape(-1)] = np.arange(256)
+    nib = torch.stack([((w >> (4 * x)) & 15).to(torch.uint8) for x in range(8)], dim=-1)   # [k16][c64][lane][blk][x]
+    nib = nib.permute(0, 1, 3, 2, 4).reshape(k16, n // 64, 4, 256)[..., torch.from_numpy(inv)]
+    q = nib.reshape(k16, n // 64, 4, 16, 16).permute(1, 2, 3, 0, 4).reshape(n, k)
+    o = np.arange(n)
+    at = (o // 64) * 64 + 8 * (o % 8) + (o % 64) // 8
+    s = torch.from_numpy(np.ascontiguousarray(scales[:k // 128]).view(np.int16)).view(torch.float16)
+    s = s[:, torch.from_numpy(at)].T.float()
+    return ((q.reshape(n, k // 128, 128).float() - 8.0) * s[:, :, None]).half().float().reshape(n, k)
 
 
 class CpuModel:

@@ -90,6 +90,35 @@ def pack_marlin(q: np.ndarray, scales_f16: np.ndarray, order: np.ndarray, zeros:
     return np.ascontiguousarray(words), sc
 
 
+def marlin_block(q: np.ndarray, scales_f16: np.ndarray, rows16, zeros: np.ndarray | None = None):
+    """The host half of Gemm::put_block (src/cuda/core.rs:636-652): the words [k/16][32] (marlin_word, :244-253) and
+    scales [tables * k/128][16] (marlin_scale, :255-260) of the 16 stored rows `rows16`."""
+    rows16 = np.asarray(rows16)
+    k = q.shape[1]
+    r, c = _marlin_lane_maps()
+    a = q[rows16].astype(np.uint32).reshape(16, k // 16, 16).transpose(1, 0, 2)   # [k16][r][c]
+    gth = a[:, r, c]                                                                # [k16][lane][x]
+    words = np.zeros(gth.shape[:-1], dtype=np.uint32)
+    for x in range(8):
+        words |= gth[..., x] << np.uint32(4 * x)
+    sc = np.ascontiguousarray(scales_f16[rows16].T.astype(np.float16))             # [groups][16]
+    if zeros is not None:
+        off = ((8.0 - zeros[rows16].astype(np.float32)) * scales_f16[rows16].astype(np.float32)).astype(np.float16).T
+        sc = np.concatenate([sc, off], axis=0)
+    return words, sc
+
+
+def put_block(B: np.ndarray, S: np.ndarray, words: np.ndarray, sc: np.ndarray, block: int):
+    """marlin_put_block (kernels/marlin.cuh:614-622) on host arrays, in place: B uint32 [k/16][2n], S float16
+    [tables * k/128][n]; the block's words [k/16][32] and scales [tables * groups][16]."""
+    n = B.shape[1] // 2
+    c64, blk = block // 4, block % 4
+    lane = np.arange(32)
+    B[:, (c64 * 32 + lane) * 4 + blk] = words
+    c = blk * 16 + np.arange(16)
+    S[:sc.shape[0], c64 * 64 + 8 * (c % 8) + c // 8] = sc
+
+
 def unpack_marlin(words: np.ndarray, sc: np.ndarray):
     """Inverse of pack_marlin for the identity order: (codes uint8 [n][k], scales float16 [n][k/128])."""
     k16, n2 = words.shape
@@ -151,6 +180,13 @@ def split_for(tiles: int, cols: int, bits: int, kd: int) -> int:
         if chunks % d == 0 and d >= want:
             return d
     return chunks
+
+
+def embed_q8(table_u8: np.ndarray, scales: np.ndarray, ids) -> np.ndarray:
+    """embed_q8 (kernels/qwen.cu:85-98): row ids[t] of an int8 table as stored, (E - 128) * the scale of its 128
+    columns, in f32."""
+    rows = table_u8[np.asarray(ids)].astype(np.int32) - 128
+    return (rows.astype(np.float32) * np.repeat(scales[np.asarray(ids)].astype(np.float32), 128, axis=1)).astype(np.float32)
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -445,6 +481,29 @@ def _rule_token(S, k, v, e, beta, q=None):
         o = e[:, None] * dq + delta * kq[:, None]
     S = e[:, None, None] * S + delta[:, :, None] * k[:, None, :]
     return S, o
+
+
+def delta_chunk(S, q, k, v, e, beta, dtype=np.float64):
+    """One chunk of C tokens of the gated delta rule in the chunked (WY) form the reference states for its MLX backend
+    (src/mlx/delta.rs:6-15,85-137), for one value head: S [LVD (v)][LKD (k)], q, k [C][LKD], v [C][LVD], e, beta [C].
+    With G_i the cumulative log decay, A_ij = b_i (k_i . k_j) exp(G_i - G_j) (j < i), T = (I + A)^-1:
+      R = b (V - gam K S^T);  D = T R;  O = gam Q S^T + P D, P_ij = (q_i . k_j) exp(G_i - G_j) (j <= i);
+      S' = gam_C S + D^T (k_j exp(G_C - G_j)).
+    Returns (S', O [C][LVD]). Algebraically the token recurrence of _rule_token; sums in another order."""
+    S, q, k, v = S.astype(dtype), q.astype(dtype), k.astype(dtype), v.astype(dtype)
+    g = np.cumsum(np.log(e.astype(dtype)))
+    gam = np.exp(g)
+    dec = np.exp(np.minimum(g[:, None] - g[None, :], 0.0))
+    C = len(g)
+    strict, lower = np.tril(np.ones((C, C), bool), -1), np.tril(np.ones((C, C), bool), 0)
+    A = np.where(strict, beta.astype(dtype)[:, None] * (k @ k.T) * dec, 0.0)
+    T = np.linalg.inv(np.eye(C) + A)
+    R = beta.astype(dtype)[:, None] * (v - gam[:, None] * (k @ S.T))
+    D = T @ R
+    P = np.where(lower, (q @ k.T) * dec, 0.0)
+    O = gam[:, None] * (q @ S.T) + P @ D
+    S1 = gam[-1] * S + D.T @ (k * np.exp(g[-1] - g)[:, None])
+    return S1, O
 
 
 def delta_rule(part, cv, mem, sst, meta, seg_start, seg_len, seg_slot, seg_pos0, dtype=np.float64):

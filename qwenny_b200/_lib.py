@@ -25,6 +25,7 @@ SIGNATURES = {
     "qb_marlin_gemm_z": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_gemm_noalloc": [P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_static_scratch_bytes": [],
+    "qb_static_device_error": [],
     "qb_gemm_f16_plain": [P, P, P, P, P, I, I, I, I, P, I],
     "qb_gemm_dec": [P, P, P, P, I, P, P, I, I, I, I, I, P, I, P],
     "qb_pack_i8": [P, I, I, P, I, P, P],
@@ -50,6 +51,7 @@ SIGNATURES = {
     "qb_model_draft_sampled": [P, P, P, I, P, P, I, I, P, P, P],
     "qb_model_draft_q": [P, P, I, I, P, P, P, P],
     "qb_embed": [P, P, P, P, P, P, I, I],
+    "qb_embed_q8": [P, P, P, P, P, P, P, I, I],
     "qb_rmsnorm": [P, P, P, P, P, F, I],
     "qb_add_rmsnorm": [P, P, P, P, I, I, P, P, F],
     "qb_to_xin": [P, P, P, P, I],
@@ -104,6 +106,11 @@ SIGNATURES = {
     "qb_pack_marlin_z": [P, P, P, I, I, I, P, I, P, P],
     "qb_pack_f16": [P, I, I, P, I, P],
     "qb_split_for": [I, I, I, I],
+    "qb_marlin_block": [P, P, P, I, I, I, I, P, P, P],
+    "qb_marlin_put_block": [P, P, P, P, P, P, I, I, I, I, I, I],
+    "qb_model_learn_block": [P, P, I, P, P, P, P],
+    "qb_model_set_pool": [P, P],
+    "qb_model_graph_stats": [P, P, P, P],
 }
 # measurement-only entry points (declared in csrc/measure.h, not part of the public header)
 MEASURE_SIGNATURES = {
@@ -111,6 +118,8 @@ MEASURE_SIGNATURES = {
     "qb_marlin_trace": [P, P],
     "qb_marlin_probe": [P, I],
     "qb_attr_cache_selftest": [],
+    "qb_graph_cache_selftest": [],
+    "qb_model_fail_captures": [P, I],
 }
 _RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
             "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,

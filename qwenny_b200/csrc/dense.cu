@@ -28,6 +28,40 @@ __global__ void __launch_bounds__(ROW_THREADS) embed_kernel(const __nv_bfloat16*
     o[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
 }
 
+// out[t] = row ids[t] of an int8 embedding table as stored: (E - 128) * its scale per 128 columns (S [rows][H / 128]).
+// A thread takes 8 codes (one 64-bit load; the table may sit in mapped host memory, so the row is fetched in as few,
+// as wide requests as the block has threads) and writes two float4; the first nkeys blocks clear the argmax keys.
+__global__ void __launch_bounds__(ROW_THREADS) embed_q8_kernel(const uint8_t* E, const float* S, const int* ids, float* out,
+                                                               unsigned long long* keys, int nkeys) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0 && t < nkeys) keys[t] = 0;
+    const size_t row = (size_t)ids[t];
+    const uint2 v = ((const uint2*)(E + row * H))[threadIdx.x];
+    const float sc = S[row * (H / 128) + threadIdx.x / 16];
+    float4* o = (float4*)(out + (size_t)t * H) + 2 * threadIdx.x;
+    auto code = [](uint32_t w, int b) { return (float)((int)((w >> (8 * b)) & 255u) - 128); };
+    o[0] = make_float4(code(v.x, 0) * sc, code(v.x, 1) * sc, code(v.x, 2) * sc, code(v.x, 3) * sc);
+    o[1] = make_float4(code(v.y, 0) * sc, code(v.y, 1) * sc, code(v.y, 2) * sc, code(v.y, 3) * sc);
+}
+
+// One learned 16-row block into a Marlin matrix of n rows: thread (k16, lane) of the block's words [k16][32] writes the
+// word of lane `lane` and block `blk` of the 64-row group c64 (per k16 step 2 n words, at 128 c64 + 4 lane + blk);
+// threads (k16 < tables * groups, lane < 16) also write row lane's scale of group k16 to its permuted place.
+__global__ void __launch_bounds__(256) put_block_kernel(uint32_t* B, __half* S, const uint32_t* words, const __half* sc,
+                                                        int n, int c64, int blk, int groups, int tables, int k16s) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int k16 = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (k16 >= k16s) return;
+    B[(size_t)k16 * 2 * n + (size_t)(c64 * 32 + lane) * 4 + blk] = words[k16 * 32 + lane];
+    if (k16 < groups * tables && lane < 16) {
+        const int c = blk * 16 + lane;
+        S[(size_t)k16 * n + c64 * 64 + 8 * (c % 8) + c / 8] = sc[k16 * 16 + lane];
+    }
+}
+
 __device__ __forceinline__ void store_norm8(__half* y, const float* v, const float* w, float r) {
     uint4 o;
     o.x = pack_half2(w[0] * (v[0] * r), w[1] * (v[1] * r));
@@ -203,6 +237,22 @@ int qb_embed(qb_ctx* ctx, void* stream, const void* E, const int* ids, float* ou
     if (!ctx || !E || !ids || !out || n <= 0 || nkeys > n || (nkeys > 0 && !keys)) return QB_ERR_ARG;
     return launch(ctx, embed_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, (const __nv_bfloat16*)E, ids,
                   out, keys, nkeys);
+}
+
+int qb_embed_q8(qb_ctx* ctx, void* stream, const void* E, const float* S, const int* ids, float* out,
+                unsigned long long* keys, int nkeys, int n) {
+    if (!ctx || !E || !S || !ids || !out || n <= 0 || nkeys > n || (nkeys > 0 && !keys)) return QB_ERR_ARG;
+    return launch(ctx, embed_q8_kernel, dim3(n), dim3(ROW_THREADS), 0, (cudaStream_t)stream, (const uint8_t*)E, S, ids,
+                  out, keys, nkeys);
+}
+
+int qb_marlin_put_block(qb_ctx* ctx, void* stream, void* B, void* S, const void* words, const void* sc, int n, int c64,
+                        int blk, int groups, int tables, int k16s) {
+    if (!ctx || !B || !S || !words || !sc || n <= 0 || n % 64 || c64 < 0 || (c64 + 1) * 64 > n || blk < 0 || blk > 3 ||
+        groups <= 0 || tables < 1 || tables > 2 || k16s < groups * tables)
+        return QB_ERR_ARG;
+    return launch(ctx, put_block_kernel, dim3((k16s + 7) / 8), dim3(256), 0, (cudaStream_t)stream, (uint32_t*)B, (__half*)S,
+                  (const uint32_t*)words, (const __half*)sc, n, c64, blk, groups, tables, k16s);
 }
 
 int qb_rmsnorm(qb_ctx* ctx, void* stream, const float* x, const float* w, void* y, float eps, int n) {

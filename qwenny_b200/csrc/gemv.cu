@@ -255,7 +255,7 @@ extern "C" int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const 
 // inside the library image: every GPU that loads the library holds these QB_STATIC_SCRATCH_BYTES until exit.
 namespace {
 
-constexpr size_t STATIC_PARTIAL_BYTES = 4u << 20;   // [n / 64][sharers][4][32] float4 of one product
+constexpr size_t STATIC_PARTIAL_BYTES = 16u << 20;  // [n / 64][sharers][4][32] float4 of one product
 constexpr size_t STATIC_TICKETS = 4096;             // one per 64 outputs: n <= 262144
 constexpr size_t STATIC_BYTES = STATIC_PARTIAL_BYTES + STATIC_TICKETS * sizeof(int) + 256;
 
@@ -270,6 +270,20 @@ int g_static_sms[MAX_DEVICES] = {0};
 }  // namespace
 
 extern "C" int qb_static_scratch_bytes(void) { return (int)STATIC_BYTES; }
+
+// The error word of the allocation-free products on the current device: non-zero once one of them gave up a bounded
+// wait (its output is then incomplete). Reads and clears it; waits for the device. 0 when no such product ran yet.
+extern "C" int qb_static_device_error(void) {
+    int dev = -1;
+    QB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES || !g_static_ptr[dev]) return 0;
+    int* err = (int*)(g_static_ptr[dev] + STATIC_PARTIAL_BYTES + STATIC_TICKETS * sizeof(int));
+    int v = 0;
+    QB_CUDA(cudaDeviceSynchronize());
+    QB_CUDA(cudaMemcpy(&v, err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) QB_CUDA(cudaMemset(err, 0, sizeof(int)));
+    return v;
+}
 
 extern "C" int qb_marlin_gemm_noalloc(void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                                       int k, int row0, int epi, const int* xrows, unsigned long long* keys,

@@ -15,7 +15,12 @@ int qb_marlin_trace(qb_ctx* ctx, long long* buf);
 /* mode 1 makes the products' consumers release every stage unread, so a launch times the copy pipeline alone (its
  * results are meaningless); 0 restores the product. */
 int qb_marlin_probe(qb_ctx* ctx, int mode);
-/* Host-only check of the per-device kernel-attribute bookkeeping; 0 when it holds. */
+/* Tests: the next n graph captures of the model report out of memory without touching the GPU. */
+struct qb_model;
+int qb_model_fail_captures(struct qb_model* m, int n);
+/* Host-only checks of the step-graph cache policy (with fakes behind its hooks) and of the per-device
+ * kernel-attribute bookkeeping; 0 when they hold. */
+int qb_graph_cache_selftest(void);
 int qb_attr_cache_selftest(void);
 #ifdef __cplusplus
 }

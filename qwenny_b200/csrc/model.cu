@@ -14,6 +14,7 @@
 #include <vector>
 #include "common.cuh"
 #include "ctx.h"
+#include "graphs.h"
 #include "session.h"
 
 using namespace qb;
@@ -38,6 +39,15 @@ struct GraphKey {
     int v[10];
     bool operator<(const GraphKey& o) const { return std::memcmp(v, o.v, sizeof v) < 0; }
 };
+
+// a captured step and its kernel count
+struct StepGraph {
+    cudaGraphExec_t ex = nullptr;
+    int kernels = 0;
+};
+
+// device memory outside the cache pool that the graphs leave free (GRAPH_FLOOR, src/cuda/core.rs:1108)
+constexpr size_t GRAPH_FLOOR = (size_t)128 << 20;
 
 }  // namespace
 
@@ -74,6 +84,9 @@ struct qb_model {
     qb_mtp mtp = {};
     __half* xin2 = nullptr;
     int *mtp_rows = nullptr, *draft_ids = nullptr, *dchain = nullptr, *h_chain = nullptr;
+    uint32_t* blk_words = nullptr;   // staging of a learned draft-head block: words, scales, tokens
+    uint16_t* blk_sc = nullptr;
+    int* blk_ids = nullptr;
     // the sampler's state (Step, src/cuda/core.rs:743-756), allocated with the first call that needs it: the slots'
     // generated-token sets, the rows' parameters and results, the stored draft distributions
     unsigned* outs = nullptr;
@@ -92,7 +105,11 @@ struct qb_model {
     unsigned char* staging = nullptr;
     size_t staging_bytes = 0;
     int *d_positions = nullptr, *h_positions = nullptr;
-    std::map<GraphKey, std::pair<cudaGraphExec_t, int>> graphs;  // the graph and its kernel count
+    // the captured steps (Graphs, src/cuda/core.rs:1117-1252): least recently used out when device memory runs short
+    qb::GraphCache<GraphKey, StepGraph>* graphs = nullptr;
+    qb_pool* pool = nullptr;   // the cache pool whose free pages go back to the driver when memory is shorter still
+    int fail_captures = 0;     // measurement / tests: the next captures report out of memory without touching the GPU
+    long long graphless = 0;   // steps that ran without a graph because theirs found no memory
     bool use_graphs = true, fused = true;
     // the DeltaNet layers' small 16-bit in-projection runs on a second stream, beside the int4 one (fork / join by
     // events; inside a captured graph the two become parallel branches)
@@ -366,6 +383,22 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
     m->ctx = ctx; m->nlayers = nlayers; m->slots = slots; m->max_ctx = max_ctx;
     m->vocab_rows = vocab_rows; m->vocab_valid = vocab_valid;
     m->layers.resize(nlayers + 1);  // + the MTP layer's place
+    {
+        qb::GraphCache<GraphKey, StepGraph>::Hooks hk;
+        hk.free_mem = []() -> size_t {
+            size_t fr = 0, tot = 0;
+            return cudaMemGetInfo(&fr, &tot) == cudaSuccess ? fr : (size_t)-1;
+        };
+        hk.destroy = [](StepGraph& g) { if (g.ex) cudaGraphExecDestroy(g.ex); g.ex = nullptr; };
+        hk.sync = []() { cudaDeviceSynchronize(); };
+        hk.release = [m](size_t bytes) -> size_t {
+            if (!m->pool) return 0;
+            size_t page = qb_pool_page(m->pool), given = 0;
+            if (page) qb_pool_release(m->pool, (bytes + page - 1) / page, &given);
+            return given;
+        };
+        m->graphs = new qb::GraphCache<GraphKey, StepGraph>(hk, GRAPH_FLOOR);
+    }
     QB_CUDA(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
     m->ev.resize(2 * (nlayers + 1));
     for (auto& e : m->ev) QB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -401,7 +434,7 @@ int qb_model_create(qb_ctx* ctx, int nlayers, int slots, int max_ctx, int vocab_
 
 void qb_model_destroy(qb_model* m) {
     if (!m) return;
-    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
+    delete m->graphs;
     for (auto& e : m->ev) cudaEventDestroy(e);
     for (auto& e : m->lev) cudaEventDestroy(e);
     if (m->side) cudaStreamDestroy(m->side);
@@ -410,7 +443,7 @@ void qb_model_destroy(qb_model* m) {
     if (m->h_sampled) cudaFreeHost(m->h_sampled);
     if (m->h_spans) cudaFreeHost(m->h_spans);
     if (m->h_positions) cudaFreeHost(m->h_positions);
-    void* sb[] = {m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions, m->slot_scale, m->lpart, m->lgu};
+    void* sb[] = {m->blk_words, m->blk_sc, m->blk_ids, m->outs, m->sparams, m->sampled, m->qtok, m->qn, m->qid, m->qp, m->d_spans, m->staging, m->d_positions, m->slot_scale, m->lpart, m->lgu};
     for (void* b : sb) cudaFree(b);
     void* bufs[] = {m->xin2, m->draft_ids, m->dchain, m->h, m->xn, m->part, m->ba, m->o, m->mix, m->mid, m->cv, m->q, m->ml, m->acc, m->logits, m->keys,
                     m->seen, m->d_step};
@@ -448,6 +481,7 @@ static int set_layer_at(qb_model* m, int i, const qb_layer* l) {
     }
     m->layers[i].w = *l;
     m->layers[i].set = true;
+    m->graphs->clear();  // captured steps hold the layer's old pointers
     return QB_OK;
 }
 
@@ -455,6 +489,7 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
                       const void* lm_s) {
     if (!m || !embed_bf16 || !final_norm || !lm_w || !lm_s) return QB_ERR_ARG;
     m->embed = embed_bf16; m->final_norm = final_norm; m->lm_w = lm_w; m->lm_s = lm_s;
+    m->graphs->clear();
     return QB_OK;
 }
 
@@ -468,8 +503,7 @@ int qb_model_use_graphs(qb_model* m, int on) {
 int qb_model_use_fork(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->fork != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
-        m->graphs.clear();
+        m->graphs->clear();
     }
     m->fork = on != 0;
     return QB_OK;
@@ -479,8 +513,7 @@ int qb_model_use_fork(qb_model* m, int on) {
 int qb_model_use_fused(qb_model* m, int on) {
     if (!m) return QB_ERR_ARG;
     if (m->fused != (on != 0)) {
-        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
-        m->graphs.clear();
+        m->graphs->clear();
     }
     m->fused = on != 0;
     return QB_OK;
@@ -590,28 +623,43 @@ static int run_kind(qb_model* m, void* stream, int kind) {
                      (m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0) +
                          64 * (m->ntile ? qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) : 0),
                      m->ndseg, m->dmax, kind + (m->lora_step ? 4 : 0)}};
-    auto it = m->graphs.find(key);
-    if (it == m->graphs.end()) {
-        // a first uncaptured run sets the kernels' attributes (not allowed while capturing) and warms the caches
-        QB_TRY(launch_step(m, st));
+    if (StepGraph* g = m->graphs->find(key)) {
+        QB_CUDA(cudaGraphLaunch(g->ex, st));
+        m->step_kernels = g->kernels;
         m->launches += m->step_kernels;
-        QB_CUDA(cudaStreamSynchronize(st));
+        return QB_OK;
+    }
+    // A first run outside a capture sets the kernels' attributes (not allowed while capturing), warms the caches and
+    // IS this step; the capture that follows only records. So a capture that fails costs the graph, never the step.
+    QB_TRY(launch_step(m, st));
+    m->launches += m->step_kernels;
+    QB_CUDA(cudaStreamSynchronize(st));
+    m->graphs->make_room();
+    cudaError_t e = cudaSuccess;
+    cudaGraphExec_t ex = nullptr;
+    if (m->fail_captures > 0) {
+        m->fail_captures--;
+        e = cudaErrorMemoryAllocation;
+    } else {
         cudaGraph_t g = nullptr;
         QB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         int rc = launch_step(m, st);
-        cudaError_t e = cudaStreamEndCapture(st, &g);
+        e = cudaStreamEndCapture(st, &g);
         if (rc) { if (g) cudaGraphDestroy(g); return rc; }
-        if (e != cudaSuccess) return (int)e;
-        cudaGraphExec_t ex = nullptr;
-        e = cudaGraphInstantiate(&ex, g, 0);
-        cudaGraphDestroy(g);
-        if (e != cudaSuccess) return (int)e;
-        it = m->graphs.emplace(key, std::make_pair(ex, m->step_kernels)).first;
-        return QB_OK;  // the uncaptured run above was this step
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&ex, g, 0);
+        if (g) cudaGraphDestroy(g);
     }
-    QB_CUDA(cudaGraphLaunch(it->second.first, st));
-    m->step_kernels = it->second.second;
-    m->launches += m->step_kernels;
+    if (e == cudaErrorMemoryAllocation) {
+        // no memory for the graph: fewer graphs from now on, this step (already run) without one
+        (void)cudaGetLastError();
+        m->graphs->on_out_of_memory();
+        m->graphless++;
+        return QB_OK;
+    }
+    if (e != cudaSuccess) return (int)e;
+    StepGraph sg;
+    sg.ex = ex; sg.kernels = m->step_kernels;
+    m->graphs->insert(key, sg);
     return QB_OK;
 }
 
@@ -625,7 +673,7 @@ int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp) {
     if (mtp->head_w && (!mtp->head_s || !mtp->head_ids || mtp->head_rows <= 0 || mtp->head_rows % 256 ||
                         mtp->head_valid <= 0 || mtp->head_valid > mtp->head_rows || mtp->head_rows > m->vocab_rows))
         return QB_ERR_ARG;
-    QB_TRY(set_layer_at(m, m->nlayers, &mtp->layer));
+    QB_TRY(set_layer_at(m, m->nlayers, &mtp->layer));  // (drops the captured steps)
     m->mtp = *mtp;
     if (!m->xin2) {
         QB_TRY(dalloc(&m->xin2, (size_t)MAX_TOK * 2 * H));
@@ -633,7 +681,63 @@ int qb_model_set_mtp(qb_model* m, const qb_mtp* mtp) {
         QB_TRY(dalloc(&m->dchain, (size_t)MAX_OUT * QB_MAX_DRAFTS));
         QB_CUDA(cudaMallocHost((void**)&m->h_chain, MAX_OUT * QB_MAX_DRAFTS * sizeof(int)));
     }
+    if (mtp->head_w && !m->blk_words) {
+        // the staging of a learned draft-head block (Gemm::block_stage, src/cuda/core.rs:672-676), taken once: no device
+        // memory is taken while serving
+        QB_TRY(dalloc(&m->blk_words, (size_t)H / 16 * 32));
+        QB_TRY(dalloc(&m->blk_sc, (size_t)2 * (H / 128) * 16));
+        QB_TRY(dalloc(&m->blk_ids, (size_t)16));
+    }
     m->has_mtp = true;
+    return QB_OK;
+}
+
+// DraftHead::learn for one 16-row block (src/cuda/qwen/draft.rs:56-72; Gemm::put_block, src/cuda/core.rs:614-671): the
+// block's packed words and scales (qb_marlin_block's output, host) go through the staging buffers into rows
+// 16 block .. 16 block + 15 of the draft head, its tokens into head_ids, and the rows count as valid from now on.
+// *grew: the head's valid row count changed (the MTP steps' graphs carry it and were dropped).
+int qb_model_learn_block(qb_model* m, void* stream, int block, const uint32_t* h_words, const uint16_t* h_sc,
+                         const int* h_ids16, int* grew) {
+    if (!m || !m->has_mtp || !m->mtp.head_w || !h_words || !h_sc || !h_ids16 || block < 0 ||
+        (block + 1) * 16 > m->mtp.head_rows)
+        return QB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int groups = H / 128, tables = m->mtp.head_zero_points ? 2 : 1;
+    QB_CUDA(cudaMemcpyAsync(m->blk_words, h_words, (size_t)H / 16 * 32 * sizeof(uint32_t), cudaMemcpyHostToDevice, st));
+    QB_CUDA(cudaMemcpyAsync(m->blk_sc, h_sc, (size_t)tables * groups * 16 * sizeof(uint16_t), cudaMemcpyHostToDevice, st));
+    QB_CUDA(cudaMemcpyAsync(m->blk_ids, h_ids16, 16 * sizeof(int), cudaMemcpyHostToDevice, st));
+    QB_TRY(qb_marlin_put_block(m->ctx, stream, (void*)m->mtp.head_w, (void*)m->mtp.head_s, m->blk_words, m->blk_sc,
+                               m->mtp.head_rows, block / 4, block % 4, groups, tables, H / 16));
+    QB_CUDA(cudaMemcpyAsync((int*)m->mtp.head_ids + 16 * block, m->blk_ids, 16 * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    QB_CUDA(cudaStreamSynchronize(st));  // the host buffers are the caller's again
+    const int valid = m->mtp.head_valid > (block + 1) * 16 ? m->mtp.head_valid : (block + 1) * 16;
+    if (grew) *grew = valid != m->mtp.head_valid;
+    if (valid != m->mtp.head_valid) {
+        m->mtp.head_valid = valid;
+        m->graphs->retain([](const GraphKey& k) { return (k.v[9] & 3) == 0; });  // the MTP kinds are 1 and 2
+    }
+    return QB_OK;
+}
+
+int qb_model_set_pool(qb_model* m, qb_pool* pool) {
+    if (!m) return QB_ERR_ARG;
+    m->pool = pool;
+    return QB_OK;
+}
+
+// graphs held now, the cap on them (-1: none yet), steps that ran without a graph for want of memory
+int qb_model_graph_stats(const qb_model* m, long long* held, long long* cap, long long* graphless) {
+    if (!m) return QB_ERR_ARG;
+    if (held) *held = (long long)m->graphs->size();
+    if (cap) *cap = m->graphs->cap() == qb::GraphCache<GraphKey, StepGraph>::NO_CAP ? -1 : (long long)m->graphs->cap();
+    if (graphless) *graphless = m->graphless;
+    return QB_OK;
+}
+
+// Tests: the next `n` graph captures behave as if the driver had no memory for them (nothing touches the GPU).
+int qb_model_fail_captures(qb_model* m, int n) {
+    if (!m || n < 0) return QB_ERR_ARG;
+    m->fail_captures = n;
     return QB_OK;
 }
 
@@ -873,6 +977,7 @@ int qb_model_set_adapter(qb_model* m, int layer, const qb_lora_layer* lora) {
     }
     m->any_lora = false;
     for (int i = 0; i < m->nlayers; i++) m->any_lora |= m->layers[i].has_lora;
+    m->graphs->clear();  // captured steps hold the old adapter's pointers and the layers' adapted / plain choice
     return QB_OK;
 }
 

@@ -101,6 +101,40 @@ static int pack_marlin(const uint32_t* h_q, const float* h_scales, const uint8_t
     return QB_OK;
 }
 
+// One 16-row block of a Marlin matrix, as the draft head learns rows (the host half of Gemm::put_block,
+// src/cuda/core.rs:614-656): the stored rows h_rows16[0..16) of the quantized matrix become the block's words
+// [cols/16][32 lanes] (marlin_word, :244-253) and its scales [tables * cols/128][16] (marlin_scale, :255-260; tables = 2
+// with zero points: the scales, then (8 - z) * scale). Without zero points every stored z must be 8 (QB_ERR_ARG).
+int qb_marlin_block(const uint32_t* h_q, const float* h_scales, const uint8_t* h_zeros, int zero_points, int rows,
+                    int cols, int group, const int* h_rows16, uint32_t* h_words, uint16_t* h_sc) {
+    if (!h_q || !h_scales || !h_rows16 || !h_words || !h_sc || cols % 128 || group % 128 || cols % group) return QB_ERR_ARG;
+    if (zero_points && !h_zeros) return QB_ERR_ARG;
+    const int words = cols / 8, groups = cols / 128, qgroups = cols / group;
+    for (int r = 0; r < 16; r++) {
+        if (h_rows16[r] < 0 || h_rows16[r] >= rows) return QB_ERR_ARG;
+        if (!zero_points && h_zeros)
+            for (int gi = 0; gi < qgroups; gi++)
+                if (h_zeros[(size_t)h_rows16[r] * qgroups + gi] != 8) return QB_ERR_ARG;  // a symmetric matrix
+    }
+    for (int k16 = 0; k16 < cols / 16; k16++)
+        for (int lane = 0; lane < 32; lane++) {
+            const int g = lane / 4, t = lane % 4;
+            uint32_t word = 0;
+            for (int x = 0; x < 8; x++) {
+                const int row = h_rows16[g + 8 * ((x >> 1) & 1)], c = k16 * 16 + 2 * t + 8 * (x & 1) + (x >> 2);
+                word |= ((h_q[(size_t)row * words + c / 8] >> ((c % 8) * 4)) & 15u) << (4 * x);
+            }
+            h_words[k16 * 32 + lane] = word;
+        }
+    for (int r = 0; r < 16; r++)
+        for (int gi = 0; gi < groups; gi++) {
+            const size_t gq = (size_t)h_rows16[r] * qgroups + gi * 128 / group;
+            h_sc[gi * 16 + r] = f16_bits(h_scales[gq]);
+            if (zero_points) h_sc[(groups + gi) * 16 + r] = f16_bits((8.f - (float)h_zeros[gq]) * h_scales[gq]);
+        }
+    return QB_OK;
+}
+
 // A dense matrix (f32 [rows][cols]) -> f16 tiles of 16 rows in mma A-fragment order, [tile][cols/16][32 lanes][8]
 // (pack, src/cuda/core.rs:337-391, the f16 branch; frag :222-227). rows = n packed rows through h_order.
 int qb_pack_f16(const float* h_w, int rows, int cols, const int* h_order, int n, uint16_t* h_out) {

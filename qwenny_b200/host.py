@@ -56,6 +56,25 @@ def pack_marlin(codes: np.ndarray, scales: np.ndarray, silu: bool = False, order
     return words, s16.view(np.float16)
 
 
+def marlin_block(codes: np.ndarray, scales: np.ndarray, rows16, zeros: np.ndarray | None = None, zero_points: bool = False,
+                 group: int = QG):
+    """The host half of Gemm::put_block (src/cuda/core.rs:614-656): the 16 stored rows `rows16` of a quantized matrix
+    (codes uint8 [rows][cols] = q + 8, scales f32 [rows][cols/group], zeros uint8 or None) -> (words uint32
+    [cols/16][32], scales float16 [tables * cols/128][16])."""
+    rows, cols = codes.shape
+    q = np.ascontiguousarray(quant_words(codes))
+    sc = np.ascontiguousarray(scales, dtype=np.float32)
+    r16 = np.ascontiguousarray(rows16, dtype=np.int32)
+    assert r16.shape == (16,)
+    z = None if zeros is None else np.ascontiguousarray(zeros, dtype=np.uint8)
+    tables = 2 if zero_points else 1
+    words = np.empty((cols // 16, 32), dtype=np.uint32)
+    s16 = np.empty((tables * (cols // 128), 16), dtype=np.uint16)
+    check(lib().qb_marlin_block(_np(q), _np(sc), C.c_void_p(0) if z is None else _np(z), int(zero_points), rows, cols,
+                                group, _np(r16), _np(words), _np(s16)), "qb_marlin_block")
+    return words, s16.view(np.float16)
+
+
 def pack_f16(w: np.ndarray, order: np.ndarray | None = None) -> np.ndarray:
     """f32 [rows][cols] -> float16 [rows/16][cols/16][32][8] (mma A-fragment order)."""
     rows, cols = w.shape

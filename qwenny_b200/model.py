@@ -125,6 +125,28 @@ class Model:
         self._cols = self.mtp["head"].n if self.mtp.get("head") is not None else None
         return [list(res[i * k:(i + 1) * k]) for i in range(len(out))]
 
+    def learn_block(self, block, words, scales16, ids16) -> bool:
+        """DraftHead::learn for one 16-row block: host arrays from host.marlin_block and the block's 16 tokens. Returns
+        whether the head's valid row count grew."""
+        import numpy as np
+        w = np.ascontiguousarray(words, dtype=np.uint32)
+        sc = np.ascontiguousarray(scales16).view(np.uint16)
+        ids = np.ascontiguousarray(ids16, dtype=np.int32)
+        grew = C.c_int(0)
+        s = C.c_void_p(self.stream.cuda_stream)
+        check(lib().qb_model_learn_block(self.h, s, block, w.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p),
+                                         ids.ctypes.data_as(C.c_void_p), C.byref(grew)), "qb_model_learn_block")
+        return bool(grew.value)
+
+    def graph_stats(self):
+        """(graphs held, cap or -1, steps that ran without a graph for want of memory)."""
+        a, b, c = C.c_longlong(0), C.c_longlong(0), C.c_longlong(0)
+        check(lib().qb_model_graph_stats(self.h, C.byref(a), C.byref(b), C.byref(c)), "qb_model_graph_stats")
+        return a.value, b.value, c.value
+
+    def fail_captures(self, n: int):
+        check(lib().qb_model_fail_captures(self.h, n), "qb_model_fail_captures")
+
     def set_adapter(self, i, lora):
         """Layer i's LoRA (LayerLora, src/cuda/qwen/lora.rs:199-205): lora = dict(rank=r, inp=.., out=.., gate_up=..,
         down=..), each product None or dict(a=packed f16 device tensor, a_tiles=.., b=f16 [rows][r] device tensor in the

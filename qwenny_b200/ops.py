@@ -88,6 +88,17 @@ class Context:
     def embed(self, table, ids, out, keys, nkeys, n):
         check(lib().qb_embed(self.h, _stream(), _p(table), _p(ids), _p(out), _p(keys), nkeys, n), "qb_embed")
 
+    def embed_q8(self, table, scales, ids, out, keys, nkeys, n):
+        check(lib().qb_embed_q8(self.h, _stream(), _p(table), _p(scales), _p(ids), _p(out), _p(keys), nkeys, n),
+              "qb_embed_q8")
+
+    def marlin_put_block(self, words, scales, blk_words, blk_scales, block, tables=1):
+        """qb_marlin_put_block: the 16-row block `block` of the Marlin matrix (words int32 [k/16][2n], scales f16
+        [tables * k/128][n]) from device staging buffers blk_words [k/16][32], blk_scales [tables * k/128][16]."""
+        k16s, n = words.shape[0], words.shape[1] // 2
+        check(lib().qb_marlin_put_block(self.h, _stream(), _p(words), _p(scales), _p(blk_words), _p(blk_scales), n,
+                                        block // 4, block % 4, k16s // 8, tables, k16s), "qb_marlin_put_block")
+
     def mtp_in(self, emb, h, rows, fw, pre_e, pre_h, y, n, eps=1e-6):
         check(lib().qb_mtp_in(self.h, _stream(), _p(emb), _p(h), _p(rows), _p(fw), _p(pre_e), _p(pre_h), _p(y), eps, n),
               "qb_mtp_in")

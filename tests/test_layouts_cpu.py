@@ -107,3 +107,69 @@ def test_pack_i8_matches_oracle():
     q, scale = R.quant_i8(w)
     assert np.abs(q).max() == 127 and scale[5, 1] == 1.0 and np.all(q[5, 128:256] == 0)
     assert np.abs(R.dequant_i8(w) - w).max() <= scale.max() * 0.5 + 1e-7
+
+
+def test_marlin_block_and_put_block_assemble_pack_marlin():
+    """A matrix filled block by block (Gemm::put_block: the host's words and scales of 16 rows, then the scatter of
+    marlin_put_block) is the matrix pack_marlin makes at once, with and without zero points; the library's host half
+    equals the oracle's."""
+    g = np.random.default_rng(5)
+    rows, cols = 128, 256
+    q = g.integers(0, 16, (rows, cols)).astype(np.uint8)
+    sc = (np.abs(g.standard_normal((rows, cols // 128))) * 0.01 + 1e-4).astype(np.float16).astype(np.float32)  # f16 values
+    zeros = g.integers(0, 16, (rows, cols // 128)).astype(np.uint8)
+    order = g.permutation(rows)
+    for z in (None, zeros):
+        want_w, want_s = host.pack_marlin(q, sc, order=order, zeros=z)
+        B = np.zeros_like(want_w)
+        S = np.zeros_like(want_s)
+        for block in range(rows // 16):
+            r16 = order[16 * block:16 * block + 16]
+            w, s16 = host.marlin_block(q, sc, r16, zeros=z, zero_points=z is not None)
+            ow, os_ = R.marlin_block(q, sc.astype(np.float16), r16, z)
+            assert np.array_equal(w, ow) and np.array_equal(s16.view(np.uint16), os_.view(np.uint16))
+            R.put_block(B, S, w, s16, block)
+        assert np.array_equal(B, want_w)
+        assert np.array_equal(S.view(np.uint16), want_s.view(np.uint16))
+    # rows with zero points cannot enter a symmetric matrix (put_block's ensure!, src/cuda/core.rs:630-634)
+    with pytest.raises(Exception):
+        host.marlin_block(q, sc, order[:16], zeros=zeros, zero_points=False)
+
+
+def test_matrices_written_by_the_reference_kernel_pin_the_layout():
+    """tests/golden/ref_marlin_blocks.npz holds matrices the reference's compiled marlin_put_block wrote block by block
+    (make_golden_marlin.py): the positions of words and scales in pack_marlin's layout as executed reference code has
+    them. The oracle's and the library's packers must produce the same buffers bit for bit, and the oracle's unpack
+    must read the reference-written matrix back to the stored codes."""
+    import importlib.util
+    import os
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden_marlin", os.path.join(here, "make_golden_marlin.py"))
+    # the generator's seeded inputs, without importing its GPU side
+    src = open(spec.origin).read()
+    ns = {"np": np, "R": R}
+    exec(compile(src[src.index("ROWS, COLS ="):src.index("def write_with_reference")], spec.origin, "exec"), ns)
+    q, sc, zeros, order = ns["inputs"]()
+    gold = np.load(os.path.join(here, "ref_marlin_blocks.npz"))
+    ow, os_ = R.pack_marlin(q, sc, order)
+    assert np.array_equal(gold["words"], ow) and np.array_equal(gold["scales"], os_.view(np.uint16))
+    owz, osz = R.pack_marlin(q, sc, order, zeros)
+    assert np.array_equal(gold["words_z"], owz) and np.array_equal(gold["scales_z"], osz.view(np.uint16))
+    lw, ls = host.pack_marlin(q, sc.astype(np.float32), order=order)
+    assert np.array_equal(gold["words"], lw) and np.array_equal(gold["scales"], ls.view(np.uint16))
+    lwz, lsz = host.pack_marlin(q, sc.astype(np.float32), order=order, zeros=zeros)
+    assert np.array_equal(gold["words_z"], lwz) and np.array_equal(gold["scales_z"], lsz.view(np.uint16))
+    uq, us = R.unpack_marlin(gold["words"], gold["scales"].view(np.float16))
+    assert np.array_equal(uq, q[order]) and np.array_equal(us.view(np.uint16), sc[order].view(np.uint16))
+    # the int8 embedding lookup of the reference's embed_q8, and its cleared argmax keys
+    table, scales, ids = ns["embed_inputs"]()
+    assert np.array_equal(gold["embed_q8"], R.embed_q8(table, scales, ids))
+    assert gold["embed_keys"].tolist() == [0, 0, 1, 1]
+
+
+def test_host_bookkeeping_selftests():
+    """The step-graph cache policy (least recently used out when memory is short, three quarters kept after a capture
+    without memory) and the per-device kernel-attribute cache, each run against fakes inside the library."""
+    from qwenny_b200._lib import lib
+    assert lib().qb_graph_cache_selftest() == 0
+    assert lib().qb_attr_cache_selftest() == 0

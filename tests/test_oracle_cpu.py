@@ -172,3 +172,13 @@ def test_kv_quant_and_attention_against_float_math():
         s = (K @ q[0, h]) / 16.0
         p = np.exp(s - s.max()); p /= p.sum()
         assert np.allclose(out[0, h * R.HD:(h + 1) * R.HD], p @ V, rtol=1e-5, atol=1e-6)
+
+
+def test_threaded_dequant_equals_the_numpy_restatement():
+    """cpu_step.dequant_marlin (torch, threaded) against ref_ops.unpack_marlin + ref_ops.dequant on the same buffers."""
+    from oracle import cpu_step
+    g = np.random.default_rng(8)
+    words = g.integers(0, 2 ** 32, (512 // 16, 2 * 256), dtype=np.uint64).astype(np.uint32)
+    scales = (np.abs(g.standard_normal((512 // 128, 256))) * 0.01 + 1e-4).astype(np.float16)
+    q, s = R.unpack_marlin(words, scales)
+    assert np.array_equal(cpu_step.dequant_marlin(words, scales).numpy(), R.dequant(q, s).astype(np.float32))

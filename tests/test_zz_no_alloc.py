@@ -68,10 +68,11 @@ def test_noalloc_matches_the_context_product_twice_in_a_row(ctx):
     ta = 0xFFFFFFFF - (keys_a.cpu().numpy().view(np.uint64) & np.uint64(0xFFFFFFFF))
     tb = 0xFFFFFFFF - (keys_b.cpu().numpy().view(np.uint64) & np.uint64(0xFFFFFFFF))
     assert np.array_equal(ta, tb)
+    assert lib().qb_static_device_error() == 0   # no bounded wait of these products ran out
 
 
 def test_noalloc_refuses_what_does_not_fit():
-    assert lib().qb_static_scratch_bytes() < 5 << 20
+    assert lib().qb_static_scratch_bytes() < 17 << 20
     x = torch.zeros(5, 128, dtype=torch.float16, device="cuda")
     y = torch.zeros(8, device="cuda")
     big_n = 64 * 4096 + 256   # more 64-output groups than the array has tickets
@@ -81,3 +82,32 @@ def test_noalloc_refuses_what_does_not_fit():
     assert rc == 1003  # QB_ERR_TOO_LARGE
     rc = lib().qb_marlin_gemm_noalloc(s, _p(x), _p(w), _p(y), _p(w), 17, 256, 128, 0, 0, None, None, 0)
     assert rc == 1000  # more than 16 rows: QB_ERR_ARG
+
+
+def test_noalloc_takes_every_product_of_the_27b_step(ctx):
+    """The documented limit, shape by shape: every layer product of the 27B model at 5 and at 16 rows and the output
+    layer at 5 and 8 rows run out of the built-in array and equal the context product on the same stream-K path; the
+    output layer at 16 rows is refused before anything is enqueued."""
+    from qwenny_b200 import model as M
+    g = torch.Generator(device="cuda").manual_seed(5)
+    shapes = [(16384, 5120, "plain"), (14336, 5120, "plain"), (5120, 6144, "plain"), (34816, 5120, "silu"),
+              (5120, 17408, "plain"), (5120, 10240, "plain"), (152064, 5120, "plain")]
+    for n, k, epi in shapes:
+        w = M.Marlin.random(n, k, g)
+        for m in (5, 16):
+            x = torch.randn(m, k, generator=g, device="cuda").half()
+            y = torch.zeros(m, n // 2, dtype=torch.float16, device="cuda") if epi == "silu" else torch.zeros(m, n, device="cuda")
+            if n > 131072 and m > 8:
+                assert noalloc(x, w.words, w.scales, epi, y) == 1003   # QB_ERR_TOO_LARGE
+                m = 8
+                x, y = x[:8].contiguous(), y[:8].contiguous()
+            assert noalloc(x, w.words, w.scales, epi, y) == 0, (n, k, m)
+            ctx.tune(ctas=-2)
+            try:
+                want = ctx.marlin_gemm(x, w.words, w.scales, epi=epi)
+            finally:
+                ctx.tune()
+            torch.cuda.synchronize()
+            assert torch.equal(y, want), (n, k, m)
+        del w
+    assert lib().qb_static_device_error() == 0
