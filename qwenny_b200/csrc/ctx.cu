@@ -94,6 +94,7 @@ void qb_destroy(qb_ctx* c) {
     cudaFree(c->scratch);
     cudaFree(c->counters);
     cudaFree(c->err);
+    cudaFree(c->delta_tp);
     delete c;
 }
 

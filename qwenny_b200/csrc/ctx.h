@@ -14,6 +14,8 @@ struct qb_ctx {
     int* counters = nullptr;
     size_t ncounters = 0;
     int* err = nullptr;  // device word
+    float* delta_tp = nullptr;  // scratch of the chunked delta rule (T, P, log decays per chunk and value head), taken by
+                                // the first prompt-sized DeltaNet step
     // measurement override of the GEMV plan (0: built-in choice)
     int tune_cg = 0, tune_kg = 0, tune_nstages = 0, tune_ctas = 0;
     bool no_cluster = false, no_tc = false;

@@ -46,14 +46,23 @@ delta_prep_kernel(const float* p, int splits, int n, const float* ba, int ba_spl
     const float4 taps = ld4(cw + (size_t)ch * CONV_K);
     pdl_wait();
     const size_t stride = (size_t)n * DELTA_IN;
-    float y[PREP_TOK];
+    // every load of the tile first (they are independent), the sliding window after
+    float x[PREP_TOK], y[PREP_TOK];
+    int slots[PREP_TOK], poss[PREP_TOK];
+#pragma unroll
+    for (int i = 0; i < PREP_TOK; i++) {
+        const int t = min(tb + i, n - 1);
+        x[i] = in_sum(p, splits, stride, (size_t)t * DELTA_IN + ch);
+        slots[i] = tok_slot[t];
+        poss[i] = tok_pos[t];
+    }
     float h0 = 0.f, h1 = 0.f, h2 = 0.f;  // the conv inputs at the three positions before the current token
     int prev_slot = -1;
 #pragma unroll
     for (int i = 0; i < PREP_TOK; i++) {
         y[i] = 0.f;
         if (i < cnt) {
-            const int t = tb + i, slot = tok_slot[t], pos = tok_pos[t];
+            const int t = tb + i, slot = slots[i], pos = poss[i];
             if (slot != prev_slot) {
                 // a segment starts in this tile (or the tile starts): fetch the history, from the step's own rows of
                 // the same sequence or from the slot's ring
@@ -66,13 +75,12 @@ delta_prep_kernel(const float* p, int splits, int n, const float* ba, int ba_spl
                 h0 = hist(3); h1 = hist(2); h2 = hist(1);
                 prev_slot = slot;
             }
-            const float x = in_sum(p, splits, stride, (size_t)t * DELTA_IN + ch);
             float a = taps.x * h0;
             a = fmaf(taps.y, h1, a);
             a = fmaf(taps.z, h2, a);
-            a = fmaf(taps.w, x, a);
+            a = fmaf(taps.w, x[i], a);
             y[i] = silu(a);
-            h0 = h1; h1 = h2; h2 = x;
+            h0 = h1; h1 = h2; h2 = x[i];
         }
     }
     if (head < 2 * LK_HEADS) {  // a q or k head: L2 norm over the block's 128 channels, q also / sqrt(128)
@@ -120,131 +128,17 @@ constexpr int RLD = 64 + 8;              // ... of R, D and V (read with the tok
 // checkpoint and the bank of the rollback plan are made in the token form)
 __host__ __device__ __forceinline__ int chunked_tokens(int len) { return len >= CH + KEEP ? (len - KEEP) / CH * CH : 0; }
 
-// grid (chunks of the longest possible segment, LK_HEADS, segs), block 256. tp: [chunk index][LV_HEADS][TP_FLOATS],
-// chunk index = first token of the chunk / 64 (distinct for disjoint 64-token ranges).
-constexpr int CP_THREADS = 256;
-constexpr int CP_SMEM = (2 * CH * KLD + 2 * CH * (CH + 1) + 3 * CH * (CH + 1) + 6 * CH) * 4;
-static_assert(3 * CH * (CH + 1) <= 2 * CH * KLD, "the three A matrices reuse the q / k tiles");
-
-__global__ void __launch_bounds__(CP_THREADS)
-delta_chunk_prep_kernel(const float* cv, float* tp, const int* seg_start, const int* seg_len) {
-    extern __shared__ __align__(16) float cps[];
-    float* Ks = cps;                         // [64][KLD]; later A of the three value heads [3][64][65]
-    float* Qs = Ks + CH * KLD;
-    float* KK = Qs + CH * KLD;               // [64][65]
-    float* QK = KK + CH * (CH + 1);
-    float* Ts = QK + CH * (CH + 1);          // [3][64][65]
-    float* gs = Ts + 3 * CH * (CH + 1);      // [3][64] cumulative log decay
-    float* bs = gs + 3 * CH;                 // [3][64] beta
-    pdl_launch_dependents();
-    const int c = blockIdx.x, kh = blockIdx.y, sg = blockIdx.z, tid = threadIdx.x;
-    const int t0 = seg_start[sg], len = seg_len[sg];
-    if (c * CH >= chunked_tokens(len)) return;
-    const int tok = t0 + c * CH;
-    const int G = LV_HEADS / LK_HEADS;
-    pdl_wait();
-    for (int x = tid; x < CH * (LKD / 4); x += CP_THREADS) {
-        const int r = x / (LKD / 4), d = (x % (LKD / 4)) * 4;
-        const float* row = cv + (size_t)(tok + r) * CVW + kh * LKD + d;
-        *(float4*)(Qs + r * KLD + d) = ld4(row);
-        *(float4*)(Ks + r * KLD + d) = ld4(row + LK_HEADS * LKD);
-    }
-    if (tid < 3 * 32) {  // a warp per value head: the gates, and the running sum of the log decays
-        const int hv = tid >> 5, lane = tid & 31, h = kh * G + hv;
-        float l0 = logf(cv[(size_t)(tok + 2 * lane) * CVW + LQKV + h]);
-        float l1 = logf(cv[(size_t)(tok + 2 * lane + 1) * CVW + LQKV + h]);
-        bs[hv * CH + 2 * lane] = cv[(size_t)(tok + 2 * lane) * CVW + LQKV + LV_HEADS + h];
-        bs[hv * CH + 2 * lane + 1] = cv[(size_t)(tok + 2 * lane + 1) * CVW + LQKV + LV_HEADS + h];
-        float run = l0 + l1;  // inclusive scan of the pair sums over the lanes
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            float up = __shfl_up_sync(0xffffffffu, run, o);
-            if (lane >= o) run += up;
-        }
-        gs[hv * CH + 2 * lane] = run - l1;
-        gs[hv * CH + 2 * lane + 1] = run;
-    }
-    __syncthreads();
-    // K K^T and Q K^T: thread (ti, tj) has rows ti + 16 a and columns tj + 16 b (interleaved, so that a quarter warp's
-    // 128-bit loads fall on distinct banks)
-    {
-        const int ti = tid >> 4, tj = tid & 15;
-        float kk[4][4], qk[4][4];
-#pragma unroll
-        for (int a = 0; a < 4; a++)
-#pragma unroll
-            for (int b = 0; b < 4; b++) kk[a][b] = qk[a][b] = 0.f;
-        for (int d = 0; d < LKD; d += 4) {
-            float4 kr[4], qr[4], kc[4];
-#pragma unroll
-            for (int a = 0; a < 4; a++) {
-                kr[a] = *(const float4*)(Ks + (ti + 16 * a) * KLD + d);
-                qr[a] = *(const float4*)(Qs + (ti + 16 * a) * KLD + d);
-                kc[a] = *(const float4*)(Ks + (tj + 16 * a) * KLD + d);
-            }
-#pragma unroll
-            for (int a = 0; a < 4; a++)
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    kk[a][b] = fmaf(kr[a].x, kc[b].x, kk[a][b]); kk[a][b] = fmaf(kr[a].y, kc[b].y, kk[a][b]);
-                    kk[a][b] = fmaf(kr[a].z, kc[b].z, kk[a][b]); kk[a][b] = fmaf(kr[a].w, kc[b].w, kk[a][b]);
-                    qk[a][b] = fmaf(qr[a].x, kc[b].x, qk[a][b]); qk[a][b] = fmaf(qr[a].y, kc[b].y, qk[a][b]);
-                    qk[a][b] = fmaf(qr[a].z, kc[b].z, qk[a][b]); qk[a][b] = fmaf(qr[a].w, kc[b].w, qk[a][b]);
-                }
-        }
-#pragma unroll
-        for (int a = 0; a < 4; a++)
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                KK[(ti + 16 * a) * (CH + 1) + tj + 16 * b] = kk[a][b];
-                QK[(ti + 16 * a) * (CH + 1) + tj + 16 * b] = qk[a][b];
-            }
-    }
-    __syncthreads();
-    // A of the three value heads over the q / k tiles (done with), and P straight to global memory
-    float* As = Ks;
-    for (int x = tid; x < 3 * CH * CH; x += CP_THREADS) {
-        const int hv = x / (CH * CH), i = (x / CH) % CH, j = x % CH;
-        const float dec = j <= i ? __expf(gs[hv * CH + i] - gs[hv * CH + j]) : 0.f;
-        As[(hv * CH + i) * (CH + 1) + j] = j < i ? bs[hv * CH + i] * KK[i * (CH + 1) + j] * dec : 0.f;
-        float* out = tp + ((size_t)(tok >> 6) * LV_HEADS + kh * G + hv) * TP_FLOATS;
-        out[CH * CH + i * CH + j] = QK[i * (CH + 1) + j] * dec;
-        if (j == 0) out[2 * CH * CH + i] = gs[hv * CH + i];
-    }
-    __syncthreads();
-    // T = (I + A)^-1 by forward substitution, a thread per column: T_ic = -sum_{c <= j < i} A_ij T_jc below the unit
-    // diagonal (four running sums break the dependency chain)
-    if (tid < 3 * CH) {
-        const int hv = tid / CH, col = tid % CH;
-        const float* A = As + hv * CH * (CH + 1);
-        float* T = Ts + hv * CH * (CH + 1);
-        for (int i = 0; i < col; i++) T[i * (CH + 1) + col] = 0.f;
-        T[col * (CH + 1) + col] = 1.f;
-        for (int i = col + 1; i < CH; i++) {
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-            int j = col;
-            for (; j + 3 < i; j += 4) {
-                s0 = fmaf(A[i * (CH + 1) + j], T[j * (CH + 1) + col], s0);
-                s1 = fmaf(A[i * (CH + 1) + j + 1], T[(j + 1) * (CH + 1) + col], s1);
-                s2 = fmaf(A[i * (CH + 1) + j + 2], T[(j + 2) * (CH + 1) + col], s2);
-                s3 = fmaf(A[i * (CH + 1) + j + 3], T[(j + 3) * (CH + 1) + col], s3);
-            }
-            for (; j < i; j++) s0 = fmaf(A[i * (CH + 1) + j], T[j * (CH + 1) + col], s0);
-            T[i * (CH + 1) + col] = -((s0 + s1) + (s2 + s3));
-        }
-    }
-    __syncthreads();
-    for (int x = tid; x < 3 * CH * CH; x += CP_THREADS) {
-        const int hv = x / (CH * CH), i = (x / CH) % CH, j = x % CH;
-        tp[((size_t)(tok >> 6) * LV_HEADS + kh * G + hv) * TP_FLOATS + i * CH + j] = Ts[(hv * CH + i) * (CH + 1) + j];
-    }
-}
-
-// ---- 3 x TF32 on mma.sync m16n8k8: x = hi + lo with hi, lo TF32 values; a . b ~ lo_a hi_b + hi_a lo_b + hi_a hi_b
+// ---- 3 x TF32 on mma.sync m16n8k8: x = hi + lo, hi the upper 19 bits of x (a TF32 value), lo = x - hi exactly (the
+// tensor core ignores the 13 low bits of an operand, so lo enters with 11 more bits of x); a . b ~ lo_a hi_b + hi_a lo_b
+// + hi_a hi_b. Products that only feed the step's outputs take operands rounded to TF32 once.
 __device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float rest = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ uint32_t tf32_round(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
 }
 __device__ __forceinline__ void mma_tf32(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -265,6 +159,159 @@ __device__ __forceinline__ void mma3(float* c, const FragA& a, float b0, float b
     mma_tf32(c, a.lo, h0, h1);
     mma_tf32(c, a.hi, l0, l1);
     mma_tf32(c, a.hi, h0, h1);
+}
+
+// grid (chunks of the longest possible segment, LK_HEADS, segs), block 256. tp: [chunk index][LV_HEADS][TP_FLOATS],
+// chunk index = first token of the chunk / 64 (distinct for disjoint 64-token ranges).
+constexpr int CP_THREADS = 256;
+constexpr int CP_SMEM = (2 * CH * KLD + 2 * CH * (CH + 1) + 6 * CH) * 4;  // 102 KB: two blocks per SM
+static_assert(3 * CH * (CH + 1) <= 2 * CH * KLD, "the three A matrices reuse the q / k tiles");
+
+__global__ void __launch_bounds__(CP_THREADS)
+delta_chunk_prep_kernel(const float* cv, float* tp, const int* seg_start, const int* seg_len) {
+    extern __shared__ __align__(16) float cps[];
+    float* Ks = cps;                         // [64][KLD]; later A of the three value heads [3][64][65]
+    float* Qs = Ks + CH * KLD;
+    float* KK = Qs + CH * KLD;               // [64][65]; later scratch of the inverse
+    float* QK = KK + CH * (CH + 1);
+    float* gs = QK + CH * (CH + 1);          // [3][64] cumulative log decay
+    float* bs = gs + 3 * CH;                 // [3][64] beta
+    pdl_launch_dependents();
+    const int c = blockIdx.x, kh = blockIdx.y, sg = blockIdx.z, tid = threadIdx.x;
+    const int t0 = seg_start[sg], len = seg_len[sg];
+    if (c * CH >= chunked_tokens(len)) return;
+    const int tok = t0 + c * CH;
+    const int G = LV_HEADS / LK_HEADS;
+    pdl_wait();
+    for (int x = tid; x < CH * (LKD / 4); x += CP_THREADS) {
+        const int r = x / (LKD / 4), d = (x % (LKD / 4)) * 4;
+        const float* row = cv + (size_t)(tok + r) * CVW + kh * LKD + d;
+        cp_async16(Qs + r * KLD + d, row);
+        cp_async16(Ks + r * KLD + d, row + LK_HEADS * LKD);
+    }
+    cp_async_commit();
+    if (tid < 3 * 32) {  // a warp per value head: the gates, and the running sum of the log decays
+        const int hv = tid >> 5, lane = tid & 31, h = kh * G + hv;
+        float l0 = logf(cv[(size_t)(tok + 2 * lane) * CVW + LQKV + h]);
+        float l1 = logf(cv[(size_t)(tok + 2 * lane + 1) * CVW + LQKV + h]);
+        bs[hv * CH + 2 * lane] = cv[(size_t)(tok + 2 * lane) * CVW + LQKV + LV_HEADS + h];
+        bs[hv * CH + 2 * lane + 1] = cv[(size_t)(tok + 2 * lane + 1) * CVW + LQKV + LV_HEADS + h];
+        float run = l0 + l1;  // inclusive scan of the pair sums over the lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            float up = __shfl_up_sync(0xffffffffu, run, o);
+            if (lane >= o) run += up;
+        }
+        gs[hv * CH + 2 * lane] = run - l1;
+        gs[hv * CH + 2 * lane + 1] = run;
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // K K^T and Q K^T on the tensor cores (3 x TF32): warp (matrix, 16-row tile m) takes the column tiles of the lower
+    // triangle, 0 .. 2 m + 1
+    {
+        const int warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
+        const int m = warp & 3, nts = 2 * m + 2;
+        const float* ar = (warp >> 2 ? Qs : Ks) + (16 * m + g8) * KLD + t4;
+        const float* br = Ks + g8 * KLD + t4;
+        float* dst = warp >> 2 ? QK : KK;
+        float acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        for (int k0 = 0; k0 < LKD; k0 += 8) {
+            const FragA a = frag_a(ar[k0], ar[8 * KLD + k0], ar[k0 + 4], ar[8 * KLD + k0 + 4]);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (j < nts) mma3(acc[j], a, br[8 * j * KLD + k0], br[8 * j * KLD + k0 + 4]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float* d0 = dst + (16 * m + g8) * (CH + 1) + 8 * j + 2 * t4;
+            d0[0] = acc[j][0]; d0[1] = acc[j][1];
+            d0[8 * (CH + 1)] = acc[j][2]; d0[8 * (CH + 1) + 1] = acc[j][3];
+        }
+    }
+    __syncthreads();
+    // A of the three value heads over the q / k tiles (done with), and P straight to global memory
+    float* As = Ks;
+    for (int x = tid; x < 3 * CH * CH; x += CP_THREADS) {
+        const int hv = x / (CH * CH), i = (x / CH) % CH, j = x % CH;
+        const float dec = j <= i ? expf(gs[hv * CH + i] - gs[hv * CH + j]) : 0.f;
+        As[(hv * CH + i) * (CH + 1) + j] = j < i ? bs[hv * CH + i] * KK[i * (CH + 1) + j] * dec : 0.f;
+        float* out = tp + ((size_t)(tok >> 6) * LV_HEADS + kh * G + hv) * TP_FLOATS;
+        out[CH * CH + i * CH + j] = j <= i ? QK[i * (CH + 1) + j] * dec : 0.f;
+        if (j == 0) out[2 * CH * CH + i] = gs[hv * CH + i];
+    }
+    __syncthreads();
+    // T = (I + A)^-1, unit lower triangular, IN PLACE over A. The four 16 x 16 diagonal blocks by forward substitution,
+    // a thread per column (T_ic = -sum_{c <= j < i} A_ij T_jc), into scratch and back; then blocks merge pairwise,
+    // 16 -> 32 -> 64: for a block pair [[T11, 0], [T21, T22]] the lower left part is T21 = -T22 (A21 T11), two small
+    // products spread over the block (X = A21 T11 goes through scratch, so T21 may overwrite A21).
+    float* D0 = KK;                    // [3][4][16][17] the diagonal blocks' inverses
+    float* Xs = KK + 3 * 4 * 16 * 17;  // [3][32][33] scratch of the merges (K K^T and Q K^T are done with)
+    float* Ts = As;
+    if (tid < 3 * CH) {
+        const int hv = tid / CH, blk = (tid % CH) / 16, b0 = blk * 16, col = tid % 16;
+        const float* A = As + hv * CH * (CH + 1);
+        float* T = D0 + (hv * 4 + blk) * 16 * 17;
+        for (int i = 0; i < col; i++) T[i * 17 + col] = 0.f;
+        T[col * 17 + col] = 1.f;
+        for (int i = col + 1; i < 16; i++) {
+            float s0 = 0.f, s1 = 0.f;
+            int j = col;
+            for (; j + 1 < i; j += 2) {
+                s0 = fmaf(A[(b0 + i) * (CH + 1) + b0 + j], T[j * 17 + col], s0);
+                s1 = fmaf(A[(b0 + i) * (CH + 1) + b0 + j + 1], T[(j + 1) * 17 + col], s1);
+            }
+            if (j < i) s0 = fmaf(A[(b0 + i) * (CH + 1) + b0 + j], T[j * 17 + col], s0);
+            T[i * 17 + col] = -(s0 + s1);
+        }
+    }
+    __syncthreads();
+    for (int x = tid; x < 3 * 4 * 256; x += CP_THREADS) {
+        const int hv = x / 1024, blk = (x / 256) % 4, i = (x % 256) / 16, j = x % 16;
+        Ts[(hv * CH + blk * 16 + i) * (CH + 1) + blk * 16 + j] = D0[((hv * 4 + blk) * 16 + i) * 17 + j];
+    }
+    __syncthreads();
+    for (int half = 16; half < CH; half *= 2) {
+        const int pairs = CH / (2 * half), per = half * half;
+        // X = A21 T11 (T11 lower triangular: the sum over b starts at the column)
+        for (int x = tid; x < 3 * pairs * per; x += CP_THREADS) {
+            const int hv = x / (pairs * per), pr = (x / per) % pairs, i = (x % per) / half, j = x % half;
+            const int base = pr * 2 * half;
+            const float* A = As + hv * CH * (CH + 1) + (base + half + i) * (CH + 1) + base;
+            const float* T = Ts + hv * CH * (CH + 1) + base * (CH + 1) + base + j;
+            float s0 = 0.f, s1 = 0.f;
+            int b = j;
+            for (; b + 1 < half; b += 2) {
+                s0 = fmaf(A[b], T[b * (CH + 1)], s0);
+                s1 = fmaf(A[b + 1], T[(b + 1) * (CH + 1)], s1);
+            }
+            if (b < half) s0 = fmaf(A[b], T[b * (CH + 1)], s0);
+            Xs[(hv * 32 + pr * half + i) * 33 + j] = s0 + s1;
+        }
+        __syncthreads();
+        // T21 = -T22 X (T22 lower triangular: the sum over a ends at the row)
+        for (int x = tid; x < 3 * pairs * per; x += CP_THREADS) {
+            const int hv = x / (pairs * per), pr = (x / per) % pairs, i = (x % per) / half, j = x % half;
+            const int base = pr * 2 * half;
+            const float* T22 = Ts + hv * CH * (CH + 1) + (base + half + i) * (CH + 1) + base + half;
+            const float* X = Xs + (hv * 32 + pr * half) * 33 + j;
+            float s0 = 0.f, s1 = 0.f;
+            int a2 = 0;
+            for (; a2 + 1 <= i; a2 += 2) {
+                s0 = fmaf(T22[a2], X[a2 * 33], s0);
+                s1 = fmaf(T22[a2 + 1], X[(a2 + 1) * 33], s1);
+            }
+            if (a2 <= i) s0 = fmaf(T22[a2], X[a2 * 33], s0);
+            Ts[hv * CH * (CH + 1) + (base + half + i) * (CH + 1) + base + j] = -(s0 + s1);
+        }
+        __syncthreads();
+    }
+    for (int x = tid; x < 3 * CH * CH; x += CP_THREADS) {
+        const int hv = x / (CH * CH), i = (x / CH) % CH, j = x % CH;
+        tp[((size_t)(tok >> 6) * LV_HEADS + kh * G + hv) * TP_FLOATS + i * CH + j] = Ts[(hv * CH + i) * (CH + 1) + j];
+    }
 }
 
 constexpr int SC_THREADS = 512, SC_COLS = 64;   // threads of a scan block; value columns of its state slice
@@ -318,7 +365,7 @@ delta_scan_kernel(const float* p, int splits, int n, const float* cv, const floa
     if (l0 > 0) {
         // ================================================================ chunks
         st_rows<8>(&M.s[lc][0], S, sub);
-        const int mt = warp >> 1, nh = warp & 1;   // G1: 16 rows of [k; q] x 32 value columns per warp
+        const int mq = warp >> 2, nq = warp & 3;   // a warp's 16-row tile and 16-column tile in G1, G2 and G3
         auto load_q = [&](int tok) {
             for (int x = tid; x < CH * (LKD / 4); x += SC_THREADS) {
                 const int r = x / (LKD / 4), dd = (x % (LKD / 4)) * 4;
@@ -358,44 +405,52 @@ delta_scan_kernel(const float* p, int splits, int n, const float* cv, const floa
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // everything but P
             __syncthreads();
             if (tid < CH) {
-                M.gam[tid] = __expf(M.g[tid]);
-                M.dec[tid] = __expf(M.g[CH - 1] - M.g[tid]);
+                M.gam[tid] = expf(M.g[tid]);
+                M.dec[tid] = expf(M.g[CH - 1] - M.g[tid]);
             }
-            // ---- G1: [k; q] S^T, 128 x 64 over the 128 keys
-            float acc[4][4];
+            // ---- G1: K S^T (3 x TF32: it feeds the state) and Q S^T (q rounded once, S split: it feeds outputs only);
+            // warp (mq, nq) has rows 16 mq .. of both and the value columns 16 nq .. 16 nq + 15
+            float acck[2][4], acc[2][4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            for (int j = 0; j < 2; j++) {
+                acck[j][0] = acck[j][1] = acck[j][2] = acck[j][3] = 0.f;
+                acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+            }
             {
-                const float* ar = &M.kq[16 * mt + g8][t4];
-                const float* br = &M.s[32 * nh + g8][t4];
+                const float* ak = &M.kq[16 * mq + g8][t4];
+                const float* aq = &M.kq[CH + 16 * mq + g8][t4];
+                const float* br = &M.s[16 * nq + g8][t4];
 #pragma unroll 4
                 for (int k0 = 0; k0 < LKD; k0 += 8) {
-                    const FragA a = frag_a(ar[k0], ar[8 * KLD + k0], ar[k0 + 4], ar[8 * KLD + k0 + 4]);
+                    const FragA a = frag_a(ak[k0], ak[8 * KLD + k0], ak[k0 + 4], ak[8 * KLD + k0 + 4]);
+                    const uint32_t q4[4] = {tf32_round(aq[k0]), tf32_round(aq[8 * KLD + k0]), tf32_round(aq[k0 + 4]),
+                                            tf32_round(aq[8 * KLD + k0 + 4])};
 #pragma unroll
-                    for (int j = 0; j < 4; j++) mma3(acc[j], a, br[8 * j * KLD + k0], br[8 * j * KLD + k0 + 4]);
+                    for (int j = 0; j < 2; j++) {
+                        uint32_t h0, l0, h1, l1;
+                        tf32_split(br[8 * j * KLD + k0], h0, l0);
+                        tf32_split(br[8 * j * KLD + k0 + 4], h1, l1);
+                        mma_tf32(acck[j], a.lo, h0, h1);
+                        mma_tf32(acck[j], a.hi, l0, l1);
+                        mma_tf32(acck[j], a.hi, h0, h1);
+                        mma_tf32(acc[j], q4, l0, l1);
+                        mma_tf32(acc[j], q4, h0, h1);
+                    }
                 }
             }
             __syncthreads();  // gam / dec visible (written above), every warp done with q and with S as an operand
-            if (mt < 4) {
-                // k rows: R = b (V - gam K S^T), over V in place
 #pragma unroll
-                for (int hh = 0; hh < 2; hh++) {
-                    const int i = 16 * mt + g8 + 8 * hh;
-                    const float bi = M.b[i], gi = M.gam[i];
+            for (int hh = 0; hh < 2; hh++) {
+                // R = b (V - gam K S^T), over V in place; gam Q S^T stays in the registers until P D joins it
+                const int i = 16 * mq + g8 + 8 * hh;
+                const float bi = M.b[i], gi = M.gam[i];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        float2* rv = (float2*)&M.r[i][32 * nh + 8 * j + 2 * t4];
-                        const float2 v = *rv;
-                        *rv = make_float2(bi * (v.x - gi * acc[j][2 * hh]), bi * (v.y - gi * acc[j][2 * hh + 1]));
-                    }
-                }
-            } else {
-                // q rows: gam Q S^T stays in the registers until P D joins it
-#pragma unroll
-                for (int hh = 0; hh < 2; hh++) {
-                    const float gi = M.gam[16 * (mt - 4) + g8 + 8 * hh];
-#pragma unroll
-                    for (int j = 0; j < 4; j++) { acc[j][2 * hh] *= gi; acc[j][2 * hh + 1] *= gi; }
+                for (int j = 0; j < 2; j++) {
+                    float2* rv = (float2*)&M.r[i][16 * nq + 8 * j + 2 * t4];
+                    const float2 v = *rv;
+                    *rv = make_float2(bi * (v.x - gi * acck[j][2 * hh]), bi * (v.y - gi * acck[j][2 * hh + 1]));
+                    acc[j][2 * hh] *= gi;
+                    acc[j][2 * hh + 1] *= gi;
                 }
             }
             if (more) load_q(tok + CH);   // the q tile is free
@@ -421,8 +476,8 @@ delta_scan_kernel(const float* p, int splits, int n, const float* cv, const floa
                 }
             }
             __syncthreads();
-            if (more) load_tv(tok + CH);  // T, R (as V) and the gates are free ... but g / b feed gam, dec, b below:
-            cp_async_commit();            // they were copied to gam / dec and are not read again in this chunk; b is
+            if (more) load_tv(tok + CH);  // T, R (the value columns' place) and the gates are free: gam and dec hold what
+            cp_async_commit();            // the rest of the chunk needs of them
             // ---- G4: S' = gam_C S + D^T (k_j dec_j), 64 value columns x 128 keys over the chunk's tokens
             {
                 const int m4 = warp >> 2, nq = warp & 3;
@@ -453,21 +508,22 @@ delta_scan_kernel(const float* p, int splits, int n, const float* cv, const floa
             __syncthreads();
             if (more) load_k(tok + CH);   // the k tile is free
             cp_async_commit();
-            // ---- G3: O = gam Q S^T + P D on the q warps, straight to the output rows
-            if (mt >= 4) {
-                const int m3 = mt - 4;
-                const float* ar = &M.pm[16 * m3 + g8][t4];
-                const float* br = &M.d[t4][32 * nh + g8];
-                for (int k0 = 0; k0 < 16 * (m3 + 1); k0 += 8) {
-                    const FragA a = frag_a(ar[k0], ar[8 * TLD + k0], ar[k0 + 4], ar[8 * TLD + k0 + 4]);
+            // ---- G3: O = gam Q S^T + P D (operands rounded to TF32 once), straight to the output rows
+            {
+                const float* ar = &M.pm[16 * mq + g8][t4];
+                const float* br = &M.d[t4][16 * nq + g8];
+                for (int k0 = 0; k0 < 16 * (mq + 1); k0 += 8) {
+                    const uint32_t a4[4] = {tf32_round(ar[k0]), tf32_round(ar[8 * TLD + k0]), tf32_round(ar[k0 + 4]),
+                                            tf32_round(ar[8 * TLD + k0 + 4])};
 #pragma unroll
-                    for (int j = 0; j < 4; j++) mma3(acc[j], a, br[k0 * RLD + 8 * j], br[(k0 + 4) * RLD + 8 * j]);
+                    for (int j = 0; j < 2; j++)
+                        mma_tf32(acc[j], a4, tf32_round(br[k0 * RLD + 8 * j]), tf32_round(br[(k0 + 4) * RLD + 8 * j]));
                 }
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
-                    float* o = out + (size_t)(tok + 16 * m3 + g8 + 8 * hh) * MIX + h * LVD + vs * SC_COLS + 32 * nh + 2 * t4;
+                    float* o = out + (size_t)(tok + 16 * mq + g8 + 8 * hh) * MIX + h * LVD + vs * SC_COLS + 16 * nq + 2 * t4;
 #pragma unroll
-                    for (int j = 0; j < 4; j++) *(float2*)(o + 8 * j) = make_float2(acc[j][2 * hh], acc[j][2 * hh + 1]);
+                    for (int j = 0; j < 2; j++) *(float2*)(o + 8 * j) = make_float2(acc[j][2 * hh], acc[j][2 * hh + 1]);
                 }
             }
             __syncthreads();

@@ -329,18 +329,26 @@ def delta(args):
             print(f"  {nm:18s} min {c.min() / 1e3:6.2f}  median {np.median(c) / 1e3:6.2f}  max {c.max() / 1e3:6.2f} us")
         print("device error", ctx.device_error())
         return
-    ctx.delta_conv(part, 1, n, ba, 1, conv_w, a_log, dt_bias, mem, sst, cv, dev)
-    for _ in range(args.reps):
-        ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.reps):
-        ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1)
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / args.reps
-    print(f"delta_rule rows={n}: {us:.1f} us/launch = {us * 1e3 / n:.0f} ns/token, device error {ctx.device_error()}")
+    norm_w = torch.ones(128, device="cuda")
+    y = torch.zeros(n, MIX, dtype=torch.float16, device="cuda")
+    meta2 = meta.clone()
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / args.reps
+    us_conv = timed(lambda: ctx.delta_conv(part, 1, n, ba, 1, conv_w, a_log, dt_bias, mem, sst, cv, dev))
+    us = timed(lambda: ctx.delta_rule(part, 1, n, cv, mem, sst, meta, o, dev, 1))
+    us_norm = timed(lambda: ctx.delta_norm(part, 1, n, norm_w, o, y, meta2, dev, 1))
+    print(f"delta rows={n}: conv {us_conv:.1f} us, rule {us:.1f} us = {us * 1e3 / n:.0f} ns/token, norm {us_norm:.1f} us; "
+          f"device error {ctx.device_error()}")
 
 
 def main():

@@ -228,11 +228,12 @@ def test_fused_mixer_matches_the_three_kernels(ctx, case):
     assert torch.equal(mem1 != mem, mem2 != mem)              # the same places were written
 
 
-def test_prompt_geometry_gives_the_same_bits(ctx):
-    """Steps with prompt segments run the delta rule with 8 lanes per value column instead of 4 (twice the blocks);
-    both add a column's products in the same order: a 150-token prompt in one step (fine geometry) leaves exactly the
-    raw outputs and the end state of the same prompt in steps of 50 (decode geometry), and a 70-token continuation
-    that restarts inside the previous step's last 16 tokens replays from the bank to the same bits."""
+def test_chunked_prompt_matches_decode_sized_steps(ctx):
+    """Segments long enough run the delta rule in chunks of 64 tokens (the WY form on the tensor cores as 3 x TF32) up to
+    16..79 tokens before their end, then token by token: a 150-token prompt in one step, then an 80-token step that
+    restarts 10 tokens back (replay from the bank, one more chunk), against the same positions in steps of at most 50
+    tokens (token form throughout). Another summation order, so not bit for bit: raw outputs inside the benchmark's
+    tolerance and within 1e-4, the f32 end state within 1e-4."""
     g = synth.gen(97)
     w = [t.cuda() for t in weights(g)]
     T = 220
@@ -252,11 +253,86 @@ def test_prompt_geometry_gives_the_same_bits(ctx):
                 outs[i] = o[i - a].clone()
         mt = meta.cpu().numpy()[0]
         return outs, mem[mt[2] * R.SLOT_STATE:(mt[2] + 1) * R.SLOT_STATE].clone(), mt
-    # 150 in one step, then restart 10 tokens back (a rejected tail) with 80 tokens: both steps in the fine geometry
-    fine, sf, mf = run([(0, 150), (140, 220)])
-    # the same positions in steps of at most 50 tokens (decode geometry), restarting at 140 too
-    coarse, sc, mc = run([(0, 50), (50, 100), (100, 150), (140, 190), (190, 220)])
+    chunked, sf, mf = run([(0, 150), (140, 220)])
+    tokens, sc, mc = run([(0, 50), (50, 100), (100, 150), (140, 190), (190, 220)])
     assert mf[0] == mc[0] == T
-    for i in range(T):
-        assert torch.equal(fine[i], coarse[i]), f"position {i}"
-    assert torch.equal(sf, sc)
+    a = torch.stack([chunked[i] for i in range(T)]).cpu().numpy()
+    b = torch.stack([tokens[i] for i in range(T)]).cpu().numpy()
+    assert close(a, b).all() and np.abs(a - b).max() < 1e-4
+    assert (sf - sc).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("start", ["fresh", "continue"])
+def test_chunked_rule_2048_tokens_next_to_the_reference_kernel(ctx, ref, start):
+    """The benchmark's prompt variant (T = 2048, chunk size 64): the chunked scan against the reference's sequential
+    delta_rule kernel on the same buffers and against the f64 oracle; from zeros and continuing a random state. State
+    within 1e-4, outputs 1e-2 / 2e-3 after bf16 rounding; the banks and the conv ring are copies and must be identical."""
+    g = synth.gen(98)
+    n = 2048
+    p0 = 0 if start == "fresh" else 4096
+    mem = fresh_mem(1, g)
+    cv = rule_inputs(g, n)
+    part = torch.randn(1, n, R.DELTA_IN, generator=g)
+    meta = torch.tensor([[-1, 0, 0, 0]] if start == "fresh" else [[p0, p0 - 7, 1, 0]], dtype=torch.int32)
+    st = R.build_step([(0, 0, p0 + i) for i in range(n)], [0])
+    dv = ref_cuda.upload_step(st)
+    m1, m2 = mem.cuda(), mem.cuda()
+    o1, o2 = torch.zeros(n, R.MIX, device="cuda"), torch.zeros(n, R.MIX, device="cuda")
+    md = meta.cuda()
+    pd, cd = part.cuda(), cv.cuda()
+    ctx.delta_rule(pd, 1, n, cd, m1, SST, md, o1, dv, 1)
+    ref.delta(pd, 1, n, None, 0, None, None, None, None, m2, SST, md, cd, o2, None, st, dv, which=("rule",))
+    torch.cuda.synchronize()
+    a, b = o1.cpu().numpy(), o2.cpu().numpy()
+    assert close(a, b).all()
+    assert np.abs(a - b).max() < 1e-4
+    s1, s2 = m1.cpu().numpy(), m2.cpu().numpy()
+    assert np.abs(s1[:2 * R.SLOT_STATE] - s2[:2 * R.SLOT_STATE]).max() < 1e-4
+    assert np.array_equal(s1[2 * R.SLOT_STATE:R.SLOT_FLOATS], s2[2 * R.SLOT_STATE:R.SLOT_FLOATS])
+    # the f64 oracle on a sample of the heads would need the whole recurrence; hold the first 200 tokens to it instead
+    mo = mem.numpy().copy()
+    st2 = R.build_step([(0, 0, p0 + i) for i in range(200)], [0])
+    want = R.delta_rule(part.numpy()[:, :200], cv.numpy()[:200], mo, SST, meta.numpy(), st2["seg_start"], st2["seg_len"],
+                        st2["seg_slot"], st2["seg_pos0"])
+    assert np.abs(a[:200] - want).max() < 1e-4
+
+
+def test_rollback_after_a_chunked_prompt(ctx):
+    """A 100-token prompt (one chunk, then 36 tokens in the token form), then verify steps of 5 rows of which 3 are right
+    and a restart at the first rejected position, against the same prompt followed by one token per step: identical
+    outputs, bit for bit (the checkpoint, the bank and the replay are all made in the token form)."""
+    g = synth.gen(99)
+    w = [t.cuda() for t in weights(g)]
+    P, T = 100, 112
+    part = torch.randn(1, T, R.DELTA_IN, generator=g).cuda()
+    ba = torch.randn(1, T, 2 * R.LV_HEADS, generator=g).cuda()
+    wrong = torch.randn(1, T, R.DELTA_IN, generator=g).cuda()
+    wrong_ba = torch.randn(1, T, 2 * R.LV_HEADS, generator=g).cuda()
+
+    def sl(t, i, j):
+        return t[:, i:j].contiguous()
+
+    def prompt():
+        mem = torch.zeros(SST, device="cuda")
+        meta = torch.tensor([[-1, 0, 0, 0]], dtype=torch.int32, device="cuda")
+        layer_step(ctx, w, mem, meta, sl(part, 0, P), sl(ba, 0, P), [(0, 0, i) for i in range(P)])
+        return mem, meta
+    memA, metaA = prompt()
+    outsA = {}
+    for i in range(P, T):
+        y, _ = layer_step(ctx, w, memA, metaA, sl(part, i, i + 1), sl(ba, i, i + 1), [(0, 0, i)])
+        outsA[i] = y[0].clone()
+    memB, metaB = prompt()
+    outsB = {}
+    pos = P
+    while pos < T:
+        nrow = min(5, T - pos)
+        good = min(3, nrow)
+        pp = torch.cat([sl(part, pos, pos + good), sl(wrong, pos + good, pos + nrow)], dim=1).contiguous()
+        bb = torch.cat([sl(ba, pos, pos + good), sl(wrong_ba, pos + good, pos + nrow)], dim=1).contiguous()
+        y, _ = layer_step(ctx, w, memB, metaB, pp, bb, [(0, 0, pos + i) for i in range(nrow)])
+        for i in range(good):
+            outsB[pos + i] = y[i].clone()
+        pos += good
+    for i in range(P, T):
+        assert torch.equal(outsA[i], outsB[i]), f"position {i}"
