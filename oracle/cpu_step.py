@@ -177,73 +177,84 @@ class CpuModel:
         return h, xn
 
 
-def time_baseline(seconds: float = 15.0, threads: int | None = None, rows: int = 5, vocab: int = 151936):
-    """The CPU baseline of the benchmark: the fp32 forward of one [DeltaNet, DeltaNet, DeltaNet, attention] block of
-    the 27B shape (the matrix products and the element-wise work of a 5-row verify step; attention over 32000 int8
-    keys dequantised on the fly) plus the output layer, on `threads` host threads. The full 64-layer model does not
-    fit the host in f32 (~100 GB), so the block is timed and scaled by 16; the output layer is timed once per step.
+def host_block_model(seed: int = 0, position: int = 32000, vocab: int = 151936, layers=("delta", "delta", "delta", "attn"),
+                     max_ctx: int = 32768) -> CpuModel:
+    """One [DeltaNet, DeltaNet, DeltaNet, attention] block of the 27B shape and the output layer, built on the host
+    with the distributions of qwenny_b200.model.synthetic (random int4 words, bf16-valued scales |N(0, 0.02)| / 7 + 1e-4,
+    norms 1 + N(0, 0.02)), its caches filled as if `position` tokens had been processed. No GPU is involved."""
+    g = np.random.default_rng(seed)
+    f32 = np.float32
+
+    def marlin(n, k):
+        words = g.integers(0, 2 ** 32, (k // 16, 2 * n), dtype=np.uint64).astype(np.uint32)
+        sc = torch.from_numpy((np.abs(g.standard_normal((k // 128, n))) * (0.02 / 7) + 1e-4).astype(f32))
+        return words, sc.to(torch.bfloat16).to(torch.float16).numpy()
+
+    norm = lambda n: (1 + g.standard_normal(n) * 0.02).astype(f32)
+    cap = (max_ctx + 63) // 64 * 64
+    sst = (R.SLOT_FLOATS + 1023) // 1024 * 1024
+    ls = []
+    for kind in layers:
+        l = dict(kind=kind, input_norm=norm(R.H), post_norm=norm(R.H))
+        for name, (n, k) in dict(out=(R.H, R.MIX), gate_up=(2 * R.FF, R.H), down=(R.H, R.FF),
+                                 in_proj=(R.DELTA_IN if kind == "delta" else R.ATTN_IN, R.H)).items():
+            l[name + "_words"], l[name + "_scales"] = marlin(n, k)
+        if kind == "delta":
+            l["in_ba"] = (g.standard_normal((2 * R.LV_HEADS // 16, R.H // 16, 32, 8)) * 0.02).astype(np.float16)
+            l["conv_w"] = (g.standard_normal((R.LQKV, 4)) * 0.3).astype(f32)
+            l["a_log"] = (g.standard_normal(R.LV_HEADS) * 0.5).astype(f32)
+            l["dt_bias"] = (g.standard_normal(R.LV_HEADS) * 0.5).astype(f32)
+            l["norm_w"] = norm(R.LVD)
+            l["mem"] = (g.standard_normal(sst) * 0.01).astype(f32)
+            l["meta"] = np.array([[position, position, 0, 0]], dtype=np.int32)
+            l["sst"] = sst
+        else:
+            l["q_norm"], l["k_norm"] = norm(R.HD), norm(R.HD)
+            l["inv_freq"] = (1.0 / (R.THETA ** (np.arange(0, R.ROT, 2, dtype=np.float64) / R.ROT))).astype(f32)
+            nb = R.NKV * cap
+            l["kc"] = g.integers(1, 256, nb * R.HD, dtype=np.uint8)
+            l["vc"] = g.integers(1, 256, nb * R.HD, dtype=np.uint8)
+            l["ks"] = np.abs(g.standard_normal(nb) * 0.05).astype(f32)
+            l["vs"] = np.abs(g.standard_normal(nb) * 0.05).astype(f32)
+            l["cap"] = cap
+        ls.append(l)
+    rows = (vocab + 255) // 256 * 256
+    lm_w, lm_s = marlin(rows, R.H)
+    embed = (g.standard_normal((4096, R.H)) * 0.02).astype(f32)  # token ids below 4096 are enough for the timed rows
+    return CpuModel(ls, embed, norm(R.H), lm_w, lm_s, vocab, 1)
+
+
+def time_step_baseline(seconds: float = 15.0, threads: int | None = None, rows: int = 5, position: int = 32000,
+                       vocab: int = 151936, model: "CpuModel | None" = None):
+    """The CPU baseline of the benchmark: CpuModel.step, the oracle of the full path with the real op arithmetic
+    (int4 weights dequantised once to f32 as the reference's fp32 check path does, tools/make_reference.py:25-39; conv,
+    gated delta rule with its rollback plan, RoPE, int8 KV quantisation, attention over `position` int8 keys, norms),
+    on a verify step of `rows` rows at `position`: one [DeltaNet x3, attention] block and the output layer are timed
+    on `threads` host threads and the block is scaled by 16 (the 64-layer model in f32 does not fit a host).
     Returns dict(step_s, rows_per_s, cores, sample)."""
     if threads:
         torch.set_num_threads(threads)
     threads = torch.get_num_threads()
-    g = torch.Generator().manual_seed(0)
-    H, FF = R.H, R.FF
-    mk = lambda n, k: torch.randn(n, k, generator=g) * 0.01
-    blocks = []
-    for kind in ("delta", "delta", "delta", "attn"):
-        blocks.append(dict(kind=kind, inp=mk(R.DELTA_IN if kind == "delta" else R.ATTN_IN, H), out=mk(H, R.MIX),
-                           gu=mk(2 * FF, H), down=mk(H, FF)))
-    lm = mk(vocab, H)
-    ctx_keys = 32000
-    kc = torch.randint(-127, 128, (R.NKV, ctx_keys, R.HD), generator=g, dtype=torch.int8)
-    vc = torch.randint(-127, 128, (R.NKV, ctx_keys, R.HD), generator=g, dtype=torch.int8)
-    ksc, vsc = torch.rand(R.NKV, ctx_keys, generator=g) * 0.05, torch.rand(R.NKV, ctx_keys, generator=g) * 0.05
-    S = torch.randn(R.LV_HEADS, R.LVD, R.LKD, generator=g) * 0.01
-    x = torch.randn(rows, H, generator=g)
-
-    def norm(t):
-        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + 1e-6)
-
-    def block_pass():
-        h = x
-        for b in blocks:
-            p = norm(h) @ b["inp"].T
-            if b["kind"] == "delta":
-                q = torch.nn.functional.normalize(p[:, :2048].view(rows, 16, 128), dim=-1).repeat_interleave(3, 1)
-                k = torch.nn.functional.normalize(p[:, 2048:4096].view(rows, 16, 128), dim=-1).repeat_interleave(3, 1)
-                v = p[:, 4096:10240].view(rows, 48, 128)
-                St, o = S, []
-                for t in range(rows):
-                    dk = torch.einsum("hvk,hk->hv", St, k[t])
-                    d = (v[t] - 0.9 * dk) * 0.5
-                    o.append(0.9 * torch.einsum("hvk,hk->hv", St, q[t]) + d * (k[t] * q[t]).sum(-1, keepdim=True))
-                    St = 0.9 * St + d[:, :, None] * k[t][:, None, :]
-                mix = norm(torch.stack(o)).reshape(rows, -1) * torch.nn.functional.silu(p[:, 10240:])
-            else:
-                qh = p[:, :12288].view(rows, 24, 2, 256)[:, :, 0]
-                o = []
-                for gi in range(R.NKV):
-                    K = kc[gi].float() * ksc[gi][:, None]
-                    V = vc[gi].float() * vsc[gi][:, None]
-                    sc = torch.einsum("rhd,kd->rhk", qh[:, gi * 6:(gi + 1) * 6], K) / 16
-                    o.append(torch.softmax(sc, -1) @ V)
-                mix = torch.cat(o, 1).reshape(rows, -1)
-            h = h + mix @ b["out"].T
-            gu = norm(h) @ b["gu"].T
-            h = h + (torch.nn.functional.silu(gu[:, :FF]) * gu[:, FF:]) @ b["down"].T
-        return h
-
-    block_pass()  # warm-up
+    m = model if model is not None else host_block_model(position=position, vocab=vocab)
+    lm, full_valid = m.lm, m.vocab_valid
+    m.lm, m.vocab_valid = lm[:256], 256   # the block alone first: a 256-row stand-in for the output layer
+    pos = position
+    toks = lambda p: [(1000 + i, 0, p + i) for i in range(rows)]
+    m.step(toks(pos), list(range(rows)))   # warm-up
     t0, nb = time.time(), 0
     while True:
-        hlast = block_pass()
+        m.step(toks(pos), list(range(rows)))   # the same positions again: the drafts were "rejected", state rolls back
         nb += 1
         if time.time() - t0 > seconds * 0.8:
             break
     tb = (time.time() - t0) / nb
+    xn = np.random.default_rng(1).standard_normal((rows, R.H)).astype(np.float16)
     t1 = time.time()
-    _ = (norm(hlast) @ lm.T).argmax(-1)
+    logits = CpuModel._mm(xn, lm)
+    R.key_token(R.argmax_keys(logits, vocab))
     tl = time.time() - t1
+    m.lm, m.vocab_valid = lm, full_valid
     step_s = 16 * tb + tl
     return dict(step_s=step_s, rows_per_s=rows / step_s, cores=threads,
-                sample=f"{nb} passes of one [DeltaNet x3, attention] block x16 + 1 output layer, {rows} rows, f32 torch CPU")
+                sample=f"{nb} verify steps of {rows} rows at position {position} through one [DeltaNet x3, attention] "
+                       f"block of the CPU oracle (CpuModel.step: real op arithmetic, f32 weights), x16, + 1 output layer")

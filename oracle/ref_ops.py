@@ -386,25 +386,33 @@ def attn_decode(q, gate, kc, vc, ks, vs, tok_slot, tok_pos, cap, emulate_f16: bo
     tensor cores (:93-96, :198-216)."""
     n = q.shape[0]
     out = np.zeros((n, MIX), dtype=np.float32)
+    # the cache of a (slot, kv head) is decoded once per call, for the longest prefix any of the slot's tokens sees
+    longest = {}
     for t in range(n):
-        s, keys = int(tok_slot[t]), int(tok_pos[t]) + 1
+        s = int(tok_slot[t])
+        longest[s] = max(longest.get(s, 0), int(tok_pos[t]) + 1)
+    for s, most in longest.items():
         for g in range(NKV):
-            K = cache_keys(kc, s, g, cap, keys).astype(np.float64)
-            V = cache_values(vc, s, g, cap, keys).astype(np.float64)
-            ksc = ks[(s * NKV + g) * cap:(s * NKV + g) * cap + keys].astype(np.float64)
-            vsc = vs[(s * NKV + g) * cap:(s * NKV + g) * cap + keys].astype(np.float64)
-            for hh in range(GROUP):
-                h = g * GROUP + hh
-                qv = q[t, h].astype(np.float16).astype(np.float64) if emulate_f16 else q[t, h].astype(np.float64)
-                sc = (K @ qv) * ksc
-                m = sc.max()
-                p = np.exp2(sc - m)
-                l = p.sum()
-                pv = p * vsc
+            K = cache_keys(kc, s, g, cap, most).astype(np.float64)
+            V = cache_values(vc, s, g, cap, most).astype(np.float64)
+            base = (s * NKV + g) * cap
+            ksc, vsc = ks[base:base + most].astype(np.float64), vs[base:base + most].astype(np.float64)
+            for t in range(n):
+                if int(tok_slot[t]) != s:
+                    continue
+                keys = int(tok_pos[t]) + 1
+                qh = q[t, g * GROUP:(g + 1) * GROUP]
+                qv = qh.astype(np.float16).astype(np.float64) if emulate_f16 else qh.astype(np.float64)
+                sc = (K[:keys] @ qv.T) * ksc[:keys, None]          # [keys][GROUP]
+                p = np.exp2(sc - sc.max(axis=0, keepdims=True))
+                l = p.sum(axis=0)
+                pv = p * vsc[:keys, None]
                 if emulate_f16:
                     pv = pv.astype(np.float16).astype(np.float64)
-                o = pv @ V
-                out[t, h * HD:(h + 1) * HD] = (gate[t, h * HD:(h + 1) * HD] * (o / l)).astype(np.float32)
+                o = pv.T @ V[:keys]                                   # [GROUP][HD]
+                for hh in range(GROUP):
+                    h = g * GROUP + hh
+                    out[t, h * HD:(h + 1) * HD] = (gate[t, h * HD:(h + 1) * HD] * (o[hh] / l[hh])).astype(np.float32)
     return out
 
 

@@ -47,78 +47,100 @@ __host__ __device__ inline int dec_chunk(int keys) {
 __host__ __device__ inline int dec_splits(int keys) { int c = dec_chunk(keys); return (keys + c - 1) / c; }
 
 // ------------------------------------------------------------------------------------------------ attn_prep
-constexpr int PREP_WARPS = NH + 2 * NKV;
+// grid (n tokens, 2): block (t, 0) makes the 24 query heads and their gates (a warp per head), block (t, 1) the 4 key
+// and 4 value heads and stores them in the cache. A warp's lane owns dims lane + 32 j of its head: the RoPE pair
+// (d, d + 32) of the 64 rotated dims is then elements 0 and 1 of one lane, and the sum of squares adds the lane's eight
+// values in dim order, then the lanes as a butterfly: the order that makes the int8 codes the reference's, bit for bit.
+constexpr int HEAD_VALS = HD / 32;
 
-__global__ void __launch_bounds__(32 * PREP_WARPS)
+struct HeadRow {
+    float v[HEAD_VALS];
+};
+
+// the head row at `col` of token t's in-projection, summed over the split-K parts
+__device__ __forceinline__ HeadRow head_row(const float* part, int splits, int n, int t, int col, int lane) {
+    HeadRow r;
+#pragma unroll
+    for (int j = 0; j < HEAD_VALS; j++) r.v[j] = 0.f;
+    for (int sp = 0; sp < splits; sp++) {
+        const float* p = part + ((size_t)sp * n + t) * ATTN_IN + col + lane;
+#pragma unroll
+        for (int j = 0; j < HEAD_VALS; j++) r.v[j] += p[32 * j];
+    }
+    return r;
+}
+
+// RMSNorm with the head's weight (pre-biased 1 + w), then the rotation of the first 64 dims by pos * inv_freq
+__device__ __forceinline__ void norm_and_rotate(HeadRow& r, const float* w_lane, float angle) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < HEAD_VALS; j++) ss += r.v[j] * r.v[j];
+    const float rms = rsqrtf(warp_sum(ss) / HD + EPS);
+#pragma unroll
+    for (int j = 0; j < HEAD_VALS; j++) r.v[j] = w_lane[j] * (r.v[j] * rms);
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    const float a = r.v[0], b = r.v[1];
+    r.v[0] = a * cs - b * sn;
+    r.v[1] = b * cs + a * sn;
+}
+
+// One head row into the int8 cache: a scale per (position, head) = max |v| / 127, code = round(v * 127 / max) + 128.
+// KEY: the row's place is [pos][256] in kslot order; else the 16-position block [pos / 16][256][16] in vslot order.
+template <bool KEY>
+__device__ __forceinline__ void store_quantised(const HeadRow& r, uint8_t* head_cache, float* head_scales, int pos, int lane) {
+    float mx = 0.f;
+#pragma unroll
+    for (int j = 0; j < HEAD_VALS; j++) mx = fmaxf(mx, fabsf(r.v[j]));
+    mx = warp_max(mx);
+    const float inv = mx > 0.f ? 127.f / mx : 0.f;
+#pragma unroll
+    for (int j = 0; j < HEAD_VALS; j++) {
+        const int d = lane + 32 * j;
+        const uint8_t code = (uint8_t)(__float2int_rn(r.v[j] * inv) + 128);
+        head_cache[KEY ? (size_t)pos * HD + kslot(d) : vslot(pos, d)] = code;
+    }
+    if (lane == 0) head_scales[pos] = mx / 127.f;
+}
+
+__global__ void __launch_bounds__(32 * NH)
 attn_prep_kernel(const float* part, int splits, int n, const float* q_norm, const float* k_norm, const float* inv_freq,
                  float qscale, float* q, float* out, uint8_t* kc, uint8_t* vc, float* ks, float* vs,
                  const int* tok_slot, const int* tok_pos, int cap) {
     pdl_launch_dependents();
-    const int t = blockIdx.x, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // warp w: query head w (its q and gate), then the key heads, then the value heads
-    int col;
-    const float* nw;
-    if (w < NH) { col = w * 2 * HD; nw = q_norm; }
-    else if (w < NH + NKV) { col = QG_ROWS + (w - NH) * HD; nw = k_norm; }
-    else { col = QG_ROWS + NKV * HD + (w - NH - NKV) * HD; nw = nullptr; }
-    float nv[HD / 32];
-    if (nw) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool cache_block = blockIdx.y == 1;
+    if (cache_block && warp >= 2 * NKV) return;
+    // the norm weight of the lane's dims and its rotation frequency do not depend on earlier kernels
+    const bool normed = !cache_block || warp < NKV;
+    float w_lane[HEAD_VALS];
 #pragma unroll
-        for (int j = 0; j < HD / 32; j++) nv[j] = nw[lane + 32 * j];
-    }
-    float fr = inv_freq[lane];
+    for (int j = 0; j < HEAD_VALS; j++) w_lane[j] = normed ? (cache_block ? k_norm : q_norm)[lane + 32 * j] : 0.f;
+    const float freq = inv_freq[lane];
     pdl_wait();
     const int pos = tok_pos[t];
-    // the lane owns dims lane + 32 j: the RoPE pair (d, d + 32), d < 32, is j = 0 and 1 of one lane
-    float v[HD / 32], gl[HD / 32];
+    if (!cache_block) {
+        // query head `warp`: rows [q; gate] of the head are adjacent in the in-projection
+        HeadRow qr = head_row(part, splits, n, t, warp * 2 * HD, lane);
+        const HeadRow gate = head_row(part, splits, n, t, warp * 2 * HD + HD, lane);
+        norm_and_rotate(qr, w_lane, (float)pos * freq);
+        float* qo = q + ((size_t)t * NH + warp) * HD + lane;
+        float* go = out + (size_t)t * MIX + warp * HD + lane;
 #pragma unroll
-    for (int j = 0; j < HD / 32; j++) v[j] = gl[j] = 0.f;
-    for (int sp = 0; sp < splits; sp++) {
-        const float* p = part + ((size_t)sp * n + t) * ATTN_IN + col + lane;
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) v[j] += p[32 * j];
-        if (w < NH) {
-#pragma unroll
-            for (int j = 0; j < HD / 32; j++) gl[j] += p[HD + 32 * j];
+        for (int j = 0; j < HEAD_VALS; j++) {
+            qo[32 * j] = qr.v[j] * qscale;
+            go[32 * j] = 1.f / (1.f + expf(-gate.v[j]));
         }
+        return;
     }
-    if (nw) {
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) ss += v[j] * v[j];
-        float r = rsqrtf(warp_sum(ss) / HD + EPS);
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) v[j] = nv[j] * (v[j] * r);
-        float sn, cs;
-        sincosf((float)pos * fr, &sn, &cs);
-        float a = v[0], b = v[1];
-        v[0] = a * cs - b * sn;
-        v[1] = b * cs + a * sn;
-    }
-    if (w < NH) {
-        float* qo = q + ((size_t)t * NH + w) * HD;
-        float* go = out + (size_t)t * MIX + w * HD;
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) {
-            qo[lane + 32 * j] = v[j] * qscale;
-            go[lane + 32 * j] = 1.f / (1.f + expf(-gl[j]));
-        }
+    const int slot = tok_slot[t], g = warp % NKV;
+    if (warp < NKV) {
+        HeadRow kr = head_row(part, splits, n, t, QG_ROWS + g * HD, lane);
+        norm_and_rotate(kr, w_lane, (float)pos * freq);
+        store_quantised<true>(kr, kc + cache_head(slot, g, cap), ks + scale_head(slot, g, cap), pos, lane);
     } else {
-        // int8 with one scale per (position, head): code = round(v * 127 / max) + 128, scale = max / 127
-        const bool key = w < NH + NKV;
-        const int g = (w - NH) % NKV, slot = tok_slot[t];
-        uint8_t* c = (key ? kc : vc) + cache_head(slot, g, cap);
-        float mx = 0.f;
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) mx = fmaxf(mx, fabsf(v[j]));
-        mx = warp_max(mx);
-        float inv = mx > 0.f ? 127.f / mx : 0.f;
-#pragma unroll
-        for (int j = 0; j < HD / 32; j++) {
-            int d = lane + 32 * j;
-            c[key ? (size_t)pos * HD + kslot(d) : vslot(pos, d)] = (uint8_t)(__float2int_rn(v[j] * inv) + 128);
-        }
-        if (lane == 0) (key ? ks : vs)[scale_head(slot, g, cap) + pos] = mx / 127.f;
+        const HeadRow vr = head_row(part, splits, n, t, QG_ROWS + NKV * HD + g * HD, lane);
+        store_quantised<false>(vr, vc + cache_head(slot, g, cap), vs + scale_head(slot, g, cap), pos, lane);
     }
 }
 
@@ -797,7 +819,7 @@ int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n
     if (!ctx || !part || !q_norm || !k_norm || !inv_freq || !q || !out || !kc || !vc || !ks || !vs || !tok_slot ||
         !tok_pos || n <= 0 || splits < 1 || cap <= 0 || cap % 64)
         return QB_ERR_ARG;
-    return launch(ctx, attn_prep_kernel, dim3(n), dim3(32 * PREP_WARPS), 0, (cudaStream_t)stream, part, splits, n,
+    return launch(ctx, attn_prep_kernel, dim3(n, 2), dim3(32 * NH), 0, (cudaStream_t)stream, part, splits, n,
                   q_norm, k_norm, inv_freq, qscale, q, out, (uint8_t*)kc, (uint8_t*)vc, ks, vs, tok_slot, tok_pos, cap);
 }
 

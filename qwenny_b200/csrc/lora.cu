@@ -5,18 +5,22 @@
 // a plain product's first partial sums (lora_add), or apply SwiGLU to a plain [gate; up] product, in the SwiGLU
 // epilogue's row order, with the delta added first (lora_silu).
 //
-// One thread owns one output row: its R halves of B sit in registers (128-bit loads, a warp reads 32 consecutive rows),
-// the tokens' xa are summed over the splits once per block into shared memory, and tokens without the adapter cost a
-// compare. The sums run in the reference's order (splits ascending; the rank's products as one fused multiply-add
-// chain), so the results have the bits of its kernels.
+// Tiling: a block covers 64 outputs x 32 tokens with 256 threads, thread = (output, token lane 0..3); a thread keeps
+// its output's R values of B in registers and walks the tile's tokens 4 apart, so decode-sized steps spread over
+// rows / 64 blocks and every B row is fetched once per 32 tokens. The tokens' xa are summed over the splits once per
+// block into shared memory (tokens without the adapter are skipped there and cost a compare later). Per (output,
+// token) the arithmetic is fixed by the reference's kernels, whose bits the results must have: splits added in
+// ascending order, the rank's products as ONE chain of fused multiply-adds in rank order, then y += s * delta.
 #include "common.cuh"
 #include "launch.h"
 
 namespace qb {
 namespace {
 
-constexpr int LTT = 8;      // tokens per block (LORA_TT)
-constexpr int LMAXM = 256;  // columns of xa at most (LORA_MAXM)
+constexpr int TILE_OUT = 64;     // outputs of a block
+constexpr int TILE_TOK = 32;     // tokens of a block
+constexpr int TOK_LANES = 4;     // threads that share an output
+constexpr int LMAXM = 256;       // columns of xa at most (LORA_MAXM of the reference)
 
 struct LoraArgs {
     const float* xa;
@@ -32,30 +36,12 @@ struct LoraArgs {
     __half* mid;
 };
 
-// One kernel for both forms. A thread owns one output of the block's tile: row o of y (the delta is added in place), or
-// SwiGLU output j of mid, whose gate row og = 16 (j / 8) + j % 8 and up row og + 8 sit in the same 16-row tile of y.
-// Grid (outputs / 256, n / 8).
-template <int R, bool SWIGLU>
-__global__ void __launch_bounds__(256) lora_kernel(const LoraArgs a) {
-    __shared__ float xs[LTT][LMAXM];  // xa of the block's tokens, summed over the splits in split order
-    __shared__ float sc[LTT];         // their slots' scales (0: the token does not use the adapter)
-    pdl_wait();
-    const int t0 = blockIdx.y * LTT, tid = threadIdx.x;
-    if (tid < LTT) sc[tid] = t0 + tid < a.n ? a.slot_scale[a.tok_slot[t0 + tid]] : 0.f;
-    __syncthreads();
-    for (int i = tid; i < LTT * a.M; i += 256) {
-        const int tl = i / a.M, c = i - tl * a.M;
-        float v = 0.f;
-        if (sc[tl] != 0.f)
-            for (int s = 0; s < a.split; s++) v += a.xa[((size_t)s * a.n + t0 + tl) * a.M + c];
-        xs[tl][c] = v;
-    }
-    __syncthreads();
-
-    // a row of B as R floats (128-bit loads), and its product with a token's xa as ONE chain of fused multiply-adds in
-    // rank order: the order the reference's kernels sum in
-    auto row_of = [&](int o, float (&b)[R]) {
-        const uint4* p = reinterpret_cast<const uint4*>(a.B + (size_t)o * R);
+// R values of B's row `o` as floats
+template <int R>
+struct BRow {
+    float b[R];
+    __device__ __forceinline__ void load(const __half* B, int o) {
+        const uint4* p = reinterpret_cast<const uint4*>(B + (size_t)o * R);
 #pragma unroll
         for (int i = 0; i < R / 8; i++) {
             const uint4 u = p[i];
@@ -67,55 +53,76 @@ __global__ void __launch_bounds__(256) lora_kernel(const LoraArgs a) {
                 b[8 * i + 2 * q + 1] = f.y;
             }
         }
-    };
-    auto delta = [&](const float (&b)[R], int tl, int off) {
-        const float* x = &xs[tl][off];
+    }
+    __device__ __forceinline__ float dot(const float* x) const {
         float d = 0.f;
 #pragma unroll
         for (int q = 0; q < R; q++) d = fmaf(b[q], x[q], d);
         return d;
-    };
+    }
+};
 
-    const int out = blockIdx.x * 256 + tid;
-    if (!SWIGLU) {
-        bool any = false;
+// PAIRS = false: an output is a row of y, the delta is added in place. PAIRS = true (the SwiGLU form): an output j is
+// an element of mid, made from the gate row 16 (j / 8) + j % 8 and the up row 8 below it of the plain product y.
+template <int R, bool PAIRS>
+__global__ void __launch_bounds__(TILE_OUT * TOK_LANES) lora_tile_kernel(const LoraArgs a) {
+    __shared__ float xs[TILE_TOK][LMAXM];
+    __shared__ float scale[TILE_TOK];
+    pdl_wait();
+    const int tid = threadIdx.x, tok0 = blockIdx.y * TILE_TOK, cnt = min(TILE_TOK, a.n - tok0);
+    if (tid < TILE_TOK) scale[tid] = tid < cnt ? a.slot_scale[a.tok_slot[tok0 + tid]] : 0.f;
+    __syncthreads();
+    bool adapted = false;
+    for (int i = 0; i < cnt; i++) adapted |= scale[i] != 0.f;
+    if (!adapted && !PAIRS) return;  // nothing to add in this tile (the SwiGLU form still has to write mid)
+    for (int i = tid; i < cnt * a.M; i += TILE_OUT * TOK_LANES) {
+        const int tl = i / a.M, c = i - tl * a.M;
+        float v = 0.f;
+        if (scale[tl] != 0.f)
+            for (int sp = 0; sp < a.split; sp++) v += a.xa[((size_t)sp * a.n + tok0 + tl) * a.M + c];
+        xs[tl][c] = v;
+    }
+    __syncthreads();
+    const int o = blockIdx.x * TILE_OUT + (tid % TILE_OUT), lane_tok = tid / TILE_OUT;
+    if (!PAIRS) {
+        if (o >= a.rows) return;
+        // which stacked module the row belongs to, and where that module's columns of xa start
+        int module = 0;
 #pragma unroll
-        for (int tl = 0; tl < LTT; tl++) any |= sc[tl] != 0.f;
-        if (!any || out >= a.rows) return;
-        // the stacked module of this row and its columns of xa
-        const int off = a.tab[4 + (out >= a.tab[0]) + (out >= a.tab[1]) + (out >= a.tab[2])];
+        for (int i = 0; i < 3; i++) module += o >= a.tab[i];
+        const int off = a.tab[4 + module];
         if (off < 0) return;
-        float b[R];
-        row_of(out, b);
-#pragma unroll
-        for (int tl = 0; tl < LTT; tl++)
-            if (sc[tl] != 0.f) a.y[(size_t)(t0 + tl) * a.ldy + out] += sc[tl] * delta(b, tl, off);
+        BRow<R> row;
+        row.load(a.B, o);
+        for (int tl = lane_tok; tl < cnt; tl += TOK_LANES) {
+            const float s = scale[tl];
+            if (s != 0.f) a.y[(size_t)(tok0 + tl) * a.ldy + o] += s * row.dot(&xs[tl][off]);
+        }
         return;
     }
-    if (out >= a.rows / 2) return;
-    const int og = 16 * (out / 8) + out % 8, ou = og + 8, offg = a.tab[4], offu = a.tab[5];
-    float bg[R], bu[R];
-    if (offg >= 0) row_of(og, bg);
-    if (offu >= 0) row_of(ou, bu);
-#pragma unroll
-    for (int tl = 0; tl < LTT; tl++) {
-        const int t = t0 + tl;
-        if (t >= a.n) break;
-        float g = a.y[(size_t)t * a.ldy + og], u = a.y[(size_t)t * a.ldy + ou];
-        if (sc[tl] != 0.f) {
-            if (offg >= 0) g += sc[tl] * delta(bg, tl, offg);
-            if (offu >= 0) u += sc[tl] * delta(bu, tl, offu);
+    if (o >= a.rows / 2) return;
+    const int gate_row = 16 * (o / 8) + o % 8, up_row = gate_row + 8, off_gate = a.tab[4], off_up = a.tab[5];
+    BRow<R> bg, bu;
+    if (adapted && off_gate >= 0) bg.load(a.B, gate_row);
+    if (adapted && off_up >= 0) bu.load(a.B, up_row);
+    for (int tl = lane_tok; tl < cnt; tl += TOK_LANES) {
+        const size_t at = (size_t)(tok0 + tl) * a.ldy;
+        float gate = a.y[at + gate_row], up = a.y[at + up_row];
+        const float s = scale[tl];
+        if (s != 0.f) {
+            if (off_gate >= 0) gate += s * bg.dot(&xs[tl][off_gate]);
+            if (off_up >= 0) up += s * bu.dot(&xs[tl][off_up]);
         }
-        a.mid[(size_t)t * (a.rows / 2) + out] = __float2half_rn(silu(g) * u);  // every token, as the epilogue rounds it
+        a.mid[(size_t)(tok0 + tl) * (a.rows / 2) + o] = __float2half_rn(silu(gate) * up);  // every token, as the epilogue rounds it
     }
 }
 
 template <int R>
-int run(qb_ctx* ctx, cudaStream_t st, const LoraArgs& a, bool with_silu) {
-    const int per = with_silu ? 512 : 256;
-    const dim3 grid((a.rows + per - 1) / per, (a.n + LTT - 1) / LTT);
-    return with_silu ? launch(ctx, lora_kernel<R, true>, grid, dim3(256), 0, st, a)
-                     : launch(ctx, lora_kernel<R, false>, grid, dim3(256), 0, st, a);
+int run(qb_ctx* ctx, cudaStream_t st, const LoraArgs& a, bool pairs) {
+    const int outs = pairs ? a.rows / 2 : a.rows;
+    const dim3 grid((outs + TILE_OUT - 1) / TILE_OUT, (a.n + TILE_TOK - 1) / TILE_TOK);
+    return pairs ? launch(ctx, lora_tile_kernel<R, true>, grid, dim3(TILE_OUT * TOK_LANES), 0, st, a)
+                 : launch(ctx, lora_tile_kernel<R, false>, grid, dim3(TILE_OUT * TOK_LANES), 0, st, a);
 }
 
 int dispatch(qb_ctx* ctx, void* stream, LoraArgs a, int rank, bool with_silu) {
