@@ -187,7 +187,9 @@ int qb_marlin_gather(qb_ctx* ctx, void* stream, const void* x, const int* rows, 
  *                 Attn::run launches them (src/cuda/qwen/attn.rs:303-336,370-375). `out` holds the gate on entry and
  *                 the gated attention output on return. part_ml / part_acc: scratch for ndec * 24 * 64 (m, l) pairs
  *                 and accumulators of 256 floats. The split size is a function of the key count alone
- *                 (qb_attn_dec_splits), as the reference's dchunk is (kernels/attn.cuh:41-46). */
+ *                 and of the context's SM count alone (qb_attn_dec_splits_sm: at most one block per SM over the four kv
+ *                 heads, 64 at most), as the reference's dchunk is of the key count (kernels/attn.cuh:41-46).
+ *                 qb_attn_dec_splits is the same for a 148-SM part. */
 int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n, const float* q_norm,
                  const float* k_norm, const float* inv_freq, float qscale, float* q, float* out, void* kc, void* vc,
                  float* ks, float* vs, const int* tok_slot, const int* tok_pos, int cap);
@@ -196,6 +198,7 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
                    const int* tok_pos, int cap, int ndseg, int ndec, int dmax, int max_keys, float* part_ml,
                    float* part_acc, float* out, void* mix_f16);
 int qb_attn_dec_splits(int keys);
+int qb_attn_dec_splits_sm(int keys, int sms);
 /* qb_attn_prefill  attn_prefill + attn_combine_tiles (+ to_xin when mix_f16 != NULL), kernels/attn.cuh:327-349,351-520,
  *                  as Attn::run launches them (src/cuda/qwen/attn.rs:338-368): ntile tiles (ptile: first token,
  *                  count; at most 64 / 6 = 10 consecutive tokens of one segment each), max_keys = tile_max_pos + 1.

@@ -61,6 +61,7 @@ SIGNATURES = {
     "qb_attn_prep": [P, P, P, I, I, P, P, P, F, P, P, P, P, P, P, P, P, I],
     "qb_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P, P, P],
     "qb_attn_dec_splits": [I],
+    "qb_attn_dec_splits_sm": [I, I],
     "qb_attn_prefill": [P, P, P, P, P, P, P, P, P, P, I, I, I, P, P, P, P],
     "qb_attn_tile_splits": [I, I],
     "qb_delta_conv": [P, P, P, I, I, P, I, P, P, P, P, LL, P, P, P],

@@ -20,7 +20,7 @@ namespace qb {
 
 constexpr float KV_OFF = 1152.f;
 constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
-constexpr int DSPLITS = 37;    // most key splits of a decode token: 4 kv heads x 37 splits = one block per SM (148)
+constexpr int DSPLITS = 37;    // most key splits of a decode token on a 148-SM part (qb_attn_dec_splits' default)
 constexpr int TSPLITS = 32;    // most key splits of a prompt tile (a power of two)
 
 __host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
@@ -37,14 +37,16 @@ __device__ __forceinline__ size_t vslot(int pos, int d) {
     return ((size_t)(pos >> 4) * HD + d) * 16 + t4 * 4 + e;
 }
 
-// Keys per split of a token with `keys` keys: a multiple of 64, at most DSPLITS splits, and the same for every key
+// Keys per split of a token with `keys` keys: a multiple of 64, at most `dsplits` splits (SM count / kv heads), and the same for every key
 // count between two multiples of 2048 (where the host cuts short segments: a token's splits must not depend on how
 // many drafts follow it in the step), so it is sized for the end of that range.
-__host__ __device__ inline int dec_chunk(int keys) {
+__host__ __device__ inline int dec_chunk(int keys, int dsplits) {
     const int range_end = ((keys - 1) / 2048 + 1) * 2048;
-    return max(64, ((range_end + DSPLITS - 1) / DSPLITS + 63) / 64 * 64);
+    return max(64, ((range_end + dsplits - 1) / dsplits + 63) / 64 * 64);
 }
-__host__ __device__ inline int dec_splits(int keys) { int c = dec_chunk(keys); return (keys + c - 1) / c; }
+__host__ __device__ inline int dec_splits(int keys, int dsplits) { int c = dec_chunk(keys, dsplits); return (keys + c - 1) / c; }
+// the most key splits of a decode token on a part with `sms` SMs: one block per SM over the kv heads, at most 64
+__host__ inline int dsplits_for(int sms) { return max(1, min(64, sms / NKV)); }
 
 // ------------------------------------------------------------------------------------------------ attn_prep
 // grid (n tokens, 2): block (t, 0) makes the 24 query heads and their gates (a warp per head), block (t, 1) the 4 key
@@ -200,7 +202,7 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
     const int first = dseg[2 * seg], nt = dseg[2 * seg + 1];
     auto token = [&](int i) { return TILES ? first + i : dtok[first + i]; };
     const int tlast = token(nt - 1), keys = tok_pos[tlast] + 1;
-    const int chunk = TILES ? tile_chunk(keys, z) : dec_chunk(keys), ns = (keys + chunk - 1) / chunk;
+    const int chunk = TILES ? tile_chunk(keys, z) : dec_chunk(keys, DSPLITS), ns = (keys + chunk - 1) / chunk;
     if (s >= ns) return;
     const int kbeg = s * chunk, ke = min(keys, kbeg + chunk), nstg = (ke - kbeg + SK - 1) / SK;
     const int slot = tok_slot[tlast];
@@ -439,6 +441,379 @@ attn_decode_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const f
             if (t4 == 0) { part_ml[pi * 2] = m[h2]; part_ml[pi * 2 + 1] = L; }
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------------ decode attention
+// Block (short segment, kv head, key split) of the decode / verify attention: 2 to 4 QUADS of four compute warps and a
+// copy warp. The keys and values of the split arrive in 64-key stages through a ring fed by bulk copies; the quads
+// take the stages in turn. Inside a quad the work of a stage is dealt so that no byte is converted twice:
+//   scores   warp w multiplies all the rows (RT tiles of 16 (token, head) rows) by the keys 16 w .. 16 w + 15 of the
+//            stage over the whole head dimension: one conversion of a key serves every row tile;
+//   softmax  the four warps agree on the rows' running maxima through shared memory, so that all of them scale by the
+//            same power of two, and exchange their 16-key slices of P (as f16 mma fragments) and of the row sums;
+//   values   warp w accumulates the output dims 64 w .. 64 w + 63 over all 64 keys of the stage (for every row tile),
+//            so the output accumulators of a row are spread over four warps (RT x 32 registers each).
+// The int8 codes go to the tensor cores as 1152 + q halves (one prmt per pair) and the offset is folded out through the
+// row sums, as in the reference (kernels/attn.cuh:38-40,198-234). The four quads' partial results meet in shared memory
+// at the end; the block writes one (m, l, acc) partial per row, or the finished rows when the segment has one split.
+template <int RT, int NQ>
+struct Dec4Cfg {
+    static constexpr int QUADS = NQ, CW = 4 * QUADS;   // compute warps
+    static constexpr int THREADS = (CW + 1) * 32;       // + the copy warp
+    static constexpr int SK = 64, NSTG = 5;             // keys per stage, ring depth
+    static constexpr int STG_BYTES = SK * HD * 2 + SK * 8;
+    static constexpr int Q_BYTES = RT * 16 * SROW * 2;
+    // per quad: the warps' row maxima [4][RT][16], their P fragments [4][RT][32 lanes] x 16 B, their (sum, ps) [4][RT][16][2]
+    static constexpr int X_MAX = 4 * RT * 16 * 4, X_P = 4 * RT * 32 * 16, X_SUM = 4 * RT * 16 * 8;
+    static constexpr int X_BYTES = X_MAX + X_P + X_SUM;
+    static constexpr int BAR_BYTES = 128;
+    static constexpr int SMEM = BAR_BYTES + Q_BYTES + QUADS * X_BYTES + NSTG * STG_BYTES;
+    static constexpr int MERGE_BYTES = 8 * 32 * (RT * 8 * 4 + RT * 6) * 4;   // two quads' registers at a time
+    static_assert(MERGE_BYTES <= NSTG * STG_BYTES, "the merge buffers reuse the ring");
+    static_assert(SMEM <= 227 * 1024, "shared memory");
+};
+
+template <int RT, int NQ>
+__global__ void __launch_bounds__(Dec4Cfg<RT, NQ>::THREADS, 1)
+attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs, const int* dseg,
+                 const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z, int dsplits, float* part_ml,
+                 float* part_acc, float* out, int* err) {
+    using C = Dec4Cfg<RT, NQ>;
+    constexpr int NSTG = C::NSTG, SK = C::SK, STG_BYTES = C::STG_BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + NSTG;
+    __half* qsh = (__half*)(smem + C::BAR_BYTES);
+    uint8_t* xch = smem + C::BAR_BYTES + C::Q_BYTES;
+    uint8_t* ring = xch + C::QUADS * C::X_BYTES;
+
+    const int seg = blockIdx.x, g = blockIdx.y, s = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NSTG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();  // the step's own keys and values are written by attn_prep just before
+
+    const int first = dseg[2 * seg], nt = dseg[2 * seg + 1];
+    const int tlast = dtok[first + nt - 1], keys = tok_pos[tlast] + 1;
+    const int chunk = dec_chunk(keys, dsplits), ns = (keys + chunk - 1) / chunk;
+    if (s >= ns) return;
+    const int kbeg = s * chunk, ke = min(keys, kbeg + chunk), nstg = (ke - kbeg + SK - 1) / SK;
+    const int slot = tok_slot[tlast];
+
+    if (warp == C::CW) {
+        // ------------------------------------------------------------ the copy warp
+        const uint64_t pol = policy_evict_first();
+        const uint8_t* kh = kc + cache_head(slot, g, cap);
+        const uint8_t* vh = vc + cache_head(slot, g, cap);
+        const float* ksh = ks + scale_head(slot, g, cap);
+        const float* vsh = vs + scale_head(slot, g, cap);
+        for (int j = 0; j < nstg; j++) {
+            const int sl = j % NSTG;
+            if (j >= NSTG) {
+                bool ok = true;
+                if (lane == 0) ok = mbar_wait(&empty[sl], ((j / NSTG) - 1) & 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    if (lane == 0) atomicExch(err, 3);
+                    return;
+                }
+            }
+            uint8_t* base = ring + sl * STG_BYTES;
+            const int kb = kbeg + j * SK;
+            if (lane == 0) mbar_expect_tx(&full[sl], STG_BYTES);
+            __syncwarp();
+            if (lane == 0) bulk_g2s(base, kh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+            if (lane == 1) bulk_g2s(base + SK * HD, vh + (size_t)kb * HD, SK * HD, &full[sl], pol);
+            if (lane == 2) bulk_g2s(base + 2 * SK * HD, ksh + kb, SK * 4, &full[sl], pol);
+            if (lane == 3) bulk_g2s(base + 2 * SK * HD + SK * 4, vsh + kb, SK * 4, &full[sl], pol);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- compute warps
+    const int quad = warp >> 2, w = warp & 3, r = lane >> 2, t4 = lane & 3;
+    constexpr int NCW = C::CW * 32;
+    // Q of the segment's rows (row = token * GROUP + head) as f16
+    for (int x = threadIdx.x; x < RT * 16 * HD / 4; x += NCW) {
+        const int row = x / (HD / 4), d = (x % (HD / 4)) * 4, tok = row / GROUP;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tok < nt) v = *(const float4*)(q + ((size_t)dtok[first + tok] * NH + g * GROUP + row % GROUP) * HD + d);
+        *(uint2*)&qsh[row * SROW + d] = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    }
+    named_bar_sync(1, NCW);
+    // this lane's rows 16 rt + r and + 8: the keys they may see end at lim; KV_OFF times the sums of their Q
+    int lim[RT][2];
+    float qoff[RT][2];
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++) {
+        float qs = 0.f;
+        const __half* qr = qsh + (rt * 16 + (lane & 15)) * SROW + (lane >> 4) * (HD / 2);
+        for (int d = 0; d < HD / 2; d += 2) {
+            const float2 f = __half22float2(*(const __half2*)(qr + d));
+            qs += f.x + f.y;
+        }
+        qs += __shfl_xor_sync(0xffffffffu, qs, 16);
+        qoff[rt][0] = KV_OFF * __shfl_sync(0xffffffffu, qs, r);
+        qoff[rt][1] = KV_OFF * __shfl_sync(0xffffffffu, qs, r + 8);
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            const int tok = (rt * 16 + r + 8 * h2) / GROUP;
+            lim[rt][h2] = tok < nt ? min(ke, tok_pos[dtok[first + tok]] + 1) : 0;
+        }
+    }
+    float m[RT][2], l[RT][2], ps[RT][2], o[RT][8][4];
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++) {
+        m[rt][0] = m[rt][1] = -INFINITY;
+        l[rt][0] = l[rt][1] = ps[rt][0] = ps[rt][1] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[rt][j][0] = o[rt][j][1] = o[rt][j][2] = o[rt][j][3] = 0.f;
+    }
+    uint32_t qa[RT];
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++) qa[rt] = smem_u32(qsh + (rt * 16 + (lane & 15)) * SROW + (lane >> 4) * 8);
+    float* xmax = (float*)(xch + quad * C::X_BYTES);                 // [4][RT][16]
+    uint4* xp = (uint4*)(xch + quad * C::X_BYTES + C::X_MAX);        // [4][RT][32]
+    float2* xsum = (float2*)(xch + quad * C::X_BYTES + C::X_MAX + C::X_P);  // [4][RT][16]
+
+    bool dead = false;
+    for (int j = quad; j < nstg; j += C::QUADS) {
+        const int sl = j % NSTG;
+        const uint32_t par = (j / NSTG) & 1;
+        if (!dead) {
+            dead = !mbar_wait(&full[sl], par);
+            if (dead && lane == 0) atomicExch(err, 4);
+        } else {
+            for (int k = 0; k < 1024 && !mbar_try_wait(&full[sl], par); k++) {}
+        }
+        const uint8_t* base = ring + sl * STG_BYTES;
+        const int kb = kbeg + j * SK + 16 * w;  // this warp's 16 keys of the stage
+        const uint8_t* kp = base + (16 * w + r) * HD + 16 * t4;
+        const float* ksc_s = (const float*)(base + 2 * SK * HD) + 16 * w;
+        const float* vsc_s = ksc_s + SK;
+        float ksc[2][2], vsc[2][2];
+#pragma unroll
+        for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int kk = 8 * nn + 2 * t4 + e;
+                const bool in = kb + kk < ke;
+                ksc[nn][e] = in ? ksc_s[kk] : 0.f;
+                vsc[nn][e] = in ? vsc_s[kk] : 0.f;
+            }
+        // ---- scores: S = Q K^T for every row tile, this warp's 16 keys
+        float sacc[RT][2][4];
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int nn = 0; nn < 2; nn++) sacc[rt][nn][0] = sacc[rt][nn][1] = sacc[rt][nn][2] = sacc[rt][nn][3] = 0.f;
+#pragma unroll
+        for (int b = 0; b < HD / 64; b++) {
+            const uint4 kf0 = *(const uint4*)(kp + 64 * b), kf1 = *(const uint4*)(kp + 8 * HD + 64 * b);
+            const uint32_t w0[4] = {kf0.x, kf0.y, kf0.z, kf0.w}, w1[4] = {kf1.x, kf1.y, kf1.z, kf1.w};
+#pragma unroll
+            for (int st = 0; st < 4; st++) {
+                const uint32_t b00 = kv_half2(w0[st], 0x4140), b01 = kv_half2(w0[st], 0x4342);
+                const uint32_t b10 = kv_half2(w1[st], 0x4140), b11 = kv_half2(w1[st], 0x4342);
+#pragma unroll
+                for (int rt = 0; rt < RT; rt++) {
+                    uint32_t a[4];
+                    ldsm_x4(a[0], a[1], a[2], a[3], qa[rt] + (b * 64 + st * 16) * 2);
+                    mma16816(sacc[rt][0], a, b00, b01);
+                    mma16816(sacc[rt][1], a, b10, b11);
+                }
+            }
+        }
+        // ---- the rows' maxima over this warp's keys, then over the quad's
+        float v[RT][2][4];
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int k = kb + 8 * nn + 2 * t4 + e;
+                        const float sv = k < lim[rt][h2] ? (sacc[rt][nn][2 * h2 + e] - qoff[rt][h2]) * ksc[nn][e] : -INFINITY;
+                        v[rt][nn][2 * h2 + e] = sv;
+                        mx = fmaxf(mx, sv);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                if (t4 == 0) xmax[(w * RT + rt) * 16 + r + 8 * h2] = mx;
+            }
+        named_bar_sync(2 + quad, 128);
+        float corr[RT][2];
+        bool grew = false;
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                float mn = m[rt][h2];
+#pragma unroll
+                for (int ww = 0; ww < 4; ww++) mn = fmaxf(mn, xmax[(ww * RT + rt) * 16 + r + 8 * h2]);
+                corr[rt][h2] = mn == -INFINITY ? 1.f : exp2f(m[rt][h2] - mn);
+                m[rt][h2] = mn;
+                grew |= corr[rt][h2] != 1.f;
+            }
+        // ---- P of this warp's keys (times the value scales, rounded to f16 as the products see it) and its row sums
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++) {
+            float pv[2][4], sum[2];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                sum[h2] = 0.f;
+#pragma unroll
+                for (int nn = 0; nn < 2; nn++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const float sv = v[rt][nn][2 * h2 + e];
+                        const float pp = sv == -INFINITY ? 0.f : exp2f(sv - m[rt][h2]);
+                        sum[h2] += pp;
+                        pv[nn][2 * h2 + e] = pp * vsc[nn][e];
+                    }
+            }
+            uint4 pa;
+            pa.x = pack_half2(pv[0][0], pv[0][1]); pa.y = pack_half2(pv[0][2], pv[0][3]);
+            pa.z = pack_half2(pv[1][0], pv[1][1]); pa.w = pack_half2(pv[1][2], pv[1][3]);
+            xp[(w * RT + rt) * 32 + lane] = pa;
+            __half2 h0, h1, h2v, h3;
+            *(uint32_t*)&h0 = pa.x; *(uint32_t*)&h1 = pa.y; *(uint32_t*)&h2v = pa.z; *(uint32_t*)&h3 = pa.w;
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2v), f3 = __half22float2(h3);
+            float pr[2] = {f0.x + f0.y + f2.x + f2.y, f1.x + f1.y + f3.x + f3.y};
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                sum[h2] += __shfl_xor_sync(0xffffffffu, sum[h2], 1);
+                sum[h2] += __shfl_xor_sync(0xffffffffu, sum[h2], 2);
+                pr[h2] += __shfl_xor_sync(0xffffffffu, pr[h2], 1);
+                pr[h2] += __shfl_xor_sync(0xffffffffu, pr[h2], 2);
+                if (t4 == 0) xsum[(w * RT + rt) * 16 + r + 8 * h2] = make_float2(sum[h2], pr[h2]);
+            }
+        }
+        named_bar_sync(2 + quad, 128);
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                float sl2 = 0.f, sp2 = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < 4; ww++) {  // in warp order: the same sum in all four warps
+                    const float2 x = xsum[(ww * RT + rt) * 16 + r + 8 * h2];
+                    sl2 += x.x;
+                    sp2 += x.y;
+                }
+                l[rt][h2] = l[rt][h2] * corr[rt][h2] + sl2;
+                ps[rt][h2] = ps[rt][h2] * corr[rt][h2] + sp2;
+            }
+        if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+                for (int jd = 0; jd < 8; jd++) {
+                    o[rt][jd][0] *= corr[rt][0]; o[rt][jd][1] *= corr[rt][0];
+                    o[rt][jd][2] *= corr[rt][1]; o[rt][jd][3] *= corr[rt][1];
+                }
+        }
+        // ---- values: O += P V over the stage's 64 keys, this warp's 64 output dims
+#pragma unroll
+        for (int kbk = 0; kbk < 4; kbk++) {
+            uint32_t pa[RT][4];
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+                const uint4 x = xp[(kbk * RT + rt) * 32 + lane];
+                pa[rt][0] = x.x; pa[rt][1] = x.y; pa[rt][2] = x.z; pa[rt][3] = x.w;
+            }
+            const uint8_t* vp = base + SK * HD + kbk * 16 * HD + (64 * w + r) * 16 + t4 * 4;
+#pragma unroll
+            for (int jd = 0; jd < 8; jd++) {
+                const uint32_t vw = *(const uint32_t*)(vp + jd * 8 * 16);
+                const uint32_t b0 = kv_half2(vw, 0x4140), b1 = kv_half2(vw, 0x4342);
+#pragma unroll
+                for (int rt = 0; rt < RT; rt++) mma16816(o[rt][jd], pa[rt], b0, b1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[sl]);
+    }
+
+    // ---- the quads merge pairwise through the ring, which is free (every stage was consumed): 1 -> 0 and 3 -> 2, then
+    // 2 -> 0. A warp's registers go to the warp of the same index in the other quad (same rows, same dims).
+    named_bar_sync(1, NCW);
+    constexpr int MF = RT * 8 * 4 + RT * 6;  // floats per lane
+    for (int round = 1; round < C::QUADS; round <<= 1) {
+        const bool sender = (quad & (2 * round - 1)) == round;
+        const bool receiver = (quad & (2 * round - 1)) == 0 && quad + round < C::QUADS;
+        float* mb = (float*)ring + (size_t)(((quad >> 1) / round % 2) * 4 + w) * 32 * MF + lane;
+        if (sender) {
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+#pragma unroll
+                for (int jd = 0; jd < 8; jd++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) mb[((rt * 8 + jd) * 4 + e) * 32] = o[rt][jd][e];
+#pragma unroll
+                for (int h2 = 0; h2 < 2; h2++) {
+                    mb[(RT * 32 + rt * 6 + h2) * 32] = m[rt][h2];
+                    mb[(RT * 32 + rt * 6 + 2 + h2) * 32] = l[rt][h2];
+                    mb[(RT * 32 + rt * 6 + 4 + h2) * 32] = ps[rt][h2];
+                }
+            }
+        }
+        named_bar_sync(1, NCW);
+        if (receiver) {
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++) {
+                float c0[2], c1[2];
+#pragma unroll
+                for (int h2 = 0; h2 < 2; h2++) {
+                    const float m1 = mb[(RT * 32 + rt * 6 + h2) * 32], mn = fmaxf(m[rt][h2], m1);
+                    c0[h2] = mn == -INFINITY ? 1.f : exp2f(m[rt][h2] - mn);
+                    c1[h2] = mn == -INFINITY ? 1.f : exp2f(m1 - mn);
+                    m[rt][h2] = mn;
+                    l[rt][h2] = l[rt][h2] * c0[h2] + mb[(RT * 32 + rt * 6 + 2 + h2) * 32] * c1[h2];
+                    ps[rt][h2] = ps[rt][h2] * c0[h2] + mb[(RT * 32 + rt * 6 + 4 + h2) * 32] * c1[h2];
+                }
+#pragma unroll
+                for (int jd = 0; jd < 8; jd++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        o[rt][jd][e] = o[rt][jd][e] * c0[e >> 1] + mb[((rt * 8 + jd) * 4 + e) * 32] * c1[e >> 1];
+            }
+        }
+        named_bar_sync(1, NCW);
+    }
+    if (quad != 0) return;
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            const float L = l[rt][h2], P = ps[rt][h2];   // already whole-row sums, the same in the four warps
+            const int row = rt * 16 + r + 8 * h2, tok = row / GROUP;
+            if (tok >= nt) continue;
+            const int i = first + tok, t = dtok[i], head = g * GROUP + row % GROUP;
+            if (ns == 1) {
+                const float f = 1.f / L;
+                float* op = out + (size_t)t * MIX + head * HD + 64 * w + 2 * t4;
+#pragma unroll
+                for (int jd = 0; jd < 8; jd++) {
+                    const float2 gt = *(float2*)(op + jd * 8);
+                    *(float2*)(op + jd * 8) = make_float2(gt.x * (o[rt][jd][2 * h2] - KV_OFF * P) * f,
+                                                          gt.y * (o[rt][jd][2 * h2 + 1] - KV_OFF * P) * f);
+                }
+            } else {
+                const size_t pi = ((size_t)i * NH + head) * z + s;
+                float* pp = part_acc + pi * HD + 64 * w + 2 * t4;
+#pragma unroll
+                for (int jd = 0; jd < 8; jd++)
+                    *(float2*)(pp + jd * 8) = make_float2(o[rt][jd][2 * h2] - KV_OFF * P, o[rt][jd][2 * h2 + 1] - KV_OFF * P);
+                if (w == 0 && t4 == 0) { part_ml[pi * 2] = m[rt][h2]; part_ml[pi * 2 + 1] = L; }
+            }
+        }
 }
 
 // ------------------------------------------------------------------------------------------------ attn_prefill
@@ -783,13 +1158,13 @@ __device__ __forceinline__ void combine_row(const float* part_ml, const float* p
 
 // block (decode token, head)
 __global__ void __launch_bounds__(HD)
-attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, float* out,
-                    __half* mix) {
+attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok, const int* dkeys, int z, int dsplits,
+                    float* out, __half* mix) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, h = blockIdx.y, t = dtok[i], d = threadIdx.x;
     const size_t o = (size_t)t * MIX + h * HD + d;
-    combine_row(part_ml, part_acc, ((size_t)i * NH + h) * z, dec_splits(dkeys[i]), out + o, mix ? mix + o : nullptr);
+    combine_row(part_ml, part_acc, ((size_t)i * NH + h) * z, dec_splits(dkeys[i], dsplits), out + o, mix ? mix + o : nullptr);
 }
 
 // block (prompt tile * PTILE + row, head)
@@ -823,7 +1198,8 @@ int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n
                   q_norm, k_norm, inv_freq, qscale, q, out, (uint8_t*)kc, (uint8_t*)vc, ks, vs, tok_slot, tok_pos, cap);
 }
 
-int qb_attn_dec_splits(int keys) { return keys > 0 ? dec_splits(keys) : 0; }
+int qb_attn_dec_splits(int keys) { return keys > 0 ? dec_splits(keys, DSPLITS) : 0; }
+int qb_attn_dec_splits_sm(int keys, int sms) { return keys > 0 && sms > 0 ? dec_splits(keys, dsplits_for(sms)) : 0; }
 
 // ndseg short segments (dseg: first index into dtok, token count; at most 8 tokens each), ndec = their tokens in
 // all, dmax = the longest segment's tokens, max_keys = the largest key count among them (sizes the grid).
@@ -835,22 +1211,25 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
         !part_acc || !out || ndseg <= 0 || ndec <= 0 || dmax <= 0 || dmax > 8 || max_keys <= 0 || cap % 64 ||
         max_keys > cap)
         return QB_ERR_ARG;
-    const int z = dec_splits(max_keys), rt = (dmax * GROUP + 15) / 16;
+    const int dsplits = dsplits_for(ctx->sms);
+    const int z = dec_splits(max_keys, dsplits), rt = (dmax * GROUP + 15) / 16;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(ndseg, NKV, z);
     int rc;
-#define QB_DEC(RT)                                                                                              \
+#define QB_DEC(RT, NQ)                                                                                          \
     {                                                                                                           \
-        using C = DecCfg<RT, 4, 4>;                                                                             \
-        rc = launch(ctx, attn_decode_kernel<RT, 4, 4, false>, grid, dim3(C::THREADS), C::SMEM, st, q,          \
-                    (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, part_ml, \
-                    part_acc, out, (__half*)nullptr, ctx->err);                                                 \
+        using C = Dec4Cfg<RT, NQ>;                                                                              \
+        rc = launch(ctx, attn_dec4_kernel<RT, NQ>, grid, dim3(C::THREADS), C::SMEM, st, q, (const uint8_t*)kc, \
+                    (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, dsplits, part_ml, part_acc, \
+                    out, ctx->err);                                                                             \
     }
-    if (rt == 1) QB_DEC(1) else if (rt == 2) QB_DEC(2) else QB_DEC(3)
+    // quads per block: as many as leave every warp its registers (a warp holds RT x 32 output accumulators per lane);
+    // measured at 5 rows: 2 quads 33.4 us, 3 quads (spills) 36.6 us, 4 quads 43.2 us
+    if (rt == 1) QB_DEC(1, 4) else if (rt == 2) QB_DEC(2, 2) else QB_DEC(3, 2)
 #undef QB_DEC
     if (rc) return rc;
     return launch(ctx, attn_combine_kernel, dim3(ndec, NH), dim3(HD), 0, st, (const float*)part_ml,
-                  (const float*)part_acc, dtok, dkeys, z, out, (__half*)mix_f16);
+                  (const float*)part_acc, dtok, dkeys, z, dsplits, out, (__half*)mix_f16);
 }
 
 int qb_attn_tile_splits(int ntile, int max_keys) { return ntile > 0 && max_keys > 0 ? tile_splits(ntile, max_keys) : 0; }

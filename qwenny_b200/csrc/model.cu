@@ -620,7 +620,7 @@ static int run_kind(qb_model* m, void* stream, int kind) {
         return QB_OK;
     }
     GraphKey key = {{m->n, m->n_out, m->segs, m->ndec, m->ntile, m->max_seg,
-                     (m->ndec ? qb_attn_dec_splits(m->dec_max_pos + 1) : 0) +
+                     (m->ndec ? qb_attn_dec_splits_sm(m->dec_max_pos + 1, m->ctx->sms) : 0) +
                          64 * (m->ntile ? qb_attn_tile_splits(m->ntile, m->tile_max_pos + 1) : 0),
                      m->ndseg, m->dmax, kind + (m->lora_step ? 4 : 0)}};
     if (StepGraph* g = m->graphs->find(key)) {

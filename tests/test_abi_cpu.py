@@ -34,6 +34,10 @@ def test_version_and_host_only_calls():
     # that follow it), never more than 37 splits (4 kv heads x 37 = one block per SM)
     for lo in range(0, 65536, 2048):
         assert all(l.qb_attn_dec_splits(k) <= 37 for k in (lo + 1, lo + 777, lo + 2048))
+    # the split count follows the SM count: one block per SM over the four kv heads, 64 splits at most
+    assert l.qb_attn_dec_splits_sm(32005, 148) == l.qb_attn_dec_splits(32005)
+    assert l.qb_attn_dec_splits_sm(32005, 132) <= 33 and l.qb_attn_dec_splits_sm(32005, 1024) <= 64
+    assert l.qb_attn_dec_splits_sm(32005, 3) >= 1
 
 
 def test_argument_errors_need_no_device():
