@@ -13,29 +13,10 @@
 //               kernels/qwen.cu:136-138)
 // The size of a key split is a function of the key count alone (dec_chunk), so a token's sums are the same whether
 // it runs alone or with drafts.
-#include "common.cuh"
+#include "attn_common.cuh"
 #include "launch.h"
 
 namespace qb {
-
-constexpr float KV_OFF = 1152.f;
-constexpr int SROW = HD + 8;   // Q row stride in halves (ldmatrix rows on distinct banks)
-constexpr int DSPLITS = 37;    // most key splits of a decode token on a 148-SM part (qb_attn_dec_splits' default)
-constexpr int TSPLITS = 32;    // most key splits of a prompt tile (a power of two)
-
-__host__ __device__ inline size_t cache_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap * HD; }
-__host__ __device__ inline size_t scale_head(int slot, int g, int cap) { return ((size_t)slot * NKV + g) * cap; }
-
-// Byte of dim d in a key row / of (position, dim) in a head's values: the reference's fragment orders
-// (kslot, vslot: kernels/attn.cuh:23-37)
-__device__ __forceinline__ int kslot(int d) {
-    int b = d >> 6, w = d & 15, t4 = (w & 7) >> 1, e = (w & 1) | ((w >> 3) << 1);
-    return b * 64 + t4 * 16 + ((d & 63) >> 4) * 4 + e;
-}
-__device__ __forceinline__ size_t vslot(int pos, int d) {
-    int j = pos & 15, t4 = (j & 7) >> 1, e = (j & 1) | ((j >> 3) << 1);
-    return ((size_t)(pos >> 4) * HD + d) * 16 + t4 * 4 + e;
-}
 
 // Keys per split of a token with `keys` keys: a multiple of 64, at most `dsplits` splits (SM count / kv heads), and the same for every key
 // count between two multiples of 2048 (where the host cuts short segments: a token's splits must not depend on how
@@ -816,308 +797,6 @@ attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const flo
         }
 }
 
-// ------------------------------------------------------------------------------------------------ attn_prefill
-// Prompt attention for steps with many tiles (one key split): block (pair of consecutive prompt tiles, kv head) = 128
-// (token, head) rows, 8 warps of 16 rows each, against all the keys up to the pair's last token. The int8 keys and
-// values of a 32-key stage arrive through the same bulk-copy ring as in the decode kernel; here the block converts
-// them ONCE to f16 in shared memory (keys as [key][dim], values transposed as [dim][key], the 128 offset subtracted
-// exactly), and every warp reads its mma B fragments from there with ldmatrix, so the conversion is shared by the 8 row
-// tiles instead of being repeated per row tile. Three f16 buffers and no block barrier in the loop: every warp converts
-// its share of stage i + 1 BEFORE it multiplies stage i, and mbarriers say when a converted stage is complete
-// (cvt, 8 arrivals) and when a buffer's products are done (done, 8 arrivals), so a warp waits only for a warp that is a
-// whole stage behind. Two tiles that are not consecutive tokens of one sequence (a segment boundary) run one after
-// the other in the same block.
-constexpr int PF_SK = 32, PF_NSTG = 2, PF_NF16 = 3, PF_WARPS = 8, PF_ROWS = 128, PF_TROWS = 64;
-constexpr int PF_RAW = PF_SK * HD * 2 + PF_SK * 8;          // key bytes, value bytes, key scales, value scales
-constexpr int PF_KROW = HD + 8;                              // halves per f16 key row (528 B: ldmatrix rows on distinct banks)
-constexpr int PF_VROW = PF_SK + 8;                           // halves per row of V^T (80 B, same reason)
-constexpr int PF_KF16 = PF_SK * PF_KROW * 2, PF_VF16 = HD * PF_VROW * 2;
-constexpr int PF_F16 = PF_KF16 + PF_VF16 + PF_SK * 8;        // + the stage's 32 key scales and 32 value scales
-constexpr int PF_Q_BYTES = PF_ROWS * SROW * 2;
-constexpr int PF_SMEM = 128 + PF_Q_BYTES + PF_NSTG * PF_RAW + PF_NF16 * PF_F16;
-static_assert(PF_SMEM <= 227 * 1024 && PF_RAW % 128 == 0 && PF_F16 % 128 == 0 && PF_TROWS >= (64 / GROUP) * GROUP, "prefill attention: shared memory");
-
-__device__ __forceinline__ uint32_t kv_exact2(uint32_t w, uint32_t sel) {
-    // two code bytes -> two halves 1024 + (q + 128), minus 1152: q exactly
-    const uint32_t off = 0x64806480u;  // 1152, 1152
-    uint32_t v = __byte_perm(w, 0x64646464u, sel);
-    __half2 r = __hsub2(*(__half2*)&v, *(const __half2*)&off);
-    return *(uint32_t*)&r;
-}
-
-__global__ void __launch_bounds__(PF_WARPS * 32, 1)
-attn_prefill_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs,
-                    const int* ptile, int ntile, const int* tok_slot, const int* tok_pos, int cap, float* out,
-                    __half* mix, int* err) {
-    constexpr int NTD = HD / 8;
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t* full = (uint64_t*)smem;
-    uint64_t* empty = full + PF_NSTG;
-    uint64_t* cvt = empty + PF_NSTG;   // per f16 buffer: its stage is converted (all warps)
-    uint64_t* done = cvt + PF_NF16;    // per f16 buffer: its stage is multiplied (all warps)
-    __half* qsh = (__half*)(smem + 128);
-    uint8_t* ring = smem + 128 + PF_Q_BYTES;
-    uint8_t* f16b = ring + PF_NSTG * PF_RAW;
-    const int g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, t4 = lane & 3;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < PF_NSTG; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], PF_WARPS); }
-        for (int i = 0; i < PF_NF16; i++) { mbar_init(&cvt[i], PF_WARPS); mbar_init(&done[i], PF_WARPS); }
-        mbar_fence_init();
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-    pdl_wait();
-
-    // the block's tiles: 2 pair, 2 pair + 1 (the last pairs, with the longest contexts, first)
-    const int pair = gridDim.x - 1 - blockIdx.x, ta = 2 * pair, tb = ta + 1;
-    const int firstA = ptile[2 * ta], ntA = ptile[2 * ta + 1];
-    int firstB = 0, ntB = 0;
-    bool paired = false;
-    if (tb < ntile) {
-        firstB = ptile[2 * tb]; ntB = ptile[2 * tb + 1];
-        paired = firstB == firstA + ntA && tok_slot[firstB] == tok_slot[firstA] && tok_pos[firstB] == tok_pos[firstA] + ntA;
-    }
-    const int npass = tb < ntile && !paired ? 2 : 1;
-    const uint64_t pol = policy_evict_first();
-    int jbase = 0;  // stages streamed by earlier passes: slots and parities run on
-    bool copy_ok = true, dead = false;
-
-    for (int pass = 0; pass < npass; pass++) {
-        // rows 0..63: tile g0; rows 64..127: tile g1 (present only in a pair)
-        const int first0 = pass == 0 ? firstA : firstB, nt0 = pass == 0 ? ntA : ntB;
-        const int first1 = firstB, nt1 = paired ? ntB : 0;
-        const int tlast = nt1 ? first1 + nt1 - 1 : first0 + nt0 - 1;
-        const int keys = tok_pos[tlast] + 1, slot = tok_slot[tlast], nstg = (keys + PF_SK - 1) / PF_SK;
-        const uint8_t* kh = kc + cache_head(slot, g, cap);
-        const uint8_t* vh = vc + cache_head(slot, g, cap);
-        const float* ksh = ks + scale_head(slot, g, cap);
-        const float* vsh = vs + scale_head(slot, g, cap);
-        auto issue = [&](int i) {
-            const int J = jbase + i, sl = J % PF_NSTG;
-            if (J >= PF_NSTG) {
-                bool ok = true;
-                if (lane == 0) ok = mbar_wait(&empty[sl], ((J / PF_NSTG) - 1) & 1);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) {
-                    if (lane == 0 && copy_ok) atomicExch(err, 5);
-                    copy_ok = false;
-                    return;
-                }
-            }
-            uint8_t* base = ring + sl * PF_RAW;
-            const int kb = i * PF_SK;
-            if (lane == 0) mbar_expect_tx(&full[sl], PF_RAW);
-            __syncwarp();
-            if (lane == 0) bulk_g2s(base, kh + (size_t)kb * HD, PF_SK * HD, &full[sl], pol);
-            if (lane == 1) bulk_g2s(base + PF_SK * HD, vh + (size_t)kb * HD, PF_SK * HD, &full[sl], pol);
-            if (lane == 2) bulk_g2s(base + 2 * PF_SK * HD, ksh + kb, PF_SK * 4, &full[sl], pol);
-            if (lane == 3) bulk_g2s(base + 2 * PF_SK * HD + PF_SK * 4, vsh + kb, PF_SK * 4, &full[sl], pol);
-        };
-        if (warp == 0) {
-            issue(0);
-            if (nstg > 1) issue(1);
-        }
-        // Q of the 128 rows (row = 64 group + token * GROUP + head) as f16
-        for (int x = threadIdx.x; x < PF_ROWS * HD / 4; x += PF_WARPS * 32) {
-            int row = x / (HD / 4), d = (x % (HD / 4)) * 4, grp = row / PF_TROWS, lr = row % PF_TROWS, tok = lr / GROUP;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (tok < (grp ? nt1 : nt0))
-                v = *(const float4*)(q + ((size_t)((grp ? first1 : first0) + tok) * NH + g * GROUP + lr % GROUP) * HD + d);
-            *(uint2*)&qsh[row * SROW + d] = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
-        }
-        // this lane's rows warp * 16 + r and + 8: their tokens and the keys they may see
-        const int grp = warp / 4, firstw = grp ? first1 : first0, ntw = grp ? nt1 : nt0;
-        int lim[2], tokn[2];
-#pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-            int lr = (warp % 4) * 16 + r + 8 * h2, tok = lr / GROUP;
-            tokn[h2] = tok < ntw ? firstw + tok : -1;
-            lim[h2] = tokn[h2] >= 0 ? tok_pos[tokn[h2]] + 1 : 0;
-        }
-        int wmax = max(lim[0], lim[1]);  // the warp's rows see no key from here on
-#pragma unroll
-        for (int o_ = 4; o_ < 32; o_ <<= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o_));
-        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[NTD][4];
-#pragma unroll
-        for (int j = 0; j < NTD; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-        const uint32_t qa = smem_u32(qsh + (warp * 16 + (lane & 15)) * SROW + (lane >> 4) * 8);
-        __syncthreads();  // Q is complete
-
-        // Wait for stage i's bytes, convert this warp's share into f16 buffer J % 3 (once its previous stage has been
-        // multiplied by every warp), give the raw slot back, and say so.
-        auto convert = [&](int i) {
-            const int J = jbase + i, sl = J % PF_NSTG, fbi = J % PF_NF16;
-            bool ok = true;
-            if (!dead) {
-                ok = mbar_wait(&full[sl], (J / PF_NSTG) & 1);
-                if (ok && J >= PF_NF16) ok = mbar_wait(&done[fbi], ((J / PF_NF16) - 1) & 1);
-                if (!ok) { dead = true; if (lane == 0) atomicExch(err, 6); }
-            }
-            const uint8_t* raw = ring + sl * PF_RAW;
-            uint8_t* fb = f16b + fbi * PF_F16;
-            __half* kf = (__half*)fb;
-            __half* vf = (__half*)(fb + PF_KF16);
-            float* scf = (float*)(fb + PF_KF16 + PF_VF16);
-            const int kb0 = i * PF_SK, ke = keys;
-            // ---- the block's conversion of the stage, 1/8 per warp. Keys: warp w takes keys 4 w .. 4 w + 3, a quarter
-            // warp per key (its 8 lanes read 128 contiguous bytes); byte group (b, t4) of a key holds, word s, dims
-            // 64 b + 16 s + 2 t4 + {0, 1} and + {8, 9}.
-            {
-                const int key = 4 * warp + (lane >> 3), b2 = (lane >> 2) & 1;
-#pragma unroll
-                for (int it = 0; it < 2; it++) {
-                    const int b = b2 + 2 * it;
-                    uint4 w4 = *(const uint4*)(raw + key * HD + b * 64 + t4 * 16);
-                    uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
-                    __half* dst = kf + key * PF_KROW + b * 64 + 2 * t4;
-#pragma unroll
-                    for (int s4 = 0; s4 < 4; s4++) {
-                        *(uint32_t*)(dst + s4 * 16) = kv_exact2(ws[s4], 0x4140);
-                        *(uint32_t*)(dst + s4 * 16 + 8) = kv_exact2(ws[s4], 0x4342);
-                    }
-                }
-                // values: warp w takes dims 32 w .. 32 w + 31 of both 16-key blocks; the 16 bytes of (block, dim) hold,
-                // word t, keys 2 t + {0, 1} and 2 t + 8 + {0, 1}
-#pragma unroll
-                for (int kb = 0; kb < 2; kb++) {
-                    const int d = 32 * warp + lane;
-                    uint4 w4 = *(const uint4*)(raw + PF_SK * HD + (kb * HD + d) * 16);
-                    uint4 lo = make_uint4(kv_exact2(w4.x, 0x4140), kv_exact2(w4.y, 0x4140), kv_exact2(w4.z, 0x4140),
-                                          kv_exact2(w4.w, 0x4140));
-                    uint4 hi = make_uint4(kv_exact2(w4.x, 0x4342), kv_exact2(w4.y, 0x4342), kv_exact2(w4.z, 0x4342),
-                                          kv_exact2(w4.w, 0x4342));
-                    *(uint4*)(vf + d * PF_VROW + kb * 16) = lo;
-                    *(uint4*)(vf + d * PF_VROW + kb * 16 + 8) = hi;
-                }
-                if (warp == 0) {  // the scales; keys past the end count for nothing
-                    const float* sc = (const float*)(raw + 2 * PF_SK * HD);
-                    bool in = kb0 + lane < ke;
-                    scf[lane] = in ? sc[lane] : 0.f;
-                    scf[PF_SK + lane] = in ? sc[PF_SK + lane] : 0.f;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&empty[sl]);  // the raw stage is consumed
-                mbar_arrive(&cvt[fbi]);   // this warp's share of the f16 stage is written
-            }
-        };
-        convert(0);
-        for (int i = 0; i < nstg; i++) {
-            const int J = jbase + i, fbi = J % PF_NF16;
-            if (warp == 0 && i + 2 < nstg && copy_ok) issue(i + 2);
-            if (i + 1 < nstg) convert(i + 1);
-            if (!dead) {
-                dead = !mbar_wait(&cvt[fbi], (J / PF_NF16) & 1);
-                if (dead && lane == 0) atomicExch(err, 7);
-            }
-            uint8_t* fb = f16b + fbi * PF_F16;
-            __half* kf = (__half*)fb;
-            __half* vf = (__half*)(fb + PF_KF16);
-            float* scf = (float*)(fb + PF_KF16 + PF_VF16);
-            const int kb0 = i * PF_SK;
-
-            if (kb0 < wmax) {
-                // ---- S = Q K^T over the stage's 32 keys (4 n-tiles)
-                float sacc[4][4];
-#pragma unroll
-                for (int nn = 0; nn < 4; nn++) sacc[nn][0] = sacc[nn][1] = sacc[nn][2] = sacc[nn][3] = 0.f;
-                const uint32_t ka = smem_u32(kf + ((lane >> 4) * 8 + (lane & 7)) * PF_KROW + ((lane >> 3) & 1) * 8);
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; kk++) {
-                    uint32_t a[4], b0[4], b1[4];
-                    ldsm_x4(a[0], a[1], a[2], a[3], qa + kk * 32);
-                    ldsm_x4(b0[0], b0[1], b0[2], b0[3], ka + kk * 32);
-                    ldsm_x4(b1[0], b1[1], b1[2], b1[3], ka + 16 * PF_KROW * 2 + kk * 32);
-                    mma16816(sacc[0], a, b0[0], b0[1]);
-                    mma16816(sacc[1], a, b0[2], b0[3]);
-                    mma16816(sacc[2], a, b1[0], b1[1]);
-                    mma16816(sacc[3], a, b1[2], b1[3]);
-                }
-                // ---- scale, mask, online softmax per row; P times the value scales as the A fragments of P V
-                float pv[4][4], corr[2];
-                bool grew = false;
-#pragma unroll
-                for (int h2 = 0; h2 < 2; h2++) {
-                    float v[4][2], mx = -INFINITY;
-#pragma unroll
-                    for (int nn = 0; nn < 4; nn++) {
-                        float2 kscl = *(const float2*)(scf + 8 * nn + 2 * t4);
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            int k = kb0 + 8 * nn + 2 * t4 + e;
-                            v[nn][e] = k < lim[h2] ? sacc[nn][2 * h2 + e] * (e ? kscl.y : kscl.x) : -INFINITY;
-                            mx = fmaxf(mx, v[nn][e]);
-                        }
-                    }
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    float mn = fmaxf(m[h2], mx);
-                    corr[h2] = mn == -INFINITY ? 1.f : exp2f(m[h2] - mn);
-                    m[h2] = mn;
-                    float sum = 0.f;
-#pragma unroll
-                    for (int nn = 0; nn < 4; nn++) {
-                        float2 vscl = *(const float2*)(scf + PF_SK + 8 * nn + 2 * t4);
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            float p = v[nn][e] == -INFINITY ? 0.f : exp2f(v[nn][e] - mn);
-                            sum += p;
-                            pv[nn][2 * h2 + e] = p * (e ? vscl.y : vscl.x);
-                        }
-                    }
-                    l[h2] = l[h2] * corr[h2] + sum;
-                    grew |= corr[h2] != 1.f;
-                }
-                if (__any_sync(0xffffffffu, grew)) {
-#pragma unroll
-                    for (int j = 0; j < NTD; j++) {
-                        o[j][0] *= corr[0]; o[j][1] *= corr[0];
-                        o[j][2] *= corr[1]; o[j][3] *= corr[1];
-                    }
-                }
-                // ---- O += P V: two k16 steps of keys, 32 n-tiles of dims
-                const uint32_t va = smem_u32(vf + ((lane >> 4) * 8 + (lane & 7)) * PF_VROW + ((lane >> 3) & 1) * 8);
-#pragma unroll
-                for (int k2 = 0; k2 < 2; k2++) {
-                    uint32_t pa[4] = {pack_half2(pv[2 * k2][0], pv[2 * k2][1]), pack_half2(pv[2 * k2][2], pv[2 * k2][3]),
-                                      pack_half2(pv[2 * k2 + 1][0], pv[2 * k2 + 1][1]),
-                                      pack_half2(pv[2 * k2 + 1][2], pv[2 * k2 + 1][3])};
-#pragma unroll
-                    for (int nd = 0; nd < NTD / 2; nd++) {
-                        uint32_t b[4];
-                        ldsm_x4(b[0], b[1], b[2], b[3], va + nd * 16 * PF_VROW * 2 + k2 * 32);
-                        mma16816(o[2 * nd], pa, b[0], b[1]);
-                        mma16816(o[2 * nd + 1], pa, b[2], b[3]);
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&done[fbi]);  // this warp is through with the stage's f16 buffer
-        }
-        // ---- the rows are finished: out *= O / L (the gate is there), and the f16 copy
-#pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-            float L = l[h2];
-            L += __shfl_xor_sync(0xffffffffu, L, 1);
-            L += __shfl_xor_sync(0xffffffffu, L, 2);
-            if (tokn[h2] < 0) continue;
-            const int lr = (warp % 4) * 16 + r + 8 * h2, head = g * GROUP + lr % GROUP;
-            const float f = 1.f / L;
-            const size_t ob = (size_t)tokn[h2] * MIX + head * HD + 2 * t4;
-#pragma unroll
-            for (int j = 0; j < NTD; j++) {
-                float2 gt = *(float2*)(out + ob + j * 8);
-                float2 res = make_float2(gt.x * o[j][2 * h2] * f, gt.y * o[j][2 * h2 + 1] * f);
-                *(float2*)(out + ob + j * 8) = res;
-                if (mix) *(__half2*)(mix + ob + j * 8) = __floats2half2_rn(res.x, res.y);
-            }
-        }
-        jbase += nstg;
-        __syncthreads();  // Q and the f16 buffers are free for the next pass
-    }
-}
-
 // Merge the ns key splits of one (token, head) in split order; *op *= result (the gate is there); optionally also the
 // f16 copy of the product. HD threads, thread d owns dim d; the splits' maxima and sums go through shared memory once
 // so that the accumulator loads of all splits are independent and in flight together.
@@ -1168,7 +847,6 @@ attn_combine_kernel(const float* part_ml, const float* part_acc, const int* dtok
 }
 
 // block (prompt tile * PTILE + row, head)
-constexpr int PTILE = 64 / GROUP;  // tokens of a prompt tile at most
 __global__ void __launch_bounds__(HD)
 attn_combine_tiles_kernel(const float* part_ml, const float* part_acc, const int* ptile, const int* tok_pos, int z,
                           float* out, __half* mix) {
@@ -1247,10 +925,9 @@ int qb_attn_prefill(qb_ctx* ctx, void* stream, const float* q, const void* kc, c
         return QB_ERR_ARG;
     const int z = tile_splits(ntile, max_keys);
     if (z > 1 && (!part_ml || !part_acc)) return QB_ERR_ARG;
-    if (z == 1) {  // many tiles: pairs of tiles per block, the stage converted once per block
-        return launch(ctx, attn_prefill_kernel, dim3((ntile + 1) / 2, NKV), dim3(PF_WARPS * 32), PF_SMEM,
-                      (cudaStream_t)stream, q, (const uint8_t*)kc, (const uint8_t*)vc, ks, vs, ptile, ntile, tok_slot,
-                      tok_pos, cap, out, (__half*)mix_f16, ctx->err);
+    if (z == 1) {  // many tiles: a pair of tiles per block on tcgen05 (attn_prefill_tc.cu)
+        return qb_attn_prefill_tc_launch(ctx, (cudaStream_t)stream, q, kc, vc, ks, vs, ptile, ntile, tok_slot, tok_pos,
+                                         cap, out, mix_f16);
     }
     using C = DecCfg<4, 2, 5>;  // 10 tokens x 6 heads = 60 rows: 4 row tiles; 2 warps each; 5 stages of 32 keys
     static_assert(PTILE * GROUP <= 64, "a prompt tile fills at most 4 row tiles");

@@ -51,6 +51,10 @@ int prepare_kernel(int device, const void* kern, int smem);
 
 }  // namespace qb
 
+// the many-tile prompt attention on tcgen05 (attn_prefill_tc.cu); reached through qb_attn_prefill
+int qb_attn_prefill_tc_launch(qb_ctx* ctx, cudaStream_t st, const float* q, const void* kc, const void* vc, const float* ks,
+                              const float* vs, const int* ptile, int ntile, const int* tok_slot, const int* tok_pos,
+                              int cap, float* out, void* mix_f16);
 // the prompt-sized W4A16 product on tcgen05 (w4a16_gemm_tc.cu); reached through qb_marlin_gemm for more than 16 rows
 int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m, int n,
                       int k, int row0, int epi);
