@@ -253,6 +253,19 @@ def reference_kernels(ctx, torch):
     ours = _time_us(torch, lambda: ctx.gemm_f16_plain(wp, x, n, K, rows // 16, K // split, y=yo))
     theirs = _time_us(torch, lambda: ref.gemm_f16_plain(wp, x, yo, n, K, rows // 16))
     res["in_ba_96x5120_5rows"] = {"ours_us": ours, "reference_us": theirs, "reference": "gemm_f16_t8_plain"}
+    # ---- prompt attention: 2048 rows at the end of the 32768-token cache (the last prompt chunk)
+    T, pos0 = 2048, cap - 2048
+    qp = torch.randn(T, R.NH, R.HD, generator=g, device="cuda") * (math.log2(math.e) / 16)
+    gp = torch.sigmoid(torch.randn(T, R.MIX, generator=g, device="cuda"))
+    st4 = R.build_step([(0, 0, pos0 + i) for i in range(T)], [0], short=0)
+    dv4 = ref_cuda.upload_step(st4)
+    op = gp.clone()
+    mixp = torch.zeros(T, R.MIX, dtype=torch.float16, device="cuda")
+    ours = _time_us(torch, lambda: ctx.attn_prefill(qp, kc, vc, ks, vs, dv4, st4, cap, ml, acc, op, mixp), reps=3)
+    theirs = _time_us(torch, lambda: ref.attn_prefill(qp, kc, vc, ks, vs, st4, dv4, cap, ml, acc, op), reps=3)
+    res["attention_prompt_2048rows_32768keys"] = {
+        "ours_us": ours, "reference_us": theirs, "reference": "attn_prefill (mma.sync)", "ours": "tcgen05, S / P / O in tensor memory",
+        "flops": 4.0 * R.HD * R.NH * sum(pos0 + i + 1 for i in range(T))}
     res["not_timed"] = "marlin_* (the W4A16 products): they end in an illegal-instruction fault on this GPU and are not launched"
     torch.cuda.synchronize()
     return res
