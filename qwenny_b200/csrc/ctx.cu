@@ -95,6 +95,8 @@ void qb_destroy(qb_ctx* c) {
     cudaFree(c->counters);
     cudaFree(c->err);
     cudaFree(c->delta_tp);
+    cudaFree(c->tc_part);
+    cudaFree(c->tc_tickets);
     delete c;
 }
 

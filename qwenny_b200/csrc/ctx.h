@@ -14,6 +14,8 @@ struct qb_ctx {
     int* counters = nullptr;
     size_t ncounters = 0;
     int* err = nullptr;  // device word
+    float* tc_part = nullptr;   // partial tiles of the tensor-core W4A16 product's stream-K shares (sms x 2 x 256 KB), taken with its first call
+    int* tc_tickets = nullptr;  // its per-tile tickets (QB_TC_TICKETS, zero between launches)
     float* delta_tp = nullptr;  // scratch of the chunked delta rule (T, P, log decays per chunk and value head), taken by
                                 // the first prompt-sized DeltaNet step
     // measurement override of the GEMV plan (0: built-in choice)
@@ -25,6 +27,7 @@ struct qb_ctx {
     long long* trace = nullptr;  // measurement: per-block timestamps of the next products
 };
 
+constexpr int QB_TC_TICKETS = 1 << 16;  // tiles of one tensor-core W4A16 product (256 outputs x 256 tokens each)
 #define QB_CUDA(x)                         \
     do {                                   \
         cudaError_t e_ = (x);              \
@@ -55,6 +58,7 @@ int prepare_kernel(int device, const void* kern, int smem);
 int qb_attn_prefill_tc_launch(qb_ctx* ctx, cudaStream_t st, const float* q, const void* kc, const void* vc, const float* ks,
                               const float* vs, const int* ptile, int ntile, const int* tok_slot, const int* tok_pos,
                               int cap, float* out, void* mix_f16);
-// the prompt-sized W4A16 product on tcgen05 (w4a16_gemm_tc.cu); reached through qb_marlin_gemm for more than 16 rows
+// the prompt-sized W4A16 product on tcgen05 (w4a16_gemm_tc.cu); reached through qb_marlin_gemm / qb_marlin_gemm_z (zp:
+// S carries the offsets' table after the scales) for more than 16 rows
 int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m, int n,
-                      int k, int row0, int epi);
+                      int k, int row0, int epi, int zp);

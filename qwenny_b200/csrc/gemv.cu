@@ -211,7 +211,7 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
     cudaStream_t st = (cudaStream_t)stream;
     // more than 16 rows: the tensor-core product (plain and SwiGLU epilogues, contiguous rows)
     if (m > 16 && epi != QB_EPI_ARGMAX && !xrows && !ctx->no_tc)
-        return qb_gemm_tc_launch(ctx, st, X, B, Y, S, m, n, k, row0, epi);
+        return qb_gemm_tc_launch(ctx, st, X, B, Y, S, m, n, k, row0, epi, 0);
     // otherwise 16-row slabs through the skinny kernel
     for (int r = 0; r < m; r += 16) {
         int mm = m - r < 16 ? m - r : 16;
@@ -229,7 +229,7 @@ extern "C" int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const vo
 // ------------------------------------------------------------------------------------------------ no-allocation variant
 // The zero-point variants (marlin_*_z, kernels/marlin.cuh:126-133): S holds the scales [k/128][n] followed by a second
 // table (8 - z) * scale in the same layout (pack_marlin with zeros, src/cuda/core.rs:262-285). Any row count: more than
-// 16 rows run as 16-row slabs through the skinny kernel (the tensor-core product has no zero-point form yet).
+// 16 contiguous rows with the plain or SwiGLU epilogue run on the tensor-core product, the rest as 16-row slabs.
 extern "C" int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m,
                                 int n, int k, int row0, int epi, const int* xrows, unsigned long long* keys,
                                 int n_valid) {
@@ -238,6 +238,8 @@ extern "C" int qb_marlin_gemm_z(qb_ctx* ctx, void* stream, const void* X, const 
     if (epi == QB_EPI_ARGMAX && !keys) return QB_ERR_ARG;
     if (epi == QB_EPI_SILU && (n % 16)) return QB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    if (m > 16 && epi != QB_EPI_ARGMAX && !xrows && !ctx->no_tc)
+        return qb_gemm_tc_launch(ctx, st, X, B, Y, S, m, n, k, row0, epi, 1);
     for (int r = 0; r < m; r += 16) {
         int mm = m - r < 16 ? m - r : 16;
         int rc = gemm_rows(ctx, st, X, B, Y, S, mm, n, k, xrows ? 0 : row0 + r, epi, xrows ? xrows + r : nullptr,

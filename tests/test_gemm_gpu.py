@@ -150,12 +150,13 @@ def test_many_rows_fall_back_to_slabs(ctx):
     assert close(y, R.marlin_gemm(x, wdq)).all()
 
 
-@pytest.mark.parametrize("m,epi", [(1, "plain"), (5, "plain"), (13, "plain"), (5, "silu"), (5, "argmax"), (40, "plain")])
+@pytest.mark.parametrize("m,epi", [(1, "plain"), (5, "plain"), (13, "plain"), (5, "silu"), (5, "argmax"), (40, "plain"),
+                                   (300, "silu"), (40, "argmax")])
 @pytest.mark.parametrize("rows,cols", [(512, 1024), (2560, 512)])
 def test_zero_point_product_vs_oracle(ctx, m, epi, rows, cols):
     """The marlin_*_z variants (asymmetric int4): w = (q - 8) * scale + (8 - z) * scale with the second table after the
-    scales; against the oracle's dequantisation (the reference's single f16 rounding of the sum) in f64. 40 rows run
-    as 16-row slabs."""
+    scales; against the oracle's dequantisation (the reference's single f16 rounding of the sum) in f64. More than 16
+    rows run on the tensor-core product (plain, SwiGLU) or as 16-row slabs (argmax)."""
     g = synth.gen(700 + m)
     silu = epi == "silu"
     x = synth.activations(m, cols, g)

@@ -69,3 +69,28 @@ def test_row0_and_prefill_chunk_shape(ctx):
     want = R.marlin_gemm(x[30:80], wdq)
     a = y.cpu().numpy()
     assert close(a[30:80], want).all() and np.all(a[:30] == 0) and np.all(a[80:] == 0)
+
+
+@pytest.mark.parametrize("m,rows,cols,silu", [(600, 1024, 2048, False), (2048, 5120, 1024, False), (520, 512, 1536, True)])
+def test_shares_of_the_tile_list_repeat_and_agree_with_whole_tiles(ctx, m, rows, cols, silu):
+    """The product deals (tile, k block) pairs to a persistent grid in equal contiguous shares when there are few tiles
+    per SM; tiles cut between blocks are summed in block order by the tile's last arriver, so a repeated launch gives
+    the same bits, and the result agrees with the same launch run as whole tiles (only the order of the f32 sums over
+    k differs) and with the oracle."""
+    x, wdq, xd, wd, sd = make(rows, cols, silu, 400 + m, m)
+    epi = "silu" if silu else "plain"
+    ctx.tune(ctas=1000)  # equal shares whatever the shape
+    try:
+        a = ctx.marlin_gemm(xd, wd, sd, epi=epi)
+        b = ctx.marlin_gemm(xd, wd, sd, epi=epi)
+        ctx.tune(ctas=1001)  # whole tiles whatever the shape
+        c = ctx.marlin_gemm(xd, wd, sd, epi=epi)
+    finally:
+        ctx.tune()
+    torch.cuda.synchronize()
+    assert ctx.device_error() == 0
+    assert torch.equal(a, b)
+    want = R.marlin_gemm(x, wdq, epi)
+    an, cn = a.float().cpu().numpy(), c.float().cpu().numpy()
+    assert close(an, want.astype(np.float32)).all() and close(cn, want.astype(np.float32)).all()
+    assert np.abs(an - cn).max() <= (2e-3 if silu else 2e-4) * max(1.0, np.abs(want).max())
