@@ -121,6 +121,7 @@ MEASURE_SIGNATURES = {
     "qb_attr_cache_selftest": [],
     "qb_graph_cache_selftest": [],
     "qb_model_fail_captures": [P, I],
+    "qb_wait_probe": [P, P, C.c_uint],
 }
 _RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
             "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,

@@ -1,5 +1,6 @@
 // Context creation and the error word.
 #include "ctx.h"
+#include "common.cuh"
 #include <array>
 #include <map>
 #include <mutex>
@@ -116,3 +117,29 @@ int qb_set_pdl(qb_ctx* c, int on) {
 }
 
 }  // extern "C"
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// Test of the waits' way out: a block waits (with the library's bounded wait, here with a short poll limit) on an
+// mbarrier that nothing ever arrives on; the wait runs out, the block records code 99 in the context's error word and
+// returns. The host reads it with qb_device_error and the context stays usable.
+namespace qb {
+__global__ void wait_probe_kernel(int* err, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(&bar, 0, limit);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok && threadIdx.x == 0) atomicExch(err, 99);
+}
+}  // namespace qb
+
+extern "C" int qb_wait_probe(qb_ctx* ctx, void* stream, unsigned limit) {
+    if (!ctx || limit == 0 || limit > (1u << 20)) return QB_ERR_ARG;
+    qb::wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->err, limit);
+    return (int)cudaGetLastError();
+}

@@ -22,6 +22,9 @@ int qb_model_fail_captures(struct qb_model* m, int n);
  * kernel-attribute bookkeeping; 0 when they hold. */
 int qb_graph_cache_selftest(void);
 int qb_attr_cache_selftest(void);
+/* Tests: one block waits on an mbarrier that nothing arrives on, with the library's bounded wait cut to `limit` polls
+ * (at most 2^20); the wait runs out and the context's error word reads 99 (qb_device_error). */
+int qb_wait_probe(qb_ctx* ctx, void* stream, unsigned limit);
 #ifdef __cplusplus
 }
 #endif

@@ -52,6 +52,10 @@ class Context:
     def device_error(self) -> int:
         return lib().qb_device_error(self.h)
 
+    def wait_probe(self, limit: int = 1 << 12, stream=None):
+        """Tests: a block waits `limit` polls on an mbarrier nothing arrives on and records error 99."""
+        check(lib().qb_wait_probe(self.h, stream, limit), "qb_wait_probe")
+
     def set_pdl(self, on: bool):
         check(lib().qb_set_pdl(self.h, int(on)), "qb_set_pdl")
 

@@ -111,3 +111,26 @@ def test_noalloc_takes_every_product_of_the_27b_step(ctx):
             assert torch.equal(y, want), (n, k, m)
         del w
     assert lib().qb_static_device_error() == 0
+
+
+@pytest.mark.gpu
+def test_a_wait_that_runs_out_is_reported_and_the_context_lives_on(ctx):
+    """Every device-side wait of the library is the same bounded poll loop; when it runs out the kernel records a code
+    in the context's error word and returns. Here a block waits (4096 polls) on an mbarrier that nothing arrives on:
+    qb_device_error reads 99 once, then 0, and the next product on the context is right."""
+    import numpy as np
+    from oracle import ref_ops as R
+    from qwenny_b200 import host, synth
+    assert ctx.device_error() == 0
+    ctx.wait_probe(1 << 12)
+    torch.cuda.synchronize()
+    assert ctx.device_error() == 99
+    assert ctx.device_error() == 0
+    g = synth.gen(5)
+    x = synth.activations(5, 512, g)
+    codes, sc = synth.int4_matrix(256, 512, g)
+    words, s16 = host.pack_marlin(codes, sc)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    y = ctx.marlin_gemm(dev(x), dev(words.view(np.int32)), dev(s16.view(np.int16)).view(torch.float16)).cpu().numpy()
+    want = R.marlin_gemm(x, R.dequant(codes, sc.astype(np.float16)))
+    assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max()) and ctx.device_error() == 0
