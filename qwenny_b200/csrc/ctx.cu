@@ -119,6 +119,20 @@ int qb_set_pdl(qb_ctx* c, int on) {
 }  // extern "C"
 
 
+namespace qb {
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+}  // namespace qb
+
 // ---------------------------------------------------------------------------------------------------------------
 // Test of the waits' way out: a block waits (with the library's bounded wait, here with a short poll limit) on an
 // mbarrier that nothing ever arrives on; the wait runs out, the block records code 99 in the context's error word and

@@ -1,6 +1,7 @@
 // The library context: what the reference's Gemm::load allocates once per model (src/cuda/core.rs:437-464) — the SM
 // count and the scratch its blocks reduce through — plus the device error word of the bounded waits.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/qwenny_b200.h"
@@ -35,6 +36,12 @@ constexpr int QB_TC_TICKETS = 1 << 16;  // tiles of one tensor-core W4A16 produc
     } while (0)
 
 namespace qb {
+
+// cuTensorMapEncodeTiled, resolved through the runtime (the library does not link the driver); null when unavailable
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled();
 
 // Kernel attributes (the opt-in to more than 48 KB of dynamic shared memory, the shared-memory carve-out) belong to the
 // device that is current when cudaFuncSetAttribute runs, so what has been set is remembered per (device, kernel), not

@@ -12,9 +12,10 @@ struct GemvPlan {
     int cluster_s;  // > 0: clustered split K with this many ranks per column block
 };
 
-static int smem_of(int cg, int kg, int m, int nstages, int zp = 0) {
+static int smem_of(int cg, int kg, int m, int nstages, int zp = 0) {  // GemvCfg<cg, kg, .>::smem
     int nw = cg * kg, tk = kg * 128, tn = cg * 64;
-    return 128 + (tk + 8) * 2 + nstages * (nw * 4096 + (1 + zp) * kg * tn * 2 + m * (tk + 8) * 2);
+    int stage = (nw * 4096 + (1 + zp) * kg * tn * 2 + m * (tk + 8) * 2 + 127) / 128 * 128;
+    return 128 + ((tk + 8) * 2 + 127) / 128 * 128 + nstages * stage;
 }
 
 // Blocks of the persistent grid and the most of them that can share one column block (the scratch stride).
@@ -94,7 +95,33 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
     }
     lc.attrs = at;
     lc.numAttrs = nat;
-    QB_CUDA(cudaLaunchKernelEx(&lc, kern, a));
+    GemvMaps maps = {};
+    EncodeTiled enc = encode_tiled();
+    if (!enc) return QB_ERR_UNSUPPORTED;
+    a.xmap = (!a.xrows && C::XTENSOR) ? 1 : 0;
+    if (a.xmap) {
+        // X: m rows of K halves = K/4 8-byte elements from row0 on; box: a padded row (XROW halves) x m rows
+        const cuuint64_t xd[2] = {(cuuint64_t)(a.K / 4), (cuuint64_t)a.m}, xs[1] = {(cuuint64_t)a.K * 2};
+        const cuuint32_t xb[2] = {(cuuint32_t)(C::XROW / 4), (cuuint32_t)a.m}, one[2] = {1, 1};
+        if (enc(&maps.x, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)(a.X + (size_t)a.row0 * a.K), xd, xs, xb, one,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return QB_ERR_ARG;
+    }
+    if (C::TENSOR) {
+        // weights: K/16 rows of 2N words = N 8-byte elements; a stage's box: CG x 64 elements x TK/16 rows
+        const cuuint64_t wd[2] = {(cuuint64_t)a.N, (cuuint64_t)(a.K / 16)}, ws[1] = {(cuuint64_t)a.N * 8};
+        const cuuint32_t wb[2] = {(cuuint32_t)(CG * 64), (cuuint32_t)(C::TK / 16)}, one[2] = {1, 1};
+        // scales (and offsets): K/128 (x 2) rows of N halves; box TN x KG
+        const cuuint64_t sd[2] = {(cuuint64_t)a.N, (cuuint64_t)((1 + a.zp) * (a.K / 128))}, ss[1] = {(cuuint64_t)a.N * 2};
+        const cuuint32_t sb[2] = {(cuuint32_t)C::TN, (cuuint32_t)KG};
+        if (enc(&maps.w, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)a.B, wd, ws, wb, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            enc(&maps.s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)a.S, sd, ss, sb, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return QB_ERR_ARG;
+    }
+    QB_CUDA(cudaLaunchKernelEx(&lc, kern, maps, a));
     return QB_OK;
 }
 

@@ -408,31 +408,12 @@ __global__ void __launch_bounds__(THREADS, 1) w4a16_gemm_tc_kernel(const __grid_
 
 using namespace qb;
 
-namespace {
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
-            qr == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-}  // namespace
 
 // Y = X . W^T for m > 16 rows: plain (f32 [m][n]) or SwiGLU (f16 [m][n/2]). X f16 [.][k], rows row0 .. row0 + m - 1.
 int qb_gemm_tc_launch(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B, void* Y, const void* S, int m, int n,
                       int k, int row0, int epi, int zp) {
     if (n % tc::BO || k % 128 || m < 1) return QB_ERR_ARG;
-    EncodeTiled enc = encode_tiled();
+    qb::EncodeTiled enc = qb::encode_tiled();
     if (!enc) return QB_ERR_UNSUPPORTED;
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};

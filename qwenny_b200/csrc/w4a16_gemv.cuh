@@ -28,11 +28,26 @@
 // Epilogues as the reference's: plain f32 [m][n]; SwiGLU of interleaved gate/up blocks -> f16 [m][n/2]
 // (kernels/marlin.cuh:472-498); plain + argmax keys over the first n_valid outputs (:499-517).
 #pragma once
+#include <cuda.h>
 #include "common.cuh"
 
 namespace qb {
 
 enum { EPI_PLAIN = 0, EPI_SILU = 1, EPI_ARGMAX = 2 };
+
+// tensor maps of the weights ([K/16] rows of N 8-byte elements) and of the scale table(s) ([K/128 (x 2)] rows of N halves)
+// and of the step's X rows when they are contiguous ([m] rows of K/4 8-byte elements; the box is XROW halves wide, so
+// the rows land in shared memory with the pad the ldmatrix reads want; the last k tile's pad reads past the row: zeros)
+struct GemvMaps {
+    CUtensorMap w, s, x;
+};
+
+__device__ __forceinline__ void tma_tile_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n" ::
+            "r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
 
 struct GemvArgs {
     const __half* X;      // [rows][K] f16
@@ -48,6 +63,7 @@ struct GemvArgs {
     int* counters;        // [N/64] tickets, zero between launches
     unsigned long long* keys;
     int n_valid;
+    int xmap;             // the X rows arrive by the tensor map (contiguous rows, a padded row fits a box)
     int zp;               // zero points: S holds a second table [K/128][N] of (8 - z) * scale after the scales
     int* err;             // set non-zero when a bounded wait ran out
     int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone)
@@ -73,10 +89,16 @@ struct GemvCfg {
     static constexpr int S_BYTES = KG * TN * 2;
     static constexpr int RED_BYTES = (KG > 1 ? KG - 1 : 1) * CG * NT * 2048;  // lives in a consumed stage's weights
     static constexpr int BAR_BYTES = 128;
+    static constexpr int ZROW_BYTES = (XROW * 2 + 127) / 128 * 128;
+    // tiles of up to 256 outputs: a stage's weights and its scales arrive as ONE tensor-map TMA load each (a box of
+    // TK / 16 rows of CG x 512 bytes; KG rows of TN scales) instead of TK / 16 + KG bulk copies: the copy warp has 7
+    // operations to issue per stage, not 23, which is worth 7-11 % of a large product's time
+    static constexpr bool TENSOR = CG <= 4;
+    static constexpr bool XTENSOR = XROW / 4 <= 256;  // a padded X row fits one box (8-byte elements, at most 256)
     // a stage holds the weights, the group scales and the m live rows of X; one zero row serves the other token rows
-    // (zp: the zero-point offsets of the stage's groups follow its scales)
-    static constexpr int stage_bytes(int m, int zp = 0) { return W_BYTES + (1 + zp) * S_BYTES + m * XROW * 2; }
-    static constexpr int smem(int nstages, int m, int zp = 0) { return BAR_BYTES + XROW * 2 + nstages * stage_bytes(m, zp); }
+    // (zp: the zero-point offsets of the stage's groups follow its scales); stages start on 128-byte boundaries
+    static constexpr int stage_bytes(int m, int zp = 0) { return (W_BYTES + (1 + zp) * S_BYTES + m * XROW * 2 + 127) / 128 * 128; }
+    static constexpr int smem(int nstages, int m, int zp = 0) { return BAR_BYTES + ZROW_BYTES + nstages * stage_bytes(m, zp); }
     static_assert(RED_BYTES <= W_BYTES, "the reduction buffer fits a stage's weights");
 };
 
@@ -150,13 +172,13 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, float (&acc)[NT
 
 // ZP: the zero-point variant (a.zp set): compiled apart so that the symmetric product carries none of it
 template <int CG, int KG, int NT, int EPI, int ZP = 0>
-__global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kernel(const __grid_constant__ GemvMaps maps, const GemvArgs a) {
     using C = GemvCfg<CG, KG, NT>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + GEMV_MAX_STAGES;
     uint8_t* zrow = smem + C::BAR_BYTES;              // XROW halves of zeros: the token rows m .. 8 NT - 1
-    uint8_t* stages = zrow + C::XROW * 2;
+    uint8_t* stages = zrow + C::ZROW_BYTES;
     const int STAGE_BYTES = C::stage_bytes(a.m, ZP);  // weights | scales (| offsets) | m rows of X
     const int X_OFF = C::W_BYTES + (1 + ZP) * C::S_BYTES;
 
@@ -194,7 +216,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         // ------------------------------------------------------------ producer
         const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
         const uint32_t mine = (uint32_t)(end - beg);
-        const uint32_t tx = C::W_BYTES + (1 + ZP) * C::S_BYTES + a.m * C::TK * 2;
+        const uint32_t tx = C::W_BYTES + (1 + ZP) * C::S_BYTES + a.m * (a.xmap ? C::XROW : C::TK) * 2;
         // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
         auto issue = [&](int cb, int st, int slot, int what) {
             int n0 = cb * C::TN, k0 = st * C::TK;
@@ -202,17 +224,27 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             if (what != 1) {
                 if (lane == 0) mbar_expect_tx(&full[slot], tx);
                 __syncwarp();
-                const uint8_t* wsrc = (const uint8_t*)a.B + ((size_t)(k0 / 16) * 2 * a.N + (size_t)(n0 / 64) * 128) * 4;
-                for (int c = lane; c < C::TK / 16; c += 32)
-                    bulk_g2s(base + c * (CG * 512), wsrc + (size_t)c * 8 * a.N, CG * 512, &full[slot], pol_w);
-                if (lane < KG)
-                    bulk_g2s(base + C::W_BYTES + lane * (C::TN * 2),
-                             a.S + (size_t)(k0 / 128 + lane) * a.N + n0, C::TN * 2, &full[slot], pol_w);
-                if (ZP && lane >= 8 && lane < 8 + KG)
-                    bulk_g2s(base + C::W_BYTES + C::S_BYTES + (lane - 8) * (C::TN * 2),
-                             a.S + (size_t)(a.K / 128 + k0 / 128 + lane - 8) * a.N + n0, C::TN * 2, &full[slot], pol_w);
+                if (C::TENSOR) {
+                    if (lane == 0) {
+                        tma_tile_2d(base, &maps.w, n0, k0 / 16, &full[slot], pol_w);
+                        tma_tile_2d(base + C::W_BYTES, &maps.s, n0, k0 / 128, &full[slot], pol_w);
+                        if (ZP) tma_tile_2d(base + C::W_BYTES + C::S_BYTES, &maps.s, n0, a.K / 128 + k0 / 128, &full[slot], pol_w);
+                    }
+                } else {
+                    const uint8_t* wsrc = (const uint8_t*)a.B + ((size_t)(k0 / 16) * 2 * a.N + (size_t)(n0 / 64) * 128) * 4;
+                    for (int c = lane; c < C::TK / 16; c += 32)
+                        bulk_g2s(base + c * (CG * 512), wsrc + (size_t)c * 8 * a.N, CG * 512, &full[slot], pol_w);
+                    if (lane < KG)
+                        bulk_g2s(base + C::W_BYTES + lane * (C::TN * 2),
+                                 a.S + (size_t)(k0 / 128 + lane) * a.N + n0, C::TN * 2, &full[slot], pol_w);
+                    if (ZP && lane >= 8 && lane < 8 + KG)
+                        bulk_g2s(base + C::W_BYTES + C::S_BYTES + (lane - 8) * (C::TN * 2),
+                                 a.S + (size_t)(a.K / 128 + k0 / 128 + lane - 8) * a.N + n0, C::TN * 2, &full[slot], pol_w);
+                }
             }
-            if (what != 0) {
+            if (what != 0 && a.xmap) {
+                if (lane == 0) tma_tile_2d(base + X_OFF, &maps.x, k0 / 4, 0, &full[slot], pol_x);
+            } else if (what != 0) {
                 if (lane < a.m) {
                     int row = a.xrows ? a.xrows[lane] : a.row0 + lane;
                     bulk_g2s(base + X_OFF + lane * (C::XROW * 2), a.X + (size_t)row * a.K + k0, C::TK * 2,
