@@ -464,7 +464,11 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             return;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[pslot]);  // the reduction buffer is read: the slot goes back to the copy warp
+        // the reduction buffer is read: the slot goes back to the copy warp (the kg = 0 warps keep it a little longer:
+        // a finishing block stages the other blocks' partial sums in it; with one k group per tile no barrier has
+        // been met yet, and every warp must be done with the stage's words before one of them writes there)
+        if (KG == 1) named_bar_sync(1, C::NW * 32);
+        if (lane == 0 && kg != 0) mbar_arrive(&empty[pslot]);
         if (kg == 0) {
             const int colgrp = pcb * CG + cg;  // 64 outputs
             bool finish = true;
@@ -493,18 +497,41 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
                         for (int b = 0; b < 4; b++)
 #pragma unroll
                             for (int i = 0; i < 4; i++) acc[j][b][i] = 0.f;
-                    for (int s = 0; s < nshare; s++) {
+                    // The partial sums of UCH sharers at a time come into the warp's part of the slot by cp.async (L2
+                    // only), all in flight together, and are added from there in block order: a column block of a
+                    // long-k matrix has some 15 sharers, and one L2 round trip each was 5 us of tail.
+                    constexpr int UCH = (2 * KG / NT) < 1 ? 1 : ((2 * KG / NT) > 4 ? 4 : (2 * KG / NT));
+                    float4* stg = red + (size_t)cg * UCH * (NT * 4 * 32);
+                    for (int s0 = 0; s0 < nshare; s0 += UCH) {
 #pragma unroll
-                        for (int j = 0; j < NT; j++)
+                        for (int u = 0; u < UCH; u++)
+                            if (s0 + u < nshare) {
 #pragma unroll
-                            for (int b = 0; b < 4; b++) {
-                                float4 v = __ldcg(p0 + (size_t)s * (NT * 4 * 32) + (j * 4 + b) * 32 + lane);
-                                acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
+                                for (int q = 0; q < NT * 4; q++)
+                                    cp_async16(stg + (u * NT * 4 + q) * 32 + lane,
+                                               p0 + (size_t)(s0 + u) * (NT * 4 * 32) + q * 32 + lane);
                             }
+                        cp_async_commit();
+                        cp_async_wait_all();
+                        __syncwarp();
+#pragma unroll
+                        for (int u = 0; u < UCH; u++)
+                            if (s0 + u < nshare) {
+#pragma unroll
+                                for (int j = 0; j < NT; j++)
+#pragma unroll
+                                    for (int b = 0; b < 4; b++) {
+                                        float4 v = stg[(u * NT * 4 + j * 4 + b) * 32 + lane];
+                                        acc[j][b][0] += v.x; acc[j][b][1] += v.y; acc[j][b][2] += v.z; acc[j][b][3] += v.w;
+                                    }
+                            }
+                        __syncwarp();
                     }
                     if (lane == 0) a.counters[colgrp] = 0;  // left zero for the next product
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[pslot]);
             if (finish) gemv_epilogue<NT, EPI>(a, acc, colgrp * 64, lane);
         }
 #pragma unroll
