@@ -184,7 +184,8 @@ extern "C" int qb_marlin_trace(qb_ctx* ctx, long long* buf) {
 }
 
 // Measurement only: 1 makes the products' consumers release every stage unread, which times the copy pipeline alone
-// (results are then meaningless); 0 restores the product.
+// (results are then meaningless); 2 (tests) makes the copy warp leave out its second stage and cuts the consumers' wait
+// to 1024 polls: the wait runs out, the warps record error 2, walk on and the kernel ends; 0 restores the product.
 extern "C" int qb_marlin_probe(qb_ctx* ctx, int mode) {
     ctx->probe = mode;
     return QB_OK;
@@ -215,6 +216,7 @@ static int gemm_rows(qb_ctx* ctx, cudaStream_t st, const void* X, const void* B,
     a.m = m; a.N = n; a.K = k; a.row0 = row0;
     a.nstages = p.nstages; a.maxc = 1;
     a.probe = ctx->probe;
+    a.wait_limit = ctx->probe == 2 ? 1024u : WAIT_LIMIT;
     a.trace = ctx->trace;
     if (ctx->trace) ctx->trace += 4 * 1024;  // the next product's slots
     a.scratch = (float4*)ctx->scratch; a.counters = ctx->counters; a.keys = keys; a.n_valid = n_valid; a.err = ctx->err;

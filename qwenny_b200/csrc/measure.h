@@ -13,7 +13,8 @@ int qb_marlin_tune(qb_ctx* ctx, int cg, int kg, int nstages, int ctas_per_sm);
  * last stage consumed, end; 4 x 1024 int64 per call) into consecutive slices of `buf`; NULL switches it off. */
 int qb_marlin_trace(qb_ctx* ctx, long long* buf);
 /* mode 1 makes the products' consumers release every stage unread, so a launch times the copy pipeline alone (its
- * results are meaningless); 0 restores the product. */
+ * results are meaningless); mode 2 (tests) makes the copy warp leave out its second stage and cuts the consumers' wait
+ * to 1024 polls: their wait runs out, they record error 2 and walk on, the kernel ends; 0 restores the product. */
 int qb_marlin_probe(qb_ctx* ctx, int mode);
 /* Tests: the next n graph captures of the model report out of memory without touching the GPU. */
 struct qb_model;

@@ -66,7 +66,9 @@ struct GemvArgs {
     int xmap;             // the X rows arrive by the tensor map (contiguous rows, a padded row fits a box)
     int zp;               // zero points: S holds a second table [K/128][N] of (8 - z) * scale after the scales
     int* err;             // set non-zero when a bounded wait ran out
-    int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone)
+    int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone);
+                          // 2 (tests) = the copy warp leaves out its second stage, so the consumers' wait for it runs out
+    uint32_t wait_limit;  // polls the consumers give a stage (WAIT_LIMIT; short under probe 2)
     long long* trace;     // measurement only (may be null): per block {start, first stage landed, last stage
                           // consumed, end} in ns of the global timer
 };
@@ -264,7 +266,8 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         for (uint32_t it = 0; it < early; it++, next()) issue(cb, st, (int)it, 0);
         pdl_wait();
         cb = cb0; st = st0;
-        for (uint32_t it = 0; it < pre; it++, next()) issue(cb, st, (int)it, it < early ? 1 : 2);
+        for (uint32_t it = 0; it < pre; it++, next())
+            if (!(a.probe == 2 && it == 1)) issue(cb, st, (int)it, it < early ? 1 : 2);
         bool ok = true;
         int slot = 0;
         uint32_t par = 0;  // parity of the consumers' release this slot is waiting for
@@ -299,7 +302,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     for (int x = beg; x < end; x++) {
         {
             if (!dead) {
-                dead = !mbar_wait(&full[slot], par);
+                dead = !mbar_wait(&full[slot], par, a.wait_limit);
                 if (dead && lane == 0) atomicExch(a.err, 2);
             } else {
                 for (int i = 0; i < 1024 && !mbar_try_wait(&full[slot], par); i++) {}

@@ -134,3 +134,38 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_lives_on(ctx):
     y = ctx.marlin_gemm(dev(x), dev(words.view(np.int32)), dev(s16.view(np.int16)).view(torch.float16)).cpu().numpy()
     want = R.marlin_gemm(x, R.dequant(codes, sc.astype(np.float16)))
     assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max()) and ctx.device_error() == 0
+
+
+@pytest.mark.gpu
+def test_a_product_whose_stage_never_lands_gives_up_and_reports_it(ctx):
+    """The skinny product's own way out: the copy warp leaves out the second stage of every block (a measurement switch),
+    the consumers' wait for it runs out after 1024 polls, each warp records error 2, walks the rest of its schedule
+    and the kernel ends. qb_device_error reports 2; afterwards the same product on the same context is right again
+    (tickets and ring barriers are left usable)."""
+    import numpy as np
+    from oracle import ref_ops as R
+    from qwenny_b200 import host, synth
+    g = synth.gen(8)
+    # (5120 x 6144, the out-projection: 480 tile stages on 296 blocks, so many blocks have a second stage)
+    x = synth.activations(5, 6144, g)
+    codes, sc = synth.int4_matrix(5120, 6144, g)
+    words, s16 = host.pack_marlin(codes, sc)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    xd, wd, sd = dev(x), dev(words.view(np.int32)), dev(s16.view(np.int16)).view(torch.float16)
+    want = R.marlin_gemm(x, R.dequant(codes, sc.astype(np.float16)))
+    assert ctx.device_error() == 0
+    for ctas in (-2, 2):  # equal shares of the persistent grid, and a cluster per column block
+        ctx.tune(ctas=ctas)
+        try:
+            lib().qb_marlin_probe(ctx.h, 2)
+            ctx.marlin_gemm(xd, wd, sd)
+            lib().qb_marlin_probe(ctx.h, 0)
+            torch.cuda.synchronize()
+            assert ctx.device_error() == 2
+            for _ in range(2):
+                y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
+                assert np.abs(y - want).max() < 2e-3 * max(1.0, np.abs(want).max())
+            assert ctx.device_error() == 0
+        finally:
+            lib().qb_marlin_probe(ctx.h, 0)
+            ctx.tune()
