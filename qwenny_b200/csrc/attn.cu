@@ -18,17 +18,6 @@
 
 namespace qb {
 
-// Keys per split of a token with `keys` keys: a multiple of 64, at most `dsplits` splits (SM count / kv heads), and the same for every key
-// count between two multiples of 2048 (where the host cuts short segments: a token's splits must not depend on how
-// many drafts follow it in the step), so it is sized for the end of that range.
-__host__ __device__ inline int dec_chunk(int keys, int dsplits) {
-    const int range_end = ((keys - 1) / 2048 + 1) * 2048;
-    return max(64, ((range_end + dsplits - 1) / dsplits + 63) / 64 * 64);
-}
-__host__ __device__ inline int dec_splits(int keys, int dsplits) { int c = dec_chunk(keys, dsplits); return (keys + c - 1) / c; }
-// the most key splits of a decode token on a part with `sms` SMs: one block per SM over the kv heads, at most 64
-__host__ inline int dsplits_for(int sms) { return max(1, min(64, sms / NKV)); }
-
 // ------------------------------------------------------------------------------------------------ attn_prep
 // grid (n tokens, 2): block (t, 0) makes the 24 query heads and their gates (a warp per head), block (t, 1) the 4 key
 // and 4 value heads and stores them in the cache. A warp's lane owns dims lane + 32 j of its head: the RoPE pair
@@ -457,8 +446,8 @@ struct Dec4Cfg {
 template <int RT, int NQ>
 __global__ void __launch_bounds__(Dec4Cfg<RT, NQ>::THREADS, 1)
 attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const float* ks, const float* vs, const int* dseg,
-                 const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z, int dsplits, float* part_ml,
-                 float* part_acc, float* out, int* err) {
+                 const int* dtok, const int* tok_slot, const int* tok_pos, int cap, int z, int dsplits, int old_margin,
+                 float* part_ml, float* part_acc, float* out, int* err) {
     using C = Dec4Cfg<RT, NQ>;
     constexpr int NSTG = C::NSTG, SK = C::SK, STG_BYTES = C::STG_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -475,8 +464,9 @@ attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const flo
     }
     __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();  // the step's own keys and values are written by attn_prep just before
-
+    // The step's token lists are uploaded before its first kernel, so they are read ahead of the kernel before (this
+    // step's attn_prep), and so are the stages of keys and values that earlier steps wrote: whatever ends `old_margin`
+    // positions or more before the segment's last key (0: nothing is read ahead).
     const int first = dseg[2 * seg], nt = dseg[2 * seg + 1];
     const int tlast = dtok[first + nt - 1], keys = tok_pos[tlast] + 1;
     const int chunk = dec_chunk(keys, dsplits), ns = (keys + chunk - 1) / chunk;
@@ -491,8 +481,13 @@ attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const flo
         const uint8_t* vh = vc + cache_head(slot, g, cap);
         const float* ksh = ks + scale_head(slot, g, cap);
         const float* vsh = vs + scale_head(slot, g, cap);
+        bool waited = false;
         for (int j = 0; j < nstg; j++) {
             const int sl = j % NSTG;
+            if (!waited && (old_margin <= 0 || kbeg + (j + 1) * SK > keys - old_margin)) {
+                pdl_wait();
+                waited = true;
+            }
             if (j >= NSTG) {
                 bool ok = true;
                 if (lane == 0) ok = mbar_wait(&empty[sl], ((j / NSTG) - 1) & 1);
@@ -517,6 +512,7 @@ attn_dec4_kernel(const float* q, const uint8_t* kc, const uint8_t* vc, const flo
     // ---------------------------------------------------------------- compute warps
     const int quad = warp >> 2, w = warp & 3, r = lane >> 2, t4 = lane & 3;
     constexpr int NCW = C::CW * 32;
+    pdl_wait();  // q and the gates come from this step's attn_prep
     // Q of the segment's rows (row = token * GROUP + head) as f16
     for (int x = threadIdx.x; x < RT * 16 * HD / 4; x += NCW) {
         const int row = x / (HD / 4), d = (x % (HD / 4)) * 4, tok = row / GROUP;
@@ -893,13 +889,16 @@ int qb_attn_decode(qb_ctx* ctx, void* stream, const float* q, const void* kc, co
     const int z = dec_splits(max_keys, dsplits), rt = (dmax * GROUP + 15) / 16;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(ndseg, NKV, z);
+    // a step has at most 64 decode tokens: whatever lies 64 positions or more before a segment's last key is from
+    // earlier steps
+    const int old_margin = ndec <= 64 ? 64 : 0;
     int rc;
 #define QB_DEC(RT, NQ)                                                                                          \
     {                                                                                                           \
         using C = Dec4Cfg<RT, NQ>;                                                                              \
         rc = launch(ctx, attn_dec4_kernel<RT, NQ>, grid, dim3(C::THREADS), C::SMEM, st, q, (const uint8_t*)kc, \
-                    (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, dsplits, part_ml, part_acc, \
-                    out, ctx->err);                                                                             \
+                    (const uint8_t*)vc, ks, vs, dseg, dtok, tok_slot, tok_pos, cap, z, dsplits, old_margin, part_ml,   \
+                    part_acc, out, ctx->err);                                                                             \
     }
     // quads per block: as many as leave every warp its registers (a warp holds RT x 32 output accumulators per lane);
     // measured at 5 rows: 2 quads 33.4 us, 3 quads (spills) 36.6 us, 4 quads 43.2 us

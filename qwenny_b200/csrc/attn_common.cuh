@@ -24,6 +24,17 @@ __device__ __forceinline__ size_t vslot(int pos, int d) {
     return ((size_t)(pos >> 4) * HD + d) * 16 + t4 * 4 + e;
 }
 
+// Keys per split of a token with `keys` keys: a multiple of 64, at most `dsplits` splits (SM count / kv heads), and the same for every key
+// count between two multiples of 2048 (where the host cuts short segments: a token's splits must not depend on how
+// many drafts follow it in the step), so it is sized for the end of that range.
+__host__ __device__ inline int dec_chunk(int keys, int dsplits) {
+    const int range_end = ((keys - 1) / 2048 + 1) * 2048;
+    return max(64, ((range_end + dsplits - 1) / dsplits + 63) / 64 * 64);
+}
+__host__ __device__ inline int dec_splits(int keys, int dsplits) { int c = dec_chunk(keys, dsplits); return (keys + c - 1) / c; }
+// the most key splits of a decode token on a part with `sms` SMs: one block per SM over the kv heads, at most 64
+__host__ inline int dsplits_for(int sms) { return max(1, min(64, sms / NKV)); }
+
 constexpr int PTILE = 64 / GROUP;  // tokens of a prompt tile at most
 
 }  // namespace qb
