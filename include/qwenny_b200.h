@@ -189,7 +189,12 @@ int qb_marlin_gather(qb_ctx* ctx, void* stream, const void* x, const int* rows, 
  *                 and accumulators of 256 floats. The split size is a function of the key count alone
  *                 and of the context's SM count alone (qb_attn_dec_splits_sm: at most one block per SM over the four kv
  *                 heads, 64 at most), as the reference's dchunk is of the key count (kernels/attn.cuh:41-46).
- *                 qb_attn_dec_splits is the same for a 148-SM part. */
+ *                 qb_attn_dec_splits is the same for a 148-SM part. With at most 64 decode tokens in the call
+ *                 (ndec) the kernel reads the token lists (dseg, dtok, tok_slot, tok_pos) and the cache entries that
+ *                 lie 64 positions or more before a segment's last key AHEAD of the kernel enqueued before it on the
+ *                 stream (programmatic dependent launch): those must be complete by then, which holds when the lists
+ *                 are uploaded before the step's kernels and such cache entries were written by earlier steps, as in
+ *                 the reference's host. Everything else (q, the gate, the step's own keys and values) waits. */
 int qb_attn_prep(qb_ctx* ctx, void* stream, const float* part, int splits, int n, const float* q_norm,
                  const float* k_norm, const float* inv_freq, float qscale, float* q, float* out, void* kc, void* vc,
                  float* ks, float* vs, const int* tok_slot, const int* tok_pos, int cap);
