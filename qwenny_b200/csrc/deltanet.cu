@@ -95,45 +95,72 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
     bool lp_pending = false;  // a cluster barrier phase this block has arrived at and not yet waited for
     for (int c0 = 0; c0 < len; c0 += TCH) {
         const int m = min(TCH, len - c0);
-        // ---- ONE round trip of independent loads: conv inputs (step rows or ring), z, gates, the ring share; all of
-        // them into registers first, the shared-memory stores after
+        // ---- ONE round trip of independent loads: conv inputs (step rows or ring), z, gates, the ring share.
+        // With one split of the in-projection (the usual case) the conv inputs and z go straight to shared memory as
+        // 16-byte asynchronous copies from a short loop (L2 only: another kernel wrote them): a handful of
+        // instructions per thread. Unrolled into some thirty register loads with their own address arithmetic the
+        // same staging took 2 us just to ISSUE: the kernel runs once per launch, so every instruction of it is also
+        // an instruction fetched cold.
         constexpr int NROW = TCH + CONV_K - 1, NZV = (TCH * FCOLS + FNT - 1) / FNT;
-        // conv inputs: thread tid takes channel tid of every row, and threads below FCH - FNT also channel FNT + tid
-        float xv[NROW][2], zv[NZV], ringv[4], gate = 0.f;
-        const int gc0 = gchan(tid), gc1 = gchan(min(FNT + tid, FCH - 1));
-        const bool two = FNT + tid < FCH;
-#pragma unroll
-        for (int row = 0; row < NROW; row++) {
-            xv[row][0] = xv[row][1] = 0.f;
-            const int si = c0 + row - (CONV_K - 1), qp = p0 + si;
-            if (row < m + CONV_K - 1 && qp >= 0) {
-                if (si >= 0) {
-                    // (one split is the common case: a plain load, so that every row's loads are in flight together;
-                    // a warp issues in order, and a sum inside a loop would wait for each load before the next)
-                    const float* pr = p + (size_t)(t0 + si) * DELTA_IN;
-                    xv[row][0] = __ldcg(pr + gc0);
-                    if (two) xv[row][1] = __ldcg(pr + gc1);
-                    for (int s = 1; s < splits; s++) {
-                        pr += (size_t)n * DELTA_IN;
-                        xv[row][0] += __ldcg(pr + gc0);
-                        if (two) xv[row][1] += __ldcg(pr + gc1);
-                    }
+        float ringv[4], gate = 0.f;
+        const bool direct = splits == 1;
+        if (direct) {
+            const int nrow = m + CONV_K - 1;
+            for (int e = tid; e < nrow * (FCH / 4); e += FNT) {
+                const int row = e / (FCH / 4), c = (e - row * (FCH / 4)) * 4;
+                const int si = c0 + row - (CONV_K - 1), qp = p0 + si;
+                float* dst = &R.x[row][c];
+                if (qp < 0) {
+                    *(float4*)dst = make_float4(0.f, 0.f, 0.f, 0.f);
                 } else {
-                    const float* rr = sm0 + SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV;
-                    xv[row][0] = __ldcg(rr + gc0);
-                    if (two) xv[row][1] = __ldcg(rr + gc1);
+                    cp_async16(dst, si >= 0 ? p + (size_t)(t0 + si) * DELTA_IN + gchan(c)
+                                            : sm0 + SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV + gchan(c));
                 }
             }
+            for (int e = tid; e < m * (FCOLS / 4); e += FNT) {
+                const int tk = e / (FCOLS / 4), c = (e - tk * (FCOLS / 4)) * 4;
+                cp_async16(&R.z[tk][c], p + (size_t)(t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + hf * FCOLS + c);
+            }
+            cp_async_commit();
         }
+        // several splits: thread tid takes channel tid of every row, and threads below FCH - FNT also channel FNT + tid
+        float xv[NROW][2], zv[NZV];
+        const int gc0 = gchan(tid), gc1 = gchan(min(FNT + tid, FCH - 1));
+        const bool two = FNT + tid < FCH;
+        if (!direct) {
 #pragma unroll
-        for (int u = 0; u < NZV; u++) {
-            const int x = u * FNT + tid;
-            zv[u] = 0.f;
-            if (x < m * FCOLS) {
-                int tk = x / FCOLS, c = x - tk * FCOLS;
-                const float* pz = p + (size_t)(t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + hf * FCOLS + c;
-                zv[u] = __ldcg(pz);
-                for (int s = 1; s < splits; s++) zv[u] += __ldcg(pz + (size_t)s * n * DELTA_IN);
+            for (int row = 0; row < NROW; row++) {
+                xv[row][0] = xv[row][1] = 0.f;
+                const int si = c0 + row - (CONV_K - 1), qp = p0 + si;
+                if (row < m + CONV_K - 1 && qp >= 0) {
+                    if (si >= 0) {
+                        // (the first split's value is a plain load, so that every row's first loads are in flight
+                        // together: a warp issues in order, and a sum inside a loop waits for each load before the next)
+                        const float* pr = p + (size_t)(t0 + si) * DELTA_IN;
+                        xv[row][0] = __ldcg(pr + gc0);
+                        if (two) xv[row][1] = __ldcg(pr + gc1);
+                        for (int s = 1; s < splits; s++) {
+                            pr += (size_t)n * DELTA_IN;
+                            xv[row][0] += __ldcg(pr + gc0);
+                            if (two) xv[row][1] += __ldcg(pr + gc1);
+                        }
+                    } else {
+                        const float* rr = sm0 + SLOT_RING + (size_t)(qp & (CR - 1)) * LQKV;
+                        xv[row][0] = __ldcg(rr + gc0);
+                        if (two) xv[row][1] = __ldcg(rr + gc1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NZV; u++) {
+                const int x = u * FNT + tid;
+                zv[u] = 0.f;
+                if (x < m * FCOLS) {
+                    int tk = x / FCOLS, c = x - tk * FCOLS;
+                    const float* pz = p + (size_t)(t0 + c0 + tk) * DELTA_IN + LQKV + h * LVD + hf * FCOLS + c;
+                    zv[u] = __ldcg(pz);
+                    for (int s = 1; s < splits; s++) zv[u] += __ldcg(pz + (size_t)s * n * DELTA_IN);
+                }
             }
         }
 #pragma unroll
@@ -156,17 +183,19 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
             for (int s = 0; s < 8; s++) gate += gs[s];
             for (int s = 8; s < ba_splits; s++) gate += __ldcg(pb + (size_t)s * n * (2 * LV_HEADS));
         }
+        if (!direct) {
 #pragma unroll
-        for (int row = 0; row < NROW; row++) {
-            if (row < m + CONV_K - 1) {
-                R.x[row][tid] = xv[row][0];
-                if (two) R.x[row][FNT + tid] = xv[row][1];
+            for (int row = 0; row < NROW; row++) {
+                if (row < m + CONV_K - 1) {
+                    R.x[row][tid] = xv[row][0];
+                    if (two) R.x[row][FNT + tid] = xv[row][1];
+                }
             }
-        }
 #pragma unroll
-        for (int u = 0; u < NZV; u++) {
-            const int x = u * FNT + tid;
-            if (x < m * FCOLS) R.z[x / FCOLS][x % FCOLS] = zv[u];
+            for (int u = 0; u < NZV; u++) {
+                const int x = u * FNT + tid;
+                if (x < m * FCOLS) R.z[x / FCOLS][x % FCOLS] = zv[u];
+            }
         }
         if (tid < 2 * m) {
             int tk = tid >> 1, which = tid & 1;
@@ -178,6 +207,7 @@ delta_fused_kernel(const float* p, int splits, int n, const float* ba, int ba_sp
                 R.e[tk] = expf(-expf(alog) * sp);
             }
         }
+        if (direct) cp_async_wait_all();
         __syncthreads();
         stamp(2);
         // ---- conv + SiLU
