@@ -49,6 +49,12 @@ __device__ __forceinline__ void tma_tile_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// the copy engine reads a tensor map's 128 bytes before its first copy through it: asking for them at the kernel's very
+// start takes that round trip off the first stage
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");
+}
+
 struct GemvArgs {
     const __half* X;      // [rows][K] f16
     const int* xrows;     // X row of token t (null: row0 + t)
@@ -185,6 +191,10 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     const int X_OFF = C::W_BYTES + (1 + ZP) * C::S_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == C::NW * 32) {
+        if (C::TENSOR) { prefetch_tensormap(&maps.w); prefetch_tensormap(&maps.s); }
+        if (a.xmap) prefetch_tensormap(&maps.x);
+    }
     const int nstages = a.nstages;
     // stream-K: stage x of the matrix is (column block x / kst, k stage x % kst); block i owns [b(i), b(i+1))
     const int kst = a.K / C::TK;
