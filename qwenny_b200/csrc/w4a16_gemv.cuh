@@ -213,22 +213,21 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
 
     const int bid = blockIdx.y * gridDim.x + blockIdx.x;
     if (a.trace && threadIdx.x == 0) a.trace[bid * 4] = global_ns();
-    if (threadIdx.x == 0) {
+    // The copy warp's first lane sets up the ring's barriers itself and requests the block's first stage of weights
+    // before the block meets: the weights do not depend on the previous kernel, and every launch is as long as its
+    // first stage takes to arrive plus the streaming.
+    if (threadIdx.x == C::NW * 32) {
         for (int i = 0; i < nstages; i++) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], C::NW);
         }
         mbar_fence_init();
     }
-    for (int i = threadIdx.x; i < C::XROW * 2 / 16; i += C::THREADS) ((uint4*)zrow)[i] = make_uint4(0, 0, 0, 0);
-    __syncthreads();
-    pdl_launch_dependents();
-
+    const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+    const uint32_t mine = (uint32_t)(end - beg);
+    const uint32_t tx = C::W_BYTES + (1 + ZP) * C::S_BYTES + a.m * (a.xmap ? C::XROW : C::TK) * 2;
     if (warp == C::NW) {
         // ------------------------------------------------------------ producer
-        const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
-        const uint32_t mine = (uint32_t)(end - beg);
-        const uint32_t tx = C::W_BYTES + (1 + ZP) * C::S_BYTES + a.m * (a.xmap ? C::XROW : C::TK) * 2;
         // what stage `it` of this block copies: 0 = weights and scales, 1 = X, 2 = both
         auto issue = [&](int cb, int st, int slot, int what) {
             int n0 = cb * C::TN, k0 = st * C::TK;
@@ -273,7 +272,11 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         // (only the first stage's: with the whole ring requested at once by every block, the first stages land behind
         // the later ones' traffic; the rest follow right after the wait, while the consumers are busy with stage 0)
         const uint32_t early = min(pre, 1u);
+        __syncwarp();
         for (uint32_t it = 0; it < early; it++, next()) issue(cb, st, (int)it, 0);
+        for (int i = lane; i < C::XROW * 2 / 16; i += 32) ((uint4*)zrow)[i] = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+        pdl_launch_dependents();
         pdl_wait();
         cb = cb0; st = st0;
         for (uint32_t it = 0; it < pre; it++, next())
@@ -293,6 +296,8 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     }
 
     // ---------------------------------------------------------------- consumers
+    __syncthreads();  // the ring's barriers are set up and the zero row is written (by the copy warp)
+    pdl_launch_dependents();
     pdl_wait();
     const int cg = warp % CG, kg = warp / CG, g = lane >> 2, t = lane & 3;
     float acc[NT][4][4];
