@@ -24,7 +24,7 @@ extern "C" {
 #define QB_ERR_ARG 1000      /* a shape or pointer the kernels cannot take */
 #define QB_ERR_DEVICE 1001   /* a bounded device-side wait ran out (see qb_device_error) */
 #define QB_ERR_UNSUPPORTED 1002
-#define QB_ERR_TOO_LARGE 1003 /* a size beyond a fixed capacity (qb_marlin_gemm_noalloc) */
+#define QB_ERR_TOO_LARGE 1003 /* a size beyond a fixed capacity (qb_marlin_gemm_noalloc; a product of more than 2^31 tile stages x blocks) */
 
 typedef struct qb_ctx qb_ctx;
 

@@ -28,12 +28,18 @@ static void grid_of(const qb_ctx* ctx, const GemvPlan& p, int n, int k, int* gri
     *grid = (int)g;
     *maxc = (int)((kst + per - 1) / per) + 1;
 }
+// the kernel divides its (column block, k stage) list among the blocks in 32-bit arithmetic
+static bool schedule_fits(const qb_ctx* ctx, const GemvPlan& p, int n, int k) {
+    const long long total = (long long)(n / (p.cg * 64)) * (k / (p.kg * 128));
+    return (total + 1) * ((long long)ctx->sms * p.ctas + 1) < (1ll << 31);
+}
 
 template <int CG, int KG, int NT, int EPI, int ZP = 0>
 static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& p) {
     using C = GemvCfg<CG, KG, NT>;
     auto kern = w4a16_gemv_kernel<CG, KG, NT, EPI, ZP>;
     int smem = C::smem(p.nstages, a.m, a.zp);
+    if (!schedule_fits(ctx, p, a.N, a.K)) return QB_ERR_TOO_LARGE;
     if (int rc = prepare_kernel(ctx->device, (const void*)kern, smem)) return rc;
     cudaLaunchConfig_t lc = {};
     cudaLaunchAttribute at[2];

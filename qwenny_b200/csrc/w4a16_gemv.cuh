@@ -199,17 +199,19 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
     // stream-K: stage x of the matrix is (column block x / kst, k stage x % kst); block i owns [b(i), b(i+1))
     const int kst = a.K / C::TK;
     const bool clustered = a.cluster_s > 0;
-    const long long total = (long long)(a.N / C::TN) * kst, G = gridDim.x;
+    // (32-bit arithmetic: the host refuses a product with (stages + 1) x (blocks + 1) beyond 2^31; a 64-bit division
+    // is a subroutine of a hundred instructions, twice on the way to the first copy and twice in the tail)
+    const uint32_t total = (uint32_t)(a.N / C::TN) * (uint32_t)kst, G = gridDim.x;
     int beg, end;
     if (clustered) {  // rank blockIdx.x of the cluster of column block blockIdx.y
         beg = blockIdx.y * kst + (int)blockIdx.x * kst / a.cluster_s;
         end = blockIdx.y * kst + ((int)blockIdx.x + 1) * kst / a.cluster_s;
     } else {
-        beg = (int)((long long)blockIdx.x * total / G);
-        end = (int)((long long)(blockIdx.x + 1) * total / G);
+        beg = (int)(blockIdx.x * total / G);
+        end = (int)((blockIdx.x + 1) * total / G);
     }
     // the block that owns stage x: the largest i with b(i) <= x
-    auto owner = [&](long long x) { return (int)(((x + 1) * G + total - 1) / total - 1); };
+    auto owner = [&](uint32_t x) { return (int)(((x + 1) * G + total - 1) / total - 1); };
 
     const int bid = blockIdx.y * gridDim.x + blockIdx.x;
     if (a.trace && threadIdx.x == 0) a.trace[bid * 4] = global_ns();
@@ -491,7 +493,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             const int colgrp = pcb * CG + cg;  // 64 outputs
             bool finish = true;
             // the blocks that share column block cb, in k order: first .. last
-            const int first = owner((long long)pcb * kst), nshare = owner((long long)pcb * kst + kst - 1) - first + 1;
+            const int first = owner((uint32_t)(pcb * kst)), nshare = owner((uint32_t)(pcb * kst + kst - 1)) - first + 1;
             if (nshare > 1) {
                 float4* mine = a.scratch + ((size_t)colgrp * a.maxc + (blockIdx.x - first)) * (NT * 4 * 32);
 #pragma unroll
