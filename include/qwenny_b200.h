@@ -54,6 +54,13 @@ const char* qb_version(void);
 int qb_marlin_gemm(qb_ctx* ctx, void* stream, const void* X, const void* B, void* Y, const void* S, int m, int n,
                    int k, int row0, int epi, const int* xrows, unsigned long long* keys, int n_valid);
 
+/* A hint for the next products of up to 16 rows on this context: how many stages of their weights (36 KB per block
+ * each) they may request before they wait for the kernel enqueued before them (programmatic dependent launch). 1, the
+ * default, suits a product behind another large kernel; 2 a product behind a small one (a norm), whose wait would
+ * otherwise leave the memory idle; a product's ring has three stages and 3 is slower than 1. Stays until changed. The
+ * reference has no counterpart (its products start when the kernel before them has ended). */
+int qb_marlin_early(qb_ctx* ctx, int stages);
+
 /* The zero-point variants marlin_*_z (kernels/marlin.cuh:126-133,588-594): same arguments; S holds the scales followed
  * by the table (8 - z) * scale (qb_pack_marlin_z). w = (q - 8) * scale + (8 - z) * scale; the second term needs only
  * the group's sum of x, which the kernel has anyway. More than 16 rows run as 16-row slabs. */

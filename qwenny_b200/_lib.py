@@ -22,6 +22,7 @@ SIGNATURES = {
     "qb_version": [],
     "qb_set_pdl": [P, I],
     "qb_marlin_gemm": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
+    "qb_marlin_early": [P, I],
     "qb_marlin_gemm_z": [P, P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_marlin_gemm_noalloc": [P, P, P, P, P, I, I, I, I, I, P, P, I],
     "qb_static_scratch_bytes": [],

@@ -25,6 +25,8 @@ struct qb_ctx {
     // programmatic dependent launch on the launches that support it
     bool pdl = false;
     int probe = 0;               // measurement: see qb_marlin_probe
+    int early = 1;               // stages of weights the next skinny product requests before it waits for the kernel
+                                 // before it (set by the caller that knows what that kernel is; see model.cu)
     long long* trace = nullptr;  // measurement: per-block timestamps of the next products
 };
 

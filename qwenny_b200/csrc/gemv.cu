@@ -75,6 +75,7 @@ static int launch_cfg(qb_ctx* ctx, cudaStream_t st, GemvArgs a, const GemvPlan& 
         cluster_s = s;
     }
     a.cluster_s = cluster_s;
+    a.early = ctx->early > 0 ? ctx->early : 1;
     if (cluster_s > 0) {
 
         a.maxc = 1;
@@ -194,6 +195,12 @@ extern "C" int qb_marlin_trace(qb_ctx* ctx, long long* buf) {
 // to 1024 polls: the wait runs out, the warps record error 2, walk on and the kernel ends; 0 restores the product.
 extern "C" int qb_marlin_probe(qb_ctx* ctx, int mode) {
     ctx->probe = mode;
+    return QB_OK;
+}
+
+extern "C" int qb_marlin_early(qb_ctx* ctx, int stages) {
+    if (!ctx || stages < 1 || stages > GEMV_MAX_STAGES) return QB_ERR_ARG;
+    ctx->early = stages;
     return QB_OK;
 }
 

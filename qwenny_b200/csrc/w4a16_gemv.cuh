@@ -70,6 +70,7 @@ struct GemvArgs {
     unsigned long long* keys;
     int n_valid;
     int xmap;             // the X rows arrive by the tensor map (contiguous rows, a padded row fits a box)
+    int early;            // stages of weights requested before the wait for the previous kernel
     int zp;               // zero points: S holds a second table [K/128][N] of (8 - z) * scale after the scales
     int* err;             // set non-zero when a bounded wait ran out
     int probe;            // measurement only: 1 = consumers release every stage unread (the copy pipeline alone);
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
         auto next = [&]() { if (++st == kst) { st = 0; cb++; } };
         // (only the first stage's: with the whole ring requested at once by every block, the first stages land behind
         // the later ones' traffic; the rest follow right after the wait, while the consumers are busy with stage 0)
-        const uint32_t early = min(pre, 1u);
+        const uint32_t early = min(pre, (uint32_t)a.early);
         __syncwarp();
         for (uint32_t it = 0; it < early; it++, next()) issue(cb, st, (int)it, 0);
         for (int i = lane; i < C::XROW * 2 / 16; i += 32) ((uint4*)zrow)[i] = make_uint4(0, 0, 0, 0);
