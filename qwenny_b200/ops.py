@@ -59,6 +59,10 @@ class Context:
     def set_pdl(self, on: bool):
         check(lib().qb_set_pdl(self.h, int(on)), "qb_set_pdl")
 
+    def early(self, stages=1):
+        """How many stages of weights the next skinny products request before they wait for the kernel before them."""
+        check(lib().qb_marlin_early(self.h, stages), "qb_marlin_early")
+
     def tune(self, cg=0, kg=0, nstages=0, ctas=0):
         check(lib().qb_marlin_tune(self.h, cg, kg, nstages, ctas), "qb_marlin_tune")
 

@@ -144,6 +144,32 @@ def test_model_shapes_vs_oracle(ctx, n, k):
     assert np.abs(a - want).max() < 1e-4 * np.abs(want).max()
 
 
+def test_stages_requested_ahead_of_the_kernel_before_do_not_change_the_result(ctx):
+    """qb_marlin_early: one, two or all three of a block's first stages of weights may be requested before the product
+    waits for the kernel enqueued before it (here: the kernel that writes its X). Same bits every time, with programmatic
+    dependent launch on, on a clustered product, on equal shares of a persistent grid and on the SwiGLU form."""
+    from qwenny_b200._lib import lib
+    ctx.set_pdl(True)
+    try:
+        for rows, cols, silu in ((16384, 5120, False), (5120, 17408, False), (2048, 1024, True)):
+            x, wdq, xd, wd, sd = make(rows, cols, silu, rows + cols + 7, 5)
+            x32 = xd.float()
+            outs = []
+            for stages in (1, 2, 3):
+                ctx.early(stages)
+                xk = (x32 * 1.0).half()            # a kernel right before the product writes its X
+                outs.append(ctx.marlin_gemm(xk, wd, sd, epi="silu" if silu else "plain").clone())
+            ctx.early(1)
+            torch.cuda.synchronize()
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+            assert close(outs[0].float().cpu().numpy(), R.marlin_gemm(x, wdq, "silu" if silu else "plain")).all()
+        assert lib().qb_marlin_early(ctx.h, 0) == 1000 and lib().qb_marlin_early(None, 1) == 1000   # QB_ERR_ARG
+        assert ctx.device_error() == 0
+    finally:
+        ctx.early(1)
+        ctx.set_pdl(False)
+
+
 def test_many_rows_fall_back_to_slabs(ctx):
     x, wdq, xd, wd, sd = make(512, 512, False, 21, 40)
     y = ctx.marlin_gemm(xd, wd, sd).cpu().numpy()
