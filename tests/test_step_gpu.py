@@ -168,3 +168,33 @@ def test_step_errors(small):
         m.step([(1, 0, 0)], [3])                      # logit row out of range
     with pytest.raises(QbError):
         m.step([(1, 0, 600)], [0])                    # position beyond the context
+
+
+def test_launching_ahead_of_the_kernel_before_does_not_change_a_bit():
+    """With programmatic dependent launch a kernel is resident while the one before it still runs, and several of them
+    use that: the products request their first stages of weights, the DeltaNet mixer loads its state, the decode
+    attention reads the token lists and the keys and values that earlier steps wrote. None of it may change a result:
+    the same model on a context with it on and on one with it off, a prompt and then verify steps of 5 rows (each
+    rewriting the 4 positions its predecessor drafted), logits equal bit for bit at every step."""
+    from qwenny_b200.ops import Context
+    kw = dict(nlayers=4, slots=1, max_ctx=512, vocab=2000, seed=11, pattern=("delta", "delta", "delta", "attn"))
+    on, off = Context(0), Context(0)
+    on.set_pdl(True)
+    a, b = M.synthetic(on, **kw), M.synthetic(off, **kw)
+    seq = [(31 + 17 * i) % 2000 for i in range(400)]
+    pos = 0
+
+    def both(n, out):
+        nonlocal pos
+        toks = [(seq[pos + i], 0, pos + i) for i in range(n)]
+        a.step(toks, out)
+        b.step(toks, out)
+        assert torch.equal(a.logits(), b.logits()), pos
+    both(130, [129])                 # a prompt in one chunk: the attention's keys of 64 positions and more ago exist
+    pos += 130
+    for _ in range(24):
+        both(5, list(range(5)))      # a verify step ...
+        pos += 1                     # ... of which one token is kept: the next step rewrites the other four positions
+    assert on.device_error() == 0 and off.device_error() == 0
+    a.close()
+    b.close()
