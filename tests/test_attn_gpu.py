@@ -130,6 +130,36 @@ def test_attn_decode_row_invariance_and_two_slots(ctx):
         assert torch.equal(one[0], full[t])
 
 
+def test_attn_decode_more_than_64_decode_tokens(ctx):
+    """Up to 64 decode tokens in a call, the kernel requests the cache entries that lie 64 positions or more before a
+    segment's last key ahead of the kernel enqueued before it; with more it waits first. 13 slots x 5 tokens = 65
+    tokens (the host's planner stops at 64; the C entry point does not), with programmatic dependent launch on, against
+    the CPU oracle on three of the rows, and bit for bit against the same rows run as 13 calls of 5 tokens."""
+    g = synth.gen(88)
+    slots, cap, n = 13, 512, 65
+    cache = make_cache(slots, cap, g, 0)
+    dc = [t.cuda() for t in cache]
+    q = torch.randn(n, R.NH, R.HD, generator=g) * QSCALE
+    gate = torch.sigmoid(torch.randn(n, R.MIX, generator=g))
+    toks = [(0, s, 300 + 7 * s + i) for s in range(slots) for i in range(5)]
+    st = R.build_step(toks, list(range(n)), max_dec=128)
+    assert st["ndec"] == 65 and st["ntile"] == 0
+    ctx.set_pdl(True)
+    try:
+        full = run_decode(ctx, q.cuda(), gate.cuda(), dc, st, ref_cuda.upload_step(st), cap, n)
+        for s in (0, 6, 12):
+            st1 = R.build_step(toks[5 * s:5 * s + 5], list(range(5)))
+            one = run_decode(ctx, q[5 * s:5 * s + 5].cuda().contiguous(), gate[5 * s:5 * s + 5].cuda().contiguous(), dc, st1,
+                             ref_cuda.upload_step(st1), cap, 5)
+            assert torch.equal(one, full[5 * s:5 * s + 5])
+    finally:
+        ctx.set_pdl(False)
+    rows = [0, 32, 64]
+    want = R.attn_decode(q.numpy()[rows], gate.numpy()[rows], *[t.numpy() for t in cache], st["tok_slot"][rows],
+                         st["tok_pos"][rows], cap)
+    assert close(full.cpu().numpy()[rows], want).all()
+
+
 def run_prefill(impl, q, gate, cache, st, dv, cap, n, mix=False):
     kc, vc, ks, vs = cache
     out = gate.clone()
