@@ -354,7 +354,11 @@ __global__ void __launch_bounds__(GemvCfg<CG, KG, NT>::THREADS) w4a16_gemv_kerne
             const uint32_t sixteenth = 0x2c002c00u;  // half2(0.0625, 0.0625)
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-                uint4 w = wp[ks * CG * 32];
+                // (a volatile load: in program order with the ldmatrix loads. Left to itself the compiler sometimes
+                // requests the stage's eight words together at the top, at the 96-register limit of two blocks per SM,
+                // and the products are 4 % slower for it; which of the two it does changed with unrelated edits)
+                uint4 w;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(smem_u32(wp + ks * CG * 32)));
                 if ((ks & 1) == 0) {
 #pragma unroll
                     for (int j = 0; j < NT; j++) {
