@@ -45,3 +45,4 @@ def test_argument_errors_need_no_device():
     assert l.qb_row_order(17, 1, None) == 1000          # QB_ERR_ARG
     assert l.qb_marlin_gemm(None, None, None, None, None, None, 5, 256, 128, 0, 0, None, None, 0) == 1000
     assert l.qb_model_step(None, None, None, 0, None, 0) == 1000
+    assert l.qb_marlin_early(None, 2) == 1000
