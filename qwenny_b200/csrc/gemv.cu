@@ -153,11 +153,16 @@ static int launch_shape(qb_ctx* ctx, cudaStream_t st, const GemvArgs& a, const G
 // SM allow.
 static GemvPlan pick(const qb_ctx* ctx, int n, int k, int m, int cg, int kg, int ctas, int zp = 0) {
     GemvPlan p;
-    bool deep = false;  // long k, few column blocks: equal shares of the persistent grid beat a cluster per column block (17.5 against 18.4 us at 5120 x 17408)
+    bool deep = false;  // equal shares of a persistent grid instead of a cluster per column block (long k that is no multiple of 512)
     if (cg) { p.cg = cg; p.kg = kg; }
     else if (n >= 65536 && n % 512 == 0 && !zp) { p.cg = 8; p.kg = 1; }  // the output layer: no k groups to add up per piece
     else if (n >= 8192 && k % 256 == 0) { p.cg = 4; p.kg = 2; }
-    else if (k >= 16384 && k % 256 == 0 && n % 256 == 0) { p.cg = 4; p.kg = 2; deep = true; }  // few outputs, long k (down)
+    // few outputs, long k (down, 5120 x 17408): 128 x 512 tiles, 40 column blocks in clusters of 7 ranks, like the
+    // out-projection: 13.4 us on its own and 4.87 ms per 64-layer step, against 15.5 us and 5.03 ms as equal shares of
+    // a persistent grid of 256 x 256 tiles (whose column blocks had some 15 sharers to add up) and 5.04 ms as 256 x 256
+    // tiles in clusters of 8
+    else if (k >= 16384 && k % 512 == 0 && n % 128 == 0) { p.cg = 2; p.kg = 4; }
+    else if (k >= 16384 && k % 256 == 0 && n % 256 == 0) { p.cg = 4; p.kg = 2; deep = true; }
     else if (k % 512 == 0 && n % 128 == 0) { p.cg = 2; p.kg = 4; }
     else if (k % 256 == 0) { p.cg = 4; p.kg = 2; }
     else { p.cg = 4; p.kg = 1; }
