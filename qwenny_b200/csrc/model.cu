@@ -172,12 +172,9 @@ int launch_in_proj(qb_model* m, cudaStream_t st, int layer, int& k) {
         if (m->fork) QB_CUDA(cudaEventRecord(m->ev[2 * layer + 1], m->side));
     }
     const int rows = L.kind == QB_LAYER_DELTA ? DELTA_IN : ATTN_IN;
-    // (behind a norm: two stages of weights before the wait; measured per position in the layer, 64 layers x 5 rows:
-    // in 2, out 1, gate_up 2 gives some 90 us per step over one stage everywhere; 3 is slower)
-    c->early = 2;
-    int rc = qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0);
-    c->early = 1;
-    QB_TRY(rc); k++;
+    // (one stage of weights before the wait, the default: as 64 x 1024 tiles the in-projection gains nothing from
+    // two, 4679 against 4707 us per 64-layer step; gate_up, behind the other norm, does: see launch_layer_tail)
+    QB_TRY(qb_marlin_gemm(c, s, m->xn, L.in_proj_w, m->part, L.in_proj_s, n, rows, H, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     return QB_OK;
 }
 
@@ -228,7 +225,10 @@ int launch_layer_tail(qb_model* m, cudaStream_t st, const qb_layer& L, const flo
     void* s = (void*)st;
     QB_TRY(qb_marlin_gemm(c, s, m->mix, L.out_w, m->part, L.out_s, n, H, MIX, 0, QB_EPI_PLAIN, nullptr, nullptr, 0)); k++;
     QB_TRY(qb_add_rmsnorm(c, s, m->h, m->part, 1, n, L.post_norm, m->xn, EPS)); k++;
-    c->early = 2;  // gate_up behind the norm: two stages of weights before the wait (see in_proj)
+    // gate_up waits some 2.5 us for the norm in front of it with the memory idle: it requests TWO stages of weights
+    // before that wait (measured per position in the layer, 64 layers x 5 rows: some 40 us per step over one stage;
+    // three, the whole ring, is slower than one)
+    c->early = 2;
     int rc = qb_marlin_gemm(c, s, m->xn, L.gate_up_w, m->mid, L.gate_up_s, n, 2 * FF, H, 0, QB_EPI_SILU, nullptr, nullptr, 0);
     c->early = 1;  // down follows gate_up directly: nothing idle to fill (4842 against 4880 us per step with two)
     if (rc == QB_OK) { k++; rc = qb_marlin_gemm(c, s, m->mid, L.down_w, m->part, L.down_s, n, H, FF, 0, QB_EPI_PLAIN, nullptr, nullptr, 0); }
