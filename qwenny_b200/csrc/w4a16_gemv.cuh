@@ -3,7 +3,8 @@
 //
 // Replaces marlin::mul<1,8,8,*> (kernels/marlin.cuh:171-582 of the reference) for steps of up to 16 tokens. It is a
 // bandwidth-bound GEMV, organised around the HBM stream rather than around the tensor pipe:
-//  * a producer warp streams the weights with descriptor-free bulk async copies (cp.async.bulk, the TMA engine)
+//  * a producer warp streams the weights with three tensor-map loads per stage (cp.async.bulk.tensor.2d: words,
+//    scales, X rows; plain bulk copies where a box does not fit: 512-output tiles, gathered rows)
 //    into a ring of shared-memory stages; a stage is TN = 64 CG outputs x TK = 128 KG columns of packed int4
 //    (4 KB per consumer warp), its group scales and the matching slice of X; full/empty mbarriers, no __syncthreads
 //    in the stream;
@@ -17,7 +18,8 @@
 //  * two ways to deal the work. Matrices whose column blocks x k splits fit one wave of blocks run CLUSTERED: one
 //    thread-block cluster per column block, rank r takes the r-th equal share of its k stages, and the ranks' f32
 //    partials meet in rank 0 through distributed shared memory (no global traffic, no fences), added in rank order.
-//    Larger matrices run STREAM-K:
+//    (With 64 x 1024 tiles and as many block slots as column blocks the cluster is one block: its eight warps' k
+//    groups add up in shared memory and nothing crosses blocks.) Larger matrices run STREAM-K:
 //  * the stages of the whole matrix, numbered column block by column block, are cut into one equal contiguous
 //    range per block of a persistent grid (stream-K), so every SM streams the same number of bytes whatever the
 //    shape and the copy pipeline never drains between column blocks. The KG warps of a column group add up in
