@@ -39,7 +39,7 @@ int qb_create(int device, qb_ctx** out);
 void qb_destroy(qb_ctx* ctx);
 /* Non-zero once a kernel gave up a bounded wait (1 producer, 2 consumer, ...); reads and clears the word (syncs). */
 int qb_device_error(qb_ctx* ctx);
-int qb_sm_count(const qb_ctx* ctx);
+int qb_sm_count(const qb_ctx* ctx); /* 0 for a null context */
 const char* qb_version(void);
 
 /* ---- W4A16 product over a Marlin-packed matrix. Replaces the launches of Gemm::marlin
@@ -425,7 +425,7 @@ int qb_model_step_kernels(const qb_model* m);    /* kernels of one step of the l
  * qb_pack_marlin  pack_marlin + marlin_word + marlin_scale (symmetric), src/cuda/core.rs:244-311; h_q is the
  *                 stored matrix as Quant holds it (src/checkpoint.rs:20-31): u32 [rows][cols/8], q + 8 in nibbles
  * qb_pack_f16     pack (f16 branch) + frag, src/cuda/core.rs:222-227,337-391
- * qb_split_for    split_for, src/cuda/core.rs:393-398 */
+ * qb_split_for    split_for, src/cuda/core.rs:393-398 (0 for an argument that is not positive) */
 int qb_row_order(int rows, int silu, int* h_order);
 int qb_pack_marlin(const uint32_t* h_q, const float* h_scales, int rows, int cols, int group, const int* h_order,
                    int n, uint32_t* h_words, uint16_t* h_scales_f16);

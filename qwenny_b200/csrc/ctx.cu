@@ -102,6 +102,7 @@ void qb_destroy(qb_ctx* c) {
 }
 
 int qb_device_error(qb_ctx* c) {
+    if (!c) return QB_ERR_ARG;
     int v = 0;
     QB_CUDA(cudaDeviceSynchronize());
     QB_CUDA(cudaMemcpy(&v, c->err, sizeof(int), cudaMemcpyDeviceToHost));
@@ -109,9 +110,10 @@ int qb_device_error(qb_ctx* c) {
     return v;
 }
 
-int qb_sm_count(const qb_ctx* c) { return c->sms; }
+int qb_sm_count(const qb_ctx* c) { return c ? c->sms : 0; }
 
 int qb_set_pdl(qb_ctx* c, int on) {
+    if (!c) return QB_ERR_ARG;
     c->pdl = on != 0;
     return QB_OK;
 }

@@ -198,6 +198,7 @@ int qb_pack_i8(const float* h_w, int rows, int cols, const int* h_order, int n, 
 
 // Split-K factor of the dense decode products (split_for, src/cuda/core.rs:393-398).
 int qb_split_for(int tiles, int cols, int bits, int kd) {
+    if (tiles <= 0 || cols <= 0 || bits <= 0 || bits > 2048 || kd <= 0) return 0;  // no split: the reference's host would stop on the division
     const int UNITS = 1024;
     int stage_cols = 2048 / bits, chunks = cols / stage_cols;
     int want = std::max((UNITS + tiles - 1) / tiles, (cols + kd - 1) / kd);

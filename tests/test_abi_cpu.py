@@ -46,3 +46,34 @@ def test_argument_errors_need_no_device():
     assert l.qb_marlin_gemm(None, None, None, None, None, None, 5, 256, 128, 0, 0, None, None, 0) == 1000
     assert l.qb_model_step(None, None, None, 0, None, 0) == 1000
     assert l.qb_marlin_early(None, 2) == 1000
+
+
+_NULL_CALLS = """
+import ctypes as C
+from qwenny_b200 import _lib
+l = _lib.lib()
+for n in sorted(_lib.SIGNATURES):
+    args = []
+    for t in _lib.SIGNATURES[n]:
+        if t is C.c_void_p or (isinstance(t, type) and issubclass(t, C._Pointer)):
+            args.append(None)
+        else:
+            args.append(0.0 if t is C.c_float else 0)
+    print(n, getattr(l, n)(*args), flush=True)
+"""
+
+
+def test_no_entry_dereferences_a_null_argument():
+    """Every entry called with null pointers and zeros, in a child process (a fault there must not end the test run):
+    none may crash; those that take a context, a model, a pool or a region answer QB_ERR_ARG, 0 or null."""
+    import subprocess
+    import sys
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-c", _NULL_CALLS], capture_output=True, text=True, timeout=300, env=env)
+    seen = dict(line.split(" ", 1) for line in r.stdout.strip().splitlines())
+    assert r.returncode == 0, f"crashed after {list(seen)[-1] if seen else 'nothing'}: rc {r.returncode}\n{r.stderr[-500:]}"
+    assert set(seen) == set(_lib.SIGNATURES)
+    free_standing = {"qb_version", "qb_static_scratch_bytes", "qb_static_device_error"}
+    for n, v in seen.items():
+        if n not in free_standing:
+            assert v in ("1000", "0", "None"), f"{n}(nulls) answered {v}"
