@@ -349,6 +349,24 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
  * graph. Steps with segments longer than 8 tokens (prompt attention) return QB_ERR_UNSUPPORTED. */
 int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
+/* Model::step with `marks` (src/cuda/qwen/mod.rs:1125-1143, Step::upload's third argument, src/cuda/core.rs:872-880):
+ * segment s of the step adds h_marks[h_marks_at[s] .. h_marks_at[s + 1]] to its slot's seen set instead of its own
+ * tokens (a verify step marks the history committed since the slot's last step, not its drafts). h_marks_at holds one
+ * entry more than the step has segments; at most 2560 marks per step. A step that is refused (QB_ERR_ARG) leaves the
+ * state of the step before it in place. */
+int qb_model_step_marks(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out,
+                        const uint32_t* h_marks, const int* h_marks_at);
+int qb_model_upload_marks(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out,
+                          const uint32_t* h_marks, const int* h_marks_at);
+/* The step's host arrays alone (Step::upload without the copies; no device, no model): h_arrays takes
+ * qb_step_ints() ints, of which array i starts at offsets[i], i = ids, tok_slot, tok_pos, seg_start, seg_len,
+ * seg_slot, seg_pos0, dtok, dseg, dkeys, ptile, out_rows, mark, mark_at, mtp_rows, row_first (16 offsets); shape
+ * takes n, n_out, segs, ndec, ntile, ndseg, dmax, max_seg, dec_max_pos, tile_max_pos (10 ints: Step's counts,
+ * src/cuda/core.rs:700-727). h_marks / h_marks_at may both be null (every token of a segment is marked). */
+int qb_step_arrays(const qb_tok* h_toks, int n, const int* h_out, int n_out, const uint32_t* h_marks,
+                   const int* h_marks_at, int slots, int max_ctx, int vocab_valid, int* h_arrays, long long* offsets,
+                   int* shape);
+int qb_step_ints(void);
 /* The MTP draft step (what turns steps/s into accepted tok/s). qb_model_set_mtp: Mtp::load's
  * pointers. qb_model_draft: Engine::draft with greedy rows = draft_chains (src/cuda/qwen/mod.rs:870-896): k <=
  * QB_MAX_DRAFTS drafts for each row of h_out, from the hidden states the last qb_model_step left at h_rows; h_drafts

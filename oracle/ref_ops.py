@@ -587,9 +587,10 @@ def delta_norm(part, norm_w, out, meta, seg_len, seg_slot, seg_pos0):
 # ---------------------------------------------------------------------------------------------------------------
 # Step metadata (Step::upload, src/cuda/core.rs:835-926) for the decode-attention path
 
-def build_step(toks, out_rows, short=8, max_dec=64, ptile=10, cut=16 * DSPLITS):
+def build_step(toks, out_rows, short=8, max_dec=64, ptile=10, cut=16 * DSPLITS, marks=None):
     """toks: list of (id, slot, pos). Returns the dict of host arrays the kernels read (ids, tok_slot, tok_pos,
-    seg_*, dtok, dseg, dkeys, ptile, out_rows) and the host-side counts."""
+    seg_*, dtok, dseg, dkeys, ptile, out_rows, mark, mark_at, row_first) and the host-side counts. marks: per segment
+    the tokens to add to its slot's seen set (None: the segment's own tokens), core.rs:872-880."""
     n = len(toks)
     seg = [[], [], [], []]
     for i, (_, slot, pos) in enumerate(toks):
@@ -617,7 +618,15 @@ def build_step(toks, out_rows, short=8, max_dec=64, ptile=10, cut=16 * DSPLITS):
                 ptl += [st + o, min(ln - o, ptile)]
     i32 = lambda v: np.asarray(v, dtype=np.int32)
     pos = lambda t: toks[t][2]
+    mark, mark_at = [], [0]
+    assert marks is None or len(marks) == len(seg[0])
+    for i, (st, ln) in enumerate(zip(seg[0], seg[1])):
+        mark += [int(t) for t in marks[i]] if marks is not None else [toks[t][0] for t in range(st, st + ln)]
+        mark_at.append(len(mark))
+    assert len(mark) <= 2048 + 8 * 64
+    row_first = [max(st for st in seg[0] if st <= o) for o in out_rows]  # core.rs:893-894
     return dict(
+        mark=i32(mark), mark_at=i32(mark_at), row_first=i32(row_first),
         n=n, n_out=len(out_rows), segs=len(seg[0]), ndec=len(dtok), ntile=len(ptl) // 2, ndseg=len(dseg) // 2,
         dmax=max([dseg[i] for i in range(1, len(dseg), 2)], default=0), max_seg=max(seg[1], default=0),
         dec_max_pos=max([pos(t) for t in dtok], default=0),

@@ -76,6 +76,10 @@ SIGNATURES = {
     "qb_model_set_head": [P, P, P, P, P],
     "qb_model_step": [P, P, P, I, P, I],
     "qb_model_upload": [P, P, P, I, P, I],
+    "qb_model_step_marks": [P, P, P, I, P, I, P, P],
+    "qb_model_upload_marks": [P, P, P, I, P, I, P, P],
+    "qb_step_arrays": [P, I, P, I, P, P, I, I, I, P, P, P],
+    "qb_step_ints": [],
     "qb_model_run": [P, P],
     "qb_model_use_graphs": [P, I],
     "qb_model_argmax": [P, P, P, I],

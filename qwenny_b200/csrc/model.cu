@@ -17,16 +17,15 @@
 #include "ctx.h"
 #include "graphs.h"
 #include "session.h"
+#include "step_arrays.h"
 
 using namespace qb;
+using namespace qb::step;  // the step's limits (MAX_TOK, MAX_OUT, ...), its array layout and the builder of the arrays
 
 namespace {
 
-constexpr int MAX_TOK = 2048, MAX_OUT = 64;     // src/cuda/core.rs:16-19
-constexpr int SHORT_SEG = 8, MAX_DEC = 64;      // attn::segments, src/cuda/qwen/attn.rs:17-19
-constexpr int DCUT = 2048;                      // short segments are cut where pos / DCUT changes (attn.rs:27)
+static_assert(PTILE == 64 / GROUP, "a prompt tile is 64 rows of (token, query head of a kv head)");
 constexpr int GRAPH_TOK = 32;                   // steps of up to this many tokens are replayed as graphs (core.rs:27)
-constexpr int PTILE = 64 / GROUP;                // tokens of a prompt tile (attn.rs:18)
 constexpr int PAIRS = 64 * 128;                 // (decode token, split) pairs of the partial buffers (attn.rs:29)
 
 struct Layer {
@@ -124,21 +123,6 @@ struct qb_model {
 };
 
 namespace {
-
-struct StepLayout {
-    // offsets (ints) of the step arrays inside the single step allocation
-    size_t ids, tok_slot, tok_pos, seg_start, seg_len, seg_slot, seg_pos0, dtok, dseg, dkeys, ptile, out_rows, mark,
-        mark_at, mtp_rows, row_first, total;
-    StepLayout() {
-        size_t o = 0;
-        auto take = [&](size_t n) { size_t r = o; o += (n + 3) / 4 * 4; return r; };
-        ids = take(MAX_TOK); tok_slot = take(MAX_TOK); tok_pos = take(MAX_TOK);
-        seg_start = take(MAX_TOK); seg_len = take(MAX_TOK); seg_slot = take(MAX_TOK); seg_pos0 = take(MAX_TOK);
-        dtok = take(MAX_TOK); dseg = take(2 * MAX_TOK); dkeys = take(MAX_TOK); ptile = take(2 * MAX_TOK); out_rows = take(MAX_OUT);
-        mark = take(MAX_TOK + 8 * MAX_OUT); mark_at = take(MAX_TOK + 1); mtp_rows = take(MAX_TOK); row_first = take(MAX_OUT);
-        total = o;
-    }
-};
 
 template <class T>
 int dalloc(T** p, size_t n) {
@@ -531,85 +515,55 @@ int qb_model_use_fused(qb_model* m, int on) {
 
 // Step::upload: the step's tokens (each sequence's contiguous and in order), the rows whose logits are wanted.
 // Every token of a segment is added to its slot's seen set (the reference's `marks: None`).
-static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows);
+static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows,
+                       const uint32_t* marks = nullptr, const int* marks_at = nullptr);
 
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out) {
     return upload_step(m, stream, toks, n, out, n_out, nullptr);
 }
 
+int qb_model_upload_marks(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out,
+                          const uint32_t* marks, const int* marks_at) {
+    if (!marks || !marks_at) return QB_ERR_ARG;
+    return upload_step(m, stream, toks, n, out, n_out, nullptr, marks, marks_at);
+}
+
+// The arrays alone, on the host (no device, no model): what qb_model_upload would copy to the device
+int qb_step_arrays(const qb_tok* toks, int n, const int* out, int n_out, const uint32_t* marks, const int* marks_at,
+                   int slots, int max_ctx, int vocab_valid, int* h_arrays, long long* offsets, int* shape) {
+    if (!h_arrays || !offsets || !shape) return QB_ERR_ARG;
+    const StepLayout L;
+    const size_t off[16] = {L.ids,  L.tok_slot, L.tok_pos, L.seg_start, L.seg_len,  L.seg_slot, L.seg_pos0, L.dtok,
+                            L.dseg, L.dkeys,    L.ptile,   L.out_rows,  L.mark,     L.mark_at,  L.mtp_rows, L.row_first};
+    for (int i = 0; i < 16; i++) offsets[i] = (long long)off[i];
+    StepShape sh;
+    QB_TRY(build_step_arrays(toks, n, out, n_out, nullptr, marks, marks_at, slots, max_ctx, vocab_valid, h_arrays, &sh));
+    const int v[10] = {sh.n, sh.n_out, sh.segs, sh.ndec, sh.ntile, sh.ndseg, sh.dmax, sh.max_seg, sh.dec_max_pos, sh.tile_max_pos};
+    for (int i = 0; i < 10; i++) shape[i] = v[i];
+    return QB_OK;
+}
+int qb_step_ints(void) { return (int)StepLayout().total; }
+
 // rows (MTP steps): per token the row of the residual stream of the step before that holds its hidden state
-static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows) {
-    if (!m || !toks || n < 1 || n > MAX_TOK || n_out < 0 || n_out > MAX_OUT || (n_out && !out)) return QB_ERR_ARG;
-    for (int i = 0; i < n_out; i++)
-        if (out[i] < 0 || out[i] >= n) return QB_ERR_ARG;
-    StepLayout L;
-    m->h_cur ^= 1;
-    QB_CUDA(cudaEventSynchronize(m->h_event[m->h_cur]));  // the copy that last read this mirror has run
-    int* h = m->h_step = m->h_mirror[m->h_cur];
-    int segs = 0;
-    for (int i = 0; i < n; i++) {
-        const qb_tok& t = toks[i];
-        if ((int)t.slot >= m->slots || (int)t.pos >= m->max_ctx || (int)t.id >= m->vocab_valid) return QB_ERR_ARG;
-        h[L.ids + i] = (int)t.id; h[L.tok_slot + i] = (int)t.slot; h[L.tok_pos + i] = (int)t.pos;
-        if (i > 0 && toks[i - 1].slot == t.slot) {
-            if (toks[i - 1].pos + 1 != t.pos) return QB_ERR_ARG;  // positions of a slot not consecutive
-            h[L.seg_len + segs - 1]++;
-        } else {
-            for (int s = 0; s < segs; s++)
-                if (h[L.seg_slot + s] == (int)t.slot) return QB_ERR_ARG;  // a slot in two segments
-            h[L.seg_start + segs] = i; h[L.seg_len + segs] = 1; h[L.seg_slot + segs] = (int)t.slot;
-            h[L.seg_pos0 + segs] = (int)t.pos;
-            segs++;
-        }
-    }
-    int ndec = 0, ndseg = 0, ntile = 0, dmax = 0, max_seg = 0, dec_max_pos = 0, tile_max_pos = 0, nmark = 0;
-    for (int s = 0; s < segs; s++) {
-        int st = h[L.seg_start + s], len = h[L.seg_len + s];
-        max_seg = len > max_seg ? len : max_seg;
-        if (len <= SHORT_SEG && ndec + len <= MAX_DEC) {
-            int a = st;
-            while (a < st + len) {
-                int part = (int)toks[a].pos / DCUT, e = a + 1;
-                while (e < st + len && (int)toks[e].pos / DCUT == part) e++;
-                h[L.dseg + 2 * ndseg] = ndec; h[L.dseg + 2 * ndseg + 1] = e - a;
-                for (int t = a; t < e; t++) {
-                    h[L.dtok + ndec] = t;
-                    h[L.dkeys + ndec] = (int)toks[e - 1].pos + 1;
-                    ndec++;
-                }
-                dmax = e - a > dmax ? e - a : dmax;
-                dec_max_pos = (int)toks[e - 1].pos > dec_max_pos ? (int)toks[e - 1].pos : dec_max_pos;
-                ndseg++;
-                a = e;
-            }
-        } else {
-            for (int o = 0; o < len; o += PTILE) {  // prompt tiles of 64 / GROUP consecutive tokens
-                int cnt = len - o < PTILE ? len - o : PTILE, last = (int)toks[st + o + cnt - 1].pos;
-                h[L.ptile + 2 * ntile] = st + o; h[L.ptile + 2 * ntile + 1] = cnt;
-                tile_max_pos = last > tile_max_pos ? last : tile_max_pos;
-                ntile++;
-            }
-        }
-        h[L.mark_at + s] = nmark;
-        for (int t = st; t < st + len; t++) h[L.mark + nmark++] = (int)toks[t].id;
-    }
-    h[L.mark_at + segs] = nmark;
-    for (int i = 0; i < n_out; i++) {
-        h[L.out_rows + i] = out[i];
-        int first = 0;  // the first token of the row's segment (Step::upload, src/cuda/core.rs:893-894)
-        for (int sg = 0; sg < segs; sg++)
-            if (h[L.seg_start + sg] <= out[i]) first = h[L.seg_start + sg];
-        h[L.row_first + i] = first;
-    }
-    if (rows)
-        for (int i = 0; i < n; i++) h[L.mtp_rows + i] = rows[i];
+static int upload_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out, const int* rows,
+                       const uint32_t* marks, const int* marks_at) {
+    if (!m) return QB_ERR_ARG;
+    if (!toks || n < 1 || n > MAX_TOK || n_out < 0 || n_out > MAX_OUT || (n_out && !out)) return QB_ERR_ARG;
+    const int cur = m->h_cur ^ 1;
+    QB_CUDA(cudaEventSynchronize(m->h_event[cur]));  // the copy that last read this mirror has run
+    int* h = m->h_mirror[cur];
+    StepShape sh;
+    // (a step that is refused leaves the arrays and counts of the step before in place)
+    QB_TRY(build_step_arrays(toks, n, out, n_out, rows, marks, marks_at, m->slots, m->max_ctx, m->vocab_valid, h, &sh));
+    m->h_cur = cur;
+    m->h_step = h;
     QB_CUDA(cudaMemcpyAsync(m->d_step, h, m->step_ints * sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     QB_CUDA(cudaEventRecord(m->h_event[m->h_cur], (cudaStream_t)stream));
     m->lora_step = false;
     if (m->any_lora && !rows)  // the MTP layer is not adapted (mtp_launch, src/cuda/qwen/mod.rs:933-934)
         for (int i = 0; i < n && !m->lora_step; i++) m->lora_step = m->h_scale[toks[i].slot] != 0.f;
-    m->n = n; m->n_out = n_out; m->segs = segs; m->ndec = ndec; m->ntile = ntile; m->ndseg = ndseg; m->dmax = dmax;
-    m->max_seg = max_seg; m->dec_max_pos = dec_max_pos; m->tile_max_pos = tile_max_pos;
+    m->n = sh.n; m->n_out = sh.n_out; m->segs = sh.segs; m->ndec = sh.ndec; m->ntile = sh.ntile; m->ndseg = sh.ndseg;
+    m->dmax = sh.dmax; m->max_seg = sh.max_seg; m->dec_max_pos = sh.dec_max_pos; m->tile_max_pos = sh.tile_max_pos;
     return QB_OK;
 }
 
@@ -788,6 +742,13 @@ int qb_model_draft(qb_model* m, void* stream, const qb_tok* toks, int n, const i
 
 int qb_model_step(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out) {
     QB_TRY(qb_model_upload(m, stream, toks, n, out, n_out));
+    return qb_model_run(m, stream);
+}
+
+// Model::step with `marks` (src/cuda/qwen/mod.rs:1125-1143): the tokens each segment adds to its slot's seen set
+int qb_model_step_marks(qb_model* m, void* stream, const qb_tok* toks, int n, const int* out, int n_out,
+                        const uint32_t* marks, const int* marks_at) {
+    QB_TRY(qb_model_upload_marks(m, stream, toks, n, out, n_out, marks, marks_at));
     return qb_model_run(m, stream);
 }
 

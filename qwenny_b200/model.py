@@ -265,12 +265,24 @@ class Model:
             arr[i].id, arr[i].slot, arr[i].pos = int(tid), int(slot), int(pos)
         return arr
 
-    def step(self, toks, out):
-        """toks: [(id, slot, pos)], sequences contiguous and in order; out: indices whose logits are wanted."""
+    def step(self, toks, out, marks=None):
+        """toks: [(id, slot, pos)], sequences contiguous and in order; out: indices whose logits are wanted; marks
+        (optional): per segment the tokens to add to its slot's seen set instead of the segment's own."""
         arr = self._toks(toks)
         o = (C.c_int * max(1, len(out)))(*out)
         s = C.c_void_p(self.stream.cuda_stream)
-        check(lib().qb_model_step(self.h, s, arr, len(toks), o, len(out)), "qb_model_step")
+        if marks is None:
+            check(lib().qb_model_step(self.h, s, arr, len(toks), o, len(out)), "qb_model_step")
+        else:
+            nseg = 1 + sum(1 for i in range(1, len(toks)) if toks[i][1] != toks[i - 1][1])
+            if len(marks) != nseg:
+                raise ValueError(f"{len(marks)} mark lists for a step of {nseg} segments")
+            flat = [int(t) for seg in marks for t in seg]
+            at = [0]
+            for seg in marks:
+                at.append(at[-1] + len(seg))
+            mk, ma = (C.c_uint32 * max(1, len(flat)))(*flat), (C.c_int * len(at))(*at)
+            check(lib().qb_model_step_marks(self.h, s, arr, len(toks), o, len(out), mk, ma), "qb_model_step_marks")
         self._n, self._n_out, self._cols = len(toks), len(out), None
 
     def argmax(self, n_out=None):
@@ -299,6 +311,14 @@ class Model:
     def hidden(self) -> torch.Tensor:
         self.stream.synchronize()
         return _device_copy(lib().qb_model_hidden(self.h), (self._n, H), torch.float32)
+
+    def seen(self, slot: int) -> np.ndarray:
+        """The seen set of a slot (Step::seen, src/cuda/core.rs:928-931) as a bool per vocabulary row."""
+        self.stream.synchronize()
+        w = self.lm_head.n // 32
+        ptr = lib().qb_model_seen(self.h) + 4 * w * int(slot)
+        words = _device_copy(ptr, (w,), torch.int32).cpu().numpy().view(np.uint32)
+        return ((words[:, None] >> np.arange(32, dtype=np.uint32)) & 1).astype(bool).reshape(-1)
 
     def xn(self) -> torch.Tensor:
         self.stream.synchronize()

@@ -73,7 +73,7 @@ def test_no_entry_dereferences_a_null_argument():
     seen = dict(line.split(" ", 1) for line in r.stdout.strip().splitlines())
     assert r.returncode == 0, f"crashed after {list(seen)[-1] if seen else 'nothing'}: rc {r.returncode}\n{r.stderr[-500:]}"
     assert set(seen) == set(_lib.SIGNATURES)
-    free_standing = {"qb_version", "qb_static_scratch_bytes", "qb_static_device_error"}
+    free_standing = {"qb_version", "qb_static_scratch_bytes", "qb_static_device_error", "qb_step_ints"}
     for n, v in seen.items():
         if n not in free_standing:
             assert v in ("1000", "0", "None"), f"{n}(nulls) answered {v}"

@@ -155,6 +155,31 @@ def test_rows_are_invariant_to_drafts(ctx):
         pos += min(n, 3)  # the rest are treated as rejected drafts and run again
 
 
+def test_marks_choose_what_a_step_adds_to_the_seen_sets(ctx):
+    """Model::step's `marks` (src/cuda/qwen/mod.rs:1125-1143): without them a segment's own tokens enter its slot's seen
+    set, with them the listed tokens do (a verify step marks the committed history, not its drafts); the logits do not
+    depend on them."""
+    m = M.synthetic(ctx, nlayers=2, slots=2, max_ctx=512, vocab=2000, seed=5, pattern=("delta", "attn"))
+    members = lambda slot: set(np.nonzero(m.seen(slot))[0].tolist())
+    m.step([(10, 0, 0), (11, 0, 1), (12, 0, 2)], [0, 1, 2])
+    a = m.logits().clone()
+    assert members(0) == {10, 11, 12} and members(1) == set()
+    m.step([(10, 1, 0), (11, 1, 1), (12, 1, 2)], [0, 1, 2], marks=[[11, 1999]])
+    assert torch.equal(a, m.logits())
+    assert members(0) == {10, 11, 12} and members(1) == {11, 1999}
+    # a verify step of slot 0 (one committed token, two drafts) beside a decode token of slot 1 that marks nothing
+    m.step([(13, 0, 3), (500, 0, 4), (501, 0, 5), (7, 1, 3)], [0, 1, 2, 3], marks=[[13], []])
+    assert members(0) == {10, 11, 12, 13} and members(1) == {11, 1999}
+    m.step([(500, 0, 4), (7, 1, 4)], [0, 1])
+    assert members(0) == {10, 11, 12, 13, 500} and members(1) == {7, 11, 1999}
+    from qwenny_b200 import QbError
+    with pytest.raises(QbError):
+        m.step([(1, 0, 5)], [0], marks=[[2000]])     # a mark beyond the vocabulary
+    with pytest.raises(ValueError):
+        m.step([(1, 0, 5)], [0], marks=[[1], [2]])   # a mark list per segment
+    assert members(0) == {10, 11, 12, 13, 500}
+
+
 def test_step_errors(small):
     m, _ = small
     from qwenny_b200 import QbError
