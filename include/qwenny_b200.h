@@ -467,6 +467,52 @@ int qb_marlin_put_block(qb_ctx* ctx, void* stream, void* B, void* S, const void*
                         int blk, int groups, int tables, int k16s);
 int qb_split_for(int tiles, int cols, int bits, int kd);
 
+/* ---- which token has which row of the draft head, and how that changes while a server runs: Rows / Adaptive of
+ * src/draft_vocab.rs:22-201 (host only; the head's weights are written by qb_model_learn_block). Every committed token
+ * adds 1 to its row's score, the scores halve every 20,000 committed tokens; a token without a row waits until 16 do,
+ * which then get a new tile of 16 rows while the head has room (cap) and else the rows of the coldest tokens (score
+ * below 1), rewritten in place.
+ * qb_draft_vocab_create     Rows::new: `n` rows (a multiple of 16, at most cap, cap a multiple of 16) with their scores
+ *                           (null: 0); QB_ERR_ARG for a token twice or beyond the vocabulary
+ * qb_draft_vocab_load       Adaptive::load: the rows saved by an earlier run if they fit this vocabulary (else none of
+ *                           them), then the seed's tokens that are new while there is room (65,536 rows); whole tiles
+ * qb_draft_vocab_get        the token and score of each row (either may be null); cap >= qb_draft_vocab_rows
+ * qb_draft_vocab_row_of     a token's row, -1 without one
+ * qb_draft_vocab_may_change Rows::may_change: whether these tokens can change a tile
+ * qb_draft_vocab_learn      Adaptive::learn: takes in the tokens a step commits; when tiles changed, publish(user, ids,
+ *                           n_ids, tiles, n_tiles) is to put them into the head (tiles ascending; the tokens of tile t
+ *                           are ids[16 t .. 16 t + 16]); if it returns non-zero the rows are as before and that code is
+ *                           returned. *changed (optional): tiles published. publish may be null (bookkeeping only).
+ * qb_draft_vocab_dirty / _saved   whether rows changed since the host last saved them (the reference writes them to
+ *                           its cache directory at most once a minute; where and when is the host's choice here)
+ * qb_draft_ids_pt           draft_ids (:231-268): the token ids in the bytes of a mtp_draft_vocab_ids.pt file (a zip
+ *                           archive whose stored entry * /data/0 holds int64 values), repeats dropped; *n = their count
+ *                           (QB_ERR_TOO_LARGE when cap is less). 1: not a zip archive or truncated, 2: no tensor data,
+ *                           3: the entry is compressed or no whole int64s, 4: a token id beyond the vocabulary
+ * qb_model_learn            DraftHead::learn (src/cuda/qwen/draft.rs:55-68): qb_draft_vocab_learn whose publish packs
+ *                           every changed tile from the stored output layer (h_q, h_scales, h_zeros, zero_points,
+ *                           rows, cols, group as for qb_marlin_block) and writes it with qb_model_learn_block; *grew:
+ *                           the head's valid rows grew (the MTP steps' graphs were dropped) */
+typedef struct qb_draft_vocab qb_draft_vocab;
+typedef int (*qb_publish_fn)(void* user, const uint32_t* ids, int n_ids, const int* tiles, int n_tiles);
+int qb_draft_vocab_create(int vocab, const uint32_t* ids, const float* score, int n, int cap, qb_draft_vocab** out);
+int qb_draft_vocab_load(int vocab, const uint32_t* saved_ids, const float* saved_score, int n_saved,
+                        const uint32_t* seed_ids, int n_seed, qb_draft_vocab** out);
+void qb_draft_vocab_destroy(qb_draft_vocab* v);
+int qb_draft_vocab_rows(const qb_draft_vocab* v);
+int qb_draft_vocab_get(const qb_draft_vocab* v, uint32_t* ids, float* score, int cap);
+int qb_draft_vocab_row_of(const qb_draft_vocab* v, uint32_t token);
+int qb_draft_vocab_waiting(const qb_draft_vocab* v, uint32_t token);
+int qb_draft_vocab_pending(const qb_draft_vocab* v);
+int qb_draft_vocab_dirty(const qb_draft_vocab* v);
+int qb_draft_vocab_saved(qb_draft_vocab* v);
+int qb_draft_vocab_may_change(const qb_draft_vocab* v, const uint32_t* toks, int n);
+int qb_draft_vocab_learn(qb_draft_vocab* v, const uint32_t* toks, int n, qb_publish_fn publish, void* user, int* changed);
+int qb_draft_ids_pt(const uint8_t* bytes, size_t len, int vocab, uint32_t* ids, int cap, int* n);
+int qb_model_learn(qb_model* m, void* stream, qb_draft_vocab* v, const uint32_t* toks, int n, const uint32_t* h_q,
+                   const float* h_scales, const uint8_t* h_zeros, int zero_points, int rows, int cols, int group,
+                   int* grew);
+
 /* Programmatic dependent launch for the kernels that support it (their weight prefetch then overlaps the tail of
  * the previous kernel of the stream). Off by default. */
 int qb_set_pdl(qb_ctx* ctx, int on);

@@ -80,6 +80,20 @@ SIGNATURES = {
     "qb_model_upload_marks": [P, P, P, I, P, I, P, P],
     "qb_step_arrays": [P, I, P, I, P, P, I, I, I, P, P, P],
     "qb_step_ints": [],
+    "qb_draft_vocab_create": [I, P, P, I, I, C.POINTER(P)],
+    "qb_draft_vocab_load": [I, P, P, I, P, I, C.POINTER(P)],
+    "qb_draft_vocab_destroy": [P],
+    "qb_draft_vocab_rows": [P],
+    "qb_draft_vocab_get": [P, P, P, I],
+    "qb_draft_vocab_row_of": [P, C.c_uint32],
+    "qb_draft_vocab_waiting": [P, C.c_uint32],
+    "qb_draft_vocab_pending": [P],
+    "qb_draft_vocab_dirty": [P],
+    "qb_draft_vocab_saved": [P],
+    "qb_draft_vocab_may_change": [P, P, I],
+    "qb_draft_vocab_learn": [P, P, I, P, P, P],
+    "qb_draft_ids_pt": [P, C.c_size_t, I, P, I, P],
+    "qb_model_learn": [P, P, P, P, I, P, P, P, I, I, I, I, P],
     "qb_model_run": [P, P],
     "qb_model_use_graphs": [P, I],
     "qb_model_argmax": [P, P, P, I],
@@ -128,7 +142,7 @@ MEASURE_SIGNATURES = {
     "qb_model_fail_captures": [P, I],
     "qb_wait_probe": [P, P, C.c_uint],
 }
-_RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_model_logits": P,
+_RESTYPE = {"qb_version": C.c_char_p, "qb_destroy": None, "qb_model_destroy": None, "qb_draft_vocab_destroy": None, "qb_model_logits": P,
             "qb_model_hidden": P, "qb_model_xn": P, "qb_model_seen": P, "qb_model_launches": LL, "qb_model_kv_bytes": C.c_size_t,
             "qb_model_state_bytes": C.c_size_t, "qb_pool_destroy": None, "qb_pool_page": C.c_size_t,
             "qb_pool_available": C.c_size_t, "qb_region_ptr": P, "qb_region_size": C.c_size_t}

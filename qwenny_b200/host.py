@@ -121,3 +121,41 @@ def sample_row(logits: np.ndarray, seen_words, outs_words, step, row, q=None) ->
                                    _np(qi) if qi is not None else None, _np(qp) if qp is not None else None,
                                    0 if qi is None else len(qi), C.byref(tok), C.byref(acc)), "qb_host_sample_row")
     return tok.value, bool(acc.value)
+
+
+class DraftVocab:
+    """Which token has which row of a draft head (Rows / Adaptive, src/draft_vocab.rs:22-201): a handle on the library's
+    bookkeeping. ids: the token of each row (a multiple of 16), cap: the head's rows at most."""
+
+    def __init__(self, vocab: int, ids, score=None, cap: int = 65536):
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        sc = None if score is None else np.ascontiguousarray(score, dtype=np.float32)
+        self.h = C.c_void_p()
+        check(lib().qb_draft_vocab_create(int(vocab), _np(ids), C.c_void_p(0) if sc is None else _np(sc), len(ids), int(cap),
+                                          C.byref(self.h)), "qb_draft_vocab_create")
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().qb_draft_vocab_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def ids(self) -> np.ndarray:
+        n = lib().qb_draft_vocab_rows(self.h)
+        out = np.empty(max(1, n), dtype=np.uint32)
+        check(lib().qb_draft_vocab_get(self.h, _np(out), C.c_void_p(0), n), "qb_draft_vocab_get")
+        return out[:n]
+
+    def scores(self) -> np.ndarray:
+        n = lib().qb_draft_vocab_rows(self.h)
+        out = np.empty(max(1, n), dtype=np.float32)
+        check(lib().qb_draft_vocab_get(self.h, C.c_void_p(0), _np(out), n), "qb_draft_vocab_get")
+        return out[:n]
+
+    def row_of(self, token: int) -> int:
+        return lib().qb_draft_vocab_row_of(self.h, int(token))

@@ -138,6 +138,24 @@ class Model:
                                          ids.ctypes.data_as(C.c_void_p), C.byref(grew)), "qb_model_learn_block")
         return bool(grew.value)
 
+    def learn(self, vocab, toks, stored_words, scales, zeros=None, zero_points=False, group=128) -> bool:
+        """DraftHead::learn (src/cuda/qwen/draft.rs:55-68): the tokens a step commits go into the bookkeeping `vocab`
+        (host.DraftVocab); every tile of 16 rows that changed is packed from the stored output layer (stored_words u32
+        [rows][cols/8] as host.quant_words gives them, scales f32 [rows][cols/group], zeros u8 or None) and written
+        into the draft head. Returns whether the head's valid row count grew."""
+        import numpy as np
+        q = np.ascontiguousarray(stored_words, dtype=np.uint32)
+        sc = np.ascontiguousarray(scales, dtype=np.float32)
+        z = None if zeros is None else np.ascontiguousarray(zeros, dtype=np.uint8)
+        t = np.ascontiguousarray(toks, dtype=np.uint32)
+        rows, cols = q.shape[0], q.shape[1] * 8
+        grew = C.c_int(0)
+        s = C.c_void_p(self.stream.cuda_stream)
+        ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+        check(lib().qb_model_learn(self.h, s, vocab.h, ptr(t), len(t), ptr(q), ptr(sc), C.c_void_p(0) if z is None else ptr(z),
+                                   int(zero_points), rows, cols, int(group), C.byref(grew)), "qb_model_learn")
+        return bool(grew.value)
+
     def graph_stats(self):
         """(graphs held, cap or -1, steps that ran without a graph for want of memory)."""
         a, b, c = C.c_longlong(0), C.c_longlong(0), C.c_longlong(0)

@@ -76,4 +76,4 @@ def test_no_entry_dereferences_a_null_argument():
     free_standing = {"qb_version", "qb_static_scratch_bytes", "qb_static_device_error", "qb_step_ints"}
     for n, v in seen.items():
         if n not in free_standing:
-            assert v in ("1000", "0", "None"), f"{n}(nulls) answered {v}"
+            assert v in ("1000", "0", "None") or (n == "qb_draft_vocab_row_of" and v == "-1"), f"{n}(nulls) answered {v}"

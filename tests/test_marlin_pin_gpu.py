@@ -249,3 +249,59 @@ def test_a_draft_head_learns_blocks(ctx):
         r16 = np.arange(16 * block, 16 * block + 16)
         m2.learn_block(block, *host.marlin_block(q, sc.astype(np.float32), r16), ids[r16])
     assert chain(m2) == want
+
+
+def test_a_draft_head_learns_the_tokens_steps_commit(ctx):
+    """DraftHead::learn (src/cuda/qwen/draft.rs:55-68) through qb_model_learn: a head of 256 rows (of 512 at most) over a
+    stored output layer takes in committed tokens; tokens with rows only count, 64 tokens without one become four new
+    tiles written in place from the stored rows, and with the head full the rows of the coldest tokens are rewritten.
+    After every change the head's buffers are, bit for bit, the stored rows of its tokens packed at once."""
+    from qwenny_b200 import model as M
+    cap, vocab = 512, 2000
+    q, sc, _ = stored(2048, R.H, 82)  # the stored output layer: a row per token
+    sc = sc.astype(np.float32)
+    qw = host.quant_words(q)
+    g = np.random.default_rng(2)
+    perm = g.permutation(vocab).astype(np.int64)
+    seed, fresh, later = perm[:256], perm[256:512], perm[512:528]
+    shape_w, shape_s = host.pack_marlin(q[:cap], sc[:cap])
+    part_w, part_s = np.zeros_like(shape_w), np.zeros_like(shape_s)
+    half_w, half_s = host.pack_marlin(q[seed], sc[seed])
+    part_w[:, :512] = half_w
+    part_s[:, :256] = half_s
+    ids0 = np.zeros(cap, dtype=np.int32)
+    ids0[:256] = seed
+    m = M.synthetic(ctx, nlayers=2, slots=1, max_ctx=256, vocab=vocab, seed=34, pattern=("delta", "attn"), mtp=True,
+                    draft_rows=cap)
+    d = dict(m.mtp)
+    d["head"] = M.Marlin(torch.from_numpy(part_w.view(np.int32)).cuda(),
+                         torch.from_numpy(part_s.view(np.int16)).cuda().view(torch.float16))
+    d["head_valid"] = 256
+    d["head_ids"] = torch.from_numpy(ids0).cuda()
+    m.set_mtp(d)
+    dv = host.DraftVocab(vocab, seed, cap=cap)
+
+    def head_is(ids):
+        n = len(ids)
+        w, s = host.pack_marlin(q[ids], sc[ids])
+        got_w = m.mtp["head"].words.cpu().numpy().view(np.uint32)
+        got_s = m.mtp["head"].scales.cpu().numpy().view(np.uint16)
+        return (np.array_equal(got_w[:, :2 * n], w) and np.array_equal(got_s[:, :n], s.view(np.uint16)) and
+                np.array_equal(m.mtp["head_ids"].cpu().numpy()[:n], ids.astype(np.int32)) and
+                np.array_equal(dv.ids().astype(np.int64), ids))
+
+    assert not m.learn(dv, seed[:40], qw, sc) and head_is(seed)             # tokens with rows only count
+    assert not m.learn(dv, fresh[:15], qw, sc) and head_is(seed)            # fifteen new ones wait
+    assert m.learn(dv, fresh[15:64], qw, sc)                                # 64: four tiles at the end
+    assert head_is(np.concatenate([seed, fresh[:64]]))
+    assert m.learn(dv, fresh[64:], qw, sc) and head_is(np.concatenate([seed, fresh]))  # the head is full now
+    # full: sixteen more tokens take the rows of cold tokens (score 0: the seed's rows 40.., never committed)
+    assert not m.learn(dv, later, qw, sc)
+    ids = dv.ids().astype(np.int64)
+    assert head_is(ids) and set(later.tolist()) <= set(ids.tolist())
+    assert set(seed[:40].tolist()) <= set(ids.tolist()) and set(fresh.tolist()) <= set(ids.tolist())
+    # and the drafts come from the head's tokens
+    toks = [(17 + i, 0, i) for i in range(5)]
+    m.step(toks, [4])
+    chain = m.draft([(m.argmax()[0], 0, 5)], [4], [0], 4)
+    assert all(t in set(ids.tolist()) for t in chain[0])
