@@ -77,3 +77,14 @@ def test_no_entry_dereferences_a_null_argument():
     for n, v in seen.items():
         if n not in free_standing:
             assert v in ("1000", "0", "None") or (n == "qb_draft_vocab_row_of" and v == "-1"), f"{n}(nulls) answered {v}"
+
+
+def test_the_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: include/qwenny_b200.h compiles as C99 on its own (what a cgo / bindgen / ctypes
+    binding reads), with no warnings under -Wall -Wextra -pedantic."""
+    import subprocess
+    src = tmp_path / "hdr.c"
+    src.write_text('#include "qwenny_b200.h"\nint main(void) { return QB_OK; }\n')
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                        "-I", os.path.join(ROOT, "include"), str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
