@@ -43,7 +43,10 @@ int qb_sm_count(const qb_ctx* ctx); /* 0 for a null context */
 const char* qb_version(void);
 
 /* ---- W4A16 product over a Marlin-packed matrix. Replaces the launches of Gemm::marlin
- * (src/cuda/core.rs:569-612) of marlin_m1_n8_{plain,silu,argmax} (kernels/marlin.cuh:588-602) for m <= 16 rows.
+ * (src/cuda/core.rs:569-612) of marlin_m1_n8_{plain,silu,argmax} (kernels/marlin.cuh:588-602) for m <= 16 rows and of
+ * marlin_m{1..4}_n16_* (the prompt chunks' products, kernels/qwen.cu:48) beyond: more than 16 contiguous rows with the
+ * plain or SwiGLU epilogue run on the tensor-core product (tcgen05), gathered rows and the argmax epilogue as 16-row
+ * slabs of the first.
  *   X      f16 [.][k]; rows row0 .. row0+m-1 are read, or rows xrows[0..m) when xrows != NULL (this folds
  *          marlin_gather, kernels/marlin.cuh:605-608, into the product)
  *   B      Marlin words, k/16 x 2n u32 (src/cuda/core.rs:262-311 pack_marlin); S f16 [k/128][n] permuted scales
@@ -346,7 +349,7 @@ int qb_model_set_head(qb_model* m, const void* embed_bf16, const float* final_no
 /* Model::step = Step::upload (src/cuda/core.rs:835-926) + Graphs::run (:1151-1192) of launch_step
  * (src/cuda/qwen/mod.rs:744-766). h_toks, h_out: host arrays; sequences contiguous and in order; errors as the
  * reference's ensure!s (QB_ERR_ARG). Steps of up to 32 tokens are captured once per shape and replayed as a CUDA
- * graph. Steps with segments longer than 8 tokens (prompt attention) return QB_ERR_UNSUPPORTED. */
+ * graph; larger ones (prompt chunks of up to 2048 tokens, any mix of segments) launch their kernels directly. */
 int qb_model_step(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 int qb_model_upload(qb_model* m, void* stream, const qb_tok* h_toks, int n, const int* h_out, int n_out);
 /* Model::step with `marks` (src/cuda/qwen/mod.rs:1125-1143, Step::upload's third argument, src/cuda/core.rs:872-880):
