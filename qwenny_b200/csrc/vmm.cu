@@ -254,14 +254,23 @@ int qb_region_map(qb_region* r, void* stream, size_t from, size_t to, int* ok) {
         if (rc) return rc;
         if (!h) return QB_ERR_TOO_LARGE;  // another region took the pages in between
         const CUdeviceptr at = r->base + i * p->page;
-        QB_DRV(drv()->MemMap(at, p->page, 0, h, 0));
-        QB_DRV(drv()->MemSetAccess(at, p->page, &access, 1));
+        // (a page the driver refuses to map goes back to the pool: nothing is lost on the way out)
+        CUresult mr = drv()->MemMap(at, p->page, 0, h, 0);
+        if (mr == CUDA_SUCCESS) {
+            mr = drv()->MemSetAccess(at, p->page, &access, 1);
+            if (mr != CUDA_SUCCESS) drv()->MemUnmap(at, p->page);
+        }
+        if (mr != CUDA_SUCCESS) {
+            std::lock_guard<std::mutex> g(p->mu);
+            p->free.push_back(h);
+            return 2000 + (int)mr;
+        }
+        r->pages[i] = h;
+        r->mapped[i] = 1;
         {
             cudaError_t e = cudaMemsetAsync((void*)at, 0, p->page, (cudaStream_t)stream);
             if (e != cudaSuccess) return (int)e;
         }
-        r->pages[i] = h;
-        r->mapped[i] = 1;
     }
     return QB_OK;
 }
@@ -290,7 +299,7 @@ int qb_region_unmap(qb_region* r, void* stream, size_t from, size_t to) {
 
 // Region::read / write: bytes [from, from + n) to / from the host; the range must be mapped (QB_ERR_ARG otherwise)
 int qb_region_read(qb_region* r, void* stream, size_t from, void* out, size_t n) {
-    if (!r || !out || from + n > r->size || !all_mapped(r, from, n)) return QB_ERR_ARG;
+    if (!r || !out || from + n < from || from + n > r->size || !all_mapped(r, from, n)) return QB_ERR_ARG;
     if (n == 0) return QB_OK;
     cudaError_t e = cudaMemcpyAsync(out, (const void*)(r->base + from), n, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
@@ -298,7 +307,7 @@ int qb_region_read(qb_region* r, void* stream, size_t from, void* out, size_t n)
 }
 
 int qb_region_write(qb_region* r, void* stream, size_t from, const void* data, size_t n) {
-    if (!r || !data || from + n > r->size || !all_mapped(r, from, n)) return QB_ERR_ARG;
+    if (!r || !data || from + n < from || from + n > r->size || !all_mapped(r, from, n)) return QB_ERR_ARG;
     if (n == 0) return QB_OK;
     // on the stream, waited for: the stream's next kernels would not wait for a copy on the legacy stream
     cudaError_t e = cudaMemcpyAsync((void*)(r->base + from), data, n, cudaMemcpyHostToDevice, (cudaStream_t)stream);
