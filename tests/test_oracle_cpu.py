@@ -125,6 +125,54 @@ def test_delta_rule_matches_the_textbook_recurrence():
     assert np.allclose(Sn, S.numpy(), rtol=1e-10, atol=1e-12)
 
 
+@pytest.mark.parametrize("dims", [(2, 4, 16, 16), (1, 2, 128, 128)])
+def test_chunked_delta_rule_matches_the_token_recurrence(dims):
+    """The design of the reference's own unit test of its chunked form (chunked_matches_tokens, src/mlx/delta.rs:194-240):
+    two chunks of 64 tokens, keys and queries of unit length shared by the value heads of a key head, log decays in
+    (-0.5, 0), beta in (0, 1), a state in (-1, 1); the chunked (WY) form the prompt scan uses and the token recurrence
+    must agree to 1e-4 in f32 arithmetic (the reference's bound) on every output, on the state after the first chunk
+    and on the end state, and to rounding in f64."""
+    lk, hv, dk, dv = dims
+    CH, n = 64, 128
+    state = [7]
+
+    def values(shape, lo, hi):  # the test's generator: a 64-bit LCG, 24 bits per value
+        out = np.empty(int(np.prod(shape)), dtype=np.float32)
+        for i in range(out.size):
+            state[0] = (state[0] * 6364136223846793005 + 1442695040888963407) % (1 << 64)
+            out[i] = np.float32(lo) + np.float32(hi - lo) * np.float32((state[0] >> 40) / float(1 << 24))
+        return out.reshape(shape)
+
+    unit = lambda x: x / np.sqrt((x * x).sum(-1, keepdims=True))
+    q1, k1 = unit(values((n, lk, dk), -1, 1)), unit(values((n, lk, dk), -1, 1))
+    q, k = np.repeat(q1, hv // lk, axis=1), np.repeat(k1, hv // lk, axis=1)
+    v = values((n, hv, dv), -1, 1)
+    e = np.exp(values((n, hv), -0.5, 0.0))
+    b = values((n, hv), 0.0, 1.0)
+    s0 = values((hv, dv, dk), -1, 1)
+    for dtype, tol in ((np.float32, 1e-4), (np.float64, 1e-10)):
+        S_tok, outs = s0.astype(dtype), []
+        at_ch = None
+        for t in range(n):
+            S_tok, o = R._rule_token(S_tok, k[t].astype(dtype), v[t].astype(dtype), e[t].astype(dtype), b[t].astype(dtype),
+                                     q[t].astype(dtype))
+            outs.append(o)
+            if t + 1 == CH:
+                at_ch = S_tok.copy()
+        outs = np.stack(outs)
+        worst = 0.0
+        for h in range(hv):
+            S = s0[h]
+            for c in range(0, n, CH):
+                S, O = R.delta_chunk(S, q[c:c + CH, h], k[c:c + CH, h], v[c:c + CH, h], e[c:c + CH, h], b[c:c + CH, h],
+                                     dtype=dtype)
+                worst = max(worst, float(np.abs(O - outs[c:c + CH, h]).max()))
+                if c == 0:
+                    assert np.abs(S - at_ch[h]).max() < tol, "state at CH"
+            assert np.abs(S - S_tok[h]).max() < tol, "end states differ"
+        assert worst < tol, f"outputs differ by {worst}"
+
+
 def test_plan_worked_examples():
     """The rollback plan on the cases the reference's comments walk through (kernels/qwen_deltanet.cuh:12-19,62-82)."""
     p = R.plan([100, 95, 1, 0], 100, 5)           # a verify step continuing at `end`
